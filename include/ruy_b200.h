@@ -1,0 +1,242 @@
+/* ruy_b200.h -- C ABI of libruy_b200.so, the B200 (sm_100a) implementation of
+ * ruy's matrix-multiplication hot path.
+ *
+ * ruy (google/ruy) has no FFI layer: its boundary is the C++ template
+ * ruy::Mul(lhs, rhs, mul_params, context, &dst) (ruy/ruy.h:37-50,98-104), which
+ * type-erases its arguments into ruy::TrMulParams (ruy/trmul_params.h:61-90)
+ * and hands them to MulFrontEndFromTrMulParams (ruy/frontend.cc:25-35).  This
+ * header is that type-erased boundary restated as plain C: every entry point
+ * takes POD structs, raw pointers and sizes.  The ruy-compatible C++ headers
+ * shipped beside this file (include/ruy/ruy.h ...) and the Python mirror
+ * (ruy_b200/api.py) are thin shims that flatten their arguments into
+ * ruyb200_mul_desc and call these functions.
+ *
+ * All functions return RUYB200_OK (0) or a negative ruyb200_status.  Nothing
+ * here ever computes on the CPU: if no sm_100-class device is usable the calls
+ * fail with RUYB200_ERR_NO_DEVICE.
+ */
+#ifndef RUY_B200_H_
+#define RUY_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RUYB200_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define RUYB200_API __attribute__((visibility("default")))
+#else
+#define RUYB200_API
+#endif
+
+typedef enum ruyb200_status {
+  RUYB200_OK = 0,
+  RUYB200_ERR_INVALID = -1,      /* descriptor failed validation; nothing was launched */
+  RUYB200_ERR_UNSUPPORTED = -2,  /* type combination outside ruy's type space */
+  RUYB200_ERR_NO_DEVICE = -3,    /* no usable CUDA device / driver */
+  RUYB200_ERR_CUDA = -4,         /* a CUDA runtime call failed; see ruyb200_last_error */
+  RUYB200_ERR_TIMEOUT = -5,      /* a bounded device-side wait gave up (kernel returned cleanly) */
+  RUYB200_ERR_OOM = -6
+} ruyb200_status;
+
+/* Scalar types of ruy's supported (Lhs,Rhs,Accum,Dst) quadruples (ruy/BUILD:1195-1207). */
+typedef enum ruyb200_dtype {
+  RUYB200_I8 = 0,
+  RUYB200_U8 = 1,
+  RUYB200_I16 = 2,
+  RUYB200_I32 = 3,
+  RUYB200_F32 = 4
+} ruyb200_dtype;
+
+/* ruy::Order (ruy/matrix.h:30). */
+enum { RUYB200_COL_MAJOR = 0, RUYB200_ROW_MAJOR = 1 };
+/* ruy::CachePolicy (ruy/matrix.h:117-122). */
+enum {
+  RUYB200_NEVER_CACHE = 0,
+  RUYB200_CACHE_IF_LARGE_SPEEDUP = 1,
+  RUYB200_CACHE_IF_SIGNIFICANT_SPEEDUP = 2,
+  RUYB200_ALWAYS_CACHE = 3
+};
+/* ruy::ChannelDimension (ruy/mul_params.h:30-38). */
+enum { RUYB200_CHANNEL_ROW = 0, RUYB200_CHANNEL_COL = 1 };
+/* ruy::Path bit values on x86 (ruy/path.h:55-90). */
+enum {
+  RUYB200_PATH_NONE = 0,
+  RUYB200_PATH_STANDARD_CPP = 0x1,
+  RUYB200_PATH_INTERNAL_VARIANT1 = 0x2,
+  RUYB200_PATH_INTERNAL_VARIANT2 = 0x4,
+  RUYB200_PATH_INTERNAL_VARIANT3 = 0x8,
+  RUYB200_PATH_AVX = 0x10,
+  RUYB200_PATH_AVX2_FMA = 0x20,
+  RUYB200_PATH_AVX512 = 0x40
+};
+/* Requantization contract.  REFERENCE = ruy::detail::MultiplyByQuantizedMultiplier
+ * (ruy/apply_multiplier.cc:48-65), used by ReferenceMul, Path::kStandardCpp and the
+ * ARM kernels.  X86 = the two-step rounding of ruy's AVX/AVX2/AVX-512 kernels
+ * (ruy/kernel_avx512.cc:340-465).  FROM_PATH picks X86 when the most significant
+ * enabled path of the context is one of kAvx/kAvx2Fma/kAvx512 and REFERENCE otherwise. */
+enum { RUYB200_ROUNDING_FROM_PATH = 0, RUYB200_ROUNDING_REFERENCE = 1, RUYB200_ROUNDING_X86 = 2 };
+/* ruy::PerformanceAdvisory (ruy/performance_advisory.h:21-24). */
+enum { RUYB200_ADVISORY_NONE = 0, RUYB200_ADVISORY_REALLOCATED_PERCHANNEL_BUFFER = 1 };
+
+/* Which device kernel served the last ruyb200_mul (diagnostic; ruy has no counterpart). */
+enum {
+  RUYB200_KERNEL_NONE = 0,
+  RUYB200_KERNEL_GENERIC = 1,   /* CUDA-core kernel, any type / layout / stride */
+  RUYB200_KERNEL_TC_I8 = 2,     /* tcgen05 kind::i8, TMA-staged, fused epilogue */
+  RUYB200_KERNEL_SGEMM = 3,     /* fp32 FFMA tiled kernel */
+  RUYB200_KERNEL_GEMV = 4,      /* one-column bandwidth kernel */
+  RUYB200_KERNEL_BATCH_I8 = 5   /* persistent many-small-muls kernel (plans) */
+};
+
+/* A non-owning matrix view: ruy::Matrix<T> / ruy::Mat<T> (ruy/matrix.h:132-165,
+ * ruy/mat.h:207-242) with the scalar type erased.  `data` may be a host pointer
+ * (pageable or pinned) or a device pointer; the library classifies it. */
+typedef struct ruyb200_matrix {
+  void* data;
+  int32_t rows;
+  int32_t cols;
+  int32_t stride;        /* elements between adjacent columns (col-major) or rows (row-major) */
+  int32_t zero_point;    /* must be 0 for F32 (ruy/validate.h:33-38) */
+  uint8_t order;         /* RUYB200_COL_MAJOR / RUYB200_ROW_MAJOR */
+  uint8_t dtype;         /* ruyb200_dtype */
+  uint8_t cache_policy;  /* RUYB200_*_CACHE */
+  uint8_t reserved;
+} ruyb200_matrix;
+
+/* ruy::MulParams<Accum,Dst> (ruy/mul_params.h:102-223) with types erased.
+ * accum_dtype is RUYB200_I32 or RUYB200_F32.  For the float case bias points to
+ * floats and clamp_* hold float bit patterns in .f; multipliers are ignored.
+ * Per-channel pointers, when non-NULL, take precedence over the scalar pair
+ * (ruy/apply_multiplier.h:66-79).  Per-channel buffers hold one entry per dst
+ * row (CHANNEL_ROW) or column (CHANNEL_COL); the library never reads past that
+ * count, so the capacity rounding only matters for the advisory flag. */
+typedef union ruyb200_scalar {
+  int32_t i;
+  float f;
+} ruyb200_scalar;
+
+typedef struct ruyb200_mul_params {
+  const void* bias;
+  const int32_t* multiplier_fixedpoint_perchannel;
+  const int32_t* multiplier_exponent_perchannel;
+  int32_t multiplier_fixedpoint;
+  int32_t multiplier_exponent;
+  ruyb200_scalar clamp_min;
+  ruyb200_scalar clamp_max;
+  uint8_t channel_dimension;
+  uint8_t perchannel_buffers_capacity_rounding_log2;
+  uint8_t accum_dtype;
+  uint8_t rounding_mode;  /* RUYB200_ROUNDING_* */
+} ruyb200_mul_params;
+
+typedef struct ruyb200_mul_desc {
+  ruyb200_matrix lhs;
+  ruyb200_matrix rhs;
+  ruyb200_matrix dst;
+  ruyb200_mul_params params;
+} ruyb200_mul_desc;
+
+typedef struct ruyb200_ctx ruyb200_ctx;
+typedef struct ruyb200_plan ruyb200_plan;
+
+/* ---- library ---------------------------------------------------------- */
+
+/* ABI version of the loaded library (== RUYB200_ABI_VERSION it was built with). */
+RUYB200_API int ruyb200_abi_version(void);
+/* Number of usable CUDA devices, or a negative status. */
+RUYB200_API int ruyb200_device_count(void);
+/* Message of the last failure on the calling thread ("" if none). */
+RUYB200_API const char* ruyb200_last_error(void);
+
+/* ---- context: ruy::Context (ruy/context.h:38-112) ---------------------- */
+
+/* Replaces ruy::Context::Context().  device < 0 means the current CUDA device.
+ * The context owns one CUDA stream, a device scratch arena and the device-side
+ * prepacked cache.  Like ruy's, a context is not thread-safe: one per calling
+ * thread (ruy/ruy.h:84-87). */
+RUYB200_API int ruyb200_ctx_create(int device, ruyb200_ctx** out);
+/* Same, but all work is enqueued on `cuda_stream` (a cudaStream_t) owned by the caller. */
+RUYB200_API int ruyb200_ctx_create_on_stream(int device, void* cuda_stream, ruyb200_ctx** out);
+RUYB200_API int ruyb200_ctx_destroy(ruyb200_ctx* ctx);
+
+/* ruy::Context::{max_num_threads,set_max_num_threads}: kept for API parity; the
+ * value is stored and returned but does not change how the device is used. */
+RUYB200_API int ruyb200_ctx_set_max_num_threads(ruyb200_ctx* ctx, int value);
+RUYB200_API int ruyb200_ctx_get_max_num_threads(const ruyb200_ctx* ctx);
+/* ruy::Context::{set,get}_runtime_enabled_paths (ruy/context.h:96-99). A mask of 0
+ * restores the default (all of kDefaultPaths, or RUY_PATHS from the environment, ruy/ctx.cc:150-173). */
+RUYB200_API int ruyb200_ctx_set_runtime_enabled_paths(ruyb200_ctx* ctx, uint32_t path_mask);
+RUYB200_API uint32_t ruyb200_ctx_get_runtime_enabled_paths(ruyb200_ctx* ctx);
+/* ruy::Context::last_used_path: most significant bit of compiled & enabled (ruy/ctx.cc:175-178). */
+RUYB200_API uint32_t ruyb200_ctx_last_used_path(const ruyb200_ctx* ctx);
+/* ruy::Context::performance_advisory (ruy/context.h:79). */
+RUYB200_API int ruyb200_ctx_performance_advisory(const ruyb200_ctx* ctx, int advisory);
+/* ruy::Context::ClearPrepackedCache (ruy/context.h:85). */
+RUYB200_API int ruyb200_ctx_clear_prepacked_cache(ruyb200_ctx* ctx);
+/* PrepackedCache budget (ruy/prepacked_cache.h:45, default 256 MiB there; here the
+ * default is 8 GiB of HBM).  Entries are evicted least-recently-used first. */
+RUYB200_API int ruyb200_ctx_set_prepacked_cache_budget(ruyb200_ctx* ctx, size_t bytes);
+/* Introspection of the prepacked cache (ruy::PrepackedCache::{TotalSize,MatrixCount} as
+ * used by ruy/prepacked_cache_test.cc). */
+RUYB200_API size_t ruyb200_ctx_prepacked_cache_bytes(const ruyb200_ctx* ctx);
+RUYB200_API int ruyb200_ctx_prepacked_cache_entries(const ruyb200_ctx* ctx);
+/* Counters: [0] kernel launches, [1] cache hits, [2] cache misses, [3] H2D bytes staged,
+ * [4] D2H bytes staged, [5] id of the kernel that served the last mul (RUYB200_KERNEL_*). */
+RUYB200_API int ruyb200_ctx_counters(const ruyb200_ctx* ctx, uint64_t out[6]);
+/* The cudaStream_t the context enqueues on. */
+RUYB200_API void* ruyb200_ctx_stream(const ruyb200_ctx* ctx);
+/* Blocks until everything enqueued by this context has finished; reports device-side
+ * status words (RUYB200_ERR_TIMEOUT) raised by bounded waits. */
+RUYB200_API int ruyb200_ctx_sync(ruyb200_ctx* ctx);
+
+/* ---- the operation ----------------------------------------------------- */
+
+/* Replaces ruy::Mul / MulFrontEnd (ruy/ruy.h:37-50, ruy/frontend.h:82-95).
+ * Synchronous, like ruy: dst is valid when the call returns.  Host operands are
+ * staged to the device and the result copied back; device operands are used in place. */
+RUYB200_API int ruyb200_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc);
+/* Stream-ordered variant for device-resident operands: validates, enqueues on the
+ * context's stream and returns without synchronizing.  All pointers in `desc`
+ * (matrices and per-channel buffers) must be device pointers.  Additive: ruy has no
+ * asynchronous entry point. */
+RUYB200_API int ruyb200_mul_async(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc);
+/* Host-side validation only (ruy/validate.h:40-83 plus pointer / stride / shape checks). */
+RUYB200_API int ruyb200_validate(const ruyb200_mul_desc* desc);
+
+/* ---- plans: many independent muls in one launch ------------------------ */
+
+/* Additive surface (ruy::Mul is one-matmul-per-call).  A plan plays the role that
+ * TrMul's BlockMap + atomic block queue (ruy/trmul.cc:78-119, ruy/block_map.cc:339-471)
+ * play inside one mul, across many: the descriptors are validated once, LHS operands
+ * with a caching policy are prepacked into the context's device cache, the work list is
+ * sorted and uploaded, and every ruyb200_plan_run replays it with a single persistent
+ * launch.  All operand pointers must be device pointers that stay valid for the life of
+ * the plan. */
+RUYB200_API int ruyb200_plan_create(ruyb200_ctx* ctx, const ruyb200_mul_desc* descs, int n, ruyb200_plan** out);
+/* Enqueue the whole plan on the context's stream (no synchronization). */
+RUYB200_API int ruyb200_plan_run(ruyb200_plan* plan);
+RUYB200_API int ruyb200_plan_destroy(ruyb200_plan* plan);
+/* Algorithmic bytes (operands read once + dst written once + per-channel params) and
+ * 2*rows*cols*depth operations summed over the plan's muls. */
+RUYB200_API int ruyb200_plan_stats(const ruyb200_plan* plan, uint64_t* bytes, uint64_t* ops);
+
+/* ---- packing: PackImpl / RunPack (ruy/pack.h:105-151) -------------------- */
+
+/* Packs a device- or host-resident integer matrix into the device layout the tensor-core
+ * kernel consumes (depth-contiguous, depth padded to 16 bytes) and computes the per-row /
+ * per-column sums used for the zero-point terms.  side: 0 = LHS, 1 = RHS.  Exposed for
+ * tests and benchmarks; ruyb200_mul calls it internally.  `packed` (device, capacity
+ * packed_capacity bytes) and `sums` (device int32[width]) are caller-provided. */
+RUYB200_API int ruyb200_pack(ruyb200_ctx* ctx, const ruyb200_matrix* src, int side, void* packed,
+                 size_t packed_capacity, int32_t* sums, int32_t* packed_depth);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* RUY_B200_H_ */

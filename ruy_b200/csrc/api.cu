@@ -1,0 +1,844 @@
+// Host side of libruy_b200.so: the C ABI of include/ruy_b200.h.
+//
+// This file plays the role of ruy's front end and middle end for the device:
+//   validate          ruy/validate.h:40-83
+//   canonicalize      CreateTrMulParams: Mul -> TrMul view, row-major dst => operand swap
+//                     (ruy/create_trmul_params.h:465-480)
+//   prepare operands  PreparePackedMatrices + PrepackedCache (ruy/prepare_packed_matrices.cc:38-95,
+//                     ruy/prepacked_cache.cc:79-127), with the cache resident in HBM
+//   dispatch          TrMul (ruy/trmul.cc:309-422): pick the kernel and launch it
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <string>
+#include <tuple>
+#include <vector>
+
+#include "common.cuh"
+#include "plan.h"
+
+using namespace ruyb200;
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(int status, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  g_last_error = buf;
+  return status;
+}
+
+#define CUDA_TRY(expr)                                                                   \
+  do {                                                                                   \
+    cudaError_t e__ = (expr);                                                            \
+    if (e__ != cudaSuccess)                                                              \
+      return fail(e__ == cudaErrorMemoryAllocation ? RUYB200_ERR_OOM : RUYB200_ERR_CUDA, \
+                  "%s: %s", #expr, cudaGetErrorString(e__));                             \
+  } while (0)
+
+size_t dtype_size(int dtype) {
+  switch (dtype) {
+    case RUYB200_I8:
+    case RUYB200_U8:
+      return 1;
+    case RUYB200_I16:
+      return 2;
+    default:
+      return 4;
+  }
+}
+
+bool dtype_range(int dtype, int64_t* lo, int64_t* hi) {
+  switch (dtype) {
+    case RUYB200_I8: *lo = -128; *hi = 127; return true;
+    case RUYB200_U8: *lo = 0; *hi = 255; return true;
+    case RUYB200_I16: *lo = -32768; *hi = 32767; return true;
+    case RUYB200_I32: *lo = INT32_MIN; *hi = INT32_MAX; return true;
+    default: return false;
+  }
+}
+
+constexpr uint32_t kCompiledPaths = RUYB200_PATH_STANDARD_CPP | RUYB200_PATH_AVX | RUYB200_PATH_AVX2_FMA |
+                                    RUYB200_PATH_AVX512;
+constexpr uint32_t kX86Paths = RUYB200_PATH_AVX | RUYB200_PATH_AVX2_FMA | RUYB200_PATH_AVX512;
+// Width of the "kernel cell" used by the caching heuristics (ruy/prepare_packed_matrices.cc:51-61):
+// here the row count of one tensor-core tile.
+constexpr int kKernelWidth = 128;
+
+uint32_t most_significant_bit(uint32_t v) {
+  uint32_t r = 0;
+  while (v) {
+    r = v & (~v + 1);
+    v &= v - 1;
+  }
+  return r;
+}
+
+// Device scratch that converges to a single block, reset at the start of every mul
+// (the role of ruy::Allocator, ruy/allocator.h:59-96).  All use is ordered on one stream.
+struct Arena {
+  struct Block {
+    char* p;
+    size_t cap;
+  };
+  std::vector<Block> blocks;
+  size_t cur = 0;
+  size_t off = 0;
+
+  void* alloc(size_t bytes) {
+    bytes = (bytes + 255) & ~size_t(255);
+    if (bytes == 0) bytes = 256;
+    while (cur < blocks.size()) {
+      if (off + bytes <= blocks[cur].cap) {
+        void* r = blocks[cur].p + off;
+        off += bytes;
+        return r;
+      }
+      cur++;
+      off = 0;
+    }
+    size_t cap = std::max<size_t>(bytes, size_t(1) << 20);
+    if (!blocks.empty()) cap = std::max(cap, blocks.back().cap * 2);
+    char* p = nullptr;
+    if (cudaMalloc(&p, cap) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    blocks.push_back({p, cap});
+    cur = blocks.size() - 1;
+    off = bytes;
+    return p;
+  }
+  // Must only be called when no enqueued work can still touch the blocks being merged.
+  void reset(bool may_merge) {
+    if (may_merge && blocks.size() > 1) {
+      size_t total = 0;
+      for (auto& b : blocks) {
+        total += b.cap;
+        cudaFree(b.p);
+      }
+      blocks.clear();
+      char* p = nullptr;
+      if (cudaMalloc(&p, total) == cudaSuccess) {
+        blocks.push_back({p, total});
+      } else {
+        cudaGetLastError();
+      }
+    }
+    cur = 0;
+    off = 0;
+  }
+  void release() {
+    for (auto& b : blocks) cudaFree(b.p);
+    blocks.clear();
+    cur = off = 0;
+  }
+};
+
+// Key of the prepacked cache: the source pointer, the layout of the TrMul view and the zero
+// point (ruy/prepacked_cache.h:68-80), plus the side and element type.
+typedef std::tuple<const void*, int, int, int64_t, int64_t, int, int, int> CacheKey;
+
+struct CacheEntry {
+  void* packed = nullptr;
+  int32_t* sums = nullptr;
+  int packed_depth = 0;
+  size_t bytes = 0;
+  uint64_t stamp = 0;
+};
+
+}  // namespace
+
+struct ruyb200_ctx {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  bool own_stream = false;
+  int sm_count = 148;
+  int max_num_threads = 1;
+  uint32_t enabled_paths = 0;  // 0 = not set explicitly
+  uint32_t last_used_path = 0;
+  int advisory = RUYB200_ADVISORY_NONE;
+  Arena arena;
+  std::map<CacheKey, CacheEntry> cache;
+  size_t cache_bytes = 0;
+  size_t cache_budget = size_t(8) << 30;
+  uint64_t cache_clock = 0;
+  int* d_status = nullptr;
+  int* h_status = nullptr;  // pinned
+  uint64_t counters[6] = {0, 0, 0, 0, 0, 0};
+  int force_kernel = 0;  // RUYB200_KERNEL_* or 0
+};
+
+namespace {
+
+struct DeviceGuard {
+  int prev = -1;
+  explicit DeviceGuard(int dev) {
+    cudaGetDevice(&prev);
+    if (prev != dev) cudaSetDevice(dev);
+  }
+  ~DeviceGuard() {
+    int cur = -1;
+    cudaGetDevice(&cur);
+    if (prev >= 0 && cur != prev) cudaSetDevice(prev);
+  }
+};
+
+bool is_device_pointer(const void* p) {
+  if (!p) return false;
+  cudaPointerAttributes attr;
+  if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  return attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
+}
+
+uint32_t effective_paths(const ruyb200_ctx* ctx) {
+  // ruy/ctx.cc:150-173: an explicit setting (which always keeps kStandardCpp, ruy/ctx.cc:67-76)
+  // wins over RUY_PATHS (hex, taken verbatim), which wins over detection.  There is no CPU to
+  // detect here, so "detection" reports every path.
+  if (ctx->enabled_paths) return ctx->enabled_paths | RUYB200_PATH_STANDARD_CPP;
+  const char* env = getenv("RUY_PATHS");
+  if (env && *env) {
+    const uint32_t v = (uint32_t)strtoul(env, nullptr, 16) & 0xFF;
+    if (v) return v;
+  }
+  return kCompiledPaths | 0xE;
+}
+
+bool paths_explicit(const ruyb200_ctx* ctx) {
+  if (ctx->enabled_paths) return true;
+  const char* env = getenv("RUY_PATHS");
+  return env && *env && strtoul(env, nullptr, 16) != 0;
+}
+
+int validate_desc(const ruyb200_mul_desc* d) {
+  if (!d) return fail(RUYB200_ERR_INVALID, "null descriptor");
+  const ruyb200_matrix* ms[3] = {&d->lhs, &d->rhs, &d->dst};
+  const char* names[3] = {"lhs", "rhs", "dst"};
+  for (int i = 0; i < 3; i++) {
+    const ruyb200_matrix* m = ms[i];
+    if (m->dtype > RUYB200_F32) return fail(RUYB200_ERR_UNSUPPORTED, "%s: unknown dtype %d", names[i], m->dtype);
+    if (m->order > 1) return fail(RUYB200_ERR_INVALID, "%s: bad order", names[i]);
+    if (m->rows < 0 || m->cols < 0) return fail(RUYB200_ERR_INVALID, "%s: negative dimension", names[i]);
+    const int inner = m->order == RUYB200_COL_MAJOR ? m->rows : m->cols;
+    if (m->stride < inner) return fail(RUYB200_ERR_INVALID, "%s: stride %d < %d", names[i], m->stride, inner);
+    if (m->rows > 0 && m->cols > 0 && !m->data) return fail(RUYB200_ERR_INVALID, "%s: null data", names[i]);
+    if (m->cache_policy > RUYB200_ALWAYS_CACHE) return fail(RUYB200_ERR_INVALID, "%s: bad cache policy", names[i]);
+    if (m->dtype == RUYB200_F32) {
+      if (m->zero_point) return fail(RUYB200_ERR_INVALID, "%s: float zero_point must be 0", names[i]);
+    } else {
+      int64_t lo, hi;
+      dtype_range(m->dtype, &lo, &hi);
+      if (m->zero_point < lo || m->zero_point > hi)
+        return fail(RUYB200_ERR_INVALID, "%s: zero_point outside the scalar type's range", names[i]);
+    }
+  }
+  if (d->lhs.cols != d->rhs.rows || d->lhs.rows != d->dst.rows || d->rhs.cols != d->dst.cols)
+    return fail(RUYB200_ERR_INVALID, "shape mismatch: lhs %dx%d rhs %dx%d dst %dx%d", d->lhs.rows, d->lhs.cols,
+                d->rhs.rows, d->rhs.cols, d->dst.rows, d->dst.cols);
+  const ruyb200_mul_params& p = d->params;
+  if (p.channel_dimension > 1) return fail(RUYB200_ERR_INVALID, "bad channel_dimension");
+  if (p.rounding_mode > RUYB200_ROUNDING_X86) return fail(RUYB200_ERR_INVALID, "bad rounding_mode");
+  const int L = d->lhs.dtype, R = d->rhs.dtype, D = d->dst.dtype;
+  if (p.accum_dtype == RUYB200_F32) {
+    if (L != RUYB200_F32 || R != RUYB200_F32 || D != RUYB200_F32)
+      return fail(RUYB200_ERR_UNSUPPORTED, "float accumulation needs float operands and destination");
+    return RUYB200_OK;
+  }
+  if (p.accum_dtype != RUYB200_I32) return fail(RUYB200_ERR_UNSUPPORTED, "accumulator must be int32 or float");
+  if (L == RUYB200_F32 || R == RUYB200_F32 || D == RUYB200_F32 || L == RUYB200_I32 || R == RUYB200_I32)
+    return fail(RUYB200_ERR_UNSUPPORTED, "unsupported integer type combination");
+  const bool has16 = L == RUYB200_I16 || R == RUYB200_I16;
+  if (has16) {
+    if (L == RUYB200_I16 && R == RUYB200_I16) return fail(RUYB200_ERR_UNSUPPORTED, "int16 x int16 is not supported");
+    // ruy/validate.h:47-57
+    if (d->lhs.zero_point || d->rhs.zero_point || d->dst.zero_point)
+      return fail(RUYB200_ERR_INVALID, "16-bit inputs require all zero points to be 0");
+  }
+  if (!(L == RUYB200_U8 && R == RUYB200_U8)) {
+    // ruy/validate.h:59-65
+    int64_t llo, lhi, rlo, rhi;
+    dtype_range(L, &llo, &lhi);
+    dtype_range(R, &rlo, &rhi);
+    if (d->lhs.zero_point == llo && d->rhs.zero_point == rlo)
+      return fail(RUYB200_ERR_INVALID, "lhs and rhs zero points are both the lowest value of their types");
+  }
+  if (D != RUYB200_I32) {
+    const bool pc = p.multiplier_fixedpoint_perchannel || p.multiplier_exponent_perchannel;
+    if (pc && !(p.multiplier_fixedpoint_perchannel && p.multiplier_exponent_perchannel))
+      return fail(RUYB200_ERR_INVALID, "per-channel multiplier needs both the fixedpoint and the exponent buffer");
+    if (!pc) {
+      // ruy/apply_multiplier.cc:45-51
+      if (p.multiplier_fixedpoint < 0) return fail(RUYB200_ERR_INVALID, "multiplier_fixedpoint < 0");
+      if (p.multiplier_exponent < -31 || p.multiplier_exponent > 30)
+        return fail(RUYB200_ERR_INVALID, "multiplier_exponent outside [-31, 30]");
+    }
+    int64_t lo, hi;
+    dtype_range(D, &lo, &hi);
+    if (p.clamp_min.i < lo || p.clamp_max.i > hi)
+      return fail(RUYB200_ERR_INVALID, "clamp outside the destination type's range");
+  }
+  return RUYB200_OK;
+}
+
+// TrMul view of a matrix: side 0 = LHS (width = rows, depth = cols), side 1 = RHS.
+SideView side_view(const ruyb200_matrix& m, int side, const void* data) {
+  SideView s;
+  s.data = data;
+  s.dtype = m.dtype;
+  s.zero_point = m.zero_point;
+  const bool row_major = m.order == RUYB200_ROW_MAJOR;
+  if (side == 0) {
+    s.width = m.rows;
+    s.stride_w = row_major ? m.stride : 1;
+    s.stride_k = row_major ? 1 : m.stride;
+  } else {
+    s.width = m.cols;
+    s.stride_w = row_major ? 1 : m.stride;
+    s.stride_k = row_major ? m.stride : 1;
+  }
+  return s;
+}
+
+size_t storage_span_bytes(const ruyb200_matrix& m) {
+  const int inner = m.order == RUYB200_COL_MAJOR ? m.rows : m.cols;
+  const int outer = m.order == RUYB200_COL_MAJOR ? m.cols : m.rows;
+  if (inner <= 0 || outer <= 0) return 0;
+  return ((size_t)(outer - 1) * (size_t)m.stride + (size_t)inner) * dtype_size(m.dtype);
+}
+
+void cache_evict_one(ruyb200_ctx* ctx) {
+  auto oldest = ctx->cache.begin();
+  for (auto it = ctx->cache.begin(); it != ctx->cache.end(); ++it) {
+    if (it->second.stamp < oldest->second.stamp) oldest = it;
+  }
+  ctx->cache_bytes -= oldest->second.bytes;
+  cudaFree(oldest->second.packed);
+  ctx->cache.erase(oldest);
+}
+
+// ruy/prepare_packed_matrices.cc:38-66.
+bool should_cache(const ruyb200_matrix& m, int other_width) {
+  switch (m.cache_policy) {
+    case RUYB200_ALWAYS_CACHE: return true;
+    case RUYB200_CACHE_IF_LARGE_SPEEDUP: return other_width <= kKernelWidth;
+    case RUYB200_CACHE_IF_SIGNIFICANT_SPEEDUP: return other_width <= 4 * kKernelWidth;
+    default: return false;
+  }
+}
+
+int packed_depth_for(int depth, int dtype) {
+  const int per16 = 16 / (int)dtype_size(dtype);
+  return std::max(per16, (depth + per16 - 1) / per16 * per16);
+}
+
+// A fully resolved mul: device pointers only, canonical (n = destination-contiguous) view.
+struct Resolved {
+  SideView m_side, n_side;
+  DstView dst;
+  Epilogue ep;
+  int depth;
+};
+
+// One operand: finds or builds its device-resident form.
+//   cached   -> packed copy + sums from the prepacked cache (built on a miss)
+//   host     -> staged into the arena
+//   device   -> used in place
+// `need_sums`: the other side has a non-zero zero point (integer case).
+// `want_packed`: the tensor-core kernel will run and this operand is not in its layout.
+int prepare_side(ruyb200_ctx* ctx, const ruyb200_matrix& m, int side, int depth, bool cache_it, bool need_sums,
+                 bool tc_path, SideView* out, const int32_t** sums_out) {
+  *sums_out = nullptr;
+  const bool integer = m.dtype != RUYB200_F32;
+  SideView src = side_view(m, side, m.data);
+  const size_t esz = dtype_size(m.dtype);
+  const bool on_device = is_device_pointer(m.data);
+  if (src.width == 0 || depth == 0) {
+    *out = src;
+    if (need_sums && src.width > 0) {
+      int32_t* z = (int32_t*)ctx->arena.alloc(sizeof(int32_t) * src.width);
+      if (!z) return fail(RUYB200_ERR_OOM, "arena allocation failed");
+      CUDA_TRY(cudaMemsetAsync(z, 0, sizeof(int32_t) * src.width, ctx->stream));
+      *sums_out = z;
+    }
+    return RUYB200_OK;
+  }
+
+  auto stage_to_device = [&](SideView* v) -> int {
+    const size_t span = storage_span_bytes(m);
+    void* dptr = ctx->arena.alloc(span);
+    if (!dptr) return fail(RUYB200_ERR_OOM, "arena allocation of %zu bytes failed", span);
+    CUDA_TRY(cudaMemcpyAsync(dptr, m.data, span, cudaMemcpyHostToDevice, ctx->stream));
+    ctx->counters[3] += span;
+    v->data = dptr;
+    return RUYB200_OK;
+  };
+
+  if (cache_it) {
+    CacheKey key(m.data, src.width, depth, src.stride_w, src.stride_k, m.zero_point, (int)m.dtype, side);
+    auto it = ctx->cache.find(key);
+    if (it == ctx->cache.end()) {
+      ctx->counters[2]++;
+      const int pd = packed_depth_for(depth, m.dtype);
+      const size_t data_bytes = ((size_t)src.width * pd * esz + 255) & ~size_t(255);
+      const size_t sums_bytes = integer ? (((size_t)src.width * 4 + 255) & ~size_t(255)) : 0;
+      const size_t total = data_bytes + sums_bytes;
+      // ruy/prepacked_cache.cc:104-127: make room first, oldest entries go first
+      while (!ctx->cache.empty() && ctx->cache_bytes + total > ctx->cache_budget) cache_evict_one(ctx);
+      void* buf = nullptr;
+      CUDA_TRY(cudaMalloc(&buf, total));
+      SideView staged = src;
+      if (!on_device) {
+        int rc = stage_to_device(&staged);
+        if (rc) {
+          cudaFree(buf);
+          return rc;
+        }
+      }
+      CacheEntry e;
+      e.packed = buf;
+      e.sums = integer ? (int32_t*)((char*)buf + data_bytes) : nullptr;
+      e.packed_depth = pd;
+      e.bytes = total;
+      cudaError_t ce = launch_pack(staged, depth, pd, e.packed, e.sums, ctx->stream);
+      ctx->counters[0]++;
+      if (ce != cudaSuccess) {
+        cudaFree(buf);
+        return fail(RUYB200_ERR_CUDA, "pack launch: %s", cudaGetErrorString(ce));
+      }
+      ctx->cache_bytes += total;
+      it = ctx->cache.emplace(key, e).first;
+    } else {
+      ctx->counters[1]++;
+    }
+    it->second.stamp = ++ctx->cache_clock;
+    out->data = it->second.packed;
+    out->dtype = m.dtype;
+    out->zero_point = m.zero_point;
+    out->width = src.width;
+    out->stride_w = it->second.packed_depth;
+    out->stride_k = 1;
+    *sums_out = it->second.sums;
+    return RUYB200_OK;
+  }
+
+  SideView v = src;
+  if (!on_device) {
+    int rc = stage_to_device(&v);
+    if (rc) return rc;
+  }
+  const bool layout_ok = v.stride_k == 1 && ((uintptr_t)v.data % 16 == 0) && ((v.stride_w * (int64_t)esz) % 16 == 0);
+  if (tc_path && !layout_ok) {
+    // PackImpl: re-tile into the depth-contiguous padded layout, sums on the way
+    const int pd = packed_depth_for(depth, m.dtype);
+    void* packed = ctx->arena.alloc((size_t)v.width * pd * esz);
+    int32_t* sums = need_sums ? (int32_t*)ctx->arena.alloc(sizeof(int32_t) * v.width) : nullptr;
+    if (!packed || (need_sums && !sums)) return fail(RUYB200_ERR_OOM, "arena allocation failed");
+    cudaError_t ce = launch_pack(v, depth, pd, packed, sums, ctx->stream);
+    ctx->counters[0]++;
+    if (ce != cudaSuccess) return fail(RUYB200_ERR_CUDA, "pack launch: %s", cudaGetErrorString(ce));
+    v.data = packed;
+    v.stride_w = pd;
+    v.stride_k = 1;
+    *sums_out = sums;
+  } else if (need_sums) {
+    int32_t* sums = (int32_t*)ctx->arena.alloc(sizeof(int32_t) * v.width);
+    if (!sums) return fail(RUYB200_ERR_OOM, "arena allocation failed");
+    cudaError_t ce = launch_sums(v, depth, sums, ctx->stream);
+    ctx->counters[0]++;
+    if (ce != cudaSuccess) return fail(RUYB200_ERR_CUDA, "sums launch: %s", cudaGetErrorString(ce));
+    *sums_out = sums;
+  }
+  *out = v;
+  return RUYB200_OK;
+}
+
+// Copies a small host vector (bias / multipliers) into the arena unless it already lives on the device.
+int stage_vector(ruyb200_ctx* ctx, const void* p, size_t count, const void** out) {
+  *out = p;
+  if (!p || count == 0 || is_device_pointer(p)) return RUYB200_OK;
+  void* d = ctx->arena.alloc(count * 4);
+  if (!d) return fail(RUYB200_ERR_OOM, "arena allocation failed");
+  CUDA_TRY(cudaMemcpyAsync(d, p, count * 4, cudaMemcpyHostToDevice, ctx->stream));
+  ctx->counters[3] += count * 4;
+  *out = d;
+  return RUYB200_OK;
+}
+
+int choose_kernel(const ruyb200_ctx* ctx, const ruyb200_mul_desc& d) {
+  if (ctx->force_kernel) return ctx->force_kernel;
+  if (d.params.accum_dtype == RUYB200_F32) return RUYB200_KERNEL_SGEMM;
+  const bool both8 = dtype_size(d.lhs.dtype) == 1 && dtype_size(d.rhs.dtype) == 1;
+  if (both8 && d.lhs.cols > 0) return RUYB200_KERNEL_TC_I8;
+  return RUYB200_KERNEL_GENERIC;
+}
+
+int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous) {
+  int rc = validate_desc(desc);
+  if (rc) return rc;
+  const ruyb200_mul_desc& d = *desc;
+  DeviceGuard guard(ctx->device);
+  ctx->advisory = RUYB200_ADVISORY_NONE;  // ruy/frontend.h:90
+  const uint32_t paths = effective_paths(ctx);
+  ctx->last_used_path = most_significant_bit(paths & kCompiledPaths);
+  if (d.dst.rows == 0 || d.dst.cols == 0) return RUYB200_OK;
+
+  const bool dst_on_device = is_device_pointer(d.dst.data);
+  if (!synchronous) {
+    const void* ptrs[6] = {d.lhs.data, d.rhs.data, d.dst.data, d.params.bias, d.params.multiplier_fixedpoint_perchannel,
+                           d.params.multiplier_exponent_perchannel};
+    for (const void* p : ptrs) {
+      if (p && !is_device_pointer(p)) return fail(RUYB200_ERR_INVALID, "ruyb200_mul_async needs device pointers");
+    }
+  }
+  ctx->arena.reset(synchronous);
+
+  const int depth = d.lhs.cols;
+  const bool is_float = d.params.accum_dtype == RUYB200_F32;
+  int kernel = choose_kernel(ctx, d);
+  if (kernel == RUYB200_KERNEL_TC_I8 && (is_float || dtype_size(d.lhs.dtype) != 1 || dtype_size(d.rhs.dtype) != 1 ||
+                                         depth == 0)) {
+    kernel = RUYB200_KERNEL_GENERIC;
+  }
+  if (kernel == RUYB200_KERNEL_SGEMM && !is_float) kernel = RUYB200_KERNEL_GENERIC;
+  const bool tc = kernel == RUYB200_KERNEL_TC_I8;
+
+  // ruy/create_trmul_params.h:294-319: ruy re-allocates per-channel buffers that are shorter
+  // than the padded width and says so; here nothing is read past the logical size, the
+  // advisory is kept for callers that watch it.
+  const bool channel_row = d.params.channel_dimension == RUYB200_CHANNEL_ROW;
+  const int nch = channel_row ? d.dst.rows : d.dst.cols;
+  if (!is_float && (d.params.bias || d.params.multiplier_fixedpoint_perchannel)) {
+    const int rounding = 1 << d.params.perchannel_buffers_capacity_rounding_log2;
+    const int capacity = (nch + rounding - 1) / rounding * rounding;
+    const int padded = (nch + 15) / 16 * 16;
+    if (capacity < padded) ctx->advisory = RUYB200_ADVISORY_REALLOCATED_PERCHANNEL_BUFFER;
+  }
+
+  // operands
+  SideView lhs_v, rhs_v;
+  const int32_t *lhs_sums = nullptr, *rhs_sums = nullptr;
+  const bool generic = kernel == RUYB200_KERNEL_GENERIC;
+  // the generic kernel subtracts zero points while loading and needs no sums
+  const bool need_lhs_sums = !is_float && !generic && d.rhs.zero_point != 0;
+  const bool need_rhs_sums = !is_float && !generic && d.lhs.zero_point != 0;
+  rc = prepare_side(ctx, d.lhs, 0, depth, should_cache(d.lhs, d.rhs.cols), need_lhs_sums, tc, &lhs_v, &lhs_sums);
+  if (rc) return rc;
+  rc = prepare_side(ctx, d.rhs, 1, depth, should_cache(d.rhs, d.lhs.rows), need_rhs_sums, tc, &rhs_v, &rhs_sums);
+  if (rc) return rc;
+
+  Epilogue ep;
+  memset(&ep, 0, sizeof(ep));
+  const void* p;
+  rc = stage_vector(ctx, d.params.bias, nch, &p);
+  if (rc) return rc;
+  ep.bias = p;
+  if (!is_float && d.dst.dtype != RUYB200_I32) {
+    rc = stage_vector(ctx, d.params.multiplier_fixedpoint_perchannel, nch, &p);
+    if (rc) return rc;
+    ep.mfp_pc = (const int32_t*)p;
+    rc = stage_vector(ctx, d.params.multiplier_exponent_perchannel, nch, &p);
+    if (rc) return rc;
+    ep.mexp_pc = (const int32_t*)p;
+    ep.mfp = d.params.multiplier_fixedpoint;
+    ep.mexp = d.params.multiplier_exponent;
+  }
+  ep.clamp_min = d.params.clamp_min.i;
+  ep.clamp_max = d.params.clamp_max.i;
+  ep.dst_zp = d.dst.zero_point;
+  ep.depth = depth;
+  ep.dst_dtype = d.dst.dtype;
+  ep.is_float = is_float;
+  int rounding = d.params.rounding_mode;
+  if (rounding == RUYB200_ROUNDING_FROM_PATH) {
+    rounding = (paths_explicit(ctx) && (ctx->last_used_path & kX86Paths)) ? RUYB200_ROUNDING_X86
+                                                                            : RUYB200_ROUNDING_REFERENCE;
+  }
+  // ruy's x86 back end has 8-bit and int8 x int16 kernels only (ruy/kernel_x86.h:34-233); with an
+  // int16 LHS (after the row-major-dst operand swap) it falls back to the standard C++ kernel and
+  // therefore to the reference rounding.
+  const int canonical_lhs_dtype = d.dst.order == RUYB200_COL_MAJOR ? d.lhs.dtype : d.rhs.dtype;
+  if (canonical_lhs_dtype == RUYB200_I16) rounding = RUYB200_ROUNDING_REFERENCE;
+  ep.rounding_x86 = rounding == RUYB200_ROUNDING_X86;
+
+  // destination: n is its contiguous dimension.  Col-major dst: n = row (LHS side);
+  // row-major dst: n = col (RHS side) -- ruy's operand swap (ruy/create_trmul_params.h:474-479).
+  const size_t dst_esz = dtype_size(d.dst.dtype);
+  const bool dst_col_major = d.dst.order == RUYB200_COL_MAJOR;
+  const int dst_inner = dst_col_major ? d.dst.rows : d.dst.cols;
+  const int dst_outer = dst_col_major ? d.dst.cols : d.dst.rows;
+  void* dst_dev = d.dst.data;
+  if (!dst_on_device) {
+    dst_dev = ctx->arena.alloc((size_t)dst_outer * d.dst.stride * dst_esz);
+    if (!dst_dev) return fail(RUYB200_ERR_OOM, "arena allocation failed");
+  }
+  Resolved r;
+  r.depth = depth;
+  r.dst.data = dst_dev;
+  r.dst.stride_m = d.dst.stride;
+  r.dst.size_m = dst_outer;
+  r.dst.size_n = dst_inner;
+  if (dst_col_major) {
+    r.n_side = lhs_v;
+    r.m_side = rhs_v;
+    ep.sums_n = lhs_sums;
+    ep.sums_m = rhs_sums;
+    ep.channel_on_n = channel_row;
+  } else {
+    r.n_side = rhs_v;
+    r.m_side = lhs_v;
+    ep.sums_n = rhs_sums;
+    ep.sums_m = lhs_sums;
+    ep.channel_on_n = !channel_row;
+  }
+  ep.zp_m = r.m_side.zero_point;
+  ep.zp_n = r.n_side.zero_point;
+  r.ep = ep;
+
+  cudaError_t ce;
+  if (tc) {
+    if (!tc_i8_eligible(r.m_side, r.n_side)) return fail(RUYB200_ERR_CUDA, "internal: operands not packed for the tensor-core kernel");
+    TcI8Launch L;
+    L.m_side = r.m_side;
+    L.n_side = r.n_side;
+    L.dst = r.dst;
+    L.ep = r.ep;
+    L.depth = depth;
+    L.sm_count = ctx->sm_count;
+    L.status = ctx->d_status;
+    ce = launch_tc_i8(L, ctx->stream);
+  } else if (kernel == RUYB200_KERNEL_SGEMM) {
+    ce = launch_sgemm(r.m_side, r.n_side, r.dst, r.ep, ctx->stream);
+  } else {
+    ce = launch_generic(r.m_side, r.n_side, r.dst, r.ep, ctx->stream);
+  }
+  ctx->counters[0]++;
+  ctx->counters[5] = kernel;
+  if (ce != cudaSuccess) return fail(RUYB200_ERR_CUDA, "kernel launch: %s", cudaGetErrorString(ce));
+
+  if (!dst_on_device) {
+    CUDA_TRY(cudaMemcpy2DAsync(d.dst.data, (size_t)d.dst.stride * dst_esz, dst_dev, (size_t)d.dst.stride * dst_esz,
+                               (size_t)dst_inner * dst_esz, dst_outer, cudaMemcpyDeviceToHost, ctx->stream));
+    ctx->counters[4] += (size_t)dst_inner * dst_esz * dst_outer;
+  }
+  if (synchronous) return ruyb200_ctx_sync(ctx);
+  return RUYB200_OK;
+}
+
+}  // namespace
+
+// ---- exported C ABI ------------------------------------------------------------------------
+
+extern "C" {
+
+int ruyb200_abi_version(void) { return RUYB200_ABI_VERSION; }
+
+int ruyb200_device_count(void) {
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess) {
+    cudaGetLastError();
+    return fail(RUYB200_ERR_NO_DEVICE, "no CUDA device or driver");
+  }
+  return n;
+}
+
+const char* ruyb200_last_error(void) { return g_last_error.c_str(); }
+
+int ruyb200_ctx_create_on_stream(int device, void* cuda_stream, ruyb200_ctx** out) {
+  if (!out) return fail(RUYB200_ERR_INVALID, "null out pointer");
+  *out = nullptr;
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) {
+    cudaGetLastError();
+    return fail(RUYB200_ERR_NO_DEVICE, "no CUDA device available (this library has no CPU path)");
+  }
+  if (device < 0) CUDA_TRY(cudaGetDevice(&device));
+  if (device >= count) return fail(RUYB200_ERR_INVALID, "device %d out of range (%d devices)", device, count);
+  cudaDeviceProp prop;
+  CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10) {
+    return fail(RUYB200_ERR_NO_DEVICE, "device %d is sm_%d%d; this library is built for sm_100a only", device,
+                prop.major, prop.minor);
+  }
+  DeviceGuard guard(device);
+  ruyb200_ctx* ctx = new ruyb200_ctx;
+  ctx->device = device;
+  ctx->sm_count = prop.multiProcessorCount;
+  if (cuda_stream) {
+    ctx->stream = (cudaStream_t)cuda_stream;
+  } else {
+    if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) {
+      delete ctx;
+      return fail(RUYB200_ERR_CUDA, "cudaStreamCreate failed: %s", cudaGetErrorString(cudaGetLastError()));
+    }
+    ctx->own_stream = true;
+  }
+  if (cudaMalloc(&ctx->d_status, sizeof(int)) != cudaSuccess || cudaMemset(ctx->d_status, 0, sizeof(int)) != cudaSuccess ||
+      cudaMallocHost(&ctx->h_status, sizeof(int)) != cudaSuccess) {
+    cudaGetLastError();
+    ruyb200_ctx_destroy(ctx);
+    return fail(RUYB200_ERR_CUDA, "context allocation failed");
+  }
+  *ctx->h_status = 0;
+  const char* fk = getenv("RUYB200_FORCE_KERNEL");
+  if (fk && !strcmp(fk, "generic")) ctx->force_kernel = RUYB200_KERNEL_GENERIC;
+  *out = ctx;
+  return RUYB200_OK;
+}
+
+int ruyb200_ctx_create(int device, ruyb200_ctx** out) { return ruyb200_ctx_create_on_stream(device, nullptr, out); }
+
+int ruyb200_ctx_destroy(ruyb200_ctx* ctx) {
+  if (!ctx) return RUYB200_OK;
+  DeviceGuard guard(ctx->device);
+  if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+  ruyb200_ctx_clear_prepacked_cache(ctx);
+  ctx->arena.release();
+  if (ctx->d_status) cudaFree(ctx->d_status);
+  if (ctx->h_status) cudaFreeHost(ctx->h_status);
+  if (ctx->own_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
+  cudaGetLastError();
+  delete ctx;
+  return RUYB200_OK;
+}
+
+int ruyb200_ctx_set_max_num_threads(ruyb200_ctx* ctx, int value) {
+  if (!ctx || value < 1) return fail(RUYB200_ERR_INVALID, "max_num_threads must be >= 1");
+  ctx->max_num_threads = value;
+  return RUYB200_OK;
+}
+
+int ruyb200_ctx_get_max_num_threads(const ruyb200_ctx* ctx) { return ctx ? ctx->max_num_threads : 0; }
+
+int ruyb200_ctx_set_runtime_enabled_paths(ruyb200_ctx* ctx, uint32_t path_mask) {
+  if (!ctx) return fail(RUYB200_ERR_INVALID, "null context");
+  ctx->enabled_paths = path_mask & 0xFF;
+  return RUYB200_OK;
+}
+
+uint32_t ruyb200_ctx_get_runtime_enabled_paths(ruyb200_ctx* ctx) { return ctx ? effective_paths(ctx) : 0; }
+
+uint32_t ruyb200_ctx_last_used_path(const ruyb200_ctx* ctx) { return ctx ? ctx->last_used_path : 0; }
+
+int ruyb200_ctx_performance_advisory(const ruyb200_ctx* ctx, int advisory) {
+  return ctx && advisory != RUYB200_ADVISORY_NONE && (ctx->advisory & advisory) ? 1 : 0;
+}
+
+int ruyb200_ctx_clear_prepacked_cache(ruyb200_ctx* ctx) {
+  if (!ctx) return fail(RUYB200_ERR_INVALID, "null context");
+  DeviceGuard guard(ctx->device);
+  if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+  for (auto& kv : ctx->cache) cudaFree(kv.second.packed);
+  ctx->cache.clear();
+  ctx->cache_bytes = 0;
+  return RUYB200_OK;
+}
+
+int ruyb200_ctx_set_prepacked_cache_budget(ruyb200_ctx* ctx, size_t bytes) {
+  if (!ctx) return fail(RUYB200_ERR_INVALID, "null context");
+  ctx->cache_budget = bytes;
+  return RUYB200_OK;
+}
+
+size_t ruyb200_ctx_prepacked_cache_bytes(const ruyb200_ctx* ctx) { return ctx ? ctx->cache_bytes : 0; }
+
+int ruyb200_ctx_prepacked_cache_entries(const ruyb200_ctx* ctx) { return ctx ? (int)ctx->cache.size() : 0; }
+
+int ruyb200_ctx_counters(const ruyb200_ctx* ctx, uint64_t out[6]) {
+  if (!ctx || !out) return fail(RUYB200_ERR_INVALID, "null argument");
+  for (int i = 0; i < 6; i++) out[i] = ctx->counters[i];
+  return RUYB200_OK;
+}
+
+void* ruyb200_ctx_stream(const ruyb200_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
+
+int ruyb200_ctx_sync(ruyb200_ctx* ctx) {
+  if (!ctx) return fail(RUYB200_ERR_INVALID, "null context");
+  DeviceGuard guard(ctx->device);
+  CUDA_TRY(cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+  CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+  if (*ctx->h_status != 0) {
+    const int code = *ctx->h_status;
+    *ctx->h_status = 0;
+    cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream);
+    cudaStreamSynchronize(ctx->stream);
+    return fail(RUYB200_ERR_TIMEOUT, "a bounded device-side wait gave up (role code %d); results are invalid", code);
+  }
+  return RUYB200_OK;
+}
+
+int ruyb200_validate(const ruyb200_mul_desc* desc) { return validate_desc(desc); }
+
+int ruyb200_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc) {
+  if (!ctx) return fail(RUYB200_ERR_INVALID, "null context");
+  return run_mul(ctx, desc, true);
+}
+
+int ruyb200_mul_async(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc) {
+  if (!ctx) return fail(RUYB200_ERR_INVALID, "null context");
+  return run_mul(ctx, desc, false);
+}
+
+int ruyb200_pack(ruyb200_ctx* ctx, const ruyb200_matrix* src, int side, void* packed, size_t packed_capacity,
+                 int32_t* sums, int32_t* packed_depth) {
+  if (!ctx || !src || !packed || side < 0 || side > 1) return fail(RUYB200_ERR_INVALID, "bad argument");
+  if (src->dtype > RUYB200_F32 || src->dtype == RUYB200_I32) return fail(RUYB200_ERR_UNSUPPORTED, "bad dtype");
+  DeviceGuard guard(ctx->device);
+  const int depth = side == 0 ? src->cols : src->rows;
+  const int pd = packed_depth_for(depth, src->dtype);
+  if (packed_depth) *packed_depth = pd;
+  SideView v = side_view(*src, side, src->data);
+  if ((size_t)v.width * pd * dtype_size(src->dtype) > packed_capacity)
+    return fail(RUYB200_ERR_INVALID, "packed buffer too small");
+  ctx->arena.reset(false);
+  if (!is_device_pointer(src->data)) {
+    const size_t span = storage_span_bytes(*src);
+    void* dptr = ctx->arena.alloc(span);
+    if (!dptr) return fail(RUYB200_ERR_OOM, "arena allocation failed");
+    CUDA_TRY(cudaMemcpyAsync(dptr, src->data, span, cudaMemcpyHostToDevice, ctx->stream));
+    v.data = dptr;
+  }
+  cudaError_t ce = launch_pack(v, depth, pd, packed, src->dtype == RUYB200_F32 ? nullptr : sums, ctx->stream);
+  ctx->counters[0]++;
+  if (ce != cudaSuccess) return fail(RUYB200_ERR_CUDA, "pack launch: %s", cudaGetErrorString(ce));
+  return ruyb200_ctx_sync(ctx);
+}
+
+}  // extern "C"
+
+// ---- plan support (used by plan.cu) -----------------------------------------------------------
+namespace ruyb200 {
+
+cudaStream_t ctx_stream(ruyb200_ctx* ctx) { return ctx->stream; }
+int ctx_device(ruyb200_ctx* ctx) { return ctx->device; }
+int ctx_sm_count(ruyb200_ctx* ctx) { return ctx->sm_count; }
+int* ctx_status_word(ruyb200_ctx* ctx) { return ctx->d_status; }
+void ctx_count_launch(ruyb200_ctx* ctx, int kernel) {
+  ctx->counters[0]++;
+  ctx->counters[5] = kernel;
+}
+int ctx_fail(int status, const char* msg) { return fail(status, "%s", msg); }
+int ctx_validate(const ruyb200_mul_desc* d) { return validate_desc(d); }
+bool ptr_on_device(const void* p) { return is_device_pointer(p); }
+int ctx_rounding_is_x86(ruyb200_ctx* ctx, int rounding_mode) {
+  if (rounding_mode == RUYB200_ROUNDING_X86) return 1;
+  if (rounding_mode == RUYB200_ROUNDING_REFERENCE) return 0;
+  const uint32_t paths = effective_paths(ctx);
+  ctx->last_used_path = most_significant_bit(paths & kCompiledPaths);
+  return paths_explicit(ctx) && (ctx->last_used_path & kX86Paths) ? 1 : 0;
+}
+int ctx_run_mul_async(ruyb200_ctx* ctx, const ruyb200_mul_desc* d) { return run_mul(ctx, d, false); }
+
+}  // namespace ruyb200

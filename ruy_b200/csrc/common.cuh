@@ -1,0 +1,149 @@
+// Internal declarations shared by the CUDA translation units of libruy_b200.so.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/ruy_b200.h"
+
+namespace ruyb200 {
+
+// One side of the "TrMul" view (ruy/create_trmul_params.h:465-480): a width x depth matrix
+// addressed as data[w * stride_w + k * stride_k] (in elements).  The LHS is width = rows,
+// the RHS is width = cols; a depth-contiguous ("K-major") side has stride_k == 1.
+struct SideView {
+  const void* data;
+  int64_t stride_w;
+  int64_t stride_k;
+  int32_t width;
+  int32_t zero_point;
+  uint8_t dtype;
+};
+
+// Everything the fused epilogue needs (ruy/kernel.h:213-237, ruy/kernel_common.h:94-213).
+// "n" indexes the destination's contiguous dimension, "m" the other one; which of them is
+// the row index depends on the destination's storage order.
+struct Epilogue {
+  const void* bias;            // int32 or float, indexed by channel
+  const int32_t* mfp_pc;       // per-channel fixed-point multipliers or nullptr
+  const int32_t* mexp_pc;      // per-channel exponents or nullptr
+  const int32_t* sums_m;       // sum over depth of the m-side operand, per m (needed when zp_n != 0)
+  const int32_t* sums_n;       // sum over depth of the n-side operand, per n (needed when zp_m != 0)
+  int32_t mfp;
+  int32_t mexp;
+  int32_t clamp_min;           // int32, or float bits when is_float
+  int32_t clamp_max;
+  int32_t zp_m;                // zero point of the m-side operand
+  int32_t zp_n;                // zero point of the n-side operand
+  int32_t dst_zp;
+  int32_t depth;
+  uint8_t channel_on_n;        // 1: per-channel buffers are indexed by n, 0: by m
+  uint8_t rounding_x86;        // 1: two-step x86 rounding, 0: reference rounding
+  uint8_t dst_dtype;           // ruyb200_dtype
+  uint8_t is_float;
+};
+
+// Destination addressing: element (m, n) lives at dst[m * stride_m + n] (n contiguous).
+struct DstView {
+  void* data;
+  int64_t stride_m;
+  int32_t size_m;
+  int32_t size_n;
+};
+
+// ruy::detail::MultiplyByQuantizedMultiplier (ruy/apply_multiplier.cc:48-65).
+__device__ __forceinline__ int32_t requant_reference(int32_t x, int32_t m, int e) {
+  const int total_shift = 31 - e;
+  const long long round = 1ll << (total_shift - 1);
+  const long long r = (long long)x * (long long)m + round;
+  return (int32_t)(r >> total_shift);
+}
+
+// The rounding of ruy's x86 kernels (ruy/kernel_avx512.cc:340-465): wrapping left shift,
+// rounding doubling high multiply, then rounding right shift with an overflow guard.
+__device__ __forceinline__ int32_t requant_x86(int32_t x, int32_t m, int e) {
+  const int ls = e > 0 ? e : 0;
+  const int rs = e < 0 ? -e : 0;
+  const int32_t a = (int32_t)((uint32_t)x << ls);
+  const int32_t t = (int32_t)(((long long)a * (long long)m + (1ll << 30)) >> 31);
+  const int32_t nudge = rs > 0 ? (int32_t)(1u << (rs - 1)) : 0;
+  if (t > 0x7fffffff - nudge) return (int32_t)(1u << (31 - rs));
+  return (t + nudge) >> rs;
+}
+
+// Raw int32 dot product -> final int32 value before the narrowing cast.
+// `raw` is sum_k M[m,k]*N[n,k] over the stored (not zero-point-shifted) values.
+__device__ __forceinline__ int32_t finish_int(int32_t raw, int m, int n, const Epilogue& ep) {
+  uint32_t acc = (uint32_t)raw;
+  const int ch = ep.channel_on_n ? n : m;
+  if (ep.bias) acc += (uint32_t)((const int32_t*)ep.bias)[ch];
+  if (ep.zp_m) acc -= (uint32_t)ep.zp_m * (uint32_t)ep.sums_n[n];
+  if (ep.zp_n) acc -= (uint32_t)ep.zp_n * (uint32_t)ep.sums_m[m];
+  if (ep.zp_m && ep.zp_n) acc += (uint32_t)ep.zp_m * (uint32_t)ep.zp_n * (uint32_t)ep.depth;
+  int32_t v = (int32_t)acc;
+  if (ep.dst_dtype != RUYB200_I32) {
+    const int32_t mult = ep.mfp_pc ? ep.mfp_pc[ch] : ep.mfp;
+    const int e = ep.mexp_pc ? ep.mexp_pc[ch] : ep.mexp;
+    v = ep.rounding_x86 ? requant_x86(v, mult, e) : requant_reference(v, mult, e);
+  }
+  v = (int32_t)((uint32_t)v + (uint32_t)ep.dst_zp);
+  if (ep.dst_dtype != RUYB200_I32) {
+    v = min(v, ep.clamp_max);
+    v = max(v, ep.clamp_min);
+  }
+  return v;
+}
+
+__device__ __forceinline__ float finish_float(float acc, int m, int n, const Epilogue& ep) {
+  const int ch = ep.channel_on_n ? n : m;
+  if (ep.bias) acc += ((const float*)ep.bias)[ch];
+  acc = fminf(acc, __int_as_float(ep.clamp_max));
+  acc = fmaxf(acc, __int_as_float(ep.clamp_min));
+  return acc;
+}
+
+__device__ __forceinline__ void store_int(const DstView& d, uint8_t dtype, int m, int n, int32_t v) {
+  const int64_t off = (int64_t)m * d.stride_m + n;
+  switch (dtype) {
+    case RUYB200_I8: ((int8_t*)d.data)[off] = (int8_t)v; break;
+    case RUYB200_U8: ((uint8_t*)d.data)[off] = (uint8_t)v; break;
+    case RUYB200_I16: ((int16_t*)d.data)[off] = (int16_t)v; break;
+    default: ((int32_t*)d.data)[off] = v; break;
+  }
+}
+
+// ---- launchers (host side); each enqueues on `stream` and returns a cudaError_t ----------
+
+// CUDA-core kernel for any supported type combination, order and stride.
+cudaError_t launch_generic(const SideView& m_side, const SideView& n_side, const DstView& dst,
+                           const Epilogue& ep, cudaStream_t stream);
+
+// Sum over depth of every width-row of a side (int32, wrap-around).
+cudaError_t launch_sums(const SideView& side, int depth, int32_t* sums, cudaStream_t stream);
+
+// PackImpl analogue: writes the side as [width][packed_depth] depth-contiguous with zero
+// padding and (for integer types, when sums != nullptr) its per-width sums.
+cudaError_t launch_pack(const SideView& side, int depth, int packed_depth, void* packed,
+                        int32_t* sums, cudaStream_t stream);
+
+// tcgen05 kind::i8 GEMM.  Both sides must be 8-bit, depth-contiguous, with 16-byte aligned
+// base and stride_w (bytes).  `status` is a device word that receives a non-zero code if a
+// bounded wait gives up.
+struct TcI8Launch {
+  SideView m_side;
+  SideView n_side;
+  DstView dst;
+  Epilogue ep;
+  int depth;
+  int sm_count;
+  int* status;
+};
+cudaError_t launch_tc_i8(const TcI8Launch& args, cudaStream_t stream);
+// True when the operands satisfy launch_tc_i8's requirements.
+bool tc_i8_eligible(const SideView& m_side, const SideView& n_side);
+
+// fp32 kernels.
+cudaError_t launch_sgemm(const SideView& m_side, const SideView& n_side, const DstView& dst,
+                         const Epilogue& ep, cudaStream_t stream);
+
+}  // namespace ruyb200

@@ -1,0 +1,217 @@
+// CUDA-core kernels: the any-type / any-layout matmul (the role Path::kStandardCpp's
+// Kernel plays in ruy, ruy/kernel.h:176-241), the zero-point sums, and the packing kernel
+// (ruy/pack.h:105-151).
+#include "common.cuh"
+
+namespace ruyb200 {
+
+namespace {
+
+__device__ __forceinline__ int32_t load_as_int(const void* p, uint8_t dtype, int64_t idx) {
+  switch (dtype) {
+    case RUYB200_I8: return ((const int8_t*)p)[idx];
+    case RUYB200_U8: return ((const uint8_t*)p)[idx];
+    case RUYB200_I16: return ((const int16_t*)p)[idx];
+    default: return ((const int32_t*)p)[idx];
+  }
+}
+
+constexpr int kTile = 32;    // dst tile edge per block
+constexpr int kChunk = 32;   // depth chunk staged in shared memory
+
+// One block computes a kTile x kTile destination tile; operands are staged through shared
+// memory in depth chunks with loads coalesced along whichever dimension is contiguous.
+// Accumulates (m - zp_m) * (n - zp_n) directly, as ReferenceMul does, so no sums are needed.
+template <bool kFloat>
+__global__ void __launch_bounds__(256) generic_mul_kernel(SideView ms, SideView ns, DstView dst, Epilogue ep) {
+  __shared__ int32_t sm[kTile][kChunk + 1];
+  __shared__ int32_t sn[kTile][kChunk + 1];
+  const int m0 = blockIdx.y * kTile;
+  const int n0 = blockIdx.x * kTile;
+  const int tx = threadIdx.x % 32;   // n within tile
+  const int ty = threadIdx.x / 32;   // 8 groups, 4 m each
+  int32_t iacc[4] = {0, 0, 0, 0};
+  float facc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int k0 = 0; k0 < ep.depth; k0 += kChunk) {
+    // stage: thread t loads 4 elements per side
+    for (int e = threadIdx.x; e < kTile * kChunk; e += 256) {
+      // choose the fast-varying index along the contiguous dimension of each side
+      int wm, km, wn, kn;
+      if (ms.stride_k == 1) { km = e % kChunk; wm = e / kChunk; } else { wm = e % kTile; km = e / kTile; }
+      if (ns.stride_k == 1) { kn = e % kChunk; wn = e / kChunk; } else { wn = e % kTile; kn = e / kTile; }
+      int32_t vm = 0, vn = 0;
+      if (m0 + wm < ms.width && k0 + km < ep.depth) {
+        const int64_t idx = (int64_t)(m0 + wm) * ms.stride_w + (int64_t)(k0 + km) * ms.stride_k;
+        vm = kFloat ? __float_as_int(((const float*)ms.data)[idx]) : load_as_int(ms.data, ms.dtype, idx) - ms.zero_point;
+      }
+      if (n0 + wn < ns.width && k0 + kn < ep.depth) {
+        const int64_t idx = (int64_t)(n0 + wn) * ns.stride_w + (int64_t)(k0 + kn) * ns.stride_k;
+        vn = kFloat ? __float_as_int(((const float*)ns.data)[idx]) : load_as_int(ns.data, ns.dtype, idx) - ns.zero_point;
+      }
+      sm[wm][km] = vm;
+      sn[wn][kn] = vn;
+    }
+    __syncthreads();
+#pragma unroll 4
+    for (int k = 0; k < kChunk; k++) {
+      const int32_t bn = sn[tx][k];
+#pragma unroll
+      for (int r = 0; r < 4; r++) {
+        const int32_t am = sm[ty * 4 + r][k];
+        if (kFloat) {
+          facc[r] = fmaf(__int_as_float(am), __int_as_float(bn), facc[r]);
+        } else {
+          iacc[r] = (int32_t)((uint32_t)iacc[r] + (uint32_t)(am * bn));
+        }
+      }
+    }
+    __syncthreads();
+  }
+  Epilogue e2 = ep;
+  e2.zp_m = 0;  // zero points were already subtracted while staging
+  e2.zp_n = 0;
+  const int n = n0 + tx;
+#pragma unroll
+  for (int r = 0; r < 4; r++) {
+    const int m = m0 + ty * 4 + r;
+    if (m < dst.size_m && n < dst.size_n) {
+      if (kFloat) {
+        ((float*)dst.data)[(int64_t)m * dst.stride_m + n] = finish_float(facc[r], m, n, e2);
+      } else {
+        store_int(dst, ep.dst_dtype, m, n, finish_int(iacc[r], m, n, e2));
+      }
+    }
+  }
+}
+
+// One warp per width-row; lanes stride over depth.
+__global__ void sums_kernel(SideView s, int depth, int32_t* sums) {
+  const int w = blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
+  if (w >= s.width) return;
+  const int lane = threadIdx.x % 32;
+  uint32_t acc = 0;
+  const bool vec = s.stride_k == 1 && (s.dtype == RUYB200_I8 || s.dtype == RUYB200_U8) &&
+                   (((uintptr_t)s.data + (uint64_t)w * s.stride_w) % 16 == 0);
+  int k = 0;
+  if (vec) {
+    const uint4* row = (const uint4*)((const char*)s.data + (int64_t)w * s.stride_w);
+    const int nvec = depth / 16;
+    for (int v = lane; v < nvec; v += 32) {
+      const uint4 q = row[v];
+      if (s.dtype == RUYB200_I8) {
+        int a = 0;
+        a = __dp4a((int)q.x, 0x01010101, a);
+        a = __dp4a((int)q.y, 0x01010101, a);
+        a = __dp4a((int)q.z, 0x01010101, a);
+        a = __dp4a((int)q.w, 0x01010101, a);
+        acc += (uint32_t)a;
+      } else {
+        unsigned a = 0;
+        a = __dp4a(q.x, 0x01010101u, a);
+        a = __dp4a(q.y, 0x01010101u, a);
+        a = __dp4a(q.z, 0x01010101u, a);
+        a = __dp4a(q.w, 0x01010101u, a);
+        acc += a;
+      }
+    }
+    k = nvec * 16;
+  }
+  for (int kk = k + lane; kk < depth; kk += 32) {
+    acc += (uint32_t)load_as_int(s.data, s.dtype, (int64_t)w * s.stride_w + (int64_t)kk * s.stride_k);
+  }
+  acc = __reduce_add_sync(0xffffffffu, acc);
+  if (lane == 0) sums[w] = (int32_t)acc;
+}
+
+// Packing: out[w][k] (depth-contiguous, packed_depth elements per row, zero padded) and sums.
+// Block = 32 x 8 threads handling 32 widths; loops over depth in chunks of 32 through a
+// shared-memory tile so that both the read and the write are coalesced for either source order.
+template <typename T>
+__global__ void __launch_bounds__(256) pack_kernel(SideView s, int depth, int packed_depth, T* out, int32_t* sums) {
+  __shared__ T tile[32][33];
+  __shared__ uint32_t part[32][9];
+  const int tx = threadIdx.x % 32;
+  const int ty = threadIdx.x / 32;
+  const int w0 = blockIdx.x * 32;
+  uint32_t acc[4] = {0, 0, 0, 0};
+  const T* src = (const T*)s.data;
+  for (int k0 = 0; k0 < packed_depth; k0 += 32) {
+    // load tile[w][k]
+    for (int r = 0; r < 4; r++) {
+      int w, k;
+      if (s.stride_k == 1) { k = tx; w = ty + 8 * r; } else { w = tx; k = ty + 8 * r; }
+      T v = 0;
+      if (w0 + w < s.width && k0 + k < depth) {
+        v = src[(int64_t)(w0 + w) * s.stride_w + (int64_t)(k0 + k) * s.stride_k];
+      }
+      tile[w][k] = v;
+    }
+    __syncthreads();
+    for (int r = 0; r < 4; r++) {
+      const int w = ty + 8 * r;
+      const int k = tx;
+      const T v = tile[w][k];
+      if (w0 + w < s.width && k0 + k < packed_depth) {
+        out[(int64_t)(w0 + w) * packed_depth + k0 + k] = v;
+      }
+      acc[r] += (uint32_t)(int32_t)v;
+    }
+    __syncthreads();
+  }
+  if (sums) {
+    for (int r = 0; r < 4; r++) {
+      const uint32_t t = __reduce_add_sync(0xffffffffu, acc[r]);
+      if (tx == 0 && w0 + ty + 8 * r < s.width) sums[w0 + ty + 8 * r] = (int32_t)t;
+    }
+  }
+  (void)part;
+}
+
+}  // namespace
+
+cudaError_t launch_generic(const SideView& m_side, const SideView& n_side, const DstView& dst,
+                           const Epilogue& ep, cudaStream_t stream) {
+  if (dst.size_m <= 0 || dst.size_n <= 0) return cudaSuccess;
+  dim3 grid((dst.size_n + kTile - 1) / kTile, (dst.size_m + kTile - 1) / kTile);
+  if (grid.y > 65535) return cudaErrorInvalidConfiguration;
+  if (ep.is_float) {
+    generic_mul_kernel<true><<<grid, 256, 0, stream>>>(m_side, n_side, dst, ep);
+  } else {
+    generic_mul_kernel<false><<<grid, 256, 0, stream>>>(m_side, n_side, dst, ep);
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_sums(const SideView& side, int depth, int32_t* sums, cudaStream_t stream) {
+  if (side.width <= 0) return cudaSuccess;
+  const int warps_per_block = 8;
+  const int grid = (side.width + warps_per_block - 1) / warps_per_block;
+  sums_kernel<<<grid, warps_per_block * 32, 0, stream>>>(side, depth, sums);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_pack(const SideView& side, int depth, int packed_depth, void* packed,
+                        int32_t* sums, cudaStream_t stream) {
+  if (side.width <= 0) return cudaSuccess;
+  const int grid = (side.width + 31) / 32;
+  switch (side.dtype) {
+    case RUYB200_I8:
+      pack_kernel<int8_t><<<grid, 256, 0, stream>>>(side, depth, packed_depth, (int8_t*)packed, sums);
+      break;
+    case RUYB200_U8:
+      pack_kernel<uint8_t><<<grid, 256, 0, stream>>>(side, depth, packed_depth, (uint8_t*)packed, sums);
+      break;
+    case RUYB200_I16:
+      pack_kernel<int16_t><<<grid, 256, 0, stream>>>(side, depth, packed_depth, (int16_t*)packed, sums);
+      break;
+    case RUYB200_F32:
+      // floats are moved as 32-bit patterns; no sums
+      pack_kernel<int32_t><<<grid, 256, 0, stream>>>(side, depth, packed_depth, (int32_t*)packed, nullptr);
+      break;
+    default:
+      return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace ruyb200

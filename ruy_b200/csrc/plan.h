@@ -1,0 +1,21 @@
+// Internal glue between the context (api.cu) and plans (plan.cu).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include "../../include/ruy_b200.h"
+
+namespace ruyb200 {
+
+cudaStream_t ctx_stream(ruyb200_ctx* ctx);
+int ctx_device(ruyb200_ctx* ctx);
+int ctx_sm_count(ruyb200_ctx* ctx);
+int* ctx_status_word(ruyb200_ctx* ctx);
+void ctx_count_launch(ruyb200_ctx* ctx, int kernel);
+int ctx_fail(int status, const char* msg);
+int ctx_validate(const ruyb200_mul_desc* d);
+bool ptr_on_device(const void* p);
+int ctx_rounding_is_x86(ruyb200_ctx* ctx, int rounding_mode);
+int ctx_run_mul_async(ruyb200_ctx* ctx, const ruyb200_mul_desc* d);
+
+}  // namespace ruyb200

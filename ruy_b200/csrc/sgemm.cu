@@ -1,0 +1,135 @@
+// fp32 matmul on the CUDA cores: ruy's KernelFloat* (ruy/kernel_avx512.cc:872-1236,
+// ruy/kernel_x86.h:598-912) with the bias + clamp epilogue fused.  Plain FFMA with fp32
+// accumulation in depth order keeps the result within 1e-5 relative of a double-precision
+// reference, which a single-pass TF32 tensor-core product would not.
+#include "common.cuh"
+
+namespace ruyb200 {
+
+namespace {
+
+constexpr int kBK = 16;
+
+// Block tile BM x BN, 256 threads as 16 (n) x 16 (m), each thread TM x TN outputs strided by 16
+// so that shared-memory reads are conflict-free and destination stores are coalesced along n.
+template <int BM, int BN>
+__global__ void __launch_bounds__(256) sgemm_kernel(SideView ms, SideView ns, DstView dst, Epilogue ep) {
+  constexpr int TM = BM / 16;
+  constexpr int TN = BN / 16;
+  __shared__ float As[2][kBK][BM + 4];
+  __shared__ float Bs[2][kBK][BN + 4];
+  const int tid = threadIdx.x;
+  const int tn = tid % 16;
+  const int tm = tid / 16;
+  const int m0 = blockIdx.y * BM;
+  const int n0 = blockIdx.x * BN;
+  const float* A = (const float*)ms.data;
+  const float* B = (const float*)ns.data;
+  const int depth = ep.depth;
+
+  float acc[TM][TN];
+#pragma unroll
+  for (int i = 0; i < TM; i++)
+#pragma unroll
+    for (int j = 0; j < TN; j++) acc[i][j] = 0.f;
+
+  constexpr int A_PER = BM * kBK / 256;
+  constexpr int B_PER = BN * kBK / 256;
+  float ra[A_PER], rb[B_PER];
+
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int i = 0; i < A_PER; i++) {
+      const int e = tid + i * 256;
+      int w, k;
+      if (ms.stride_k == 1) { k = e % kBK; w = e / kBK; } else { w = e % BM; k = e / BM; }
+      float v = 0.f;
+      if (m0 + w < ms.width && k0 + k < depth) v = A[(int64_t)(m0 + w) * ms.stride_w + (int64_t)(k0 + k) * ms.stride_k];
+      ra[i] = v;
+    }
+#pragma unroll
+    for (int i = 0; i < B_PER; i++) {
+      const int e = tid + i * 256;
+      int w, k;
+      if (ns.stride_k == 1) { k = e % kBK; w = e / kBK; } else { w = e % BN; k = e / BN; }
+      float v = 0.f;
+      if (n0 + w < ns.width && k0 + k < depth) v = B[(int64_t)(n0 + w) * ns.stride_w + (int64_t)(k0 + k) * ns.stride_k];
+      rb[i] = v;
+    }
+  };
+  auto stash = [&](int buf) {
+#pragma unroll
+    for (int i = 0; i < A_PER; i++) {
+      const int e = tid + i * 256;
+      int w, k;
+      if (ms.stride_k == 1) { k = e % kBK; w = e / kBK; } else { w = e % BM; k = e / BM; }
+      As[buf][k][w] = ra[i];
+    }
+#pragma unroll
+    for (int i = 0; i < B_PER; i++) {
+      const int e = tid + i * 256;
+      int w, k;
+      if (ns.stride_k == 1) { k = e % kBK; w = e / kBK; } else { w = e % BN; k = e / BN; }
+      Bs[buf][k][w] = rb[i];
+    }
+  };
+
+  fetch(0);
+  stash(0);
+  __syncthreads();
+  int buf = 0;
+  for (int k0 = 0; k0 < depth; k0 += kBK) {
+    const bool more = k0 + kBK < depth;
+    if (more) fetch(k0 + kBK);
+#pragma unroll
+    for (int k = 0; k < kBK; k++) {
+      float a[TM], b[TN];
+#pragma unroll
+      for (int i = 0; i < TM; i++) a[i] = As[buf][k][tm + 16 * i];
+#pragma unroll
+      for (int j = 0; j < TN; j++) b[j] = Bs[buf][k][tn + 16 * j];
+#pragma unroll
+      for (int i = 0; i < TM; i++)
+#pragma unroll
+        for (int j = 0; j < TN; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    if (more) {
+      stash(buf ^ 1);
+      __syncthreads();
+      buf ^= 1;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < TM; i++) {
+    const int m = m0 + tm + 16 * i;
+    if (m >= dst.size_m) continue;
+#pragma unroll
+    for (int j = 0; j < TN; j++) {
+      const int n = n0 + tn + 16 * j;
+      if (n < dst.size_n) ((float*)dst.data)[(int64_t)m * dst.stride_m + n] = finish_float(acc[i][j], m, n, ep);
+    }
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_sgemm(const SideView& m_side, const SideView& n_side, const DstView& dst,
+                         const Epilogue& ep, cudaStream_t stream) {
+  if (dst.size_m <= 0 || dst.size_n <= 0) return cudaSuccess;
+  const long long big_tiles = (long long)((dst.size_m + 127) / 128) * ((dst.size_n + 127) / 128);
+  if (big_tiles >= 32) {
+    dim3 grid((dst.size_n + 127) / 128, (dst.size_m + 127) / 128);
+    if (grid.y > 65535) return cudaErrorInvalidConfiguration;
+    sgemm_kernel<128, 128><<<grid, 256, 0, stream>>>(m_side, n_side, dst, ep);
+  } else if ((long long)((dst.size_m + 63) / 64) * ((dst.size_n + 63) / 64) >= 32) {
+    dim3 grid((dst.size_n + 63) / 64, (dst.size_m + 63) / 64);
+    sgemm_kernel<64, 64><<<grid, 256, 0, stream>>>(m_side, n_side, dst, ep);
+  } else {
+    dim3 grid((dst.size_n + 31) / 32, (dst.size_m + 31) / 32);
+    if (grid.y > 65535) return cudaErrorInvalidConfiguration;
+    sgemm_kernel<32, 32><<<grid, 256, 0, stream>>>(m_side, n_side, dst, ep);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace ruyb200
