@@ -1,0 +1,363 @@
+#!/usr/bin/env python
+"""Benchmark of the ruy::Mul hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Default workload `c3_i8`: the large projection, 4096 x 4096 int8 weights (prepacked, resident)
+times 4096 x 8192 int8 activations -> int8 with per-row multipliers, bias, zero point and clamp.
+One step = one such mul.  With N > 1 (launched under torchrun, one rank per GPU) the 8192
+columns are sharded over the ranks and the destination shards are all-gathered over NCCL inside
+the timed step (strong scaling).  Prints one JSON line on rank 0.
+
+`--impl reference` times ruy's own CPU path (the compiled reference under oracle/_ref when
+present, else the C port of the oracle) on the host cores on a bounded sample of the workload.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "int8_gemm_tops"
+UNIT = "TOP/s"
+L2_FLUSH_BYTES = 256 << 20
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu_index)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+# ------------------------------------------------------------------------------------------
+# CPU arms
+# ------------------------------------------------------------------------------------------
+
+class CpuArm:
+    """ruy's own CPU implementation of the workload on the host cores, on a bounded sample: the first
+    1024 of the 8192 columns (the weights are the full 4096 x 4096 and stay in ruy's prepacked cache).
+    Uses the compiled reference when oracle/_ref holds it, else the scalar C port on a smaller slice."""
+
+    def __init__(self, workload):
+        import oracle
+        from ruy_b200 import cases
+        from ruy_b200.api import make_desc
+        self.oracle = oracle
+        self.ref = oracle.reference()
+        dst = "int32" if workload == "c3_i32" else "int8"
+        if self.ref is not None:
+            self.case = cases.config3(dst=dst, col_begin=0, col_count=1024)
+            self.cores = os.cpu_count() or 1
+            self.kind = "reference"
+            self.ctx = self.ref.ruy_ref_ctx_create(oracle.host_simd_path(), self.cores)
+        else:
+            self.case = cases.config3(rows=512, depth=4096, cols=64, dst=dst)
+            self.cores = 1
+            self.kind = "port"
+            self.ctx = None
+        self.dst = self.case.new_dst()
+        self.bound = self.case.bind(self.dst)
+        self.desc = make_desc(self.bound[0], self.bound[1], self.bound[2], self.bound[3])
+        self.sample = f"{self.case.rows}x{self.case.depth} weights x {self.case.cols} of 8192 columns"
+
+    def seconds(self, windows=1, min_secs=0.0):
+        """Best seconds per mul over `windows` windows of at least `min_secs` (ruy/test.h:2082-2136)."""
+        if self.ref is not None:
+            return self.ref.ruy_ref_time_mul(self.ctx, C.byref(self.desc), windows, min_secs)
+        t0 = time.perf_counter()
+        self.oracle.oracle().ruy_oracle_mul(C.byref(self.desc), 1, 0)
+        return time.perf_counter() - t0
+
+    def describe(self):
+        if self.ref is not None:
+            used = {0x40: "kAvx512", 0x20: "kAvx2Fma", 0x10: "kAvx", 0x1: "kStandardCpp"}.get(
+                self.ref.ruy_ref_last_used_path(self.ctx), "?")
+            return f"{self.sample}; ruy::Mul on {used}, {self.cores} threads, weights in the prepacked cache"
+        return f"{self.sample}; scalar C port of the oracle, 1 thread"
+
+    def tops(self, secs):
+        return self.case.ops / secs / 1e12
+
+    def close(self):
+        if self.ctx is not None:
+            self.ref.ruy_ref_ctx_destroy(self.ctx)
+            self.ctx = None
+
+
+def run_reference_arm(args):
+    rank, world, local = dist_env()
+    if rank != 0:
+        return
+    arm = CpuArm(args.workload)
+    for _ in range(max(args.warmup, 1)):
+        arm.seconds()
+    secs = [arm.seconds() for _ in range(args.steps)]
+    ms = float(np.mean(secs)) * 1e3
+    value = arm.tops(float(np.mean(secs)))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "int8", "data": "synthetic",
+        "config": {"workload": args.workload, "rows": 4096, "depth": 4096, "cols": 8192,
+                   "note": "each step times one bounded sample of the workload on the host cores"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": arm.cores, "kind": arm.kind, "sample": arm.describe()},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    arm.close()
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------
+
+def run_gpu_arm(args):
+    import torch
+    import ruy_b200
+    from ruy_b200 import cases
+    from ruy_b200.api import Rounding
+
+    rank, world, local = dist_env()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the GPU arm has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    use_dist = world > 1
+    if use_dist:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    dst_name = "int32" if args.workload == "c3_i32" else "int8"
+    cols_total = 8192
+    assert cols_total % world == 0
+    shard = cols_total // world
+    case = cases.config3(dst=dst_name, col_begin=rank * shard, col_count=shard)
+    tdtype = torch.int32 if dst_name == "int32" else torch.int8
+    esz = 4 if dst_name == "int32" else 1
+
+    stream = torch.cuda.Stream(device=dev)
+    ctx = ruy_b200.Context(local, stream=stream.cuda_stream)
+    with torch.cuda.stream(stream):
+        # the gathered destination (col-major: a column shard is one contiguous range); each rank
+        # computes straight into its own slice of it
+        full = torch.zeros(cols_total * case.rows, dtype=tdtype, device=dev)
+        mine = full[rank * shard * case.rows:(rank + 1) * shard * case.rows]
+        lhs, rhs, p, d, keep = case.bind(mine, device=dev, rounding=Rounding.kReference)
+        flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
+        ruy_b200.mul(lhs, rhs, p, ctx, d)  # packs the weights into the context's device cache
+
+        def step():
+            ruy_b200.mul_async(lhs, rhs, p, ctx, d)
+            if use_dist:
+                dist.all_gather_into_tensor(full, mine)
+
+        for _ in range(max(args.warmup, 3)):
+            flush.fill_(1)
+            step()
+        stream.synchronize()
+
+        # correctness spot check (cheap): a sampled sub-block against 64-bit numpy dot products
+        out = case.dst_view(mine.cpu().numpy())
+        rs = np.arange(0, case.rows, 509)
+        cs = np.arange(0, shard, 211)
+        L = case.lhs.reshape(case.rows, case.depth).astype(np.int64)[rs]
+        R = case.rhs.reshape(shard, case.depth).astype(np.int64)[cs]
+        acc = L @ R.T
+        if dst_name == "int8":
+            acc = acc + case.bias.astype(np.int64)[rs][:, None]
+            m, e = case.mfp.astype(np.int64)[rs][:, None], case.mexp.astype(np.int64)[rs][:, None]
+            acc = np.clip(((acc * m + (1 << (30 - e))) >> (31 - e)) + case.dst_zp, -128, 127)
+        if not np.array_equal(out[np.ix_(rs, cs)].astype(np.int64), acc):
+            raise SystemExit("bench.py: GPU result does not match the reference arithmetic; refusing to report")
+
+        sampler = ClockSampler(local)
+        launches0 = ctx.counters()["launches"]
+        if use_dist:
+            dist.barrier()
+        torch.cuda.synchronize()
+        sampler.start()
+        starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+        mids = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+        stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+        wall0 = time.perf_counter()
+        for i in range(args.steps):
+            flush.fill_(i & 0xFF)          # evict the operands from L2 (not timed)
+            starts[i].record(stream)
+            ruy_b200.mul_async(lhs, rhs, p, ctx, d)
+            mids[i].record(stream)
+            if use_dist:
+                dist.all_gather_into_tensor(full, mine)
+            stops[i].record(stream)
+        stream.synchronize()
+        if use_dist:
+            dist.barrier()
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - wall0
+        clocks = sampler.stop()
+        launches = ctx.counters()["launches"] - launches0
+        step_ms = [s.elapsed_time(e) for s, e in zip(starts, stops)]
+        kern_ms = [s.elapsed_time(e) for s, e in zip(starts, mids)]
+        total_ms = float(np.sum(step_ms))
+        kernel_ms = float(np.mean(kern_ms))
+        if use_dist:
+            t = torch.tensor([total_ms, kernel_ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            total_ms, kernel_ms = float(t[0]), float(t[1])
+        ms_per_step = total_ms / args.steps
+        total_ops = 2.0 * case.rows * case.depth * cols_total
+        value = total_ops / (ms_per_step * 1e-3) / 1e12
+
+        # end to end through the public synchronous call with HOST buffers (weights stay cached)
+        host_dst = case.new_dst()
+        hl, hr, hp, hd, hkeep = case.bind(host_dst, rounding=Rounding.kReference)
+        pinned_rhs = torch.from_numpy(case.rhs).pin_memory()
+        pinned_dst = torch.empty(case.dst_storage_elems(), dtype=tdtype).pin_memory()
+        hr.data, hd.data = pinned_rhs, pinned_dst
+        # per-channel vectors and bias are host arrays as well
+        ruy_b200.mul(hl, hr, hp, ctx, hd)
+        c0 = ctx.counters()
+        e2e_steps = max(2, min(args.steps, 10))
+        if use_dist:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            ruy_b200.mul(hl, hr, hp, ctx, hd)
+        torch.cuda.synchronize()
+        e2e_s = (time.perf_counter() - t0) / e2e_steps
+        c1 = ctx.counters()
+        if use_dist:
+            t = torch.tensor([e2e_s], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_s = float(t[0])
+        e2e_value = total_ops / e2e_s / 1e12
+        h2d = (c1["h2d_bytes"] - c0["h2d_bytes"]) // e2e_steps
+        d2h = (c1["d2h_bytes"] - c0["d2h_bytes"]) // e2e_steps
+        if not np.array_equal(case.dst_view(pinned_dst.numpy())[np.ix_(rs, cs)].astype(np.int64), acc):
+            raise SystemExit("bench.py: end-to-end result mismatch")
+
+    peaks = measured_peaks()
+    # tcgen05 kind::i8 issues twice the multiply-adds per clock of kind::f16: the int8 dense peak is
+    # taken as 2 x the measured dense bf16 throughput (the burst figure: the kernel is timed alone).
+    peak_tops = 2.0 * peaks["bf16_tflops"]
+    shard_ops = 2.0 * case.rows * case.depth * shard
+    achieved = shard_ops / (kernel_ms * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": peak_tops, "unit": "TFLOP/s",
+                "frac": achieved / peak_tops, "traffic": None, "kernel": "tc_i8_kernel",
+                "peak_source": f"2 x bf16_tflops of {peaks['source']} peaks; ops are int8 multiply-adds x 2",
+                "kernel_ms": kernel_ms}
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "int8", "data": "synthetic",
+        "config": {"workload": args.workload, "rows": case.rows, "depth": case.depth, "cols": cols_total,
+                   "dst": dst_name, "sharding": f"{world} column shard(s) of {shard}" + (", dst all-gathered (NCCL) inside the step" if use_dist else ""),
+                   "l2": f"flushed between steps ({L2_FLUSH_BYTES >> 20} MiB fill, untimed)"},
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+                "ms_per_step": e2e_s * 1e3},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "roofline": roofline,
+        "wall_s": wall,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        arm = CpuArm(args.workload)
+        secs = arm.seconds(windows=4, min_secs=0.5 if arm.kind == "reference" else 0.0)
+        line["cpu_baseline"] = {"value": arm.tops(secs), "unit": UNIT, "cores": arm.cores, "kind": arm.kind,
+                                "sample": arm.describe()}
+        arm.close()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    ctx.close()
+    if use_dist:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c3_i8", choices=["c3_i8", "c3_i32"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,457 @@
+"""Parity of the CUDA library (through the C ABI) with the oracle and the golden reference outputs.
+Integer results must be bit-exact; float results within 1e-5 relative of a double-accumulated
+reference (|gpu - ref| <= 1e-5 * max(|ref|, 1))."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import ruy_b200
+import util
+from golden_cases import golden_cases
+from ruy_b200 import cases
+from ruy_b200.api import CachePolicy, ChannelDimension, Order, Path, PerformanceAdvisory, Rounding
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+FLOAT_RTOL = 1e-5
+
+
+@pytest.fixture(scope="module")
+def generic_ctx(gpu_ctx):
+    """A context whose muls are all served by the CUDA-core kernel."""
+    os.environ["RUYB200_FORCE_KERNEL"] = "generic"
+    try:
+        ctx = ruy_b200.Context(0)
+    finally:
+        del os.environ["RUYB200_FORCE_KERNEL"]
+    yield ctx
+    ctx.close()
+
+
+def assert_float_close(got, case):
+    wide = util.run_oracle(case, wide_float=True).astype(np.float64)
+    err = np.abs(got.astype(np.float64) - wide)
+    assert np.all(err <= FLOAT_RTOL * np.maximum(np.abs(wide), 1.0)), float(err.max())
+
+
+def check_case(case, ctx, where="device", sentinel=None):
+    got, storage = util.run_gpu(case, ctx, where=where, rounding=Rounding.kReference, sentinel=sentinel)
+    if case.accum == "float32":
+        assert_float_close(got, case)
+    else:
+        want = util.run_oracle(case, Rounding.kReference)
+        assert np.array_equal(got, want), f"{case.name}: {(got != want).sum()} mismatches"
+        gx, _ = util.run_gpu(case, ctx, where=where, rounding=Rounding.kX86)
+        wx = util.run_oracle(case, util.x86_rounding_for(case))
+        assert np.array_equal(gx, wx), f"{case.name} (x86 rounding): {(gx != wx).sum()} mismatches"
+    if sentinel is not None:
+        assert util.padding_untouched(case, storage, sentinel), "wrote outside the logical destination"
+
+
+@pytest.mark.parametrize("case", golden_cases(), ids=lambda c: c.name)
+def test_golden_cases_default_kernels(case, gpu_ctx):
+    g = np.load(os.path.join(GOLDEN, "ruy_reference_outputs.npz"))
+    got, _ = util.run_gpu(case, gpu_ctx, rounding=Rounding.kReference)
+    want = g[case.name + "/reference_mul"]
+    if case.accum == "float32":
+        assert_float_close(got, case)
+        assert np.all(np.abs(got - want) <= 1e-4 * np.maximum(np.abs(want), 1.0))
+        return
+    assert np.array_equal(got, want), f"{(got != want).sum()} mismatches vs ruy::ReferenceMul"
+    avx = g[case.name + "/avx512"]
+    avx = want if avx.size == 0 else avx
+    gx, _ = util.run_gpu(case, gpu_ctx, rounding=Rounding.kX86)
+    assert np.array_equal(gx, avx), f"{(gx != avx).sum()} mismatches vs ruy::Mul on kAvx512"
+
+
+@pytest.mark.parametrize("case", golden_cases()[::3], ids=lambda c: c.name)
+def test_golden_cases_generic_kernel(case, generic_ctx):
+    check_case(case, generic_ctx)
+    assert generic_ctx.counters()["last_kernel"] == "generic"
+
+
+def test_dispatch_uses_the_tensor_core_kernel_for_8bit(gpu_ctx):
+    c = cases.config0()
+    util.run_gpu(c, gpu_ctx)
+    assert gpu_ctx.counters()["last_kernel"] == "tc_i8"
+    util.run_gpu(cases.config1((50, 50, 50)), gpu_ctx)
+    assert gpu_ctx.counters()["last_kernel"] == "sgemm"
+
+
+# ruy/test_fast.cc:31-107 shape lists
+SQUARES = list(range(1, 11)) + [15, 16, 17, 31, 32, 33, 63, 64, 65, 48]
+
+
+@pytest.mark.parametrize("n", SQUARES)
+def test_squares_all_orders(n, gpu_ctx):
+    # ruy/test.h:481-498 (TestLinearAllOrders): 8 order combinations, strides one larger than minimal
+    for o, orders in enumerate(["RCC", "CCC", "RRC", "CRC", "RCR", "CCR", "RRR", "CRR"]):
+        c = cases.random_case(n, n, n, "int8", "int8", "int8", orders=orders, extra_stride=1, perchannel=bool(o % 2),
+                              channel=ChannelDimension.kCol if o % 4 >= 2 else ChannelDimension.kRow, seed=n * 8 + o)
+        check_case(c, gpu_ctx, sentinel=-77)
+
+
+@pytest.mark.parametrize("types", [("uint8", "uint8", "uint8"), ("int8", "int8", "uint8"), ("int8", "uint8", "int8"),
+                                   ("uint8", "int8", "int8"), ("uint8", "uint8", "int16"), ("int8", "int8", "int32"),
+                                   ("int8", "uint8", "int32"), ("int8", "int16", "int16"), ("int16", "int8", "int16"),
+                                   ("float32", "float32", "float32")], ids=lambda t: "x".join(t))
+def test_type_matrix(types, gpu_ctx):
+    # ruy/BUILD:1195-1207
+    l, r, d = types
+    shapes = [(3, 5, 78), (4, 5, 6), (65, 33, 17), (16, 160, 128), (130, 48, 257)]
+    for s, (rows, depth, cols) in enumerate(shapes):
+        for orders in (["RCC", "CRR"] if s % 2 else ["RCC", "CCC", "RRR"]):
+            c = cases.random_case(rows, depth, cols, l, r, d, orders=orders, extra_stride=s % 2, perchannel=bool(s % 2),
+                                  channel=ChannelDimension.kCol if s == 3 else ChannelDimension.kRow, seed=500 + s)
+            check_case(c, gpu_ctx, sentinel=None if d == "float32" else 99)
+
+
+@pytest.mark.parametrize("shape", [(1, 32767, 1), (5, 5001, 4), (2, 45984, 3), (8, 1024, 8), (8, 4096, 8)])
+def test_deep(shape, gpu_ctx):
+    # ruy/test_fast.cc:76-81, ruy/test_slow.cc:29-68 (incl. the row-sums overflow depth)
+    for l, r, d in (("int8", "int8", "int8"), ("uint8", "uint8", "uint8")):
+        check_case(cases.random_case(*shape, l, r, d, seed=31), gpu_ctx)
+        check_case(cases.random_case(*shape, l, r, d, seed=32, symmetric=False), gpu_ctx)
+
+
+@pytest.mark.parametrize("depth", [1, 2, 3, 4])
+def test_shallow(depth, gpu_ctx):
+    # ruy/test_fast.cc:83-88
+    for n in (1, 7, 64, 100):
+        check_case(cases.random_case(n, depth, n, "uint8", "uint8", "uint8", seed=n), gpu_ctx)
+
+
+@pytest.mark.parametrize("width", [1, 2, 3, 4, 5, 8])
+def test_narrow_and_gemv(width, gpu_ctx):
+    # ruy/test_fast.cc:90-107
+    for rows, depth in ((100, 50), (8, 64), (1000, 33)):
+        check_case(cases.random_case(rows, depth, width, "int8", "int8", "int8", seed=width), gpu_ctx)
+        check_case(cases.random_case(width, depth, rows, "uint8", "uint8", "uint8", orders="RCR", seed=width), gpu_ctx)
+        check_case(cases.random_case(rows, depth, width, "float32", "float32", "float32", seed=width), gpu_ctx)
+
+
+def test_host_pointers_are_staged_and_padding_preserved(gpu_ctx):
+    before = gpu_ctx.counters()
+    for c in (cases.config0(), cases.random_case(37, 100, 23, "uint8", "uint8", "uint8", orders="CRC", extra_stride=3, seed=2),
+              cases.random_case(37, 100, 23, "int8", "int8", "int32", orders="RCR", extra_stride=2, seed=3),
+              cases.config1((17, 301, 9))):
+        check_case(c, gpu_ctx, where="host", sentinel=None if c.accum == "float32" else 55)
+    after = gpu_ctx.counters()
+    assert after["h2d_bytes"] > before["h2d_bytes"] and after["d2h_bytes"] > before["d2h_bytes"]
+
+
+def test_mul_async_on_device_operands(gpu_ctx):
+    c = cases.config0(exps=(-17, -13))
+    got, _ = util.run_gpu(c, gpu_ctx, rounding=Rounding.kReference, use_async=True)
+    assert np.array_equal(got, util.run_oracle(c))
+    # host pointers are refused by the stream-ordered entry point
+    lhs, rhs, p, dst, keep = c.bind(c.new_dst())
+    with pytest.raises(ruy_b200.RuyError):
+        ruy_b200.mul_async(lhs, rhs, p, gpu_ctx, dst)
+
+
+def test_empty_and_degenerate_shapes(gpu_ctx):
+    for rows, depth, cols in ((0, 5, 4), (4, 5, 0), (3, 0, 4)):
+        c = cases.random_case(max(rows, 0), depth, max(cols, 0), "int8", "int8", "int8", seed=1)
+        got, _ = util.run_gpu(c, gpu_ctx, rounding=Rounding.kReference)
+        assert np.array_equal(got, util.run_oracle(c))
+
+
+def test_default_multiplier_is_zero(gpu_ctx):
+    # ruy/mul_params.h:259,264: an unset multiplier is 0, so every output is clamp(dst zero point)
+    c = cases.random_case(9, 9, 9, "int8", "int8", "int8", seed=4)
+    c.mfp, c.mexp, c.dst_zp = 0, 0, 7
+    got, _ = util.run_gpu(c, gpu_ctx)
+    assert (got == 7).all()
+
+
+@pytest.mark.parametrize("dst,zp,cols", [("int8", 1, 1), ("int8", 1, 8), ("int8", -1, 8), ("uint8", 1, 8),
+                                         ("int16", 1, 1), ("int16", -1, 8)])
+def test_dst_zero_point_addition_saturates(dst, zp, cols, gpu_ctx):
+    # ruy/test_overflow_dst_zero_point.cc:46-125
+    from ruy_b200.api import Layout
+    bias_v = 32767 if zp > 0 else -32768
+    want = np.iinfo(dst).max if zp > 0 else np.iinfo(dst).min
+    c = cases.MulCase("ovf", np.zeros(1, np.int8), Layout(1, 1, 1, Order.kColMajor), 0, np.zeros(cols, np.int8),
+                      Layout(1, cols, 1, Order.kColMajor), 0, dst, Layout(1, cols, 1, Order.kColMajor), zp,
+                      np.array([bias_v], np.int32), 2**31 - 1, 0)
+    got, _ = util.run_gpu(c, gpu_ctx)
+    assert (got == want).all()
+
+
+def test_examples_known_answers(gpu_ctx):
+    # example/example.cc:21-182: the tiny deterministic inputs, expected values from the oracle
+    from ruy_b200.api import Layout
+    rm, cm = Layout(2, 2, 2, Order.kRowMajor), Layout(2, 2, 2, Order.kColMajor)
+    f = np.array([1, 2, 3, 4], np.float32)
+    c = cases.MulCase("ex_float", f, rm, 0, f.copy(), cm, 0, "float32", cm, 0, np.array([1, 0], np.float32), clamp=(0.0, 15.0))
+    got, _ = util.run_gpu(c, gpu_ctx)
+    assert np.array_equal(got, np.array([[6, 12], [11, 15]], np.float32))
+    c = cases.MulCase("ex_u8", np.array([124, 125, 126, 127], np.uint8), rm, 125, np.array([129, 130, 131, 132], np.uint8),
+                      cm, 132, "uint8", cm, 129, None, 1 << 30, 0)
+    got, _ = util.run_gpu(c, gpu_ctx)
+    assert np.array_equal(got, util.run_oracle(c))
+    i = np.array([1, 2, 3, 4], np.int8)
+    c = cases.MulCase("ex_pc", i, rm, 0, i.copy(), cm, 0, "int8", cm, 0, None, np.array([3 << 28, 5 << 28], np.int32),
+                      np.array([1, -2], np.int32))
+    got, _ = util.run_gpu(c, gpu_ctx)
+    assert np.array_equal(got, util.run_oracle(c))
+    c = cases.MulCase("ex_raw", i, rm, 0, i.copy(), cm, 0, "int32", cm, 0)
+    got, _ = util.run_gpu(c, gpu_ctx)
+    assert np.array_equal(got, np.array([[5, 11], [11, 25]], np.int32))
+    c = cases.MulCase("ex_i16", i, rm, 0, np.array([1000, 2000, 3000, 4000], np.int16), cm, 0, "int16", cm, 0, None,
+                      np.array([3 << 28, 5 << 28], np.int32), np.array([1, -2], np.int32))
+    got, _ = util.run_gpu(c, gpu_ctx)
+    assert np.array_equal(got, util.run_oracle(c))
+
+
+def test_paths_select_the_rounding_contract(gpu_ctx):
+    # ruy/ctx.cc:67-76,150-178: last_used_path = most significant enabled path
+    c = cases.config0(exps=(-17, -13))
+    ref, x86 = util.run_oracle(c, Rounding.kReference), util.run_oracle(c, Rounding.kX86)
+    assert (ref != x86).any()
+    try:
+        got, _ = util.run_gpu(c, gpu_ctx)  # nothing set explicitly: the normative reference rounding
+        assert np.array_equal(got, ref)
+        assert gpu_ctx.last_used_path() == Path.kAvx512
+        gpu_ctx.set_runtime_enabled_paths(Path.kAvx512)
+        assert gpu_ctx.get_runtime_enabled_paths() == Path.kAvx512 | Path.kStandardCpp
+        got, _ = util.run_gpu(c, gpu_ctx)
+        assert np.array_equal(got, x86) and gpu_ctx.last_used_path() == Path.kAvx512
+        gpu_ctx.set_runtime_enabled_paths(Path.kAvx2Fma)
+        got, _ = util.run_gpu(c, gpu_ctx)
+        assert np.array_equal(got, x86) and gpu_ctx.last_used_path() == Path.kAvx2Fma
+        gpu_ctx.set_runtime_enabled_paths(Path.kStandardCpp)
+        got, _ = util.run_gpu(c, gpu_ctx)
+        assert np.array_equal(got, ref) and gpu_ctx.last_used_path() == Path.kStandardCpp
+    finally:
+        gpu_ctx.set_runtime_enabled_paths(Path.kNone)
+
+
+def test_context_defaults_and_advisory(gpu_ctx):
+    # ruy/context_test.cc:27-44, ruy/perchannel_buffers_reallocation_test.cc:43-98
+    assert gpu_ctx.max_num_threads == 1
+    gpu_ctx.set_max_num_threads(4)
+    assert gpu_ctx.max_num_threads == 4
+    gpu_ctx.set_max_num_threads(1)
+    c = cases.random_case(7, 8, 9, "int8", "int8", "int8", perchannel=True, seed=6)
+    util.run_gpu(c, gpu_ctx)
+    assert gpu_ctx.performance_advisory(PerformanceAdvisory.kReallocatedPerChannelBuffer)
+    c2 = cases.random_case(16, 8, 9, "int8", "int8", "int8", perchannel=True, seed=6)
+    util.run_gpu(c2, gpu_ctx)
+    assert not gpu_ctx.performance_advisory(PerformanceAdvisory.kReallocatedPerChannelBuffer)
+
+
+def test_prepacked_cache(gpu_ctx):
+    # ruy/prepacked_cache_test.cc:39-285: miss then hit, key distinctness, policies, eviction, clear
+    import torch
+    ctx = ruy_b200.Context(0)
+    try:
+        c = cases.config0(64, 96, 32, exps=(-17, -13), lhs_cache=CachePolicy.kAlwaysCache)
+        want = util.run_oracle(c)
+        dev = torch.device("cuda", 0)
+        dst = torch.zeros(c.dst_storage_elems(), dtype=torch.int8, device=dev)
+        lhs, rhs, p, d, keep = c.bind(dst, device=dev, rounding=Rounding.kReference)
+        torch.cuda.synchronize()
+        ruy_b200.mul(lhs, rhs, p, ctx, d)
+        k0 = ctx.counters()
+        assert (k0["cache_misses"], k0["cache_hits"], ctx.prepacked_cache_entries()) == (1, 0, 1)
+        assert np.array_equal(c.dst_view(dst.cpu().numpy()), want)
+        dst.zero_()
+        torch.cuda.synchronize()
+        ruy_b200.mul(lhs, rhs, p, ctx, d)
+        k1 = ctx.counters()
+        assert (k1["cache_misses"], k1["cache_hits"], ctx.prepacked_cache_entries()) == (1, 1, 1)
+        assert np.array_equal(c.dst_view(dst.cpu().numpy()), want)
+        size_one = ctx.prepacked_cache_bytes()
+        assert size_one >= 64 * 96
+        # same pointer, different zero point => a different entry (ruy/prepacked_cache.h:68-80)
+        lhs.zero_point = 1
+        torch.cuda.synchronize()
+        ruy_b200.mul(lhs, rhs, p, ctx, d)
+        assert ctx.prepacked_cache_entries() == 2
+        lhs.zero_point = 0
+        # kNeverCache never inserts; kCacheIfLargeSpeedup caches only when the other side is narrow
+        lhs.cache_policy = CachePolicy.kNeverCache
+        ctx.clear_prepacked_cache()
+        assert (ctx.prepacked_cache_entries(), ctx.prepacked_cache_bytes()) == (0, 0)
+        torch.cuda.synchronize()
+        ruy_b200.mul(lhs, rhs, p, ctx, d)
+        assert ctx.prepacked_cache_entries() == 0
+        lhs.cache_policy = CachePolicy.kCacheIfLargeSpeedup
+        ruy_b200.mul(lhs, rhs, p, ctx, d)   # rhs has 32 columns: narrow
+        assert ctx.prepacked_cache_entries() == 1
+        wide = cases.config0(64, 96, 1024, lhs_cache=CachePolicy.kCacheIfLargeSpeedup)
+        util.run_gpu(wide, ctx)
+        assert ctx.prepacked_cache_entries() == 1  # 1024 columns: not worth caching under this policy
+        # eviction: a budget of two entries keeps the most recently used ones
+        ctx.clear_prepacked_cache()
+        ctx.set_prepacked_cache_budget(2 * size_one + 64)
+        mats = []
+        for s in range(3):
+            cs = cases.config0(64, 96, 32, exps=(-17, -13), seed=40 + s, lhs_cache=CachePolicy.kAlwaysCache)
+            ds = torch.zeros(cs.dst_storage_elems(), dtype=torch.int8, device=dev)
+            bound = cs.bind(ds, device=dev, rounding=Rounding.kReference)
+            mats.append((cs, ds, bound))
+            torch.cuda.synchronize()
+            ruy_b200.mul(bound[0], bound[1], bound[2], ctx, bound[3])
+            assert np.array_equal(cs.dst_view(ds.cpu().numpy()), util.run_oracle(cs))
+        assert ctx.prepacked_cache_entries() == 2
+        misses = ctx.counters()["cache_misses"]
+        cs, ds, bound = mats[2]
+        torch.cuda.synchronize()
+        ruy_b200.mul(bound[0], bound[1], bound[2], ctx, bound[3])   # newest: still cached
+        assert ctx.counters()["cache_misses"] == misses
+        cs, ds, bound = mats[0]
+        torch.cuda.synchronize()
+        ruy_b200.mul(bound[0], bound[1], bound[2], ctx, bound[3])   # oldest: was evicted, packed again
+        assert ctx.counters()["cache_misses"] == misses + 1
+        assert np.array_equal(cs.dst_view(ds.cpu().numpy()), util.run_oracle(cs))
+    finally:
+        ctx.close()
+
+
+def test_cached_host_weights_stay_resident(gpu_ctx):
+    ctx = ruy_b200.Context(0)
+    try:
+        c = cases.config0(128, 256, 64, exps=(-17, -13), lhs_cache=CachePolicy.kAlwaysCache)
+        want = util.run_oracle(c)
+        dst = c.new_dst()
+        lhs, rhs, p, d, keep = c.bind(dst, rounding=Rounding.kReference)
+        k0 = ctx.counters()["h2d_bytes"]
+        torch.cuda.synchronize()
+        ruy_b200.mul(lhs, rhs, p, ctx, d)
+        k1 = ctx.counters()["h2d_bytes"]
+        assert np.array_equal(c.dst_view(dst), want)
+        dst[:] = 0
+        torch.cuda.synchronize()
+        ruy_b200.mul(lhs, rhs, p, ctx, d)
+        k2 = ctx.counters()["h2d_bytes"]
+        # the second call with the same weight pointer does not upload the weights again
+        assert k1 - k0 >= 128 * 256 + 64 * 256
+        assert k2 - k1 == (k1 - k0) - 128 * 256
+        assert np.array_equal(c.dst_view(dst), want)
+    finally:
+        ctx.close()
+
+
+def test_pack_entry_point(gpu_ctx):
+    import ctypes as C
+    import torch
+    from ruy_b200._lib import lib
+    c = cases.random_case(45, 70, 21, "uint8", "int8", "int32", orders="CRC", extra_stride=1, seed=12)
+    lhs, rhs, p, d, keep = c.bind(c.new_dst())
+    for side, m in ((0, lhs), (1, rhs)):
+        desc = m.to_desc()
+        width = m.layout.rows if side == 0 else m.layout.cols
+        depth = m.layout.cols if side == 0 else m.layout.rows
+        pd = (depth + 15) // 16 * 16
+        packed = torch.full((width * pd,), 7, dtype=torch.uint8, device="cuda")
+        sums = torch.zeros(width, dtype=torch.int32, device="cuda")
+        got_pd = C.c_int32()
+        rc = lib().ruyb200_pack(gpu_ctx._h, C.byref(desc), side, packed.data_ptr(), packed.numel(), sums.data_ptr(),
+                                C.byref(got_pd))
+        assert rc == 0 and got_pd.value == pd
+        logical = c.lhs if side == 0 else c.rhs
+        lay = m.layout
+        if lay.order == Order.kColMajor:
+            mat = logical.reshape(lay.cols, lay.stride)[:, :lay.rows].T
+        else:
+            mat = logical.reshape(lay.rows, lay.stride)[:, :lay.cols]
+        wk = mat if side == 0 else mat.T          # width x depth
+        out = packed.cpu().numpy().view(logical.dtype).reshape(width, pd)
+        assert np.array_equal(out[:, :depth], wk) and (out[:, depth:] == 0).all()
+        assert np.array_equal(sums.cpu().numpy(), wk.astype(np.int64).sum(axis=1))
+
+
+def test_config1_float_shapes(gpu_ctx):
+    for shape in cases.CONFIG1_SHAPES:
+        c = cases.config1(shape)
+        got, _ = util.run_gpu(c, gpu_ctx)
+        assert_float_close(got, c)
+
+
+def test_config4_layers_batch1(gpu_ctx):
+    for layer in range(len(cases.CONFIG4_LAYERS)):
+        c = cases.config4(layer, batch=1)
+        got, _ = util.run_gpu(c, gpu_ctx, rounding=Rounding.kReference)
+        want = util.run_oracle(c)
+        assert np.array_equal(got, want), (layer, int((got != want).sum()))
+        assert 0.02 < (got == got.max()).mean() + (got == got.min()).mean() < 0.98  # outputs span the range
+
+
+def test_config2_plan(gpu_ctx):
+    import torch
+    n = 48
+    cs = cases.config2(n=16384, seed=0, first=100, count=n)
+    dev = torch.device("cuda", 0)
+    bound, descs = [], []
+    for c in cs:
+        dst = torch.zeros(c.dst_storage_elems(), dtype=torch.int8, device=dev)
+        b = c.bind(dst, device=dev, rounding=Rounding.kReference)
+        bound.append((c, dst, b))
+        descs.append(ruy_b200.make_desc(b[0], b[1], b[2], b[3]))
+    plan = ruy_b200.Plan(gpu_ctx, descs)
+    nbytes, ops = plan.stats()
+    assert ops == sum(c.ops for c in cs) and nbytes == sum(c.algorithmic_bytes() for c in cs)
+    for _ in range(2):
+        torch.cuda.synchronize()
+        plan.run()
+        gpu_ctx.sync()
+        for c, dst, b in bound:
+            assert np.array_equal(c.dst_view(dst.cpu().numpy()), util.run_oracle(c)), c.name
+            dst.zero_()
+    plan.close()
+
+
+def _sampled_block_check(c, out, rows_sel, cols_sel):
+    """Bit-exact check of a sampled rows x cols sub-block of a big result against numpy int64 dots."""
+    L = c.lhs.reshape(c.rows, c.depth).astype(np.int64)[rows_sel]
+    R = c.rhs.reshape(c.cols, c.depth).astype(np.int64)[cols_sel]      # col-major depth x cols
+    acc = (L - c.lhs_zp) @ (R - c.rhs_zp).T
+    if c.bias is not None:
+        acc = acc + c.bias.astype(np.int64)[rows_sel][:, None]
+    if c.dst_dtype != "int32":
+        m = c.mfp.astype(np.int64)[rows_sel][:, None]
+        e = c.mexp.astype(np.int64)[rows_sel][:, None]
+        acc = (acc * m + (1 << (30 - e))) >> (31 - e)
+        acc = np.clip(acc + c.dst_zp, c.clamp[0], c.clamp[1])
+    got = out[np.ix_(rows_sel, cols_sel)].astype(np.int64)
+    assert np.array_equal(got, acc), int((got != acc).sum())
+
+
+def test_config3_full_size_properties(gpu_ctx):
+    """4096 x 4096 x 8192: too big for the scalar oracle, so (1) a random 96 x 96 sub-block of the
+    result is checked bit-exactly against 64-bit numpy dot products, (2) the sum of all raw
+    accumulators equals the dot product of the operands' depth-wise sums (a checksum of checksums),
+    (3) the int8 result equals the requantized int32 result element for element."""
+    import torch
+    rng = np.random.default_rng(1)
+    c32 = cases.config3(dst="int32")
+    dev = torch.device("cuda", 0)
+    d32 = torch.zeros(c32.dst_storage_elems(), dtype=torch.int32, device=dev)
+    b = c32.bind(d32, device=dev)
+    torch.cuda.synchronize()
+    ruy_b200.mul(b[0], b[1], b[2], gpu_ctx, b[3])
+    assert gpu_ctx.counters()["last_kernel"] == "tc_i8"
+    raw = c32.dst_view(d32.cpu().numpy())
+    rows_sel = np.sort(rng.choice(c32.rows, 96, replace=False))
+    cols_sel = np.sort(rng.choice(c32.cols, 96, replace=False))
+    rows_sel[0], rows_sel[-1], cols_sel[0], cols_sel[-1] = 0, c32.rows - 1, 0, c32.cols - 1
+    _sampled_block_check(c32, raw, rows_sel, cols_sel)
+    lsum = c32.lhs.reshape(c32.rows, c32.depth).astype(np.int64).sum(axis=0)
+    rsum = c32.rhs.reshape(c32.cols, c32.depth).astype(np.int64).sum(axis=0)
+    assert int(raw.astype(np.int64).sum()) == int(lsum @ rsum)
+    c8 = cases.config3(dst="int8")
+    d8 = torch.zeros(c8.dst_storage_elems(), dtype=torch.int8, device=dev)
+    b8 = c8.bind(d8, device=dev, rounding=Rounding.kReference)
+    torch.cuda.synchronize()
+    ruy_b200.mul(b8[0], b8[1], b8[2], gpu_ctx, b8[3])
+    out8 = c8.dst_view(d8.cpu().numpy())
+    _sampled_block_check(c8, out8, rows_sel, cols_sel)
+    acc = raw.astype(np.int64) + c8.bias.astype(np.int64)[:, None]
+    m, e = c8.mfp.astype(np.int64)[:, None], c8.mexp.astype(np.int64)[:, None]
+    want = np.clip(((acc * m + (1 << (30 - e))) >> (31 - e)) + c8.dst_zp, -128, 127).astype(np.int8)
+    assert np.array_equal(out8, want)
