@@ -42,55 +42,76 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
-
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clock and throttle reasons through NVML (read-only queries) every few milliseconds
+    from a host thread; `mark()` brackets the timed region so that only samples taken during it are
+    summarised (all samples since start() if the region was too short to catch three)."""
 
     def __init__(self, gpu_index):
         self.gpu_index = gpu_index
-        self.proc = None
-        self.lines = []
+        self.samples = []   # (t, sm_mhz, reasons_bitmask)
+        self.t0 = self.t1 = None
+        self.stop_flag = False
+        self.thread = None
+        self.max_mhz = None
+        try:
+            import pynvml
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(self._physical_index(gpu_index))
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self._reasons = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+        except Exception as e:  # NVML missing: report that rather than guess
+            self.nv = None
+            self.err = str(e)
+
+    @staticmethod
+    def _physical_index(local_index):
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ids = [v.strip() for v in vis.split(",") if v.strip()]
+            if local_index < len(ids) and ids[local_index].isdigit():
+                return int(ids[local_index])
+        return local_index
 
     def start(self):
-        try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.gpu_index)], stdout=subprocess.PIPE,
-                                         stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
+        if self.nv is None:
+            return
+        self.thread = threading.Thread(target=self._run, daemon=True)
+        self.thread.start()
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
+    def _run(self):
+        nv = self.nv
+        while not self.stop_flag:
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)
+                reasons = self._reasons(self.handle)
+                self.samples.append((time.perf_counter(), float(mhz), int(reasons)))
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def mark_begin(self):
+        self.t0 = time.perf_counter()
+
+    def mark_end(self):
+        self.t1 = time.perf_counter()
 
     def stop(self):
-        if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 9:
-                continue
-            try:
-                sm.append(float(parts[1]))
-                mx.append(float(parts[2]))
-            except ValueError:
-                continue
-            for name, val in zip(names, parts[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+        if self.nv is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvml unavailable: " + getattr(self, "err", "")]}
+        self.stop_flag = True
+        self.thread.join(timeout=2)
+        nv = self.nv
+        inside = [x for x in self.samples if self.t0 is not None and self.t0 <= x[0] <= (self.t1 or 1e30)]
+        window = "timed region"
+        if len(inside) < 3:
+            inside, window = self.samples, "warm-up + timed region"
+        bits = {"hw_slowdown": nv.nvmlClocksEventReasonHwSlowdown, "hw_thermal_slowdown": nv.nvmlClocksEventReasonHwThermalSlowdown,
+                "sw_thermal_slowdown": nv.nvmlClocksEventReasonSwThermalSlowdown, "sw_power_cap": nv.nvmlClocksEventReasonSwPowerCap}
+        reasons = sorted(name for name, bit in bits.items() if any(x[2] & bit for x in inside))
+        return {"sm_mhz": float(np.median([x[1] for x in inside])) if inside else None, "sm_max_mhz": self.max_mhz,
+                "reasons": reasons, "samples": len(inside), "window": window}
 
 
 def dist_env():
@@ -199,7 +220,7 @@ def run_gpu_arm(args):
         dist.init_process_group("nccl", device_id=dev)
 
     dst_name = "int32" if args.workload == "c3_i32" else "int8"
-    cols_total = 8192
+    cols_total = args.cols
     assert cols_total % world == 0
     shard = cols_total // world
     case = cases.config3(dst=dst_name, col_begin=rank * shard, col_count=shard)
@@ -222,6 +243,8 @@ def run_gpu_arm(args):
             if use_dist:
                 dist.all_gather_into_tensor(full, mine)
 
+        sampler = ClockSampler(local)
+        sampler.start()
         for _ in range(max(args.warmup, 3)):
             flush.fill_(1)
             step()
@@ -241,12 +264,11 @@ def run_gpu_arm(args):
         if not np.array_equal(out[np.ix_(rs, cs)].astype(np.int64), acc):
             raise SystemExit("bench.py: GPU result does not match the reference arithmetic; refusing to report")
 
-        sampler = ClockSampler(local)
         launches0 = ctx.counters()["launches"]
         if use_dist:
             dist.barrier()
         torch.cuda.synchronize()
-        sampler.start()
+        sampler.mark_begin()
         starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
         mids = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
         stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
@@ -264,6 +286,7 @@ def run_gpu_arm(args):
             dist.barrier()
         torch.cuda.synchronize()
         wall = time.perf_counter() - wall0
+        sampler.mark_end()
         clocks = sampler.stop()
         launches = ctx.counters()["launches"] - launches0
         step_ms = [s.elapsed_time(e) for s, e in zip(starts, stops)]
@@ -347,11 +370,13 @@ def run_gpu_arm(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3_i8", choices=["c3_i8", "c3_i32"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cols", type=int, default=8192,
+                    help="activation columns (8192 is the benchmark configuration; smaller values are for profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

@@ -32,6 +32,7 @@ __global__ void __launch_bounds__(256) generic_mul_kernel(SideView ms, SideView 
   const int ty = threadIdx.x / 32;   // 8 groups, 4 m each
   int32_t iacc[4] = {0, 0, 0, 0};
   float facc[4] = {0.f, 0.f, 0.f, 0.f};
+  float fcomp[4] = {0.f, 0.f, 0.f, 0.f};  // float sums are folded chunk by chunk with compensation
   for (int k0 = 0; k0 < ep.depth; k0 += kChunk) {
     // stage: thread t loads 4 elements per side
     for (int e = threadIdx.x; e < kTile * kChunk; e += 256) {
@@ -52,6 +53,7 @@ __global__ void __launch_bounds__(256) generic_mul_kernel(SideView ms, SideView 
       sn[wn][kn] = vn;
     }
     __syncthreads();
+    float fpart[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 4
     for (int k = 0; k < kChunk; k++) {
       const int32_t bn = sn[tx][k];
@@ -59,10 +61,19 @@ __global__ void __launch_bounds__(256) generic_mul_kernel(SideView ms, SideView 
       for (int r = 0; r < 4; r++) {
         const int32_t am = sm[ty * 4 + r][k];
         if (kFloat) {
-          facc[r] = fmaf(__int_as_float(am), __int_as_float(bn), facc[r]);
+          fpart[r] = fmaf(__int_as_float(am), __int_as_float(bn), fpart[r]);
         } else {
           iacc[r] = (int32_t)((uint32_t)iacc[r] + (uint32_t)(am * bn));
         }
+      }
+    }
+    if (kFloat) {
+#pragma unroll
+      for (int r = 0; r < 4; r++) {
+        const float y = fpart[r] - fcomp[r];
+        const float t = facc[r] + y;
+        fcomp[r] = (t - facc[r]) - y;
+        facc[r] = t;
       }
     }
     __syncthreads();

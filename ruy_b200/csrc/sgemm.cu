@@ -1,7 +1,9 @@
 // fp32 matmul on the CUDA cores: ruy's KernelFloat* (ruy/kernel_avx512.cc:872-1236,
-// ruy/kernel_x86.h:598-912) with the bias + clamp epilogue fused.  Plain FFMA with fp32
-// accumulation in depth order keeps the result within 1e-5 relative of a double-precision
-// reference, which a single-pass TF32 tensor-core product would not.
+// ruy/kernel_x86.h:598-912) with the bias + clamp epilogue fused.  Products are accumulated with
+// FFMA in fp32 over chunks of 16 depth steps, and the chunk sums are folded into the running total
+// with a compensated (Kahan) addition.  A plain fp32 chain over depth 1024 drifts by a few 1e-5 from
+// a double-precision reference once the partial sums reach ~10; the two-level sum stays below 1e-5
+// (and a single-pass TF32 tensor-core product would be at 1e-3).
 #include "common.cuh"
 
 namespace ruyb200 {
@@ -27,11 +29,11 @@ __global__ void __launch_bounds__(256) sgemm_kernel(SideView ms, SideView ns, Ds
   const float* B = (const float*)ns.data;
   const int depth = ep.depth;
 
-  float acc[TM][TN];
+  float acc[TM][TN], comp[TM][TN];
 #pragma unroll
   for (int i = 0; i < TM; i++)
 #pragma unroll
-    for (int j = 0; j < TN; j++) acc[i][j] = 0.f;
+    for (int j = 0; j < TN; j++) acc[i][j] = comp[i][j] = 0.f;
 
   constexpr int A_PER = BM * kBK / 256;
   constexpr int B_PER = BN * kBK / 256;
@@ -81,6 +83,11 @@ __global__ void __launch_bounds__(256) sgemm_kernel(SideView ms, SideView ns, Ds
   for (int k0 = 0; k0 < depth; k0 += kBK) {
     const bool more = k0 + kBK < depth;
     if (more) fetch(k0 + kBK);
+    float part[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; i++)
+#pragma unroll
+      for (int j = 0; j < TN; j++) part[i][j] = 0.f;
 #pragma unroll
     for (int k = 0; k < kBK; k++) {
       float a[TM], b[TN];
@@ -91,8 +98,18 @@ __global__ void __launch_bounds__(256) sgemm_kernel(SideView ms, SideView ns, Ds
 #pragma unroll
       for (int i = 0; i < TM; i++)
 #pragma unroll
-        for (int j = 0; j < TN; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        for (int j = 0; j < TN; j++) part[i][j] = fmaf(a[i], b[j], part[i][j]);
     }
+    // compensated fold of the chunk sum into the running total
+#pragma unroll
+    for (int i = 0; i < TM; i++)
+#pragma unroll
+      for (int j = 0; j < TN; j++) {
+        const float y = part[i][j] - comp[i][j];
+        const float t = acc[i][j] + y;
+        comp[i][j] = (t - acc[i][j]) - y;
+        acc[i][j] = t;
+      }
     if (more) {
       stash(buf ^ 1);
       __syncthreads();
@@ -116,11 +133,11 @@ __global__ void __launch_bounds__(256) sgemm_kernel(SideView ms, SideView ns, Ds
 cudaError_t launch_sgemm(const SideView& m_side, const SideView& n_side, const DstView& dst,
                          const Epilogue& ep, cudaStream_t stream) {
   if (dst.size_m <= 0 || dst.size_n <= 0) return cudaSuccess;
-  const long long big_tiles = (long long)((dst.size_m + 127) / 128) * ((dst.size_n + 127) / 128);
-  if (big_tiles >= 32) {
-    dim3 grid((dst.size_n + 127) / 128, (dst.size_m + 127) / 128);
+  const long long big_tiles = (long long)((dst.size_m + 127) / 128) * ((dst.size_n + 63) / 64);
+  if (big_tiles >= 64) {
+    dim3 grid((dst.size_n + 63) / 64, (dst.size_m + 127) / 128);
     if (grid.y > 65535) return cudaErrorInvalidConfiguration;
-    sgemm_kernel<128, 128><<<grid, 256, 0, stream>>>(m_side, n_side, dst, ep);
+    sgemm_kernel<128, 64><<<grid, 256, 0, stream>>>(m_side, n_side, dst, ep);
   } else if ((long long)((dst.size_m + 63) / 64) * ((dst.size_n + 63) / 64) >= 32) {
     dim3 grid((dst.size_n + 63) / 64, (dst.size_m + 63) / 64);
     sgemm_kernel<64, 64><<<grid, 256, 0, stream>>>(m_side, n_side, dst, ep);

@@ -8,11 +8,13 @@
 //   * warp 1   : issues tcgen05.mma kind::i8 (M=128, N<=256, K=32 per instruction), int32
 //                accumulators in tensor memory, two accumulator buffers so the epilogue of one
 //                tile overlaps the main loop of the next.
-//   * warps 2-5: epilogue.  tcgen05.ld the accumulators, apply bias, zero-point terms,
-//                the fixed-point multiplier, destination zero point and clamp
-//                (ruy/kernel.h:213-237), narrow and store.  The destination's contiguous
-//                dimension is mapped to the MMA N dimension, so each thread owns a run of
-//                consecutive destination elements and writes them with 16-byte stores.
+//   * warps 2-9: epilogue.  Per tile the per-channel terms (bias, zero-point corrections,
+//                multiplier, exponent) are staged once in shared memory; then tcgen05.ld brings
+//                32 accumulator columns at a time into registers, the fixed-point multiplier,
+//                destination zero point and clamp are applied (ruy/kernel.h:213-237), and the
+//                results are narrowed and stored.  The destination's contiguous dimension is
+//                mapped to the MMA N dimension, so each thread owns a run of consecutive
+//                destination elements and writes them with 16-byte stores.
 //
 // Every wait on an mbarrier is bounded; a wait that gives up records a code in *status,
 // raises a CTA-wide abort flag, and every role leaves its loops so that tensor memory is
@@ -33,7 +35,8 @@ constexpr int kABytes = kBlockM * kBlockKBytes;        // 16 KiB
 constexpr int kBBytes = kMaxBlockN * kBlockKBytes;     // 32 KiB
 constexpr int kStageBytes = kABytes + kBBytes;         // 48 KiB
 constexpr int kSmemBytes = kStages * kStageBytes + 1024;  // + alignment slack
-constexpr int kThreads = 192;         // 6 warps
+constexpr int kEpilogueWarps = 8;
+constexpr int kThreads = 64 + 32 * kEpilogueWarps;   // producer warp + MMA warp + epilogue warps
 constexpr int kTmemCols = 512;
 constexpr uint32_t kSpinFast = 2048;
 constexpr uint32_t kSpinLimit = 4u << 20;  // with 100 ns sleeps: well under a second
@@ -155,42 +158,70 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-// Narrow and store 16 consecutive destination elements n0..n0+15 of row m.
-__device__ __forceinline__ void store_run16(const KernelArgs& a, int m, int n0, const int32_t* v) {
-  const int esz = a.ep.dst_dtype == RUYB200_I32 ? 4 : (a.ep.dst_dtype == RUYB200_I16 ? 2 : 1);
-  char* base = (char*)a.dst.data + ((int64_t)m * a.dst.stride_m + n0) * esz;
-  const bool full = n0 + 16 <= a.size_n;
+// AND-reduction of `ok` over the epilogue threads through named barrier 1.
+__device__ __forceinline__ bool epilogue_all(bool ok) {
+  uint32_t res;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %1, 0;\n\t"
+      "bar.red.and.pred p, 1, %2, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(res)
+      : "r"((uint32_t)ok), "n"(32 * kEpilogueWarps)
+      : "memory");
+  return res != 0;
+}
+
+// Per-destination-column (n) terms of one tile, staged in shared memory by the epilogue warps.
+struct NTerms {
+  int32_t add;   // bias (if the channel runs along n) and the zero-point corrections that depend on n
+  int32_t mul;   // fixed-point multiplier (if the channel runs along n)
+  int32_t exp;   // multiplier exponent (if the channel runs along n)
+  int32_t pad;
+};
+
+// Narrow and store 32 consecutive destination elements n0..n0+31 of row m.
+template <int kDstBytes>
+__device__ __forceinline__ void store_run32(const KernelArgs& a, int m, int n0, const int32_t* v) {
+  char* base = (char*)a.dst.data + ((int64_t)m * a.dst.stride_m + n0) * kDstBytes;
+  const bool full = n0 + 32 <= a.size_n;
   if (full && (((uintptr_t)base) & 15) == 0) {
-    if (esz == 1) {
-      uint32_t w[4];
-#pragma unroll
-      for (int q = 0; q < 4; q++) {
-        w[q] = (uint32_t)(v[4 * q] & 0xff) | ((uint32_t)(v[4 * q + 1] & 0xff) << 8) |
-               ((uint32_t)(v[4 * q + 2] & 0xff) << 16) | ((uint32_t)(v[4 * q + 3] & 0xff) << 24);
-      }
-      *(uint4*)base = make_uint4(w[0], w[1], w[2], w[3]);
-    } else if (esz == 2) {
+    uint4* out = (uint4*)base;
+    if (kDstBytes == 1) {
       uint32_t w[8];
 #pragma unroll
       for (int q = 0; q < 8; q++) {
-        w[q] = (uint32_t)(v[2 * q] & 0xffff) | ((uint32_t)(v[2 * q + 1] & 0xffff) << 16);
+        w[q] = (uint32_t)(v[4 * q] & 0xff) | ((uint32_t)(v[4 * q + 1] & 0xff) << 8) |
+               ((uint32_t)(v[4 * q + 2] & 0xff) << 16) | ((uint32_t)(v[4 * q + 3] & 0xff) << 24);
       }
-      ((uint4*)base)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-      ((uint4*)base)[1] = make_uint4(w[4], w[5], w[6], w[7]);
-    } else {
+      out[0] = make_uint4(w[0], w[1], w[2], w[3]);
+      out[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    } else if (kDstBytes == 2) {
 #pragma unroll
       for (int q = 0; q < 4; q++) {
-        ((uint4*)base)[q] = make_uint4((uint32_t)v[4 * q], (uint32_t)v[4 * q + 1], (uint32_t)v[4 * q + 2],
-                                       (uint32_t)v[4 * q + 3]);
+        uint32_t w[4];
+#pragma unroll
+        for (int t = 0; t < 4; t++) {
+          w[t] = (uint32_t)(v[8 * q + 2 * t] & 0xffff) | ((uint32_t)(v[8 * q + 2 * t + 1] & 0xffff) << 16);
+        }
+        out[q] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    } else {
+#pragma unroll
+      for (int q = 0; q < 8; q++) {
+        out[q] = make_uint4((uint32_t)v[4 * q], (uint32_t)v[4 * q + 1], (uint32_t)v[4 * q + 2], (uint32_t)v[4 * q + 3]);
       }
     }
     return;
   }
-  for (int q = 0; q < 16; q++) {
+  for (int q = 0; q < 32; q++) {
     if (n0 + q < a.size_n) store_int(a.dst, a.ep.dst_dtype, m, n0 + q, v[q]);
   }
 }
 
+// kDstBytes: 1 (int8/uint8), 2 (int16), 4 (int32: raw accumulators, no multiplier, no clamp).
+// kX86: the two-step rounding of ruy's x86 kernels instead of the reference rounding.
+template <int kDstBytes, bool kX86>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ CUtensorMap map_n,
              const KernelArgs args) {
@@ -199,6 +230,7 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
   __shared__ __align__(8) uint64_t empty_bar[kStages];
   __shared__ __align__(8) uint64_t acc_full_bar[2];
   __shared__ __align__(8) uint64_t acc_empty_bar[2];
+  __shared__ __align__(16) NTerms n_terms[2][kMaxBlockN];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -213,7 +245,7 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
     }
     for (int b = 0; b < 2; b++) {
       mbar_init(&acc_full_bar[b], 1);
-      mbar_init(&acc_empty_bar[b], 4);
+      mbar_init(&acc_empty_bar[b], kEpilogueWarps);
     }
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -309,8 +341,14 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
       }
     }
   } else {
-    // ---------------- epilogue (warps 2..5) ----------------
-    const int lane_group = warp % 4;   // the TMEM lane quarter this warp may read
+    // ---------------- epilogue (warps 2..9) ----------------
+    const Epilogue& ep = args.ep;
+    const int ew = warp - 2;
+    const int lane_group = warp % 4;       // the TMEM lane quarter this warp may read
+    const int chunk_parity = ew / 4;       // the two warps of a lane quarter alternate 32-column chunks
+    const int etid = threadIdx.x - 64;
+    const bool ch_n = ep.channel_on_n != 0;
+    const int32_t zz = ep.zp_m * ep.zp_n * ep.depth;
     uint32_t tcount = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, tcount++) {
@@ -318,31 +356,73 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
       const int tn = tile % args.tiles_n;
       const int buf = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1;
+      // stage the per-n terms of this tile (overlaps the tile's main loop)
+      NTerms* nt = n_terms[buf];
+      for (int i = etid; i < args.block_n; i += 32 * kEpilogueWarps) {
+        const int n = tn * args.block_n + i;
+        NTerms t;
+        t.add = zz;
+        t.mul = ep.mfp;
+        t.exp = ep.mexp;
+        t.pad = 0;
+        if (n < args.size_n) {
+          if (ep.zp_m) t.add -= ep.zp_m * ep.sums_n[n];
+          if (ch_n) {
+            if (ep.bias) t.add += ((const int32_t*)ep.bias)[n];
+            if (ep.mfp_pc) t.mul = ep.mfp_pc[n];
+            if (ep.mexp_pc) t.exp = ep.mexp_pc[n];
+          }
+        }
+        nt[i] = t;
+      }
+      // per-m terms of this thread's row
+      const int m = tm * kBlockM + lane_group * 32 + lane;
+      const bool m_ok = m < args.size_m;
+      int32_t add_m = 0, mul_m = ep.mfp, exp_m = ep.mexp;
+      if (m_ok) {
+        if (ep.zp_n) add_m -= ep.zp_n * ep.sums_m[m];
+        if (!ch_n) {
+          if (ep.bias) add_m += ((const int32_t*)ep.bias)[m];
+          if (ep.mfp_pc) mul_m = ep.mfp_pc[m];
+          if (ep.mexp_pc) exp_m = ep.mexp_pc[m];
+        }
+      }
       if (!mbar_wait(&acc_full_bar[buf], aph, abortp)) {
         if (!*abortp) atomicCAS(args.status, 0, kTimeoutEpilogue);
         *abortp = 1;
         ok = false;
       }
-      ok = __all_sync(0xffffffffu, ok);
+      // One named-barrier reduction over all epilogue threads: it publishes the staged terms and
+      // makes the continue/abort decision collective, so no warp is ever left waiting for another
+      // that has already left the loop.
+      ok = epilogue_all(ok);
       if (!ok) break;
       tc_fence_after();
-      const int m = tm * kBlockM + lane_group * 32 + lane;
-      const bool m_ok = m < args.size_m;
       const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(buf * kMaxBlockN);
-      for (int c = 0; c < args.block_n; c += 16) {
+      for (int c = chunk_parity * 32; c < args.block_n; c += 64) {
         const int n0 = tn * args.block_n + c;
         if (n0 >= args.size_n) break;   // uniform across the warp
-        uint32_t r[16];
-        tmem_ld_16(taddr + c, r);
+        uint32_t r[32];
+        tmem_ld_32(taddr + c, r);
         tmem_ld_wait();
         if (m_ok) {
-          int32_t v[16];
+          int32_t v[32];
 #pragma unroll
-          for (int q = 0; q < 16; q++) {
-            const int n = n0 + q;
-            v[q] = n < args.size_n ? finish_int((int32_t)r[q], m, n, args.ep) : 0;
+          for (int q = 0; q < 32; q++) {
+            const NTerms t = nt[c + q];
+            int32_t x = (int32_t)(r[q] + (uint32_t)t.add + (uint32_t)add_m);
+            if (kDstBytes != 4) {
+              const int32_t mul = ch_n ? t.mul : mul_m;
+              const int e = ch_n ? t.exp : exp_m;
+              x = kX86 ? requant_x86(x, mul, e) : requant_reference(x, mul, e);
+              x = (int32_t)((uint32_t)x + (uint32_t)ep.dst_zp);
+              x = max(min(x, ep.clamp_max), ep.clamp_min);
+            } else {
+              x = (int32_t)((uint32_t)x + (uint32_t)ep.dst_zp);
+            }
+            v[q] = x;
           }
-          store_run16(args, m, n0, v);
+          store_run32<kDstBytes>(args, m, n0, v);
         }
       }
       tc_fence_before();
@@ -393,6 +473,20 @@ bool make_map(CUtensorMap* map, const SideView& s, int depth, int box_rows) {
 
 bool is_8bit(uint8_t dtype) { return dtype == RUYB200_I8 || dtype == RUYB200_U8; }
 
+template <int kDstBytes, bool kX86>
+cudaError_t launch_variant(const CUtensorMap& map_m, const CUtensorMap& map_n, const KernelArgs& a, int grid,
+                           cudaStream_t stream) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(tc_i8_kernel<kDstBytes, kX86>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kSmemBytes);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  tc_i8_kernel<kDstBytes, kX86><<<grid, kThreads, kSmemBytes, stream>>>(map_m, map_n, a);
+  return cudaGetLastError();
+}
+
 }  // namespace
 
 bool tc_i8_eligible(const SideView& m_side, const SideView& n_side) {
@@ -408,12 +502,6 @@ bool tc_i8_eligible(const SideView& m_side, const SideView& n_side) {
 }
 
 cudaError_t launch_tc_i8(const TcI8Launch& L, cudaStream_t stream) {
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(tc_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    if (e != cudaSuccess) return e;
-    attr_set = true;
-  }
   KernelArgs a;
   a.dst = L.dst;
   a.ep = L.ep;
@@ -437,8 +525,18 @@ cudaError_t launch_tc_i8(const TcI8Launch& L, cudaStream_t stream) {
   }
   const long long tiles = (long long)a.tiles_m * a.tiles_n;
   const int grid = (int)(tiles < L.sm_count ? tiles : L.sm_count);
-  tc_i8_kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_m, map_n, a);
-  return cudaGetLastError();
+  const bool x86 = L.ep.rounding_x86 != 0;
+  switch (L.ep.dst_dtype) {
+    case RUYB200_I8:
+    case RUYB200_U8:
+      return x86 ? launch_variant<1, true>(map_m, map_n, a, grid, stream)
+                 : launch_variant<1, false>(map_m, map_n, a, grid, stream);
+    case RUYB200_I16:
+      return x86 ? launch_variant<2, true>(map_m, map_n, a, grid, stream)
+                 : launch_variant<2, false>(map_m, map_n, a, grid, stream);
+    default:
+      return launch_variant<4, false>(map_m, map_n, a, grid, stream);
+  }
 }
 
 }  // namespace ruyb200
