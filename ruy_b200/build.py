@@ -27,13 +27,14 @@ def build(force=False, verbose=False):
     if not force and not _stale():
         return OUT
     nvcc = os.environ.get("NVCC", "nvcc")
+    extra = os.environ.get("RUYB200_NVCC_EXTRA", "").split()
     objs = []
     procs = []
     os.makedirs(os.path.join(HERE, "build"), exist_ok=True)
     for src in SOURCES:
         obj = os.path.join(HERE, "build", src.replace(".cu", ".o"))
         objs.append(obj)
-        cmd = [nvcc, *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
+        cmd = [nvcc, *NVCC_FLAGS, *extra, "-c", os.path.join(CSRC, src), "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")

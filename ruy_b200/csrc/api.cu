@@ -177,6 +177,7 @@ struct ruyb200_ctx {
   int* h_status = nullptr;  // pinned
   uint64_t counters[6] = {0, 0, 0, 0, 0, 0};
   int force_kernel = 0;  // RUYB200_KERNEL_* or 0
+  bool no_pair = false;  // RUYB200_NO_PAIR=1: keep the tensor-core kernel on one CTA per tile
 };
 
 namespace {
@@ -618,6 +619,7 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous) {
     L.depth = depth;
     L.sm_count = ctx->sm_count;
     L.status = ctx->d_status;
+    L.allow_pair = !ctx->no_pair;
     ce = launch_tc_i8(L, ctx->stream);
   } else if (kernel == RUYB200_KERNEL_SGEMM) {
     ce = launch_sgemm(r.m_side, r.n_side, r.dst, r.ep, ctx->stream);
@@ -694,6 +696,8 @@ int ruyb200_ctx_create_on_stream(int device, void* cuda_stream, ruyb200_ctx** ou
   *ctx->h_status = 0;
   const char* fk = getenv("RUYB200_FORCE_KERNEL");
   if (fk && !strcmp(fk, "generic")) ctx->force_kernel = RUYB200_KERNEL_GENERIC;
+  const char* np = getenv("RUYB200_NO_PAIR");
+  ctx->no_pair = np && *np && *np != '0';
   *out = ctx;
   return RUYB200_OK;
 }

@@ -137,6 +137,7 @@ struct TcI8Launch {
   int depth;
   int sm_count;
   int* status;
+  bool allow_pair;   // permit the two-CTA (cta_group::2) variant
 };
 cudaError_t launch_tc_i8(const TcI8Launch& args, cudaStream_t stream);
 // True when the operands satisfy launch_tc_i8's requirements.

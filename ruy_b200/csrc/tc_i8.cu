@@ -21,6 +21,10 @@
 // released and the kernel returns.
 #include <cuda.h>
 
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
 #include "common.cuh"
 
 namespace ruyb200 {
@@ -35,6 +39,10 @@ constexpr int kABytes = kBlockM * kBlockKBytes;        // 16 KiB
 constexpr int kBBytes = kMaxBlockN * kBlockKBytes;     // 32 KiB
 constexpr int kStageBytes = kABytes + kBBytes;         // 48 KiB
 constexpr int kSmemBytes = kStages * kStageBytes + 1024;  // + alignment slack
+// two-CTA variant: each CTA stages 128 rows of each operand per stage
+constexpr int kPairStages = 6;
+constexpr int kPairStageBytes = kABytes + 128 * kBlockKBytes;   // 32 KiB
+constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + 1024;
 constexpr int kEpilogueWarps = 8;
 constexpr int kThreads = 64 + 32 * kEpilogueWarps;   // producer warp + MMA warp + epilogue warps
 constexpr int kTmemCols = 512;
@@ -54,6 +62,7 @@ struct KernelArgs {
   int tiles_n;
   uint32_t idesc;
   int* status;
+  int debug;       // profiling knobs (0 in production): 1 = epilogue skips its math and stores, 2 = producer skips the loads
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -73,6 +82,19 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
                : "memory");
 }
 
+// Non-blocking probe (try_wait may suspend the thread for a while before answering).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -85,7 +107,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait.  Returns false if it gave up or if another role already raised the abort flag.
+// Bounded wait for the thread that feeds the tensor core: polls tightly (it is alone, and its
+// latency is on the critical path).  Returns false if it gave up or if another role already raised
+// the abort flag.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   for (uint32_t i = 0; i < kSpinLimit; i++) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -97,6 +121,28 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return false;
 }
 
+// Bounded wait that backs off almost immediately.  Every poll of an mbarrier is a shared-memory
+// access that competes with the tensor core's operand fetches, so roles that wait for a long time
+// (the producer on a free stage, the epilogue on a finished tile) sleep between polls.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < kSpinLimit; i++) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (i >= 4) {
+      if ((i & 63) == 0 && *abort_flag) return false;
+      __nanosleep(i < 64 ? 40 : 200);
+    }
+  }
+  return false;
+}
+
+// The same for a whole warp: lane 0 polls, the result is broadcast.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait_relaxed(bar, parity, abort_flag) ? 1 : 0;
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  return ok != 0;
+}
+
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -104,26 +150,75 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
-// Shared-memory matrix descriptor for a depth-contiguous tile stored as rows of 128 bytes with
-// the 128-byte swizzle: 8-row groups are 1024 bytes apart (stride byte offset), the leading
-// byte offset is unused for swizzled depth-major tiles, descriptor version 1, layout type 2.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
-  d |= (uint64_t)1 << 16;
-  d |= (uint64_t)(1024 >> 4) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
-  return d;
+// Shared-memory matrix descriptors describe a depth-contiguous tile stored as rows of 128 bytes with the
+// 128-byte swizzle: 8-row groups are 1024 bytes apart (stride byte offset); the leading byte offset is
+// unused for swizzled depth-major tiles.
+// High 32 bits of the shared-memory matrix descriptor (constant for every tile of this kernel):
+// stride byte offset 1024 >> 4 at bits 32..45, descriptor version 1 at bit 46, 128-byte swizzle at 61..63.
+constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+// Low 32 bits: start address >> 4 at bits 0..13, leading byte offset (unused, 1) at bits 16..29.
+__device__ __forceinline__ uint32_t desc_lo(uint32_t smem_addr) { return ((smem_addr & 0x3FFFF) >> 4) | (1u << 16); }
+
+// Issues the four K=32 MMAs of one 128-byte-deep stage.  The issuing thread is alone and the tensor
+// core's instruction queue is shallow, so everything this thread executes between MMAs is on the
+// critical path: descriptors are advanced with one 32-bit add each (+2 = 32 bytes along depth)
+// inside a single asm block.  `first_accumulates` is 0 only for the first stage of a tile.
+template <bool kPair>
+__device__ __forceinline__ void mma_stage4(uint32_t tmem_d, uint32_t lo_a, uint32_t lo_b, uint32_t idesc,
+                                           uint32_t first_accumulates) {
+  if (kPair) {
+    asm volatile(
+        "{\n\t.reg .pred p, t;\n\t.reg .b64 da, db;\n\t.reg .b32 la, lb;\n\t"
+        "setp.ne.u32 p, %4, 0;\n\t"
+        "setp.eq.u32 t, 0, 0;\n\t"
+        "mov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %5};\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], da, db, %3, p;\n\t"
+        "add.u32 la, %1, 2;\n\tadd.u32 lb, %2, 2;\n\tmov.b64 da, {la, %5};\n\tmov.b64 db, {lb, %5};\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], da, db, %3, t;\n\t"
+        "add.u32 la, %1, 4;\n\tadd.u32 lb, %2, 4;\n\tmov.b64 da, {la, %5};\n\tmov.b64 db, {lb, %5};\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], da, db, %3, t;\n\t"
+        "add.u32 la, %1, 6;\n\tadd.u32 lb, %2, 6;\n\tmov.b64 da, {la, %5};\n\tmov.b64 db, {lb, %5};\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], da, db, %3, t;\n\t}"
+        ::"r"(tmem_d), "r"(lo_a), "r"(lo_b), "r"(idesc), "r"(first_accumulates), "r"(kDescHi)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p, t;\n\t.reg .b64 da, db;\n\t.reg .b32 la, lb;\n\t"
+        "setp.ne.u32 p, %4, 0;\n\t"
+        "setp.eq.u32 t, 0, 0;\n\t"
+        "mov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %3, p;\n\t"
+        "add.u32 la, %1, 2;\n\tadd.u32 lb, %2, 2;\n\tmov.b64 da, {la, %5};\n\tmov.b64 db, {lb, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %3, t;\n\t"
+        "add.u32 la, %1, 4;\n\tadd.u32 lb, %2, 4;\n\tmov.b64 da, {la, %5};\n\tmov.b64 db, {lb, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %3, t;\n\t"
+        "add.u32 la, %1, 6;\n\tadd.u32 lb, %2, 6;\n\tmov.b64 da, {la, %5};\n\tmov.b64 db, {lb, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %3, t;\n\t}"
+        ::"r"(tmem_d), "r"(lo_a), "r"(lo_b), "r"(idesc), "r"(first_accumulates), "r"(kDescHi)
+        : "memory");
+  }
 }
 
-__device__ __forceinline__ void mma_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, bool accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.u32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"((uint32_t)accumulate)
-      : "memory");
+// One K=32 MMA (used for a ragged last stage).
+template <bool kPair>
+__device__ __forceinline__ void mma_one(uint32_t tmem_d, uint32_t lo_a, uint32_t lo_b, uint32_t idesc, uint32_t accumulate) {
+  if (kPair) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.u32 p, %4, 0;\n\t"
+        "mov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %5};\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], da, db, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(lo_a), "r"(lo_b), "r"(idesc), "r"(accumulate), "r"(kDescHi)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.u32 p, %4, 0;\n\t"
+        "mov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %5};\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(lo_a), "r"(lo_b), "r"(idesc), "r"(accumulate), "r"(kDescHi)
+        : "memory");
+  }
 }
 
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
@@ -152,6 +247,13 @@ __device__ __forceinline__ void tmem_ld_16(uint32_t taddr, uint32_t* r) {
         "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
+}
+
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
 }
 
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
@@ -219,15 +321,69 @@ __device__ __forceinline__ void store_run32(const KernelArgs& a, int m, int n0, 
   }
 }
 
+// ---- helpers for the two-CTA (cta_group::2) variant -------------------------------------------
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+
+// Address of the same shared-memory location in the CTA of the given cluster rank.
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t cluster_addr, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr), "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+// TMA load into this CTA's shared memory whose completion is signalled on a barrier that may live
+// in the partner CTA of the pair (no multicast: each CTA fetches its own half).
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int c0, int c1,
+                                                 uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(c0), "r"(c1), "r"(bar_cluster_addr)
+      : "memory");
+}
+
+// Arrives on the barrier at this shared-memory offset in BOTH CTAs of the pair once the MMAs
+// issued so far have completed.
+__device__ __forceinline__ void mma_commit_pair(uint64_t* bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(smem_u32(bar)), "h"((uint16_t)3)
+      : "memory");
+}
+
 // kDstBytes: 1 (int8/uint8), 2 (int16), 4 (int32: raw accumulators, no multiplier, no clamp).
 // kX86: the two-step rounding of ruy's x86 kernels instead of the reference rounding.
-template <int kDstBytes, bool kX86>
+// kPair: two CTAs on neighbouring SMs (a cluster of 2) share each 256 x 256 tile: one thread of the
+//        even CTA issues cta_group::2 MMAs that read both CTAs' shared memory, every CTA loads its
+//        own 128 rows of each operand, keeps its 128 accumulator rows in its own tensor memory and
+//        runs its own epilogue.  Halves shared-memory fill per MMA and deepens the pipeline to 6 stages.
+template <int kDstBytes, bool kX86, bool kPair>
 __global__ void __launch_bounds__(kThreads, 1)
 tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ CUtensorMap map_n,
              const KernelArgs args) {
+  constexpr int kNumStages = kPair ? kPairStages : kStages;
+  constexpr int kStageSize = kPair ? kPairStageBytes : kStageBytes;
+  constexpr int kUnitM = kPair ? 2 * kBlockM : kBlockM;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t full_bar[kStages];
-  __shared__ __align__(8) uint64_t empty_bar[kStages];
+  __shared__ __align__(8) uint64_t full_bar[kNumStages];
+  __shared__ __align__(8) uint64_t empty_bar[kNumStages];
   __shared__ __align__(8) uint64_t acc_full_bar[2];
   __shared__ __align__(8) uint64_t acc_empty_bar[2];
   __shared__ __align__(16) NTerms n_terms[2][kMaxBlockN];
@@ -236,109 +392,179 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
 
   const int warp = threadIdx.x / 32;
   const int lane = threadIdx.x % 32;
+  const uint32_t rank = kPair ? cluster_ctarank() : 0;
+  const int unit = kPair ? blockIdx.x / 2 : blockIdx.x;      // a CTA, or a pair of CTAs
+  const int units = kPair ? gridDim.x / 2 : gridDim.x;
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; s++) {
-      mbar_init(&full_bar[s], 1);
+    for (int s = 0; s < kNumStages; s++) {
+      mbar_init(&full_bar[s], 1);   // pair: only the even CTA's barriers are used; its producer expects both CTAs' bytes
       mbar_init(&empty_bar[s], 1);
     }
     for (int b = 0; b < 2; b++) {
       mbar_init(&acc_full_bar[b], 1);
-      mbar_init(&acc_empty_bar[b], kEpilogueWarps);
+      mbar_init(&acc_empty_bar[b], kPair ? 2 * kEpilogueWarps : kEpilogueWarps);
     }
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
-                 "r"(kTmemCols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (kPair) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                   "r"(kTmemCols)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                   "r"(kTmemCols)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (kPair) cluster_sync_all();   // the partner's barriers are initialised before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
 
   const int num_tiles = args.tiles_m * args.tiles_n;
   const int k_blocks = (args.depth + kBlockKBytes - 1) / kBlockKBytes;
   volatile int* abortp = &abort_flag;
+  const int n_rows_per_cta = kPair ? args.block_n / 2 : args.block_n;   // rows of the n operand this CTA stages
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      uint32_t it = 0;
-      const uint32_t stage_tx = (uint32_t)(kABytes + args.block_n * kBlockKBytes);
+      uint32_t s = 0, ph = 0;
+      uint32_t issued = 0;
+      const uint32_t stage_tx = (uint32_t)(kABytes + n_rows_per_cta * kBlockKBytes);
+      const uint32_t full0_cluster = kPair ? map_to_rank(smem_u32(&full_bar[0]), 0) : 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = unit; tile < num_tiles && ok; tile += units) {
         const int tm = tile / args.tiles_n;
         const int tn = tile % args.tiles_n;
-        for (int kb = 0; kb < k_blocks; kb++, it++) {
-          const int s = it % kStages;
-          const uint32_t ph = (it / kStages) & 1;
-          if (!mbar_wait(&empty_bar[s], ph ^ 1, abortp)) {
-            if (!*abortp) atomicCAS(args.status, 0, kTimeoutProducer);
-            *abortp = 1;
-            ok = false;
-            break;
+        const int row_m = tm * kUnitM + (int)rank * kBlockM;
+        const int row_n = tn * args.block_n + (int)rank * n_rows_per_cta;
+        for (int kb = 0; kb < k_blocks; kb++) {
+          if (!mbar_try_wait(&empty_bar[s], ph ^ 1)) {
+            if (!mbar_wait(&empty_bar[s], ph ^ 1, abortp)) {
+              if (!*abortp) atomicCAS(args.status, 0, kTimeoutProducer);
+              *abortp = 1;
+              ok = false;
+              break;
+            }
           }
-          uint8_t* sa = smem + s * kStageBytes;
+          uint8_t* sa = smem + s * kStageSize;
           uint8_t* sb = sa + kABytes;
-          mbar_expect_tx(&full_bar[s], stage_tx);
-          tma_load_2d(sa, &map_m, kb * kBlockKBytes, tm * kBlockM, &full_bar[s]);
-          tma_load_2d(sb, &map_n, kb * kBlockKBytes, tn * args.block_n, &full_bar[s]);
+          if (args.debug & 2) {   // profiling: signal the stage without fetching anything
+            if (!kPair) mbar_arrive(&full_bar[s]); else if (rank == 0) mbar_arrive(&full_bar[s]);
+          } else if (kPair) {
+            // Both CTAs' copies complete on the even CTA's barrier.  Only that CTA arrives on it, expecting
+            // the bytes of both; its partner's bytes may land first, which a transaction count tolerates
+            // because the phase cannot complete before the one pending arrival has happened.
+            const uint32_t bar = full0_cluster + s * 8;
+            if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * stage_tx);
+            tma_load_2d_pair(sa, &map_m, kb * kBlockKBytes, row_m, bar);
+            tma_load_2d_pair(sb, &map_n, kb * kBlockKBytes, row_n, bar);
+          } else {
+            mbar_expect_tx(&full_bar[s], stage_tx);
+            tma_load_2d(sa, &map_m, kb * kBlockKBytes, row_m, &full_bar[s]);
+            tma_load_2d(sb, &map_n, kb * kBlockKBytes, row_n, &full_bar[s]);
+          }
+          issued++;
+          if (++s == kNumStages) { s = 0; ph ^= 1; }
         }
       }
-      if (!ok && it > 0) {
+      if (!ok && issued > 0 && !kPair) {
         // give copies that are still in flight a bounded chance to land before the CTA exits
-        const uint32_t last = it - 1;
+        const uint32_t last = issued - 1;
         for (uint32_t i = 0; i < kSpinLimit / 64; i++) {
-          if (mbar_try_wait(&full_bar[last % kStages], (last / kStages) & 1)) break;
+          if (mbar_try_wait(&full_bar[last % kNumStages], (last / kNumStages) & 1)) break;
           __nanosleep(100);
         }
       }
     }
   } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0) {
-      uint32_t it = 0;
+    // ---------------- MMA issuer (the even CTA of a pair issues for both) ----------------
+    // The whole warp runs the loop converged and one elected lane issues the tensor-core
+    // instructions: warp-uniform operands then live in uniform registers and the few instructions
+    // between two MMAs stay short enough to keep the tensor core's shallow queue fed.
+    if (rank == 0) {
+      uint32_t s = 0, ph = 0;       // stage index and its phase, advanced incrementally
       uint32_t tcount = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, tcount++) {
+      const uint32_t lo_a0 = desc_lo(smem_u32(smem));
+      const uint32_t stage_step = (uint32_t)kStageSize >> 4;
+      const uint32_t b_off = (uint32_t)kABytes >> 4;
+      const int full_blocks = args.depth / kBlockKBytes;   // stages that hold a whole 128 bytes of depth
+      const uint32_t idesc = args.idesc;
+#ifdef RUYB200_DEBUG_KNOBS
+      long long dbg_t0 = clock64(), dbg_full = 0, dbg_acc = 0;
+#endif
+      for (int tile = unit; tile < num_tiles && ok; tile += units, tcount++) {
         const int buf = tcount & 1;
         const uint32_t aph = (tcount >> 1) & 1;
+#ifdef RUYB200_DEBUG_KNOBS
+        long long dbg_a = clock64();
+#endif
         if (!mbar_wait(&acc_empty_bar[buf], aph ^ 1, abortp)) {
           if (!*abortp) atomicCAS(args.status, 0, kTimeoutMma);
           *abortp = 1;
           break;
         }
         tc_fence_after();
+#ifdef RUYB200_DEBUG_KNOBS
+        dbg_acc += clock64() - dbg_a;
+#endif
         const uint32_t tmem_d = tmem_base + (uint32_t)(buf * kMaxBlockN);
-        for (int kb = 0; kb < k_blocks; kb++, it++) {
-          const int s = it % kStages;
-          const uint32_t ph = (it / kStages) & 1;
-          if (!mbar_wait(&full_bar[s], ph, abortp)) {
-            if (!*abortp) atomicCAS(args.status, 0, kTimeoutMma);
-            *abortp = 1;
-            ok = false;
-            break;
+        for (int kb = 0; kb < k_blocks; kb++) {
+#ifdef RUYB200_DEBUG_KNOBS
+          const bool dbg_ready = (args.debug & 16) ? mbar_test_wait(&full_bar[s], ph) : mbar_try_wait(&full_bar[s], ph);
+          if (!dbg_ready) {
+            long long dbg_b = clock64();
+#else
+          if (!mbar_try_wait(&full_bar[s], ph)) {
+#endif
+            if (!mbar_wait(&full_bar[s], ph, abortp)) {
+              if (!*abortp) atomicCAS(args.status, 0, kTimeoutMma);
+              *abortp = 1;
+              ok = false;
+              break;
+            }
+#ifdef RUYB200_DEBUG_KNOBS
+            dbg_full += clock64() - dbg_b;
+#endif
           }
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem + s * kStageBytes);
-          const uint32_t sb = sa + kABytes;
-          const int rem = args.depth - kb * kBlockKBytes;
-          const int ksteps = rem >= kBlockKBytes ? 4 : (rem + 31) / 32;
-          for (int k = 0; k < ksteps; k++) {
-            const uint64_t da = make_smem_desc(sa + k * 32);
-            const uint64_t db = make_smem_desc(sb + k * 32);
-            mma_i8(tmem_d, da, db, args.idesc, (kb | k) != 0);
+          const uint32_t lo_a = lo_a0 + s * stage_step;
+          const uint32_t lo_b = lo_a + b_off;
+          if (elect_one()) {
+            if (kb < full_blocks) {
+              mma_stage4<kPair>(tmem_d, lo_a, lo_b, idesc, kb != 0);
+            } else {
+              const int ksteps = (args.depth - kb * kBlockKBytes + 31) / 32;
+              for (int k = 0; k < ksteps; k++) mma_one<kPair>(tmem_d, lo_a + 2 * k, lo_b + 2 * k, idesc, (kb | k) != 0);
+            }
+            // frees the stage (in both CTAs of a pair) once these MMAs have read it
+            if (kPair) mma_commit_pair(&empty_bar[s]); else mma_commit(&empty_bar[s]);
           }
-          mma_commit(&empty_bar[s]);   // frees the stage once these MMAs have read it
+          __syncwarp();
+          if (++s == kNumStages) { s = 0; ph ^= 1; }
         }
-        if (ok) mma_commit(&acc_full_bar[buf]);
+        if (ok) {
+          if (elect_one()) {
+            if (kPair) mma_commit_pair(&acc_full_bar[buf]); else mma_commit(&acc_full_bar[buf]);
+          }
+          __syncwarp();
+        }
       }
+#ifdef RUYB200_DEBUG_KNOBS
+      if ((args.debug & 16) && blockIdx.x == 0 && lane == 0)
+        printf("mma warp: total %lld cycles, waiting for data %lld, waiting for a free accumulator %lld, tiles %u\n",
+               clock64() - dbg_t0, dbg_full, dbg_acc, tcount);
+#endif
     }
   } else {
     // ---------------- epilogue (warps 2..9) ----------------
@@ -351,11 +577,17 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
     const int32_t zz = ep.zp_m * ep.zp_n * ep.depth;
     uint32_t tcount = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, tcount++) {
+#ifdef RUYB200_DEBUG_KNOBS
+    long long dbg_wait = 0, dbg_busy = 0, dbg_stage = 0;
+#endif
+    for (int tile = unit; tile < num_tiles && ok; tile += units, tcount++) {
       const int tm = tile / args.tiles_n;
       const int tn = tile % args.tiles_n;
       const int buf = tcount & 1;
       const uint32_t aph = (tcount >> 1) & 1;
+#ifdef RUYB200_DEBUG_KNOBS
+      long long dbg_a = clock64();
+#endif
       // stage the per-n terms of this tile (overlaps the tile's main loop)
       NTerms* nt = n_terms[buf];
       for (int i = etid; i < args.block_n; i += 32 * kEpilogueWarps) {
@@ -376,7 +608,7 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
         nt[i] = t;
       }
       // per-m terms of this thread's row
-      const int m = tm * kBlockM + lane_group * 32 + lane;
+      const int m = tm * kUnitM + (int)rank * kBlockM + lane_group * 32 + lane;
       const bool m_ok = m < args.size_m;
       int32_t add_m = 0, mul_m = ep.mfp, exp_m = ep.mexp;
       if (m_ok) {
@@ -387,7 +619,11 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
           if (ep.mexp_pc) exp_m = ep.mexp_pc[m];
         }
       }
-      if (!mbar_wait(&acc_full_bar[buf], aph, abortp)) {
+#ifdef RUYB200_DEBUG_KNOBS
+      long long dbg_b = clock64();
+      dbg_stage += dbg_b - dbg_a;
+#endif
+      if (!mbar_wait_warp(&acc_full_bar[buf], aph, abortp)) {
         if (!*abortp) atomicCAS(args.status, 0, kTimeoutEpilogue);
         *abortp = 1;
         ok = false;
@@ -398,10 +634,14 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
       ok = epilogue_all(ok);
       if (!ok) break;
       tc_fence_after();
+#ifdef RUYB200_DEBUG_KNOBS
+      long long dbg_c = clock64();
+      dbg_wait += dbg_c - dbg_b;
+#endif
       const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(buf * kMaxBlockN);
       for (int c = chunk_parity * 32; c < args.block_n; c += 64) {
         const int n0 = tn * args.block_n + c;
-        if (n0 >= args.size_n) break;   // uniform across the warp
+        if (n0 >= args.size_n || (args.debug & 1)) break;   // uniform across the warp
         uint32_t r[32];
         tmem_ld_32(taddr + c, r);
         tmem_ld_wait();
@@ -427,15 +667,34 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty_bar[buf]);
+      if (lane == 0) {
+        if (kPair) {
+          mbar_arrive_cluster(map_to_rank(smem_u32(&acc_empty_bar[buf]), 0));   // the issuing CTA tracks both epilogues
+        } else {
+          mbar_arrive(&acc_empty_bar[buf]);
+        }
+      }
+#ifdef RUYB200_DEBUG_KNOBS
+      dbg_busy += clock64() - dbg_c;
+#endif
     }
+#ifdef RUYB200_DEBUG_KNOBS
+    if ((args.debug & 16) && blockIdx.x == 0 && threadIdx.x == 64)
+      printf("epilogue warp: staging %lld, waiting for a tile %lld, working %lld cycles over %u tiles\n", dbg_stage,
+             dbg_wait, dbg_busy, tcount);
+#endif
   }
 
   tc_fence_before();
   __syncthreads();
+  if (kPair) cluster_sync_all();   // neither CTA releases tensor memory or exits while its partner may still signal it
   tc_fence_after();
   if (warp == 0) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    if (kPair) {
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    } else {
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
   }
 }
 
@@ -473,18 +732,76 @@ bool make_map(CUtensorMap* map, const SideView& s, int depth, int box_rows) {
 
 bool is_8bit(uint8_t dtype) { return dtype == RUYB200_I8 || dtype == RUYB200_U8; }
 
-template <int kDstBytes, bool kX86>
+template <int kDstBytes, bool kX86, bool kPair>
 cudaError_t launch_variant(const CUtensorMap& map_m, const CUtensorMap& map_n, const KernelArgs& a, int grid,
                            cudaStream_t stream) {
+  constexpr int smem = kPair ? kPairSmemBytes : kSmemBytes;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(tc_i8_kernel<kDstBytes, kX86>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(tc_i8_kernel<kDstBytes, kX86, kPair>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
-  tc_i8_kernel<kDstBytes, kX86><<<grid, kThreads, kSmemBytes, stream>>>(map_m, map_n, a);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = kPair ? 2 : 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, tc_i8_kernel<kDstBytes, kX86, kPair>, map_m, map_n, a);
+}
+
+// How many 2-CTA clusters of this kernel can be resident at the same time.
+int max_resident_pairs(int sm_count) {
+  static int cached = 0;
+  if (cached) return cached;
+  int n = 0;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(sm_count / 2 * 2);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = kPairSmemBytes;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaFuncSetAttribute(tc_i8_kernel<1, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes);
+  if (cudaOccupancyMaxActiveClusters(&n, tc_i8_kernel<1, false, true>, &cfg) != cudaSuccess || n <= 0) {
+    cudaGetLastError();
+    n = sm_count / 2;
+  }
+  if (n > sm_count / 2) n = sm_count / 2;
+  if (getenv("RUYB200_VERBOSE")) fprintf(stderr, "ruy_b200: %d resident CTA pairs on %d SMs\n", n, sm_count);
+  cached = n;
+  return n;
+}
+
+template <bool kPair>
+cudaError_t launch_by_type(const CUtensorMap& map_m, const CUtensorMap& map_n, const KernelArgs& a, int grid,
+                           cudaStream_t stream) {
+  const bool x86 = a.ep.rounding_x86 != 0;
+  switch (a.ep.dst_dtype) {
+    case RUYB200_I8:
+    case RUYB200_U8:
+      return x86 ? launch_variant<1, true, kPair>(map_m, map_n, a, grid, stream)
+                 : launch_variant<1, false, kPair>(map_m, map_n, a, grid, stream);
+    case RUYB200_I16:
+      return x86 ? launch_variant<2, true, kPair>(map_m, map_n, a, grid, stream)
+                 : launch_variant<2, false, kPair>(map_m, map_n, a, grid, stream);
+    default:
+      return launch_variant<4, false, kPair>(map_m, map_n, a, grid, stream);
+  }
 }
 
 }  // namespace
@@ -508,35 +825,40 @@ cudaError_t launch_tc_i8(const TcI8Launch& L, cudaStream_t stream) {
   a.size_m = L.m_side.width;
   a.size_n = L.n_side.width;
   a.depth = L.depth;
+  a.status = L.status;
+  a.debug = 0;
+#ifdef RUYB200_DEBUG_KNOBS
+  if (getenv("RUYB200_DEBUG")) a.debug = atoi(getenv("RUYB200_DEBUG"));
+#endif
+  const uint32_t fmt_m = L.m_side.dtype == RUYB200_I8 ? 1u : 0u;
+  const uint32_t fmt_n = L.n_side.dtype == RUYB200_I8 ? 1u : 0u;
+  // Two-CTA tiles (256 x 256) when both destination dimensions are large enough to fill them.
+  const bool pair = L.allow_pair && a.size_m >= 256 && a.size_n >= 256 && L.sm_count >= 2;
   int bn = (a.size_n + 15) / 16 * 16;
   if (bn > kMaxBlockN) bn = kMaxBlockN;
   a.block_n = bn;
-  a.tiles_m = (a.size_m + kBlockM - 1) / kBlockM;
+  const int unit_m = pair ? 2 * kBlockM : kBlockM;
+  a.tiles_m = (a.size_m + unit_m - 1) / unit_m;
   a.tiles_n = (a.size_n + bn - 1) / bn;
-  const uint32_t fmt_m = L.m_side.dtype == RUYB200_I8 ? 1u : 0u;
-  const uint32_t fmt_n = L.n_side.dtype == RUYB200_I8 ? 1u : 0u;
   // instruction descriptor: int32 accumulate, operand signedness, both operands depth-major,
-  // N/8 at bit 17, M/16 at bit 24
-  a.idesc = (2u << 4) | (fmt_m << 7) | (fmt_n << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(kBlockM >> 4) << 24);
-  a.status = L.status;
+  // N/8 at bit 17, M/16 at bit 24 (M spans both CTAs of a pair)
+  a.idesc = (2u << 4) | (fmt_m << 7) | (fmt_n << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(unit_m >> 4) << 24);
   CUtensorMap map_m, map_n;
-  if (!make_map(&map_m, L.m_side, L.depth, kBlockM) || !make_map(&map_n, L.n_side, L.depth, bn)) {
+  if (!make_map(&map_m, L.m_side, L.depth, kBlockM) || !make_map(&map_n, L.n_side, L.depth, pair ? bn / 2 : bn)) {
     return cudaErrorInvalidValue;
   }
   const long long tiles = (long long)a.tiles_m * a.tiles_n;
-  const int grid = (int)(tiles < L.sm_count ? tiles : L.sm_count);
-  const bool x86 = L.ep.rounding_x86 != 0;
-  switch (L.ep.dst_dtype) {
-    case RUYB200_I8:
-    case RUYB200_U8:
-      return x86 ? launch_variant<1, true>(map_m, map_n, a, grid, stream)
-                 : launch_variant<1, false>(map_m, map_n, a, grid, stream);
-    case RUYB200_I16:
-      return x86 ? launch_variant<2, true>(map_m, map_n, a, grid, stream)
-                 : launch_variant<2, false>(map_m, map_n, a, grid, stream);
-    default:
-      return launch_variant<4, false>(map_m, map_n, a, grid, stream);
+  if (pair) {
+    // The tile schedule is static, so every pair must be resident from the start: size the grid
+    // by the number of 2-CTA clusters the device can hold at once.
+    int pairs = max_resident_pairs(L.sm_count);
+    const char* env = getenv("RUYB200_PAIRS");
+    if (env && atoi(env) > 0 && atoi(env) < pairs) pairs = atoi(env);
+    const int grid = 2 * (int)(tiles < pairs ? tiles : pairs);
+    return launch_by_type<true>(map_m, map_n, a, grid, stream);
   }
+  const int grid = (int)(tiles < L.sm_count ? tiles : L.sm_count);
+  return launch_by_type<false>(map_m, map_n, a, grid, stream);
 }
 
 }  // namespace ruyb200

@@ -80,6 +80,37 @@ def test_dispatch_uses_the_tensor_core_kernel_for_8bit(gpu_ctx):
     assert gpu_ctx.counters()["last_kernel"] == "sgemm"
 
 
+@pytest.fixture(scope="module")
+def single_cta_ctx(gpu_ctx):
+    """A context that keeps the tensor-core kernel on one CTA per tile (no CTA pairs)."""
+    os.environ["RUYB200_NO_PAIR"] = "1"
+    try:
+        ctx = ruy_b200.Context(0)
+    finally:
+        del os.environ["RUYB200_NO_PAIR"]
+    yield ctx
+    ctx.close()
+
+
+PAIR_SHAPES = [(256, 128, 256), (512, 384, 640), (300, 208, 700), (1024, 4096, 512), (257, 64, 511), (768, 32, 256)]
+
+
+@pytest.mark.parametrize("shape", PAIR_SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_large_tiles_cta_pairs_and_single_cta(shape, gpu_ctx, single_cta_ctx):
+    """Shapes with both destination dimensions >= 256 run on two-CTA (256 x 256) tiles; the same
+    cases must also be exact on the one-CTA kernel."""
+    rows, depth, cols = shape
+    combos = [("int8", "int8", "int8", "RCC"), ("uint8", "uint8", "uint8", "RCR"), ("int8", "uint8", "int32", "RCC"),
+              ("uint8", "int8", "int16", "RCR")]
+    for i, (l, r, d, orders) in enumerate(combos):
+        c = cases.random_case(rows, depth, cols, l, r, d, orders=orders, perchannel=bool(i % 2),
+                              channel=ChannelDimension.kCol if i >= 2 else ChannelDimension.kRow, seed=900 + i,
+                              symmetric=False if i % 2 else None)
+        check_case(c, gpu_ctx)
+        assert gpu_ctx.counters()["last_kernel"] == "tc_i8"
+        check_case(c, single_cta_ctx)
+
+
 # ruy/test_fast.cc:31-107 shape lists
 SQUARES = list(range(1, 11)) + [15, 16, 17, 31, 32, 33, 63, 64, 65, 48]
 
