@@ -336,8 +336,11 @@ def run_gpu_arm(args):
     peak_tops = 2.0 * peaks["bf16_tflops"]
     shard_ops = 2.0 * case.rows * case.depth * shard
     achieved = shard_ops / (kernel_ms * 1e-3) / 1e12
+    # DRAM bytes per launch of this kernel from the ncu launch list (profiles/tc_i8_kernel_c3_launch_list.md):
+    # 50.5 MB read + 2.8 MB written for the full 8192-column int8 workload on one GPU; not measured elsewhere.
+    traffic = 53.3e6 if (world == 1 and cols_total == 8192 and dst_name == "int8") else None
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peak_tops, "unit": "TFLOP/s",
-                "frac": achieved / peak_tops, "traffic": None, "kernel": "tc_i8_kernel",
+                "frac": achieved / peak_tops, "traffic": traffic, "kernel": "tc_i8_kernel",
                 "peak_source": f"2 x bf16_tflops of {peaks['source']} peaks; ops are int8 multiply-adds x 2",
                 "kernel_ms": kernel_ms}
     line = {
