@@ -208,6 +208,23 @@ RUYB200_API int ruyb200_mul_async(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc
 /* Host-side validation only (ruy/validate.h:40-83 plus pointer / stride / shape checks). */
 RUYB200_API int ruyb200_validate(const ruyb200_mul_desc* desc);
 
+/* An 8-bit mul for callers that must not allocate device memory at call time (a runtime whose own
+ * pool owns the whole device, a service under a fixed memory budget, a latency-critical loop that
+ * cannot take the synchronisation an allocation implies).  It has no counterpart in the reference:
+ * ruy::Mul always goes through a ruy::Context and its allocator.  No context is needed; the only
+ * memory used besides the operands and the destination is a 128.25 KiB static device array inside
+ * the library (zero-point sums and a status word), so: at most 16384 destination rows and 16384
+ * destination columns (larger shapes are refused with RUYB200_ERR_INVALID); int8/uint8 operands that
+ * are depth-contiguous (row-major LHS, column-major RHS) with 16-byte aligned base addresses and
+ * strides; all pointers in `desc` device pointers.  No cudaMalloc, cudaFree or other allocating
+ * call is made.  The work is enqueued on `cuda_stream` (a cudaStream_t, NULL for the default
+ * stream) of the current device and the call returns after that stream has finished.  The first
+ * call on each device looks up the array's device address (cudaGetSymbolAddress); make that first
+ * call before starting any stream capture.  Every call shares the one array: two calls whose GPU
+ * work overlaps (different streams or threads) race on it and must be serialised by the caller.
+ * rounding_mode RUYB200_ROUNDING_FROM_PATH means the reference rounding here. */
+RUYB200_API int ruyb200_mul_noalloc(const ruyb200_mul_desc* desc, void* cuda_stream);
+
 /* ---- plans: many independent muls in one launch ------------------------ */
 
 /* Additive surface (ruy::Mul is one-matmul-per-call).  A plan plays the role that

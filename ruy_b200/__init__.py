@@ -8,5 +8,5 @@ the benchmark.
 from .api import (  # noqa: F401
     CachePolicy, ChannelDimension, Context, Layout, Matrix, MulParams, Order, Path,
     PerformanceAdvisory, Plan, Rounding, RuyError, kAllPaths, kDefaultPaths,
-    make_desc, make_simple_layout, mul, mul_async, validate,
+    make_desc, make_simple_layout, mul, mul_async, mul_noalloc, validate,
 )

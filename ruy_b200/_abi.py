@@ -105,6 +105,7 @@ PROTOTYPES = {
     "ruyb200_mul": (C.c_int, [C.c_void_p, _P(MulDesc)]),
     "ruyb200_mul_async": (C.c_int, [C.c_void_p, _P(MulDesc)]),
     "ruyb200_validate": (C.c_int, [_P(MulDesc)]),
+    "ruyb200_mul_noalloc": (C.c_int, [_P(MulDesc), C.c_void_p]),
     "ruyb200_plan_create": (C.c_int, [C.c_void_p, _P(MulDesc), C.c_int, _P(C.c_void_p)]),
     "ruyb200_plan_run": (C.c_int, [C.c_void_p]),
     "ruyb200_plan_destroy": (C.c_int, [C.c_void_p]),

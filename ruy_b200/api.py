@@ -261,6 +261,13 @@ def mul_async(lhs, rhs, mul_params, context, dst):
     _check(lib().ruyb200_mul_async(context._h, C.byref(d)), "ruyb200_mul_async")
 
 
+def mul_noalloc(lhs, rhs, mul_params, dst, stream=None):
+    """ruyb200_mul_noalloc: the 8-bit mul for callers that must not allocate (no context, static scratch,
+    device-resident depth-contiguous operands, at most 16384 x 16384 destinations).  Synchronous."""
+    d = make_desc(lhs, rhs, mul_params, dst)
+    _check(lib().ruyb200_mul_noalloc(C.byref(d), C.c_void_p(stream) if stream else None), "ruyb200_mul_noalloc")
+
+
 def validate(lhs, rhs, mul_params, dst):
     d = make_desc(lhs, rhs, mul_params, dst)
     return lib().ruyb200_validate(C.byref(d))
