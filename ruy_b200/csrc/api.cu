@@ -20,6 +20,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "batch_i8.h"
 #include "plan.h"
 
 using namespace ruyb200;
@@ -155,6 +156,7 @@ struct CacheEntry {
   int packed_depth = 0;
   size_t bytes = 0;
   uint64_t stamp = 0;
+  int pins = 0;   // plans that hold pointers into this entry; pinned entries are never evicted or cleared
 };
 
 }  // namespace
@@ -320,14 +322,18 @@ size_t storage_span_bytes(const ruyb200_matrix& m) {
   return ((size_t)(outer - 1) * (size_t)m.stride + (size_t)inner) * dtype_size(m.dtype);
 }
 
-void cache_evict_one(ruyb200_ctx* ctx) {
-  auto oldest = ctx->cache.begin();
+// Evicts the least recently used unpinned entry; false if there is none.
+bool cache_evict_one(ruyb200_ctx* ctx) {
+  auto oldest = ctx->cache.end();
   for (auto it = ctx->cache.begin(); it != ctx->cache.end(); ++it) {
-    if (it->second.stamp < oldest->second.stamp) oldest = it;
+    if (it->second.pins > 0) continue;
+    if (oldest == ctx->cache.end() || it->second.stamp < oldest->second.stamp) oldest = it;
   }
+  if (oldest == ctx->cache.end()) return false;
   ctx->cache_bytes -= oldest->second.bytes;
   cudaFree(oldest->second.packed);
   ctx->cache.erase(oldest);
+  return true;
 }
 
 // ruy/prepare_packed_matrices.cc:38-66.
@@ -397,7 +403,9 @@ int prepare_side(ruyb200_ctx* ctx, const ruyb200_matrix& m, int side, int depth,
       const size_t sums_bytes = integer ? (((size_t)src.width * 4 + 255) & ~size_t(255)) : 0;
       const size_t total = data_bytes + sums_bytes;
       // ruy/prepacked_cache.cc:104-127: make room first, oldest entries go first
-      while (!ctx->cache.empty() && ctx->cache_bytes + total > ctx->cache_budget) cache_evict_one(ctx);
+      while (!ctx->cache.empty() && ctx->cache_bytes + total > ctx->cache_budget) {
+        if (!cache_evict_one(ctx)) break;
+      }
       void* buf = nullptr;
       CUDA_TRY(cudaMalloc(&buf, total));
       SideView staged = src;
@@ -708,7 +716,8 @@ int ruyb200_ctx_destroy(ruyb200_ctx* ctx) {
   if (!ctx) return RUYB200_OK;
   DeviceGuard guard(ctx->device);
   if (ctx->stream) cudaStreamSynchronize(ctx->stream);
-  ruyb200_ctx_clear_prepacked_cache(ctx);
+  for (auto& kv : ctx->cache) cudaFree(kv.second.packed);
+  ctx->cache.clear();
   ctx->arena.release();
   if (ctx->d_status) cudaFree(ctx->d_status);
   if (ctx->h_status) cudaFreeHost(ctx->h_status);
@@ -744,9 +753,15 @@ int ruyb200_ctx_clear_prepacked_cache(ruyb200_ctx* ctx) {
   if (!ctx) return fail(RUYB200_ERR_INVALID, "null context");
   DeviceGuard guard(ctx->device);
   if (ctx->stream) cudaStreamSynchronize(ctx->stream);
-  for (auto& kv : ctx->cache) cudaFree(kv.second.packed);
-  ctx->cache.clear();
-  ctx->cache_bytes = 0;
+  for (auto it = ctx->cache.begin(); it != ctx->cache.end();) {
+    if (it->second.pins > 0) {   // a live plan still reads this entry
+      ++it;
+      continue;
+    }
+    ctx->cache_bytes -= it->second.bytes;
+    cudaFree(it->second.packed);
+    it = ctx->cache.erase(it);
+  }
   return RUYB200_OK;
 }
 
@@ -844,5 +859,86 @@ int ctx_rounding_is_x86(ruyb200_ctx* ctx, int rounding_mode) {
   return paths_explicit(ctx) && (ctx->last_used_path & kX86Paths) ? 1 : 0;
 }
 int ctx_run_mul_async(ruyb200_ctx* ctx, const ruyb200_mul_desc* d) { return run_mul(ctx, d, false); }
+
+// Resolves one (already validated, device-resident) mul for a plan.  Operands whose cache policy asks for
+// it are taken from the prepacked cache (packed now on a miss) and pinned there; `pinned` receives the
+// entries to unpin when the plan dies.  *fits tells whether the mul can be an item of the batched kernel.
+int ctx_plan_item(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, BatchItem* out, bool* fits,
+                  std::vector<const void*>* pinned_sources) {
+  const ruyb200_mul_desc& d = *desc;
+  *fits = false;
+  memset(out, 0, sizeof(*out));
+  if (d.params.accum_dtype != RUYB200_I32 || d.dst.rows == 0 || d.dst.cols == 0 || d.lhs.cols == 0) return RUYB200_OK;
+  DeviceGuard guard(ctx->device);
+  const int depth = d.lhs.cols;
+  SideView views[2];
+  const ruyb200_matrix* mats[2] = {&d.lhs, &d.rhs};
+  for (int side = 0; side < 2; side++) {
+    const ruyb200_matrix& m = *mats[side];
+    const int other_width = side == 0 ? d.rhs.cols : d.lhs.rows;
+    if (should_cache(m, other_width) && dtype_size(m.dtype) == 1) {
+      const int32_t* sums = nullptr;
+      ctx->arena.reset(false);
+      int rc = prepare_side(ctx, m, side, depth, true, false, true, &views[side], &sums);
+      if (rc) return rc;
+      SideView src = side_view(m, side, m.data);
+      CacheKey key(m.data, src.width, depth, src.stride_w, src.stride_k, m.zero_point, (int)m.dtype, side);
+      auto it = ctx->cache.find(key);
+      if (it != ctx->cache.end()) {
+        it->second.pins++;
+        pinned_sources->push_back(m.data);
+      }
+    } else {
+      views[side] = side_view(m, side, m.data);
+    }
+  }
+  const bool dst_col_major = d.dst.order == RUYB200_COL_MAJOR;
+  const SideView& ms = dst_col_major ? views[0] : views[1];   // the destination's contiguous dimension
+  const SideView& ns = dst_col_major ? views[1] : views[0];
+  if (!batch_i8_fits(ms, ns, depth)) return RUYB200_OK;
+  const bool channel_row = d.params.channel_dimension == RUYB200_CHANNEL_ROW;
+  out->m_ptr = (const uint8_t*)ms.data;
+  out->n_ptr = (const uint8_t*)ns.data;
+  out->dst = (uint8_t*)d.dst.data;
+  out->bias = (const int32_t*)d.params.bias;
+  if (d.dst.dtype != RUYB200_I32) {
+    out->mfp_pc = d.params.multiplier_fixedpoint_perchannel;
+    out->mexp_pc = d.params.multiplier_exponent_perchannel;
+    out->mfp = d.params.multiplier_fixedpoint;
+    out->mexp = d.params.multiplier_exponent;
+  }
+  out->size_m = ms.width;
+  out->size_n = ns.width;
+  out->depth = depth;
+  out->stride_m = (int32_t)ms.stride_w;
+  out->stride_n = (int32_t)ns.stride_w;
+  out->dst_stride = d.dst.stride;
+  out->zp_m = ms.zero_point;
+  out->zp_n = ns.zero_point;
+  out->dst_zp = d.dst.zero_point;
+  out->clamp_min = d.params.clamp_min.i;
+  out->clamp_max = d.params.clamp_max.i;
+  uint32_t flags = 0;
+  const bool channel_on_m = dst_col_major ? channel_row : !channel_row;
+  if (!channel_on_m) flags |= kItemChannelOnN;
+  if (ms.dtype == RUYB200_I8) flags |= kItemMSigned;
+  if (ns.dtype == RUYB200_I8) flags |= kItemNSigned;
+  if (ctx_rounding_is_x86(ctx, d.params.rounding_mode)) flags |= kItemX86;
+  flags |= (uint32_t)d.dst.dtype << kItemDstShift;
+  out->flags = flags;
+  *fits = true;
+  return RUYB200_OK;
+}
+
+void ctx_unpin(ruyb200_ctx* ctx, const std::vector<const void*>& sources) {
+  for (const void* p : sources) {
+    for (auto& kv : ctx->cache) {
+      if (std::get<0>(kv.first) == p && kv.second.pins > 0) {
+        kv.second.pins--;
+        break;
+      }
+    }
+  }
+}
 
 }  // namespace ruyb200

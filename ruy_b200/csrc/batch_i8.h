@@ -1,0 +1,55 @@
+// Work-item descriptor of the persistent many-small-muls kernel (batch_i8.cu).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace ruyb200 {
+
+enum : uint32_t {
+  kItemChannelOnN = 1u << 0,   // per-channel buffers are indexed by n (else by m)
+  kItemMSigned = 1u << 1,      // m-side operand is int8 (else uint8)
+  kItemNSigned = 1u << 2,
+  kItemX86 = 1u << 3,          // x86 two-step rounding
+  kItemDstShift = 4            // 3 bits: ruyb200_dtype of the destination
+};
+
+// One small mul, fully resolved to device pointers.  "m" is the destination's contiguous dimension
+// (it sits on the tensor-memory lanes), "n" the other one; element (m, n) is stored at
+// dst[n * dst_stride + m].  Both operands are depth-contiguous with rows stride_* bytes apart.
+struct alignas(16) BatchItem {
+  const uint8_t* m_ptr;
+  const uint8_t* n_ptr;
+  uint8_t* dst;
+  const int32_t* bias;
+  const int32_t* mfp_pc;
+  const int32_t* mexp_pc;
+  int32_t size_m;
+  int32_t size_n;
+  int32_t depth;
+  int32_t stride_m;
+  int32_t stride_n;
+  int32_t dst_stride;
+  int32_t zp_m;
+  int32_t zp_n;
+  int32_t dst_zp;
+  int32_t clamp_min;
+  int32_t clamp_max;
+  int32_t mfp;
+  int32_t mexp;
+  uint32_t flags;
+  int32_t reserved[6];
+};
+static_assert(sizeof(BatchItem) == 128, "BatchItem is copied as eight 16-byte pieces");
+
+// True when a mul can be a work item: 8-bit depth-contiguous operands, all three dimensions <= 128,
+// 8-byte aligned rows.
+bool batch_i8_fits(const SideView& m_side, const SideView& n_side, int depth);
+
+// `items` and `order` (item indices, heaviest first) are device arrays; CTA b handles order[b], order[b+grid], ...
+cudaError_t launch_batch_i8(const BatchItem* items, const int32_t* order, int num_items, int sm_count, int* status,
+                            cudaStream_t stream);
+
+}  // namespace ruyb200

@@ -1,6 +1,12 @@
 // Plans: many independent muls submitted once and replayed (see ruyb200_plan_create).
+//
+// The muls whose three dimensions fit one tensor-core tile become work items of the persistent batched
+// kernel (batch_i8.cu): one launch per replay, whatever their number.  The others are replayed through
+// the ordinary single-mul dispatch.
+#include <algorithm>
 #include <vector>
 
+#include "batch_i8.h"
 #include "common.cuh"
 #include "plan.h"
 
@@ -8,7 +14,11 @@ using namespace ruyb200;
 
 struct ruyb200_plan {
   ruyb200_ctx* ctx = nullptr;
-  std::vector<ruyb200_mul_desc> descs;
+  std::vector<ruyb200_mul_desc> single;     // muls replayed one launch at a time
+  std::vector<const void*> pinned;          // prepacked-cache entries this plan reads
+  BatchItem* d_items = nullptr;
+  int32_t* d_order = nullptr;
+  int num_items = 0;
   uint64_t bytes = 0;
   uint64_t ops = 0;
 };
@@ -16,6 +26,14 @@ struct ruyb200_plan {
 namespace {
 
 size_t esize(int dtype) { return dtype == RUYB200_I8 || dtype == RUYB200_U8 ? 1 : (dtype == RUYB200_I16 ? 2 : 4); }
+
+void free_plan(ruyb200_plan* plan) {
+  if (!plan) return;
+  if (plan->d_items) cudaFree(plan->d_items);
+  if (plan->d_order) cudaFree(plan->d_order);
+  ctx_unpin(plan->ctx, plan->pinned);
+  delete plan;
+}
 
 }  // namespace
 
@@ -26,19 +44,20 @@ int ruyb200_plan_create(ruyb200_ctx* ctx, const ruyb200_mul_desc* descs, int n, 
   *out = nullptr;
   ruyb200_plan* plan = new ruyb200_plan;
   plan->ctx = ctx;
-  plan->descs.assign(descs, descs + n);
+  std::vector<BatchItem> items;
+  std::vector<long long> cost;
   for (int i = 0; i < n; i++) {
     const ruyb200_mul_desc& d = descs[i];
     int rc = ctx_validate(&d);
     if (rc) {
-      delete plan;
+      free_plan(plan);
       return rc;
     }
     const void* ptrs[6] = {d.lhs.data, d.rhs.data, d.dst.data, d.params.bias, d.params.multiplier_fixedpoint_perchannel,
                            d.params.multiplier_exponent_perchannel};
     for (const void* p : ptrs) {
       if (p && !ptr_on_device(p)) {
-        delete plan;
+        free_plan(plan);
         return ctx_fail(RUYB200_ERR_INVALID, "plans need device pointers");
       }
     }
@@ -48,6 +67,46 @@ int ruyb200_plan_create(ruyb200_ctx* ctx, const ruyb200_mul_desc* descs, int n, 
     const uint64_t nch = d.params.channel_dimension == RUYB200_CHANNEL_ROW ? r : c;
     if (d.params.bias) plan->bytes += 4 * nch;
     if (d.params.multiplier_fixedpoint_perchannel) plan->bytes += 8 * nch;
+    BatchItem item;
+    bool fits = false;
+    rc = ctx_plan_item(ctx, &d, &item, &fits, &plan->pinned);
+    if (rc) {
+      free_plan(plan);
+      return rc;
+    }
+    if (fits) {
+      items.push_back(item);
+      // packing bytes dominate; epilogue work follows the destination size
+      cost.push_back((long long)(r + c) * ((k + 31) / 32 * 32) + 4ll * r * c);
+    } else {
+      plan->single.push_back(d);
+    }
+  }
+  plan->num_items = (int)items.size();
+  if (plan->num_items > 0) {
+    std::vector<int32_t> order(items.size());
+    for (size_t i = 0; i < order.size(); i++) order[i] = (int32_t)i;
+    std::stable_sort(order.begin(), order.end(), [&](int32_t a, int32_t b) { return cost[a] > cost[b]; });
+    // CTA b takes order[b], order[b + grid], ...: reverse every other round so heavy and light items pair up
+    const int grid = std::min<int>(plan->num_items, ctx_sm_count(ctx));
+    for (size_t start = grid; start + 1 < order.size(); start += 2 * (size_t)grid) {
+      const size_t end = std::min(order.size(), start + grid);
+      std::reverse(order.begin() + start, order.begin() + end);
+    }
+    if (cudaMalloc(&plan->d_items, items.size() * sizeof(BatchItem)) != cudaSuccess ||
+        cudaMalloc(&plan->d_order, order.size() * sizeof(int32_t)) != cudaSuccess) {
+      cudaGetLastError();
+      free_plan(plan);
+      return ctx_fail(RUYB200_ERR_OOM, "plan allocation failed");
+    }
+    cudaMemcpy(plan->d_items, items.data(), items.size() * sizeof(BatchItem), cudaMemcpyHostToDevice);
+    cudaMemcpy(plan->d_order, order.data(), order.size() * sizeof(int32_t), cudaMemcpyHostToDevice);
+  }
+  // packing launched for cache misses has finished before the plan is used
+  int rc = ruyb200_ctx_sync(ctx);
+  if (rc) {
+    free_plan(plan);
+    return rc;
   }
   *out = plan;
   return RUYB200_OK;
@@ -55,7 +114,13 @@ int ruyb200_plan_create(ruyb200_ctx* ctx, const ruyb200_mul_desc* descs, int n, 
 
 int ruyb200_plan_run(ruyb200_plan* plan) {
   if (!plan) return ctx_fail(RUYB200_ERR_INVALID, "null plan");
-  for (const ruyb200_mul_desc& d : plan->descs) {
+  if (plan->num_items > 0) {
+    cudaError_t ce = launch_batch_i8(plan->d_items, plan->d_order, plan->num_items, ctx_sm_count(plan->ctx),
+                                     ctx_status_word(plan->ctx), ctx_stream(plan->ctx));
+    ctx_count_launch(plan->ctx, RUYB200_KERNEL_BATCH_I8);
+    if (ce != cudaSuccess) return ctx_fail(RUYB200_ERR_CUDA, cudaGetErrorString(ce));
+  }
+  for (const ruyb200_mul_desc& d : plan->single) {
     int rc = ctx_run_mul_async(plan->ctx, &d);
     if (rc) return rc;
   }
@@ -63,7 +128,7 @@ int ruyb200_plan_run(ruyb200_plan* plan) {
 }
 
 int ruyb200_plan_destroy(ruyb200_plan* plan) {
-  delete plan;
+  free_plan(plan);
   return RUYB200_OK;
 }
 

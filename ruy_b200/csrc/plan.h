@@ -3,7 +3,10 @@
 
 #include <cuda_runtime.h>
 
+#include <vector>
+
 #include "../../include/ruy_b200.h"
+#include "batch_i8.h"
 
 namespace ruyb200 {
 
@@ -17,5 +20,8 @@ int ctx_validate(const ruyb200_mul_desc* d);
 bool ptr_on_device(const void* p);
 int ctx_rounding_is_x86(ruyb200_ctx* ctx, int rounding_mode);
 int ctx_run_mul_async(ruyb200_ctx* ctx, const ruyb200_mul_desc* d);
+int ctx_plan_item(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, BatchItem* out, bool* fits,
+                  std::vector<const void*>* pinned_sources);
+void ctx_unpin(ruyb200_ctx* ctx, const std::vector<const void*>& sources);
 
 }  // namespace ruyb200

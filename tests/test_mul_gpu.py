@@ -429,12 +429,71 @@ def test_config2_plan(gpu_ctx):
     assert ops == sum(c.ops for c in cs) and nbytes == sum(c.algorithmic_bytes() for c in cs)
     for _ in range(2):
         torch.cuda.synchronize()
+        before = gpu_ctx.counters()["launches"]
         plan.run()
         gpu_ctx.sync()
+        assert gpu_ctx.counters()["launches"] - before == 1          # all 48 muls in one persistent launch
+        assert gpu_ctx.counters()["last_kernel"] == "batch_i8"
         for c, dst, b in bound:
             assert np.array_equal(c.dst_view(dst.cpu().numpy()), util.run_oracle(c)), c.name
             dst.zero_()
     plan.close()
+
+
+def test_plan_mixed_items(gpu_ctx):
+    """A plan with every kind of item: asymmetric uint8 (both zero-point sums computed while packing), int16 and
+    int32 destinations, row-major destinations, per-column channels, depths that are not multiples of 8 or 32,
+    a cached LHS, and muls too large for the batched kernel (replayed through the single-mul dispatch)."""
+    import torch
+    dev = torch.device("cuda", 0)
+    specs = [
+        dict(rows=16, depth=16, cols=16, lhs="uint8", rhs="uint8", dst="uint8", orders="RCC", symmetric=False),
+        dict(rows=24, depth=40, cols=128, lhs="int8", rhs="uint8", dst="int8", orders="RCR", symmetric=False, perchannel=True),
+        dict(rows=128, depth=128, cols=128, lhs="uint8", rhs="int8", dst="int16", orders="RCC", symmetric=False,
+             perchannel=True, channel=ChannelDimension.kCol),
+        dict(rows=97, depth=50, cols=33, lhs="int8", rhs="int8", dst="int32", orders="RCC"),
+        dict(rows=5, depth=7, cols=3, lhs="uint8", rhs="uint8", dst="uint8", orders="RCR", symmetric=False, extra_stride=1),
+        dict(rows=64, depth=96, cols=48, lhs="int8", rhs="int8", dst="int8", orders="RCC", perchannel=True,
+             lhs_cache=CachePolicy.kAlwaysCache),
+        dict(rows=64, depth=96, cols=48, lhs="int8", rhs="int8", dst="int8", orders="CRC", perchannel=True,
+             lhs_cache=CachePolicy.kAlwaysCache),                       # column-major LHS: packed through the cache
+        dict(rows=200, depth=64, cols=64, lhs="int8", rhs="int8", dst="int8", orders="RCC"),     # too many rows
+        dict(rows=64, depth=300, cols=64, lhs="uint8", rhs="uint8", dst="uint8", orders="RCC", symmetric=False),  # too deep
+        dict(rows=32, depth=32, cols=32, lhs="int8", rhs="int16", dst="int16", orders="RCC"),    # 16-bit operand
+    ]
+    ctx = ruy_b200.Context(0)
+    try:
+        bound, descs = [], []
+        for i, sp in enumerate(specs):
+            sp = dict(sp)
+            c = cases.random_case(sp.pop("rows"), sp.pop("depth"), sp.pop("cols"), sp.pop("lhs"), sp.pop("rhs"), sp.pop("dst"),
+                                  seed=300 + i, **sp)
+            host = c.new_dst(fill=0)
+            dst = torch.from_numpy(host).to(dev)
+            b = c.bind(dst, device=dev, rounding=Rounding.kReference)
+            bound.append((c, dst, b))
+            descs.append(ruy_b200.make_desc(b[0], b[1], b[2], b[3]))
+        plan = ruy_b200.Plan(ctx, descs)
+        assert ctx.prepacked_cache_entries() == 2
+        for rep in range(2):
+            torch.cuda.synchronize()
+            launches = ctx.counters()["launches"]
+            plan.run()
+            ctx.sync()
+            assert ctx.counters()["launches"] - launches >= 1 + 3   # one batched launch + the three singles (+ helpers)
+            for c, dst, b in bound:
+                got = c.dst_view(dst.cpu().numpy())
+                want = util.run_oracle(c, Rounding.kReference)
+                assert np.array_equal(got, want), f"{c.name}: {(got != want).sum()} mismatches (replay {rep})"
+                dst.zero_()
+        # a live plan pins its cache entries
+        ctx.clear_prepacked_cache()
+        assert ctx.prepacked_cache_entries() == 2
+        plan.close()
+        ctx.clear_prepacked_cache()
+        assert ctx.prepacked_cache_entries() == 0
+    finally:
+        ctx.close()
 
 
 def _sampled_block_check(c, out, rows_sel, cols_sel):
