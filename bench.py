@@ -370,19 +370,165 @@ def run_gpu_arm(args):
         dist.destroy_process_group()
 
 
+def run_c2_arm(args):
+    """Batched small muls (config 2): 16384 independent int8 muls with dims drawn from {16..128}, weights in the
+    prepacked cache, one plan replayed per step with a single persistent launch.  With N ranks the mul index
+    range is split evenly (no collective: the destinations stay where their consumers are)."""
+    import torch
+    import ruy_b200
+    from ruy_b200 import _abi, cases
+    from ruy_b200.api import CachePolicy, Layout, Matrix, MulParams, Order, Rounding
+
+    rank, world, local = dist_env()
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    use_dist = world > 1
+    if use_dist:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    n_total = args.muls
+    per = (n_total + world - 1) // world
+    first, count = rank * per, max(0, min(per, n_total - rank * per))
+    mine = cases.config2(n=n_total, seed=0, first=first, count=count)
+
+    def pool(arrays, dtype):
+        """One device buffer holding all arrays at 256-byte aligned offsets; returns (tensor, offsets)."""
+        offs, total = [], 0
+        item = np.dtype(dtype).itemsize
+        for a in arrays:
+            offs.append(total)
+            total += (a.size * item + 255) // 256 * 256 // item
+        host = np.zeros(max(total, 1), dtype=dtype)
+        for a, o in zip(arrays, offs):
+            host[o:o + a.size] = a
+        return torch.from_numpy(host).to(dev), offs
+
+    lhs_buf, lhs_off = pool([c.lhs for c in mine], np.int8)
+    rhs_buf, rhs_off = pool([c.rhs for c in mine], np.int8)
+    bias_buf, vec_off = pool([c.bias for c in mine], np.int32)
+    mfp_buf, _ = pool([c.mfp for c in mine], np.int32)
+    mexp_buf, _ = pool([c.mexp for c in mine], np.int32)
+    dst_buf, dst_off = pool([c.new_dst() for c in mine], np.int8)
+
+    stream = torch.cuda.Stream(device=dev)
+    ctx = ruy_b200.Context(local, stream=stream.cuda_stream)
+    descs = []
+    for i, c in enumerate(mine):
+        lhs = Matrix(lhs_buf[lhs_off[i]:], c.lhs_layout, c.lhs_zp, CachePolicy.kAlwaysCache)
+        rhs = Matrix(rhs_buf[rhs_off[i]:], c.rhs_layout, c.rhs_zp)
+        dst = Matrix(dst_buf[dst_off[i]:], c.dst_layout, c.dst_zp)
+        p = MulParams("int32", "int8")
+        p.bias = bias_buf[vec_off[i]:]
+        p.multiplier_fixedpoint_perchannel = mfp_buf[vec_off[i]:]
+        p.multiplier_exponent_perchannel = mexp_buf[vec_off[i]:]
+        p.clamp_min, p.clamp_max = c.clamp
+        p.rounding = Rounding.kReference
+        descs.append(ruy_b200.make_desc(lhs, rhs, p, dst))
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    plan = ruy_b200.Plan(ctx, descs)
+    plan_build_s = time.perf_counter() - t0
+    nbytes, ops = plan.stats()
+    with torch.cuda.stream(stream):
+        flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
+        sampler = ClockSampler(local)
+        sampler.start()
+        for _ in range(max(args.warmup, 3)):
+            flush.fill_(1)
+            plan.run()
+        ctx.sync()
+        # parity spot check against the CPU oracle on a few muls of this rank
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        import util
+        host_dst = dst_buf.cpu().numpy()
+        for i in list(range(0, len(mine), max(1, len(mine) // 8)))[:8]:
+            c = mine[i]
+            got = c.dst_view(host_dst[dst_off[i]:dst_off[i] + c.dst_storage_elems()])
+            if not np.array_equal(got, util.run_oracle(c, Rounding.kReference)):
+                raise SystemExit(f"bench.py: mul {first + i} does not match the oracle; refusing to report")
+        launches0 = ctx.counters()["launches"]
+        if use_dist:
+            dist.barrier()
+        torch.cuda.synchronize()
+        sampler.mark_begin()
+        starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+        stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+        for i in range(args.steps):
+            flush.fill_(i & 0xFF)
+            starts[i].record(stream)
+            plan.run()
+            stops[i].record(stream)
+        stream.synchronize()
+        if use_dist:
+            dist.barrier()
+        torch.cuda.synchronize()
+        sampler.mark_end()
+        clocks = sampler.stop()
+        launches = ctx.counters()["launches"] - launches0
+        ms = float(np.sum([a.elapsed_time(b) for a, b in zip(starts, stops)])) / args.steps
+        if use_dist:
+            t = torch.tensor([ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t[0])
+            tb = torch.tensor([float(nbytes), float(ops)], dtype=torch.float64, device=dev)
+            dist.all_reduce(tb)
+            total_bytes, total_ops = float(tb[0]), float(tb[1])
+        else:
+            total_bytes, total_ops = float(nbytes), float(ops)
+    peaks = measured_peaks()
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    line = {
+        "metric": "small_mul_muls_per_s", "value": n_total / (ms * 1e-3), "unit": "muls/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": {"workload": "c2", "muls": n_total, "dims": list(cases.CONFIG2_DIMS),
+                   "sharding": f"{world} shard(s) by mul index", "l2": f"flushed between steps ({L2_FLUSH_BYTES >> 20} MiB fill, untimed)",
+                   "plan_build_s": plan_build_s},
+        "gpu_launches": int(launches), "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
+                     "traffic": None, "kernel": "batch_i8_kernel", "algorithmic_bytes": nbytes,
+                     "peak_source": f"hbm_gbs of {peaks['source']} peaks"},
+        "tops": total_ops / (ms * 1e-3) / 1e12,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        import oracle
+        ref = oracle.reference()
+        if ref is not None:
+            sample = cases.config2(n=n_total, seed=0, first=0, count=min(2048, n_total))
+            keep, host_descs = [], (_abi.MulDesc * len(sample))()
+            for i, c in enumerate(sample):
+                b = c.bind(c.new_dst())
+                keep.append(b)
+                host_descs[i] = ruy_b200.make_desc(b[0], b[1], b[2], b[3])
+            cores = os.cpu_count() or 1
+            secs = ref.ruy_ref_time_batch(host_descs, len(sample), cores, oracle.host_simd_path(), 5)
+            line["cpu_baseline"] = {"value": len(sample) / secs, "unit": "muls/s", "cores": cores, "kind": "reference",
+                                    "sample": f"first {len(sample)} of {n_total} muls; {cores} host threads, one ruy::Context each, "
+                                              "LHS in ruy's prepacked cache"}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    plan.close()
+    ctx.close()
+    if use_dist:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c3_i8", choices=["c3_i8", "c3_i32"])
+    ap.add_argument("--workload", default="c3_i8", choices=["c3_i8", "c3_i32", "c2"])
+    ap.add_argument("--muls", type=int, default=16384, help="number of muls of workload c2")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cols", type=int, default=8192,
                     help="activation columns (8192 is the benchmark configuration; smaller values are for profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.workload == "c2":
+        run_c2_arm(args)
     else:
         run_gpu_arm(args)
 

@@ -5,15 +5,17 @@
 // Every SM runs one persistent CTA that walks a static, size-balanced list of items through a ring of
 // shared-memory slots:
 //
-//   * warps 0-3  : pack.  Read both operands from HBM (8-byte units, several in flight per lane) and
-//                  write them into the slot in the tensor core's depth-major core-matrix layout,
-//                  zero-padding depth to a multiple of 32 and accumulating the zero-point sums of the
-//                  rows they touch (ruy/pack.h:105-132) on the way.  Runs up to kSlots items ahead, which
-//                  is what keeps enough bytes in flight to use the HBM bandwidth.
-//   * warp 4     : one elected lane issues the item's tcgen05.mma kind::i8 (M=128, N<=128, K=32) into one
+//   * warps 0-5  : pack (ruy/pack.h:105-132).  Each warp owns one slot and one item at a time: it issues
+//                  asynchronous copies (cp.async, 8 or 16 bytes each, never waiting for them) that take
+//                  both operands from HBM straight into the slot in the tensor core's depth-major
+//                  core-matrix layout, zero-filling depth up to a multiple of 32, plus the item's
+//                  per-channel vectors.  Six whole items are in flight per SM, which is what keeps
+//                  enough bytes outstanding to use the HBM bandwidth.
+//   * warp 6     : one elected lane issues the item's tcgen05.mma kind::i8 (M=128, N<=128, K=32) into one
 //                  of four tensor-memory accumulators.
-//   * warps 5-12 : epilogue.  Stage the per-column terms in shared memory, read the accumulators
-//                  (tcgen05.ld), apply bias, zero-point terms, fixed-point multiplier, zero point, clamp
+//   * warps 8-23 : epilogue, four groups of four warps; group g drains accumulator g.  Zero-point sums
+//                  are taken from the packed tile, per-column terms are staged in shared memory, then
+//                  tcgen05.ld, bias, zero-point terms, fixed-point multiplier, zero point, clamp
 //                  (ruy/kernel.h:213-237) and store.  The destination's contiguous dimension sits on the
 //                  TMEM lanes, so the 32 lanes of a warp write 32 consecutive elements.
 //
@@ -21,6 +23,7 @@
 // role leaves its loop, so tensor memory is always released and the kernel always returns.
 #include <cuda_runtime.h>
 
+#include <cstdio>
 #include <cstring>
 
 #include "batch_i8.h"
@@ -30,14 +33,18 @@ namespace ruyb200 {
 
 namespace {
 
-constexpr int kSlots = 6;
+constexpr int kSlots = 6;                          // one per pack warp
 constexpr int kTileBytes = 16 * 1024;             // one operand: up to 128 rows x 128 bytes of depth
 constexpr int kSlotBytes = 2 * kTileBytes;
-constexpr int kAccBuffers = 4;
+constexpr int kAccBuffers = 4;                    // one per epilogue group
 constexpr int kAccCols = 128;
-constexpr int kPackWarps = 4;
-constexpr int kEpiWarps = 8;
-constexpr int kThreads = 32 * (kPackWarps + 1 + kEpiWarps);
+constexpr int kTmemCols = 512;                     // allocation must be a power of two
+constexpr int kPackWarps = kSlots;
+constexpr int kEpiGroups = kAccBuffers;
+constexpr int kEpiWarps = 4 * kEpiGroups;         // each group covers the four TMEM lane quarters
+constexpr int kMmaWarp = kPackWarps;
+constexpr int kFirstEpiWarp = 8;                  // a multiple of 4, so that (warp % 4) is the lane quarter within a group
+constexpr int kThreads = 32 * (kFirstEpiWarp + kEpiWarps);
 constexpr int kSmemBytes = kSlots * kSlotBytes + 1024;
 constexpr uint32_t kSpinLimit = 4u << 20;
 
@@ -103,29 +110,16 @@ __device__ __forceinline__ void tmem_ld_16(uint32_t taddr, uint32_t* r) {
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-// AND-reduction over the epilogue threads (named barrier 1).
-__device__ __forceinline__ bool epilogue_all(bool ok) {
+// AND-reduction over the 128 threads of one epilogue group (named barrier 1 + group).
+__device__ __forceinline__ bool group_all(bool ok, int group) {
   uint32_t res;
   asm volatile(
       "{\n\t.reg .pred p, q;\n\t"
       "setp.ne.u32 q, %1, 0;\n\t"
-      "bar.red.and.pred p, 1, %2, q;\n\t"
+      "bar.red.and.pred p, %2, 128, q;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(res)
-      : "r"((uint32_t)ok), "n"(32 * kEpiWarps)
-      : "memory");
-  return res != 0;
-}
-// AND-reduction over the pack threads (named barrier 2); doubles as their per-item barrier.
-__device__ __forceinline__ bool pack_all(bool ok) {
-  uint32_t res;
-  asm volatile(
-      "{\n\t.reg .pred p, q;\n\t"
-      "setp.ne.u32 q, %1, 0;\n\t"
-      "bar.red.and.pred p, 2, %2, q;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(res)
-      : "r"((uint32_t)ok), "n"(32 * kPackWarps)
+      : "r"((uint32_t)ok), "r"(1 + group)
       : "memory");
   return res != 0;
 }
@@ -146,74 +140,78 @@ __device__ __forceinline__ void mma_i8_nosw(uint32_t tmem_d, uint32_t addr_a, ui
       : "memory");
 }
 
-// Packs one operand (width x depth, depth-contiguous rows `stride` bytes apart) into the core-matrix
-// layout at `tile`, zero-padding depth up to kpad, and adds each row's byte sum into sums[] if wanted.
-// Lanes map to (row within a group of 8, 8-byte unit) so shared-memory stores are conflict-free.
-__device__ __forceinline__ void pack_operand(const uint8_t* __restrict__ src, int width, int depth, int stride, int kpad,
-                                             bool is_signed, uint8_t* tile, int32_t* sums, int ptid) {
-  const int units = kpad / 8;                  // 8-byte units per row, padding included
-  const uint32_t sbo = (uint32_t)(kpad / 16) * 128;
-  const int groups = (width + 7) / 8;
-  const int total = groups * 8 * units;        // (group, unit, row in group) with the row fastest
-  constexpr int kBatch = 4;
-  for (int base = ptid; base < total; base += 128 * kBatch) {
-    uint2 v[kBatch];
-    int row[kBatch], unit[kBatch];
-#pragma unroll
-    for (int b = 0; b < kBatch; b++) {
-      const int e = base + b * 128;
-      v[b] = make_uint2(0u, 0u);
-      row[b] = -1;
-      if (e < total) {
-        const int r8 = e & 7;
-        const int u = (e >> 3) % units;
-        const int g = (e >> 3) / units;
-        const int r = g * 8 + r8;
-        row[b] = r;
-        unit[b] = u;
-        const int k0 = u * 8;
-        if (r < width && k0 < depth) {
-          const uint8_t* p = src + (int64_t)r * stride + k0;
-          if (k0 + 8 <= depth) {
-            v[b] = *reinterpret_cast<const uint2*>(p);
-          } else {
-            uint32_t w[2] = {0u, 0u};
-            for (int t = 0; t < depth - k0; t++) w[t >> 2] |= (uint32_t)p[t] << (8 * (t & 3));
-            v[b] = make_uint2(w[0], w[1]);
-          }
-        }
-      }
-    }
-#pragma unroll
-    for (int b = 0; b < kBatch; b++) {
-      if (row[b] < 0) continue;
-      const int r = row[b], u = unit[b];
-      uint8_t* dst = tile + (uint32_t)(r >> 3) * sbo + (uint32_t)(u >> 1) * 128 + (uint32_t)(r & 7) * 16 + (uint32_t)(u & 1) * 8;
-      *reinterpret_cast<uint2*>(dst) = v[b];
-      if (sums && r < width) {
-        int s;
-        if (is_signed) {
-          s = __dp4a((int)v[b].x, 0x01010101, 0);
-          s = __dp4a((int)v[b].y, 0x01010101, s);
-        } else {
-          s = (int)__dp4a(v[b].x, 0x01010101u, 0u);
-          s = (int)__dp4a(v[b].y, 0x01010101u, (unsigned)s);
-        }
-        if (s) atomicAdd(&sums[r], s);
-      }
+// cp.async of `bytes` (4, 8 or 16) of which only the first src_bytes are read; the rest is zero-filled.
+template <int kBytes>
+__device__ __forceinline__ void cp_async_zfill(uint32_t dst_smem, const void* src, int src_bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], %2, %3;" ::"r"(dst_smem), "l"(src), "n"(kBytes), "r"(src_bytes) : "memory");
+}
+
+// Issues the copies that pack one operand (width x depth, depth-contiguous rows `stride` bytes apart)
+// into the core-matrix layout at `tile` (shared-memory address), starting at tile row `row_off` (a
+// multiple of 8): 8 rows x 16 bytes per core matrix, consecutive 16-byte depth chunks 128 bytes apart,
+// 8-row groups `sbo` bytes apart; depth is zero-filled up to kpad.  One warp; lane = (row within a group
+// of 8, one of 4 interleaved units), so one warp instruction covers 8 rows x (32 or 64) contiguous bytes.
+template <int kUnit>   // 8 or 16 bytes per copy
+__device__ __forceinline__ void issue_pack(const uint8_t* __restrict__ src, int width, int depth, int stride, int kpad,
+                                           uint32_t tile, int row_off, int lane) {
+  const int units = kpad / kUnit;
+  const uint32_t sbo = (uint32_t)(kpad >> 4) * 128;
+  const int groups = (width + 7) >> 3;
+  const int r8 = lane & 7;
+  const int ul = lane >> 3;
+  for (int g = 0; g < groups; g++) {
+    const int r = g * 8 + r8;
+    if (r >= width) continue;        // rows past the end stay as they are: their results are never stored
+    const uint8_t* rowp = src + (int64_t)r * stride;
+    const int tr = r + row_off;
+    const uint32_t rowdst = tile + (uint32_t)(tr >> 3) * sbo + (uint32_t)(tr & 7) * 16;
+    for (int u = ul; u < units; u += 4) {
+      const int k0 = u * kUnit;
+      int nbytes = depth - k0;
+      nbytes = nbytes < 0 ? 0 : (nbytes > kUnit ? kUnit : nbytes);
+      const uint32_t dst = kUnit == 16 ? rowdst + (uint32_t)u * 128 : rowdst + (uint32_t)(u >> 1) * 128 + (uint32_t)(u & 1) * 8;
+      cp_async_zfill<kUnit>(dst, nbytes ? rowp + k0 : rowp, nbytes);
     }
   }
 }
 
+// Sum of the bytes of one packed tile row (kpad bytes, padding is zero).
+__device__ __forceinline__ int32_t tile_row_sum(const uint8_t* tile, int tr, int kpad, bool is_signed) {
+  const uint32_t sbo = (uint32_t)(kpad >> 4) * 128;
+  const uint8_t* p = tile + (uint32_t)(tr >> 3) * sbo + (uint32_t)(tr & 7) * 16;
+  int s = 0;
+  for (int q = 0; q < (kpad >> 4); q++) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p + q * 128);
+    if (is_signed) {
+      s = __dp4a((int)v.x, 0x01010101, s);
+      s = __dp4a((int)v.y, 0x01010101, s);
+      s = __dp4a((int)v.z, 0x01010101, s);
+      s = __dp4a((int)v.w, 0x01010101, s);
+    } else {
+      s = (int)__dp4a(v.x, 0x01010101u, (unsigned)s);
+      s = (int)__dp4a(v.y, 0x01010101u, (unsigned)s);
+      s = (int)__dp4a(v.z, 0x01010101u, (unsigned)s);
+      s = (int)__dp4a(v.w, 0x01010101u, (unsigned)s);
+    }
+  }
+  return s;
+}
+
+// Requantize with per-call constants hoisted: rnd = 2^(30-e) (64 bit), sh = 31-e.
+__device__ __forceinline__ int32_t requant_ref_fast(int32_t x, int32_t mul, long long rnd, int sh) {
+  const long long p = (long long)x * (long long)mul + rnd;
+  return (int32_t)(p >> sh);
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
-batch_i8_kernel(const BatchItem* __restrict__ items, const int32_t* __restrict__ order, int num_items, int* status) {
+batch_i8_kernel(const BatchItem* __restrict__ items, int num_items, int* status) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kSlots];     // packed data of a slot is in place
   __shared__ __align__(8) uint64_t empty_bar[kSlots];    // MMAs have read the slot and the epilogue has read its header
   __shared__ __align__(8) uint64_t acc_full_bar[kAccBuffers];
   __shared__ __align__(8) uint64_t acc_empty_bar[kAccBuffers];
   __shared__ __align__(16) BatchItem slot_item[kSlots];
-  __shared__ int32_t slot_sums[kSlots][256];             // [0,128): m side rows, [128,256): n side rows
+  __shared__ __align__(16) int32_t slot_vec[kSlots][3][128];   // the item's bias / multiplier / exponent vectors
   __shared__ __align__(16) NTerm n_terms[kAccBuffers][kAccCols];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
@@ -224,19 +222,19 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const int32_t* __restrict__
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kSlots; s++) {
-      mbar_init(&full_bar[s], 32 * kPackWarps);
-      mbar_init(&empty_bar[s], 1 + kEpiWarps);
+      mbar_init(&full_bar[s], 32 + 1);       // every pack lane's copies + the header
+      mbar_init(&empty_bar[s], 1 + 4);       // the MMA commit + the four warps of the epilogue group
     }
     for (int b = 0; b < kAccBuffers; b++) {
       mbar_init(&acc_full_bar[b], 1);
-      mbar_init(&acc_empty_bar[b], kEpiWarps);
+      mbar_init(&acc_empty_bar[b], 4);
     }
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == kPackWarps) {
+  if (warp == kMmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
-                 "r"(kAccBuffers * kAccCols)
+                 "r"(kTmemCols)
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -245,52 +243,109 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const int32_t* __restrict__
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
   volatile int* abortp = &abort_flag;
-  const int my_count = (num_items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;   // items of this CTA
+  // This CTA's items are items[blockIdx.x + k * gridDim.x], k = 0 .. my_count-1, in that order.
+  const int my_count = (num_items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
 
   if (warp < kPackWarps) {
     // ---------------- pack: HBM -> shared memory, zero-point sums on the way ----------------
-    const int ptid = threadIdx.x;
-    uint32_t s = 0, ph = 0;
-    for (int it = 0; it < my_count; it++) {
-      bool ok = mbar_wait_warp(&empty_bar[s], ph ^ 1, abortp);
-      if (!ok && lane == 0) { if (!*abortp) atomicCAS(status, 0, 1); *abortp = 1; }
-      const int idx = order[blockIdx.x + it * gridDim.x];
-      const BatchItem* gi = items + idx;
-      if (ok) {
-        // header: the item descriptor travels with the slot (8 lanes x 16 bytes)
-        if (ptid < (int)(sizeof(BatchItem) / 16)) {
-          reinterpret_cast<uint4*>(&slot_item[s])[ptid] = reinterpret_cast<const uint4*>(gi)[ptid];
-        }
-        slot_sums[s][ptid] = 0;
-        slot_sums[s][ptid + 128] = 0;
+    // Pack warp w owns slot w and handles items k = w, w + kSlots, ...: kSlots items are being packed at any
+    // time, each by its own warp, which is what keeps enough loads in flight.
+    const int s = warp;
+    uint32_t ph = 0;
+    // The descriptor travels global -> register (one 16-byte piece in each of 8 lanes, fetched one item
+    // ahead) -> the slot header in shared memory, from where every role reads the fields it needs.
+    uint4 next_piece = make_uint4(0u, 0u, 0u, 0u);
+    const bool piece_lane = lane < (int)(sizeof(BatchItem) / 16);
+    if (s < my_count && piece_lane) next_piece = reinterpret_cast<const uint4*>(items + blockIdx.x + s * gridDim.x)[lane];
+#ifdef RUYB200_DEBUG_KNOBS
+    long long dbg_wait = 0, dbg_work = 0, dbg_t0 = clock64();
+#endif
+    for (int k = s; k < my_count; k += kSlots, ph ^= 1) {
+      const uint4 piece = next_piece;
+      if (k + kSlots < my_count && piece_lane) {
+        next_piece = reinterpret_cast<const uint4*>(items + blockIdx.x + (k + kSlots) * gridDim.x)[lane];
       }
-      // collective continue/abort decision; also: the sums are zero before anybody adds to them
-      if (!pack_all(ok)) break;
-      const BatchItem item = *gi;
+#ifdef RUYB200_DEBUG_KNOBS
+      long long dbg_a = clock64();
+#endif
+      if (!mbar_wait_warp(&empty_bar[s], ph ^ 1, abortp)) {
+        if (lane == 0) { if (!*abortp) atomicCAS(status, 0, 1); *abortp = 1; }
+        break;
+      }
+#ifdef RUYB200_DEBUG_KNOBS
+      long long dbg_b = clock64();
+      dbg_wait += dbg_b - dbg_a;
+#endif
+      if (piece_lane) reinterpret_cast<uint4*>(&slot_item[s])[lane] = piece;
+      __syncwarp();
+      const BatchItem& item = slot_item[s];
       const int kpad = (item.depth + 31) & ~31;
-      uint8_t* tile_m = smem + s * kSlotBytes;
-      uint8_t* tile_n = tile_m + kTileBytes;
-      pack_operand(item.m_ptr, item.size_m, item.depth, item.stride_m, kpad, (item.flags & kItemMSigned) != 0, tile_m,
-                   item.zp_n ? &slot_sums[s][0] : nullptr, ptid);
-      pack_operand(item.n_ptr, item.size_n, item.depth, item.stride_n, kpad, (item.flags & kItemNSigned) != 0, tile_n,
-                   item.zp_m ? &slot_sums[s][128] : nullptr, ptid);
-      // make this thread's generic-proxy writes visible to the tensor core's async-proxy reads, then signal
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      mbar_arrive(&full_bar[s]);
-      if (++s == kSlots) { s = 0; ph ^= 1; }
+      const uint32_t tile_m = smem_u32(smem + s * kSlotBytes);
+      const uint32_t tile_n = tile_m + kTileBytes;
+      const uint8_t* m_ptr = item.m_ptr;
+      const uint8_t* n_ptr = item.n_ptr;
+      const int size_m = item.size_m, size_n = item.size_n, depth = item.depth, stride_m = item.stride_m,
+                stride_n = item.stride_n, m_off = item.m_off;
+      if ((((uintptr_t)m_ptr | (uint32_t)stride_m) & 15) == 0) {
+        issue_pack<16>(m_ptr, size_m, depth, stride_m, kpad, tile_m, m_off, lane);
+      } else {
+        issue_pack<8>(m_ptr, size_m, depth, stride_m, kpad, tile_m, m_off, lane);
+      }
+      if ((((uintptr_t)n_ptr | (uint32_t)stride_n) & 15) == 0) {
+        issue_pack<16>(n_ptr, size_n, depth, stride_n, kpad, tile_n, 0, lane);
+      } else {
+        issue_pack<8>(n_ptr, size_n, depth, stride_n, kpad, tile_n, 0, lane);
+      }
+      // per-channel vectors (indexed along m or along n) ride along
+      const int nch = (item.flags & kItemChannelOnN) ? size_n : size_m;
+      const int32_t* vecs[3] = {item.bias, item.mfp_pc, item.mexp_pc};
+#pragma unroll
+      for (int v = 0; v < 3; v++) {
+        if (vecs[v]) {
+          for (int i = lane; i < nch; i += 32) cp_async_zfill<4>(smem_u32(&slot_vec[s][v][i]), vecs[v] + i, 4);
+        }
+      }
+      // full_bar[s] completes when every lane's copies have landed (33 arrivals: 32 deferred ones plus
+      // lane 0's ordinary arrive, which publishes the header written above)
+      asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&full_bar[s])) : "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&full_bar[s]);
+#ifdef RUYB200_DEBUG_KNOBS
+      dbg_work += clock64() - dbg_b;
+#endif
     }
-  } else if (warp == kPackWarps) {
+#ifdef RUYB200_DEBUG_KNOBS
+    if (blockIdx.x == 0 && threadIdx.x == 0)
+      printf("pack warp 0: total %lld cycles, waiting for its slot %lld, issuing copies %lld, items %d\n", clock64() - dbg_t0,
+             dbg_wait, dbg_work, (my_count + kSlots - 1) / kSlots);
+#endif
+  } else if (warp == kMmaWarp) {
     // ---------------- MMA issue ----------------
     uint32_t s = 0, ph = 0;
+#ifdef RUYB200_DEBUG_KNOBS
+    long long dbg_acc = 0, dbg_full = 0, dbg_t0 = clock64();
+#endif
     for (int it = 0; it < my_count; it++) {
       const int buf = it % kAccBuffers;
       const uint32_t aph = (it / kAccBuffers) & 1;
+#ifdef RUYB200_DEBUG_KNOBS
+      long long dbg_a = clock64();
+#endif
       bool ok = mbar_wait_warp(&acc_empty_bar[buf], aph ^ 1, abortp);
+#ifdef RUYB200_DEBUG_KNOBS
+      long long dbg_b = clock64();
+      dbg_acc += dbg_b - dbg_a;
+#endif
       ok = ok && mbar_wait_warp(&full_bar[s], ph, abortp);
+#ifdef RUYB200_DEBUG_KNOBS
+      dbg_full += clock64() - dbg_b;
+#endif
       if (!ok) {
         if (lane == 0) { if (!*abortp) atomicCAS(status, 0, 2); *abortp = 1; }
         break;
       }
+      // the slot was filled by cp.async (generic proxy); the tensor core reads it through the async proxy
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tc_fence_after();
       const int depth = slot_item[s].depth;
       const int size_n = slot_item[s].size_n;
@@ -313,106 +368,168 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const int32_t* __restrict__
       __syncwarp();
       if (++s == kSlots) { s = 0; ph ^= 1; }
     }
-  } else {
-    // ---------------- epilogue ----------------
-    const int ew = warp - (kPackWarps + 1);
+#ifdef RUYB200_DEBUG_KNOBS
+    if (blockIdx.x == 0 && lane == 0)
+      printf("mma warp: total %lld cycles, waiting for an accumulator %lld, waiting for packed data %lld, items %d\n",
+             clock64() - dbg_t0, dbg_acc, dbg_full, my_count);
+#endif
+  } else if (warp >= kFirstEpiWarp) {
+    // ---------------- epilogue: group g drains accumulator g, i.e. items g, g + 4, ... ----------------
+    const int group = (warp - kFirstEpiWarp) / 4;
     const int quarter = warp % 4;          // TMEM lane quarter this warp may read
-    const int chunk_parity = ew / 4;       // the two warps of a quarter alternate 16-column chunks
-    const int etid = threadIdx.x - 32 * (kPackWarps + 1);
-    uint32_t s = 0;
-    bool ok = true;
-    for (int it = 0; it < my_count && ok; it++) {
-      const int buf = it % kAccBuffers;
-      const uint32_t aph = (it / kAccBuffers) & 1;
-      if (!mbar_wait_warp(&acc_full_bar[buf], aph, abortp)) {
-        if (lane == 0) { if (!*abortp) atomicCAS(status, 0, 3); *abortp = 1; }
-        ok = false;
-      }
+    const int gtid = (warp - kFirstEpiWarp) % 4 * 32 + lane;
+    const int buf = group;
+    uint32_t aph = 0;
+    NTerm* nt = n_terms[buf];
+#ifdef RUYB200_DEBUG_KNOBS
+    long long dbg_wait = 0, dbg_stage = 0, dbg_work = 0, dbg_t0 = clock64();
+#endif
+    for (int it = group; it < my_count; it += kEpiGroups, aph ^= 1) {
+      const int s = it % kSlots;
+#ifdef RUYB200_DEBUG_KNOBS
+      long long dbg_a = clock64();
+#endif
+      bool ok = mbar_wait_warp(&acc_full_bar[buf], aph, abortp);
+#ifdef RUYB200_DEBUG_KNOBS
+      long long dbg_b = clock64();
+      dbg_wait += dbg_b - dbg_a;
+#endif
+      if (!ok && lane == 0) { if (!*abortp) atomicCAS(status, 0, 3); *abortp = 1; }
       // collective decision; also orders the previous item's reads of n_terms[] before this item's writes
-      ok = epilogue_all(ok);
-      if (!ok) break;
+      if (!group_all(ok, group)) break;
       tc_fence_after();
-      const BatchItem item = slot_item[s];
+      const BatchItem& item = slot_item[s];   // valid until this group has arrived on empty_bar[s]
       const bool ch_n = (item.flags & kItemChannelOnN) != 0;
       const bool x86 = (item.flags & kItemX86) != 0;
       const int dst_dtype = (int)((item.flags >> kItemDstShift) & 7u);
-      const int32_t zz = item.zp_m * item.zp_n * item.depth;
-      NTerm* nt = n_terms[buf];
-      if (etid < kAccCols) {
-        const int n = etid;
+      const bool per_n = ch_n || item.zp_m != 0;   // some term varies along n
+      const int kpad = (item.depth + 31) & ~31;
+      const uint8_t* tile_m = smem + s * kSlotBytes;
+      const uint8_t* tile_n = tile_m + kTileBytes;
+      const int32_t* vbias = item.bias ? slot_vec[s][0] : nullptr;
+      const int32_t* vmfp = item.mfp_pc ? slot_vec[s][1] : nullptr;
+      const int32_t* vmexp = item.mexp_pc ? slot_vec[s][2] : nullptr;
+      if (per_n) {
+        const int n = gtid;
         NTerm t;
-        t.add = zz;
+        t.add = item.zp_m * item.zp_n * item.depth;
         t.mul = item.mfp;
         t.exp = item.mexp;
         t.pad = 0;
         if (n < item.size_n) {
-          if (item.zp_m) t.add -= item.zp_m * slot_sums[s][128 + n];
+          // zero-point term of this destination column: the sum over depth of the n-side row, taken from the packed tile
+          if (item.zp_m) t.add -= item.zp_m * tile_row_sum(tile_n, n, kpad, (item.flags & kItemNSigned) != 0);
           if (ch_n) {
-            if (item.bias) t.add += item.bias[n];
-            if (item.mfp_pc) t.mul = item.mfp_pc[n];
-            if (item.mexp_pc) t.exp = item.mexp_pc[n];
+            if (vbias) t.add += vbias[n];
+            if (vmfp) t.mul = vmfp[n];
+            if (vmexp) t.exp = vmexp[n];
           }
         }
         nt[n] = t;
       }
-      const int m = quarter * 32 + lane;
-      const bool m_ok = m < item.size_m;
+      const int m = quarter * 32 + lane - item.m_off;     // tile row -> destination index along m
+      const bool m_ok = m >= 0 && m < item.size_m;
       int32_t add_m = 0, mul_m = item.mfp, exp_m = item.mexp;
       if (m_ok) {
-        if (item.zp_n) add_m -= item.zp_n * slot_sums[s][m];
+        if (item.zp_n) add_m -= item.zp_n * tile_row_sum(tile_m, quarter * 32 + lane, kpad, (item.flags & kItemMSigned) != 0);
         if (!ch_n) {
-          if (item.bias) add_m += item.bias[m];
-          if (item.mfp_pc) mul_m = item.mfp_pc[m];
-          if (item.mexp_pc) exp_m = item.mexp_pc[m];
+          if (vbias) add_m += vbias[m];
+          if (vmfp) mul_m = vmfp[m];
+          if (vmexp) exp_m = vmexp[m];
         }
       }
-      epilogue_all(true);                  // n_terms[] staged, slot header and sums consumed by everybody
+      const int size_m = item.size_m, size_n = item.size_n, m_off = item.m_off;
+      const int32_t cmin = item.clamp_min, cmax = item.clamp_max, dzp = item.dst_zp;
+      uint8_t* const dst_base = item.dst;
+      const int dst_stride = item.dst_stride;
+      if (per_n) group_all(true, group);   // n_terms[] staged (uniform over the group: per_n comes from the header)
+      __syncwarp();                        // this warp is done with the slot's header, vectors and tiles
       if (lane == 0) mbar_arrive(&empty_bar[s]);
-      const bool quarter_used = quarter * 32 < item.size_m;
+#ifdef RUYB200_DEBUG_KNOBS
+      long long dbg_c = clock64();
+      dbg_stage += dbg_c - dbg_b;
+#endif
+      const bool quarter_used = quarter * 32 + 32 > m_off && quarter * 32 < m_off + size_m;
       if (quarter_used) {
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * kAccCols);
         const int esz = dst_dtype == RUYB200_I32 ? 4 : (dst_dtype == RUYB200_I16 ? 2 : 1);
-        for (int c = chunk_parity * 16; c < item.size_n; c += 32) {
-          uint32_t r[16];
-          tmem_ld_16(taddr + c, r);
-          tmem_ld_wait();
-          if (m_ok) {
+        const int64_t step = (int64_t)dst_stride * esz;
+        uint8_t* out = dst_base + (int64_t)m * esz;
+        const bool fast = !per_n && !x86 && dst_dtype != RUYB200_I32;
+        const int sh = 31 - exp_m;
+        const long long rnd = 1ll << (sh - 1);
+        auto process = [&](const uint32_t (&rr)[16], int c) {
+          const int lim = size_n - c;
+          if (fast) {
 #pragma unroll
             for (int q = 0; q < 16; q++) {
-              const int n = c + q;
-              if (n < item.size_n) {
-                const NTerm t = nt[n];
-                int32_t x = (int32_t)(r[q] + (uint32_t)t.add + (uint32_t)add_m);
-                if (dst_dtype != RUYB200_I32) {
-                  const int32_t mul = ch_n ? t.mul : mul_m;
-                  const int e = ch_n ? t.exp : exp_m;
-                  x = x86 ? requant_x86(x, mul, e) : requant_reference(x, mul, e);
-                  x = (int32_t)((uint32_t)x + (uint32_t)item.dst_zp);
-                  x = max(min(x, item.clamp_max), item.clamp_min);
-                } else {
-                  x = (int32_t)((uint32_t)x + (uint32_t)item.dst_zp);
-                }
-                uint8_t* p = item.dst + ((int64_t)n * item.dst_stride + m) * esz;
-                if (esz == 1) *p = (uint8_t)x;
-                else if (esz == 2) *reinterpret_cast<int16_t*>(p) = (int16_t)x;
-                else *reinterpret_cast<int32_t*>(p) = x;
+              if (q < lim) {
+                int32_t x = requant_ref_fast((int32_t)(rr[q] + (uint32_t)add_m), mul_m, rnd, sh);
+                x = max(min(x + dzp, cmax), cmin);
+                if (esz == 1) *out = (uint8_t)x; else *reinterpret_cast<int16_t*>(out) = (int16_t)x;
+                out += step;
               }
             }
+          } else {
+#pragma unroll
+            for (int q = 0; q < 16; q++) {
+              if (q < lim) {
+                int32_t x = (int32_t)(rr[q] + (uint32_t)add_m);
+                int32_t mul = mul_m;
+                int e = exp_m;
+                if (per_n) {
+                  const NTerm t = nt[c + q];
+                  x = (int32_t)((uint32_t)x + (uint32_t)t.add);
+                  if (ch_n) { mul = t.mul; e = t.exp; }
+                }
+                if (dst_dtype != RUYB200_I32) {
+                  x = x86 ? requant_x86(x, mul, e) : requant_reference(x, mul, e);
+                  x = (int32_t)((uint32_t)x + (uint32_t)dzp);
+                  x = max(min(x, cmax), cmin);
+                } else {
+                  x = (int32_t)((uint32_t)x + (uint32_t)dzp);
+                }
+                if (esz == 1) *out = (uint8_t)x;
+                else if (esz == 2) *reinterpret_cast<int16_t*>(out) = (int16_t)x;
+                else *reinterpret_cast<int32_t*>(out) = x;
+                out += step;
+              }
+            }
+          }
+        };
+        // two register buffers: the load of the next 16 columns is in flight while 16 are processed
+        uint32_t ra[16], rb[16];
+        tmem_ld_16(taddr, ra);
+        for (int c = 0; c < size_n; c += 32) {
+          tmem_ld_wait();
+          if (c + 16 < size_n) tmem_ld_16(taddr + c + 16, rb);
+          if (m_ok) process(ra, c);
+          if (c + 16 < size_n) {
+            tmem_ld_wait();
+            if (c + 32 < size_n) tmem_ld_16(taddr + c + 32, ra);
+            if (m_ok) process(rb, c + 16);
           }
         }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty_bar[buf]);
-      if (++s == kSlots) s = 0;
+#ifdef RUYB200_DEBUG_KNOBS
+      dbg_work += clock64() - dbg_c;
+#endif
     }
+#ifdef RUYB200_DEBUG_KNOBS
+    if (blockIdx.x == 0 && lane == 0 && group == 0)
+      printf("epilogue group 0 quarter %d: total %lld cycles, waiting for a tile %lld, staging %lld, working %lld\n", quarter,
+             clock64() - dbg_t0, dbg_wait, dbg_stage, dbg_work);
+#endif
   }
 
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (warp == kPackWarps) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kAccBuffers * kAccCols)
+  if (warp == kMmaWarp) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols)
                  : "memory");
   }
 }
@@ -429,8 +546,7 @@ bool batch_i8_fits(const SideView& m_side, const SideView& n_side, int depth) {
   return depth >= 1 && depth <= 128;
 }
 
-cudaError_t launch_batch_i8(const BatchItem* items, const int32_t* order, int num_items, int sm_count, int* status,
-                            cudaStream_t stream) {
+cudaError_t launch_batch_i8(const BatchItem* items, int num_items, int grid, int* status, cudaStream_t stream) {
   if (num_items <= 0) return cudaSuccess;
   static bool attr_set = false;
   if (!attr_set) {
@@ -438,8 +554,7 @@ cudaError_t launch_batch_i8(const BatchItem* items, const int32_t* order, int nu
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
-  const int grid = num_items < sm_count ? num_items : sm_count;
-  batch_i8_kernel<<<grid, kThreads, kSmemBytes, stream>>>(items, order, num_items, status);
+  batch_i8_kernel<<<grid, kThreads, kSmemBytes, stream>>>(items, num_items, status);
   return cudaGetLastError();
 }
 

@@ -40,7 +40,8 @@ struct alignas(16) BatchItem {
   int32_t mfp;
   int32_t mexp;
   uint32_t flags;
-  int32_t reserved[6];
+  int32_t m_off;       // first tile row (TMEM lane) used by this item: 0, 32, 64 or 96; spreads small items over the lane quarters
+  int32_t reserved[5];
 };
 static_assert(sizeof(BatchItem) == 128, "BatchItem is copied as eight 16-byte pieces");
 
@@ -48,8 +49,7 @@ static_assert(sizeof(BatchItem) == 128, "BatchItem is copied as eight 16-byte pi
 // 8-byte aligned rows.
 bool batch_i8_fits(const SideView& m_side, const SideView& n_side, int depth);
 
-// `items` and `order` (item indices, heaviest first) are device arrays; CTA b handles order[b], order[b+grid], ...
-cudaError_t launch_batch_i8(const BatchItem* items, const int32_t* order, int num_items, int sm_count, int* status,
-                            cudaStream_t stream);
+// `items` is a device array already in schedule order: CTA b of `grid` handles items[b], items[b + grid], ...
+cudaError_t launch_batch_i8(const BatchItem* items, int num_items, int grid, int* status, cudaStream_t stream);
 
 }  // namespace ruyb200

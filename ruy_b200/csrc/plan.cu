@@ -16,9 +16,9 @@ struct ruyb200_plan {
   ruyb200_ctx* ctx = nullptr;
   std::vector<ruyb200_mul_desc> single;     // muls replayed one launch at a time
   std::vector<const void*> pinned;          // prepacked-cache entries this plan reads
-  BatchItem* d_items = nullptr;
-  int32_t* d_order = nullptr;
+  BatchItem* d_items = nullptr;   // in schedule order
   int num_items = 0;
+  int grid = 0;
   uint64_t bytes = 0;
   uint64_t ops = 0;
 };
@@ -30,7 +30,6 @@ size_t esize(int dtype) { return dtype == RUYB200_I8 || dtype == RUYB200_U8 ? 1 
 void free_plan(ruyb200_plan* plan) {
   if (!plan) return;
   if (plan->d_items) cudaFree(plan->d_items);
-  if (plan->d_order) cudaFree(plan->d_order);
   ctx_unpin(plan->ctx, plan->pinned);
   delete plan;
 }
@@ -87,20 +86,35 @@ int ruyb200_plan_create(ruyb200_ctx* ctx, const ruyb200_mul_desc* descs, int n, 
     std::vector<int32_t> order(items.size());
     for (size_t i = 0; i < order.size(); i++) order[i] = (int32_t)i;
     std::stable_sort(order.begin(), order.end(), [&](int32_t a, int32_t b) { return cost[a] > cost[b]; });
-    // CTA b takes order[b], order[b + grid], ...: reverse every other round so heavy and light items pair up
+    // CTA b takes positions b, b + grid, ...: reverse every other round so heavy and light items pair up
     const int grid = std::min<int>(plan->num_items, ctx_sm_count(ctx));
+    plan->grid = grid;
     for (size_t start = grid; start + 1 < order.size(); start += 2 * (size_t)grid) {
       const size_t end = std::min(order.size(), start + grid);
       std::reverse(order.begin() + start, order.begin() + end);
     }
-    if (cudaMalloc(&plan->d_items, items.size() * sizeof(BatchItem)) != cudaSuccess ||
-        cudaMalloc(&plan->d_order, order.size() * sizeof(int32_t)) != cudaSuccess) {
+    // Items that use at most 32 (64) tensor-memory lanes are rotated over the four (two) lane ranges, so
+    // that the epilogue work spreads evenly over the SM's four schedulers.
+    std::vector<BatchItem> scheduled(items.size());
+    std::vector<int> rot32(grid, 0), rot64(grid, 0);
+    for (size_t pos = 0; pos < order.size(); pos++) {
+      BatchItem it = items[order[pos]];
+      const int cta = (int)(pos % grid);
+      if (it.size_m <= 32) {
+        it.m_off = 32 * (rot32[cta]++ & 3);
+      } else if (it.size_m <= 64) {
+        it.m_off = 64 * (rot64[cta]++ & 1);
+      } else {
+        it.m_off = 0;
+      }
+      scheduled[pos] = it;
+    }
+    if (cudaMalloc(&plan->d_items, scheduled.size() * sizeof(BatchItem)) != cudaSuccess) {
       cudaGetLastError();
       free_plan(plan);
       return ctx_fail(RUYB200_ERR_OOM, "plan allocation failed");
     }
-    cudaMemcpy(plan->d_items, items.data(), items.size() * sizeof(BatchItem), cudaMemcpyHostToDevice);
-    cudaMemcpy(plan->d_order, order.data(), order.size() * sizeof(int32_t), cudaMemcpyHostToDevice);
+    cudaMemcpy(plan->d_items, scheduled.data(), scheduled.size() * sizeof(BatchItem), cudaMemcpyHostToDevice);
   }
   // packing launched for cache misses has finished before the plan is used
   int rc = ruyb200_ctx_sync(ctx);
@@ -115,8 +129,8 @@ int ruyb200_plan_create(ruyb200_ctx* ctx, const ruyb200_mul_desc* descs, int n, 
 int ruyb200_plan_run(ruyb200_plan* plan) {
   if (!plan) return ctx_fail(RUYB200_ERR_INVALID, "null plan");
   if (plan->num_items > 0) {
-    cudaError_t ce = launch_batch_i8(plan->d_items, plan->d_order, plan->num_items, ctx_sm_count(plan->ctx),
-                                     ctx_status_word(plan->ctx), ctx_stream(plan->ctx));
+    cudaError_t ce = launch_batch_i8(plan->d_items, plan->num_items, plan->grid, ctx_status_word(plan->ctx),
+                                     ctx_stream(plan->ctx));
     ctx_count_launch(plan->ctx, RUYB200_KERNEL_BATCH_I8);
     if (ce != cudaSuccess) return ctx_fail(RUYB200_ERR_CUDA, cudaGetErrorString(ce));
   }
