@@ -220,10 +220,10 @@ def run_gpu_arm(args):
         dist.init_process_group("nccl", device_id=dev)
 
     dst_name = "int32" if args.workload == "c3_i32" else "int8"
+    from ruy_b200.sharding import column_shard
     cols_total = args.cols
-    assert cols_total % world == 0
-    shard = cols_total // world
-    case = cases.config3(dst=dst_name, col_begin=rank * shard, col_count=shard)
+    first_col, shard = column_shard(cols_total, rank, world)
+    case = cases.config3(dst=dst_name, col_begin=first_col, col_count=shard)
     tdtype = torch.int32 if dst_name == "int32" else torch.int8
     esz = 4 if dst_name == "int32" else 1
 
@@ -386,9 +386,9 @@ def run_c2_arm(args):
     if use_dist:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
+    from ruy_b200.sharding import mul_range
     n_total = args.muls
-    per = (n_total + world - 1) // world
-    first, count = rank * per, max(0, min(per, n_total - rank * per))
+    first, count = mul_range(n_total, rank, world)
     mine = cases.config2(n=n_total, seed=0, first=first, count=count)
 
     def pool(arrays, dtype):
