@@ -513,13 +513,107 @@ def run_c2_arm(args):
         dist.destroy_process_group()
 
 
+def run_small_arm(args):
+    """The remaining benchmark configurations, one JSON line each (single GPU, device-resident operands, the
+    stream-ordered entry point timed with CUDA events; L2 flushed between calls): config 0 (256x512x128 int8),
+    config 1 (the five fp32 shapes) and config 4 (the uint8 pointwise-conv layers at batch 1 and 64).  Every
+    line carries the same mul timed through ruy's own CPU path on all host cores."""
+    import torch
+    import ruy_b200
+    from ruy_b200 import cases
+    from ruy_b200.api import Rounding, make_desc
+    import oracle
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    stream = torch.cuda.Stream(device=dev)
+    ctx = ruy_b200.Context(0, stream=stream.cuda_stream)
+    peaks = measured_peaks()
+    todo = []
+    if args.workload in ("c0", "small"):
+        todo.append(cases.config0())
+    if args.workload in ("c1", "small"):
+        todo.extend(cases.config1(sh) for sh in cases.CONFIG1_SHAPES)
+    if args.workload in ("c4", "small"):
+        for batch in (1, 64):
+            todo.extend(cases.config4(layer, batch=batch) for layer in range(len(cases.CONFIG4_LAYERS)))
+    ref = oracle.reference()
+    cores = os.cpu_count() or 1
+    ref_ctx = ref.ruy_ref_ctx_create(oracle.host_simd_path(), cores) if ref is not None else None
+    torch_dt = {"int8": torch.int8, "uint8": torch.uint8, "int32": torch.int32, "float32": torch.float32}
+    with torch.cuda.stream(stream):
+        flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
+        for case in todo:
+            dst = torch.zeros(case.dst_storage_elems(), dtype=torch_dt[case.dst_dtype], device=dev)
+            lhs, rhs, p, d, keep = case.bind(dst, device=dev, rounding=Rounding.kReference)
+            ruy_b200.mul(lhs, rhs, p, ctx, d)
+            kernel = ctx.counters()["last_kernel"]
+            for _ in range(3):
+                flush.fill_(1)
+                ruy_b200.mul_async(lhs, rhs, p, ctx, d)
+            stream.synchronize()
+            steps = min(args.steps, 50)
+            starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+            stops = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+            launches0 = ctx.counters()["launches"]
+            for i in range(steps):
+                flush.fill_(i & 0xFF)
+                starts[i].record(stream)
+                ruy_b200.mul_async(lhs, rhs, p, ctx, d)
+                stops[i].record(stream)
+            stream.synchronize()
+            launches = (ctx.counters()["launches"] - launches0) / steps
+            ms = float(np.median([a.elapsed_time(b) for a, b in zip(starts, stops)]))
+            # end to end with host operands through the synchronous call
+            hdst = case.new_dst()
+            hl, hr, hp, hd, hkeep = case.bind(hdst, rounding=Rounding.kReference)
+            ruy_b200.mul(hl, hr, hp, ctx, hd)
+            t0 = time.perf_counter()
+            reps = 5
+            for _ in range(reps):
+                ruy_b200.mul(hl, hr, hp, ctx, hd)
+            e2e_ms = (time.perf_counter() - t0) / reps * 1e3
+            nbytes = case.algorithmic_bytes()
+            gops = case.ops / (ms * 1e-3) / 1e9
+            gbs = nbytes / (ms * 1e-3) / 1e9
+            is_float = case.accum == "float32"
+            hbm_time = nbytes / (peaks["hbm_gbs"] * 1e9)
+            math_peak = 75e12 if is_float else 2.0 * peaks["bf16_tflops"] * 1e12
+            math_time = case.ops / math_peak
+            bound = "hbm" if hbm_time >= math_time else "tensor"
+            line = {"metric": "mul_time_us", "value": ms * 1e3, "unit": "us", "n_gpus": 1, "steps": steps, "warmup": 3,
+                    "ms_per_step": ms, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+                    "dtype": "f32" if is_float else "int8", "data": "synthetic",
+                    "config": {"workload": case.name, "rows": case.rows, "depth": case.depth, "cols": case.cols,
+                               "l2": "flushed between steps"},
+                    "kernel": kernel, "gops": gops, "gpu_launches": launches,
+                    "e2e": {"value": e2e_ms * 1e3, "unit": "us", "h2d_bytes_per_step": None, "d2h_bytes_per_step": None},
+                    "roofline": {"bound": bound, "achieved": gbs if bound == "hbm" else gops / 1e3,
+                                 "peak": peaks["hbm_gbs"] if bound == "hbm" else math_peak / 1e12,
+                                 "unit": "GB/s" if bound == "hbm" else "TFLOP/s",
+                                 "frac": (gbs / peaks["hbm_gbs"]) if bound == "hbm" else (gops / 1e3) / (math_peak / 1e12),
+                                 "traffic": None,
+                                 "peak_source": "measured hbm_gbs" if bound == "hbm" else
+                                 ("nominal fp32 FFMA 75 TFLOP/s" if is_float else "2 x measured bf16_tflops")}}
+            if ref_ctx is not None and not args.no_cpu_baseline:
+                cb = case.bind(case.new_dst())
+                cdesc = make_desc(cb[0], cb[1], cb[2], cb[3])
+                secs = ref.ruy_ref_time_mul(ref_ctx, C.byref(cdesc), 2, 0.2)
+                line["cpu_baseline"] = {"value": secs * 1e6, "unit": "us", "cores": cores, "kind": "reference",
+                                        "sample": "the same mul, ruy::Mul on the widest host SIMD path, all host threads, hot cache"}
+            print(json.dumps(line), flush=True)
+    if ref_ctx is not None:
+        ref.ruy_ref_ctx_destroy(ref_ctx)
+    ctx.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c3_i8", choices=["c3_i8", "c3_i32", "c2"])
+    ap.add_argument("--workload", default="c3_i8", choices=["c3_i8", "c3_i32", "c2", "c0", "c1", "c4", "small"])
     ap.add_argument("--muls", type=int, default=16384, help="number of muls of workload c2")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cols", type=int, default=8192,
@@ -529,6 +623,8 @@ def main():
         run_reference_arm(args)
     elif args.workload == "c2":
         run_c2_arm(args)
+    elif args.workload in ("c0", "c1", "c4", "small"):
+        run_small_arm(args)
     else:
         run_gpu_arm(args)
 

@@ -543,9 +543,14 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous) {
   // the generic kernel subtracts zero points while loading and needs no sums
   const bool need_lhs_sums = !is_float && !generic && d.rhs.zero_point != 0;
   const bool need_rhs_sums = !is_float && !generic && d.lhs.zero_point != 0;
-  rc = prepare_side(ctx, d.lhs, 0, depth, should_cache(d.lhs, d.rhs.cols), need_lhs_sums, tc, &lhs_v, &lhs_sums);
+  // The tensor-core kernel can produce the sums of its m-side operand (the RHS for a column-major destination,
+  // the LHS otherwise) itself, so no separate pass over that operand is requested for it.
+  const bool m_is_rhs = d.dst.order == RUYB200_COL_MAJOR;
+  rc = prepare_side(ctx, d.lhs, 0, depth, should_cache(d.lhs, d.rhs.cols), need_lhs_sums && !(tc && !m_is_rhs), tc, &lhs_v,
+                    &lhs_sums);
   if (rc) return rc;
-  rc = prepare_side(ctx, d.rhs, 1, depth, should_cache(d.rhs, d.lhs.rows), need_rhs_sums, tc, &rhs_v, &rhs_sums);
+  rc = prepare_side(ctx, d.rhs, 1, depth, should_cache(d.rhs, d.lhs.rows), need_rhs_sums && !(tc && m_is_rhs), tc, &rhs_v,
+                    &rhs_sums);
   if (rc) return rc;
 
   Epilogue ep;
@@ -628,6 +633,7 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous) {
     L.sm_count = ctx->sm_count;
     L.status = ctx->d_status;
     L.allow_pair = !ctx->no_pair;
+    L.fuse_sums_m = true;
     ce = launch_tc_i8(L, ctx->stream);
   } else if (kernel == RUYB200_KERNEL_SGEMM) {
     ce = launch_sgemm(r.m_side, r.n_side, r.dst, r.ep, ctx->stream);

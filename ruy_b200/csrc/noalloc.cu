@@ -182,6 +182,7 @@ extern "C" int ruyb200_mul_noalloc(const ruyb200_mul_desc* desc, void* cuda_stre
   L.sm_count = setup->sm_count;
   L.status = status;
   L.allow_pair = true;
+  L.fuse_sums_m = false;
   ce = launch_tc_i8(L, stream);
   if (ce != cudaSuccess) return ctx_fail(RUYB200_ERR_CUDA, cudaGetErrorString(ce));
 

@@ -46,6 +46,7 @@ constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + 1024;
 constexpr int kEpilogueWarps = 8;
 constexpr int kThreads = 64 + 32 * kEpilogueWarps;   // producer warp + MMA warp + epilogue warps
 constexpr int kTmemCols = 512;
+constexpr int kMaxAccBufs = 8;        // narrow tiles leave room for more accumulators, which hides the epilogue's latency
 constexpr uint32_t kSpinFast = 2048;
 constexpr uint32_t kSpinLimit = 4u << 20;  // with 100 ns sleeps: well under a second
 
@@ -61,6 +62,10 @@ struct KernelArgs {
   int tiles_m;
   int tiles_n;
   uint32_t idesc;
+  int acc_bufs;    // accumulator buffers in tensor memory: 2, 4 or 8 (512 columns / columns per tile, as a power of two)
+  int acc_shift;   // log2(acc_bufs)
+  int sums_col;    // >= 0: accumulator column that receives sum_k of the m-side row (an all-ones row of the n operand); -1: none
+  int mma_n;       // N of the MMA: block_n, plus 16 when the sums column is appended
   int* status;
   int debug;       // profiling knobs (0 in production): 1 = epilogue skips its math and stores, 2 = producer skips the loads
 };
@@ -284,9 +289,9 @@ struct NTerms {
 
 // Narrow and store 32 consecutive destination elements n0..n0+31 of row m.
 template <int kDstBytes>
-__device__ __forceinline__ void store_run32(const KernelArgs& a, int m, int n0, const int32_t* v) {
+__device__ __forceinline__ void store_run32(const KernelArgs& a, int m, int n0, int n_end, const int32_t* v) {
   char* base = (char*)a.dst.data + ((int64_t)m * a.dst.stride_m + n0) * kDstBytes;
-  const bool full = n0 + 32 <= a.size_n;
+  const bool full = n0 + 32 <= n_end;   // n_end: end of this tile's columns (and of the destination)
   if (full && (((uintptr_t)base) & 15) == 0) {
     uint4* out = (uint4*)base;
     if (kDstBytes == 1) {
@@ -317,7 +322,7 @@ __device__ __forceinline__ void store_run32(const KernelArgs& a, int m, int n0, 
     return;
   }
   for (int q = 0; q < 32; q++) {
-    if (n0 + q < a.size_n) store_int(a.dst, a.ep.dst_dtype, m, n0 + q, v[q]);
+    if (n0 + q < n_end) store_int(a.dst, a.ep.dst_dtype, m, n0 + q, v[q]);
   }
 }
 
@@ -384,8 +389,8 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kNumStages];
   __shared__ __align__(8) uint64_t empty_bar[kNumStages];
-  __shared__ __align__(8) uint64_t acc_full_bar[2];
-  __shared__ __align__(8) uint64_t acc_empty_bar[2];
+  __shared__ __align__(8) uint64_t acc_full_bar[kMaxAccBufs];
+  __shared__ __align__(8) uint64_t acc_empty_bar[kMaxAccBufs];
   __shared__ __align__(16) NTerms n_terms[2][kMaxBlockN];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
@@ -402,7 +407,7 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
       mbar_init(&full_bar[s], 1);   // pair: only the even CTA's barriers are used; its producer expects both CTAs' bytes
       mbar_init(&empty_bar[s], 1);
     }
-    for (int b = 0; b < 2; b++) {
+    for (int b = 0; b < kMaxAccBufs; b++) {
       mbar_init(&acc_full_bar[b], 1);
       mbar_init(&acc_empty_bar[b], kPair ? 2 * kEpilogueWarps : kEpilogueWarps);
     }
@@ -422,6 +427,16 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
                    : "memory");
       asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+  }
+  if (!kPair && args.sums_col >= 0) {
+    // Zero-point sums of the m-side operand for free: 16 rows of the n-side tile that no TMA box ever covers
+    // are filled with 0x01 once, so accumulator column sums_col becomes sum_k m[.,k] (ruy/pack.h:117-129 computes
+    // these sums while packing).  All bytes are equal, so the swizzle does not matter.
+    for (int st = 0; st < kNumStages; st++) {
+      uint32_t* ones = reinterpret_cast<uint32_t*>(smem + st * kStageSize + kABytes + args.sums_col * kBlockKBytes);
+      for (int i = threadIdx.x; i < 16 * kBlockKBytes / 4; i += kThreads) ones[i] = 0x01010101u;
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
@@ -504,8 +519,8 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
       long long dbg_t0 = clock64(), dbg_full = 0, dbg_acc = 0;
 #endif
       for (int tile = unit; tile < num_tiles && ok; tile += units, tcount++) {
-        const int buf = tcount & 1;
-        const uint32_t aph = (tcount >> 1) & 1;
+        const int buf = (int)(tcount & (uint32_t)(args.acc_bufs - 1));
+        const uint32_t aph = (tcount >> args.acc_shift) & 1;
 #ifdef RUYB200_DEBUG_KNOBS
         long long dbg_a = clock64();
 #endif
@@ -518,7 +533,7 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
 #ifdef RUYB200_DEBUG_KNOBS
         dbg_acc += clock64() - dbg_a;
 #endif
-        const uint32_t tmem_d = tmem_base + (uint32_t)(buf * kMaxBlockN);
+        const uint32_t tmem_d = tmem_base + (uint32_t)(buf * (kTmemCols >> args.acc_shift));
         for (int kb = 0; kb < k_blocks; kb++) {
 #ifdef RUYB200_DEBUG_KNOBS
           const bool dbg_ready = (args.debug & 16) ? mbar_test_wait(&full_bar[s], ph) : mbar_try_wait(&full_bar[s], ph);
@@ -577,42 +592,48 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
     const int32_t zz = ep.zp_m * ep.zp_n * ep.depth;
     uint32_t tcount = 0;
     bool ok = true;
+    int staged_tn[2] = {-1, -1};   // which n tile each staging buffer holds (same in every epilogue thread)
 #ifdef RUYB200_DEBUG_KNOBS
     long long dbg_wait = 0, dbg_busy = 0, dbg_stage = 0;
 #endif
     for (int tile = unit; tile < num_tiles && ok; tile += units, tcount++) {
       const int tm = tile / args.tiles_n;
       const int tn = tile % args.tiles_n;
-      const int buf = tcount & 1;
-      const uint32_t aph = (tcount >> 1) & 1;
+      const int buf = (int)(tcount & (uint32_t)(args.acc_bufs - 1));
+      const uint32_t aph = (tcount >> args.acc_shift) & 1;
 #ifdef RUYB200_DEBUG_KNOBS
       long long dbg_a = clock64();
 #endif
-      // stage the per-n terms of this tile (overlaps the tile's main loop)
-      NTerms* nt = n_terms[buf];
-      for (int i = etid; i < args.block_n; i += 32 * kEpilogueWarps) {
-        const int n = tn * args.block_n + i;
-        NTerms t;
-        t.add = zz;
-        t.mul = ep.mfp;
-        t.exp = ep.mexp;
-        t.pad = 0;
-        if (n < args.size_n) {
-          if (ep.zp_m) t.add -= ep.zp_m * ep.sums_n[n];
-          if (ch_n) {
-            if (ep.bias) t.add += ((const int32_t*)ep.bias)[n];
-            if (ep.mfp_pc) t.mul = ep.mfp_pc[n];
-            if (ep.mexp_pc) t.exp = ep.mexp_pc[n];
+      // stage the per-n terms of this tile (overlaps the tile's main loop); two staging buffers alternate,
+      // and a buffer that already holds this n tile's terms (one n tile, or an unchanged one) is kept
+      const int tb = (int)(tcount & 1);
+      NTerms* nt = n_terms[tb];
+      if (staged_tn[tb] != tn) {
+        staged_tn[tb] = tn;
+        for (int i = etid; i < args.block_n; i += 32 * kEpilogueWarps) {
+          const int n = tn * args.block_n + i;
+          NTerms t;
+          t.add = zz;
+          t.mul = ep.mfp;
+          t.exp = ep.mexp;
+          t.pad = 0;
+          if (n < args.size_n) {
+            if (ep.zp_m) t.add -= ep.zp_m * ep.sums_n[n];
+            if (ch_n) {
+              if (ep.bias) t.add += ((const int32_t*)ep.bias)[n];
+              if (ep.mfp_pc) t.mul = ep.mfp_pc[n];
+              if (ep.mexp_pc) t.exp = ep.mexp_pc[n];
+            }
           }
+          nt[i] = t;
         }
-        nt[i] = t;
       }
       // per-m terms of this thread's row
       const int m = tm * kUnitM + (int)rank * kBlockM + lane_group * 32 + lane;
       const bool m_ok = m < args.size_m;
       int32_t add_m = 0, mul_m = ep.mfp, exp_m = ep.mexp;
       if (m_ok) {
-        if (ep.zp_n) add_m -= ep.zp_n * ep.sums_m[m];
+        if (ep.zp_n && ep.sums_m) add_m -= ep.zp_n * ep.sums_m[m];
         if (!ch_n) {
           if (ep.bias) add_m += ((const int32_t*)ep.bias)[m];
           if (ep.mfp_pc) mul_m = ep.mfp_pc[m];
@@ -638,7 +659,14 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
       long long dbg_c = clock64();
       dbg_wait += dbg_c - dbg_b;
 #endif
-      const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(buf * kMaxBlockN);
+      const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(buf * (kTmemCols >> args.acc_shift));
+      if (!kPair && args.sums_col >= 0) {
+        uint32_t row_sum;
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(row_sum) : "r"(taddr + (uint32_t)args.sums_col) : "memory");
+        tmem_ld_wait();
+        add_m -= ep.zp_n * (int32_t)row_sum;
+      }
+      const int n_end = min(args.size_n, (tn + 1) * args.block_n);   // a 32-column chunk may reach past the tile's columns
       for (int c = chunk_parity * 32; c < args.block_n; c += 64) {
         const int n0 = tn * args.block_n + c;
         if (n0 >= args.size_n || (args.debug & 1)) break;   // uniform across the warp
@@ -662,7 +690,7 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
             }
             v[q] = x;
           }
-          store_run32<kDstBytes>(args, m, n0, v);
+          store_run32<kDstBytes>(args, m, n0, n_end, v);
         }
       }
       tc_fence_before();
@@ -832,17 +860,25 @@ cudaError_t launch_tc_i8(const TcI8Launch& L, cudaStream_t stream) {
 #endif
   const uint32_t fmt_m = L.m_side.dtype == RUYB200_I8 ? 1u : 0u;
   const uint32_t fmt_n = L.n_side.dtype == RUYB200_I8 ? 1u : 0u;
+  // The m-side zero-point sums can come out of the tensor core itself (an all-ones row appended to the n tile)
+  // instead of a separate pass over the m operand; that variant runs with one CTA per tile.
+  const bool fuse = L.fuse_sums_m && L.ep.zp_n != 0 && L.ep.sums_m == nullptr;
   // Two-CTA tiles (256 x 256) when both destination dimensions are large enough to fill them.
-  const bool pair = L.allow_pair && a.size_m >= 256 && a.size_n >= 256 && L.sm_count >= 2;
+  const bool pair = !fuse && L.allow_pair && a.size_m >= 256 && a.size_n >= 256 && L.sm_count >= 2;
   int bn = (a.size_n + 15) / 16 * 16;
-  if (bn > kMaxBlockN) bn = kMaxBlockN;
+  const int bn_cap = fuse ? kMaxBlockN - 16 : kMaxBlockN;
+  if (bn > bn_cap) bn = bn_cap;
   a.block_n = bn;
+  a.sums_col = fuse ? bn : -1;
+  a.mma_n = fuse ? bn + 16 : bn;
   const int unit_m = pair ? 2 * kBlockM : kBlockM;
   a.tiles_m = (a.size_m + unit_m - 1) / unit_m;
   a.tiles_n = (a.size_n + bn - 1) / bn;
+  a.acc_shift = a.mma_n <= 64 ? 3 : (a.mma_n <= 128 ? 2 : 1);
+  a.acc_bufs = 1 << a.acc_shift;
   // instruction descriptor: int32 accumulate, operand signedness, both operands depth-major,
   // N/8 at bit 17, M/16 at bit 24 (M spans both CTAs of a pair)
-  a.idesc = (2u << 4) | (fmt_m << 7) | (fmt_n << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(unit_m >> 4) << 24);
+  a.idesc = (2u << 4) | (fmt_m << 7) | (fmt_n << 10) | ((uint32_t)(a.mma_n >> 3) << 17) | ((uint32_t)(unit_m >> 4) << 24);
   CUtensorMap map_m, map_n;
   if (!make_map(&map_m, L.m_side, L.depth, kBlockM) || !make_map(&map_n, L.n_side, L.depth, pair ? bn / 2 : bn)) {
     return cudaErrorInvalidValue;
