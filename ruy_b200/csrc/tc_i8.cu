@@ -8,7 +8,7 @@
 //   * warp 1   : issues tcgen05.mma kind::i8 (M=128, N<=256, K=32 per instruction), int32
 //                accumulators in tensor memory, two accumulator buffers so the epilogue of one
 //                tile overlaps the main loop of the next.
-//   * warps 2-9: epilogue.  Per tile the per-channel terms (bias, zero-point corrections,
+//   * warps 2-9: epilogue, two groups of four warps that take tiles in turn.  Per tile the per-channel terms (bias, zero-point corrections,
 //                multiplier, exponent) are staged once in shared memory; then tcgen05.ld brings
 //                32 accumulator columns at a time into registers, the fixed-point multiplier,
 //                destination zero point and clamp are applied (ruy/kernel.h:213-237), and the
@@ -44,6 +44,7 @@ constexpr int kPairStages = 6;
 constexpr int kPairStageBytes = kABytes + 128 * kBlockKBytes;   // 32 KiB
 constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + 1024;
 constexpr int kEpilogueWarps = 8;
+constexpr int kEpilogueGroups = kEpilogueWarps / 4;   // a group covers the four TMEM lane quarters and drains whole tiles
 constexpr int kThreads = 64 + 32 * kEpilogueWarps;   // producer warp + MMA warp + epilogue warps
 constexpr int kTmemCols = 512;
 constexpr int kMaxAccBufs = 8;        // narrow tiles leave room for more accumulators, which hides the epilogue's latency
@@ -64,6 +65,7 @@ struct KernelArgs {
   uint32_t idesc;
   int acc_bufs;    // accumulator buffers in tensor memory: 2, 4 or 8 (512 columns / columns per tile, as a power of two)
   int acc_shift;   // log2(acc_bufs)
+  int epi_groups;  // 1: all eight epilogue warps drain each tile together; 2: two groups of four take tiles in turn
   int sums_col;    // >= 0: accumulator column that receives sum_k of the m-side row (an all-ones row of the n operand); -1: none
   int mma_n;       // N of the MMA: block_n, plus 16 when the sums column is appended
   int* status;
@@ -265,16 +267,16 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-// AND-reduction of `ok` over the epilogue threads through named barrier 1.
-__device__ __forceinline__ bool epilogue_all(bool ok) {
+// AND-reduction of `ok` over the threads of one epilogue group through named barrier 1 + group.
+__device__ __forceinline__ bool epilogue_all(bool ok, int group, int group_threads) {
   uint32_t res;
   asm volatile(
       "{\n\t.reg .pred p, q;\n\t"
       "setp.ne.u32 q, %1, 0;\n\t"
-      "bar.red.and.pred p, 1, %2, q;\n\t"
+      "bar.red.and.pred p, %2, %3, q;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(res)
-      : "r"((uint32_t)ok), "n"(32 * kEpilogueWarps)
+      : "r"((uint32_t)ok), "r"(1 + group), "r"(group_threads)
       : "memory");
   return res != 0;
 }
@@ -391,7 +393,7 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
   __shared__ __align__(8) uint64_t empty_bar[kNumStages];
   __shared__ __align__(8) uint64_t acc_full_bar[kMaxAccBufs];
   __shared__ __align__(8) uint64_t acc_empty_bar[kMaxAccBufs];
-  __shared__ __align__(16) NTerms n_terms[2][kMaxBlockN];
+  __shared__ __align__(16) NTerms n_terms[kEpilogueGroups][kMaxBlockN];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -409,7 +411,8 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
     }
     for (int b = 0; b < kMaxAccBufs; b++) {
       mbar_init(&acc_full_bar[b], 1);
-      mbar_init(&acc_empty_bar[b], kPair ? 2 * kEpilogueWarps : kEpilogueWarps);
+      // the warps of the group that drained it (in both CTAs of a pair)
+      mbar_init(&acc_empty_bar[b], (kEpilogueWarps / args.epi_groups) * (kPair ? 2 : 1));
     }
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -586,13 +589,20 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
     const Epilogue& ep = args.ep;
     const int ew = warp - 2;
     const int lane_group = warp % 4;       // the TMEM lane quarter this warp may read
-    const int chunk_parity = ew / 4;       // the two warps of a lane quarter alternate 32-column chunks
-    const int etid = threadIdx.x - 64;
+    // Deep main loops: all eight warps drain each tile together (two warps per lane quarter alternate 32-column
+    // chunks), so the accumulator is free again as early as possible.  Shallow ones: two groups of four warps take
+    // tiles in turn, so that the per-tile latencies (barrier, tensor-memory loads, stores) of two tiles overlap.
+    const int groups = args.epi_groups;
+    const int group = groups == 2 ? ew / 4 : 0;
+    const int group_threads = 32 * kEpilogueWarps / groups;
+    const int etid = groups == 2 ? (ew % 4) * 32 + lane : ew * 32 + lane;   // thread index within the group
+    const int c_first = groups == 2 ? 0 : (ew / 4) * 32;
+    const int c_step = groups == 2 ? 32 : 64;
     const bool ch_n = ep.channel_on_n != 0;
     const int32_t zz = ep.zp_m * ep.zp_n * ep.depth;
     uint32_t tcount = 0;
     bool ok = true;
-    int staged_tn[2] = {-1, -1};   // which n tile each staging buffer holds (same in every epilogue thread)
+    int staged_tn = -1;            // which n tile this group's staging buffer holds
 #ifdef RUYB200_DEBUG_KNOBS
     long long dbg_wait = 0, dbg_busy = 0, dbg_stage = 0;
 #endif
@@ -604,13 +614,16 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
 #ifdef RUYB200_DEBUG_KNOBS
       long long dbg_a = clock64();
 #endif
-      // stage the per-n terms of this tile (overlaps the tile's main loop); two staging buffers alternate,
-      // and a buffer that already holds this n tile's terms (one n tile, or an unchanged one) is kept
-      const int tb = (int)(tcount & 1);
-      NTerms* nt = n_terms[tb];
-      if (staged_tn[tb] != tn) {
-        staged_tn[tb] = tn;
-        for (int i = etid; i < args.block_n; i += 32 * kEpilogueWarps) {
+      if (groups == 2 && (int)(tcount & 1) != group) continue;   // the other group's tile
+      // stage the per-n terms of this tile (overlaps the tile's main loop) unless the group's buffer already holds
+      // them (there is one n tile, or it did not change)
+      NTerms* nt = n_terms[group];
+      const bool restage = staged_tn != tn;
+      if (restage) {
+        // warps of this group may still be reading the buffer for the previous tile
+        epilogue_all(true, group, group_threads);
+        staged_tn = tn;
+        for (int i = etid; i < args.block_n; i += group_threads) {
           const int n = tn * args.block_n + i;
           NTerms t;
           t.add = zz;
@@ -652,7 +665,7 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
       // One named-barrier reduction over all epilogue threads: it publishes the staged terms and
       // makes the continue/abort decision collective, so no warp is ever left waiting for another
       // that has already left the loop.
-      ok = epilogue_all(ok);
+      ok = epilogue_all(ok, group, group_threads);
       if (!ok) break;
       tc_fence_after();
 #ifdef RUYB200_DEBUG_KNOBS
@@ -660,35 +673,54 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
       dbg_wait += dbg_c - dbg_b;
 #endif
       const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(buf * (kTmemCols >> args.acc_shift));
-      if (!kPair && args.sums_col >= 0) {
-        uint32_t row_sum;
-        asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(row_sum) : "r"(taddr + (uint32_t)args.sums_col) : "memory");
-        tmem_ld_wait();
-        add_m -= ep.zp_n * (int32_t)row_sum;
-      }
       const int n_end = min(args.size_n, (tn + 1) * args.block_n);   // a 32-column chunk may reach past the tile's columns
-      for (int c = chunk_parity * 32; c < args.block_n; c += 64) {
+      const bool have_chunk = c_first < args.block_n && tn * args.block_n + c_first < args.size_n && !(args.debug & 1);
+      uint32_t r[32];
+      // the sums column and the first chunk are fetched together: one wait instead of two
+      uint32_t row_sum = 0;
+      if (!kPair && args.sums_col >= 0) {
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(row_sum) : "r"(taddr + (uint32_t)args.sums_col) : "memory");
+      }
+      if (have_chunk) tmem_ld_32(taddr + c_first, r);
+      tmem_ld_wait();
+      if (!kPair && args.sums_col >= 0) add_m -= ep.zp_n * (int32_t)row_sum;
+      // When the multiplier does not vary along n (one multiplier for the whole matrix, or one per m), the
+      // rounding term and the shift are per-thread constants.
+      const bool mul_varies_with_n = ch_n && (ep.mfp_pc != nullptr || ep.mexp_pc != nullptr);
+      const int sh_c = 31 - exp_m;
+      const long long rnd_c = 1ll << (sh_c - 1);
+      for (int c = c_first; c < args.block_n; c += c_step) {
         const int n0 = tn * args.block_n + c;
         if (n0 >= args.size_n || (args.debug & 1)) break;   // uniform across the warp
-        uint32_t r[32];
-        tmem_ld_32(taddr + c, r);
-        tmem_ld_wait();
+        if (c != c_first) {
+          tmem_ld_32(taddr + c, r);
+          tmem_ld_wait();
+        }
         if (m_ok) {
           int32_t v[32];
+          if (kDstBytes != 4 && !kX86 && !mul_varies_with_n) {
 #pragma unroll
-          for (int q = 0; q < 32; q++) {
-            const NTerms t = nt[c + q];
-            int32_t x = (int32_t)(r[q] + (uint32_t)t.add + (uint32_t)add_m);
-            if (kDstBytes != 4) {
-              const int32_t mul = ch_n ? t.mul : mul_m;
-              const int e = ch_n ? t.exp : exp_m;
-              x = kX86 ? requant_x86(x, mul, e) : requant_reference(x, mul, e);
-              x = (int32_t)((uint32_t)x + (uint32_t)ep.dst_zp);
-              x = max(min(x, ep.clamp_max), ep.clamp_min);
-            } else {
-              x = (int32_t)((uint32_t)x + (uint32_t)ep.dst_zp);
+            for (int q = 0; q < 32; q++) {
+              const int32_t x = (int32_t)(r[q] + (uint32_t)nt[c + q].add + (uint32_t)add_m);
+              const int32_t y = (int32_t)(((long long)x * (long long)mul_m + rnd_c) >> sh_c);
+              v[q] = max(min((int32_t)((uint32_t)y + (uint32_t)ep.dst_zp), ep.clamp_max), ep.clamp_min);
             }
-            v[q] = x;
+          } else {
+#pragma unroll
+            for (int q = 0; q < 32; q++) {
+              const NTerms t = nt[c + q];
+              int32_t x = (int32_t)(r[q] + (uint32_t)t.add + (uint32_t)add_m);
+              if (kDstBytes != 4) {
+                const int32_t mul = ch_n ? t.mul : mul_m;
+                const int e = ch_n ? t.exp : exp_m;
+                x = kX86 ? requant_x86(x, mul, e) : requant_reference(x, mul, e);
+                x = (int32_t)((uint32_t)x + (uint32_t)ep.dst_zp);
+                x = max(min(x, ep.clamp_max), ep.clamp_min);
+              } else {
+                x = (int32_t)((uint32_t)x + (uint32_t)ep.dst_zp);
+              }
+              v[q] = x;
+            }
           }
           store_run32<kDstBytes>(args, m, n0, n_end, v);
         }
@@ -876,6 +908,7 @@ cudaError_t launch_tc_i8(const TcI8Launch& L, cudaStream_t stream) {
   a.tiles_n = (a.size_n + bn - 1) / bn;
   a.acc_shift = a.mma_n <= 64 ? 3 : (a.mma_n <= 128 ? 2 : 1);
   a.acc_bufs = 1 << a.acc_shift;
+  a.epi_groups = L.depth <= 512 ? 2 : 1;
   // instruction descriptor: int32 accumulate, operand signedness, both operands depth-major,
   // N/8 at bit 17, M/16 at bit 24 (M spans both CTAs of a pair)
   a.idesc = (2u << 4) | (fmt_m << 7) | (fmt_n << 10) | ((uint32_t)(a.mma_n >> 3) << 17) | ((uint32_t)(unit_m >> 4) << 24);
