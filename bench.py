@@ -229,19 +229,44 @@ def run_gpu_arm(args):
 
     stream = torch.cuda.Stream(device=dev)
     ctx = ruy_b200.Context(local, stream=stream.cuda_stream)
+    mirrored = use_dist and args.gather == "mirror"
+    peer_full = flags = None
+    if mirrored:
+        from ruy_b200 import peer
+        peer_full = peer.PeerBuffer(cols_total * case.rows * esz, dev)
+        flags = peer.StepFlags(dev)
     with torch.cuda.stream(stream):
         # the gathered destination (col-major: a column shard is one contiguous range); each rank
         # computes straight into its own slice of it
-        full = torch.zeros(cols_total * case.rows, dtype=tdtype, device=dev)
+        if mirrored:
+            full = peer_full.tensor.view(tdtype)
+        else:
+            full = torch.zeros(cols_total * case.rows, dtype=tdtype, device=dev)
         mine = full[rank * shard * case.rows:(rank + 1) * shard * case.rows]
         lhs, rhs, p, d, keep = case.bind(mine, device=dev, rounding=Rounding.kReference)
         flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
         ruy_b200.mul(lhs, rhs, p, ctx, d)  # packs the weights into the context's device cache
+        shard_bytes = shard * case.rows * esz
+        mirror_ptrs = [q + rank * shard_bytes for r_, q in enumerate(peer_full.ptrs) if r_ != rank] if mirrored else []
+        step_no = [0]
+
+        def compute():
+            if mirrored:
+                # the epilogue stores each tile here and in every peer's buffer: the gather rides along with the math
+                peer.mul_async_mirrored(lhs, rhs, p, ctx, d, mirror_ptrs)
+            else:
+                ruy_b200.mul_async(lhs, rhs, p, ctx, d)
+
+        def finish():
+            if mirrored:
+                step_no[0] += 1
+                flags.signal_and_wait(ctx, step_no[0])      # every peer's tiles have landed in this rank's buffer
+            elif use_dist:
+                dist.all_gather_into_tensor(full, mine)
 
         def step():
-            ruy_b200.mul_async(lhs, rhs, p, ctx, d)
-            if use_dist:
-                dist.all_gather_into_tensor(full, mine)
+            compute()
+            finish()
 
         sampler = ClockSampler(local)
         sampler.start()
@@ -263,6 +288,17 @@ def run_gpu_arm(args):
             acc = np.clip(((acc * m + (1 << (30 - e))) >> (31 - e)) + case.dst_zp, -128, 127)
         if not np.array_equal(out[np.ix_(rs, cs)].astype(np.int64), acc):
             raise SystemExit("bench.py: GPU result does not match the reference arithmetic; refusing to report")
+        if use_dist:
+            # the gathered part: a sample of the next rank's columns must have arrived here
+            nb = (rank + 1) % world
+            nb_case = cases.config3(dst=dst_name, col_begin=nb * shard, col_count=shard)
+            nb_out = nb_case.dst_view(full[nb * shard * case.rows:(nb + 1) * shard * case.rows].cpu().numpy())
+            accn = L @ nb_case.rhs.reshape(shard, case.depth).astype(np.int64)[cs].T
+            if dst_name == "int8":
+                accn = accn + case.bias.astype(np.int64)[rs][:, None]
+                accn = np.clip(((accn * m + (1 << (30 - e))) >> (31 - e)) + case.dst_zp, -128, 127)
+            if not np.array_equal(nb_out[np.ix_(rs, cs)].astype(np.int64), accn):
+                raise SystemExit("bench.py: the gathered destination is wrong; refusing to report")
 
         launches0 = ctx.counters()["launches"]
         if use_dist:
@@ -276,10 +312,9 @@ def run_gpu_arm(args):
         for i in range(args.steps):
             flush.fill_(i & 0xFF)          # evict the operands from L2 (not timed)
             starts[i].record(stream)
-            ruy_b200.mul_async(lhs, rhs, p, ctx, d)
+            compute()
             mids[i].record(stream)
-            if use_dist:
-                dist.all_gather_into_tensor(full, mine)
+            finish()
             stops[i].record(stream)
         stream.synchronize()
         if use_dist:
@@ -348,7 +383,11 @@ def run_gpu_arm(args):
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "int8", "data": "synthetic",
         "config": {"workload": args.workload, "rows": case.rows, "depth": case.depth, "cols": cols_total,
-                   "dst": dst_name, "sharding": f"{world} column shard(s) of {shard}" + (", dst all-gathered (NCCL) inside the step" if use_dist else ""),
+                   "dst": dst_name,
+                   "sharding": f"{world} column shard(s) of {shard}" + (
+                       (", dst gathered on every rank inside the step by " +
+                        ("epilogue stores into peers' memory over NVLink + flag exchange" if mirrored else "an NCCL all-gather"))
+                       if use_dist else ""),
                    "l2": f"flushed between steps ({L2_FLUSH_BYTES >> 20} MiB fill, untimed)"},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                 "ms_per_step": e2e_s * 1e3},
@@ -365,6 +404,10 @@ def run_gpu_arm(args):
         arm.close()
     if rank == 0:
         print(json.dumps(line), flush=True)
+    if mirrored:
+        ctx.sync()
+        flags.close()
+        peer_full.close()
     ctx.close()
     if use_dist:
         dist.destroy_process_group()
@@ -616,6 +659,8 @@ def main():
     ap.add_argument("--workload", default="c3_i8", choices=["c3_i8", "c3_i32", "c2", "c0", "c1", "c4", "small"])
     ap.add_argument("--muls", type=int, default=16384, help="number of muls of workload c2")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gather", default="mirror", choices=["mirror", "nccl"],
+                    help="N>1: how the column-sharded destination is gathered (epilogue peer stores, or an NCCL all-gather)")
     ap.add_argument("--cols", type=int, default=8192,
                     help="activation columns (8192 is the benchmark configuration; smaller values are for profiler captures)")
     args = ap.parse_args()

@@ -242,6 +242,30 @@ RUYB200_API int ruyb200_plan_destroy(ruyb200_plan* plan);
  * 2*rows*cols*depth operations summed over the plan's muls. */
 RUYB200_API int ruyb200_plan_stats(const ruyb200_plan* plan, uint64_t* bytes, uint64_t* ops);
 
+/* ---- multi-GPU: destination mirrored into peers' memory ------------------------- */
+
+/* Additive (ruy has no multi-device notion).  For the column-sharded large mul each rank (one process per GPU)
+ * computes its column block and must end up with the whole destination.  Instead of a collective after the
+ * kernel, ruyb200_mul_async_mirrored makes the kernel's epilogue store every destination element both at
+ * desc->dst.data and at the corresponding address of each mirror (mirror_dst[i] is the address, in a peer GPU's
+ * buffer mapped into this process, that corresponds to desc->dst.data), so the gather overlaps the math.
+ * 8-bit operands served by the tensor-core kernel only; n_mirrors <= 7.  The peer buffers come from
+ * ruyb200_peer_alloc (plain cudaMalloc, zeroed), are exported with ruyb200_peer_export (a 64-byte
+ * cudaIpcMemHandle_t to be sent to the other processes by any means) and mapped with ruyb200_peer_open.
+ * ruyb200_peer_signal raises, after all earlier work of the context's stream, the flag words remote_flags[i]
+ * (addresses in peers' memory; the array itself lives in device memory) to `value`; ruyb200_peer_wait makes the
+ * stream wait until local_flags[0..n) have all reached `value`, giving up after 2 s with RUYB200_ERR_TIMEOUT at
+ * the next ruyb200_ctx_sync.  Only stores ever cross NVLink; no load reads a peer's memory. */
+RUYB200_API int ruyb200_mul_async_mirrored(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, void* const* mirror_dst,
+                                           int n_mirrors);
+RUYB200_API int ruyb200_peer_alloc(size_t bytes, void** out);
+RUYB200_API int ruyb200_peer_free(void* ptr);
+RUYB200_API int ruyb200_peer_export(void* ptr, unsigned char handle[64]);
+RUYB200_API int ruyb200_peer_open(const unsigned char handle[64], void** out);
+RUYB200_API int ruyb200_peer_close(void* ptr);
+RUYB200_API int ruyb200_peer_signal(ruyb200_ctx* ctx, uint32_t* const* remote_flags_device_array, int n, uint32_t value);
+RUYB200_API int ruyb200_peer_wait(ruyb200_ctx* ctx, const uint32_t* local_flags, int n, uint32_t value);
+
 /* ---- packing: PackImpl / RunPack (ruy/pack.h:105-151) -------------------- */
 
 /* Packs a device- or host-resident integer matrix into the device layout the tensor-core

@@ -105,6 +105,14 @@ PROTOTYPES = {
     "ruyb200_mul": (C.c_int, [C.c_void_p, _P(MulDesc)]),
     "ruyb200_mul_async": (C.c_int, [C.c_void_p, _P(MulDesc)]),
     "ruyb200_validate": (C.c_int, [_P(MulDesc)]),
+    "ruyb200_mul_async_mirrored": (C.c_int, [C.c_void_p, _P(MulDesc), _P(C.c_void_p), C.c_int]),
+    "ruyb200_peer_alloc": (C.c_int, [C.c_size_t, _P(C.c_void_p)]),
+    "ruyb200_peer_free": (C.c_int, [C.c_void_p]),
+    "ruyb200_peer_export": (C.c_int, [C.c_void_p, C.c_char_p]),
+    "ruyb200_peer_open": (C.c_int, [C.c_char_p, _P(C.c_void_p)]),
+    "ruyb200_peer_close": (C.c_int, [C.c_void_p]),
+    "ruyb200_peer_signal": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_uint32]),
+    "ruyb200_peer_wait": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_uint32]),
     "ruyb200_mul_noalloc": (C.c_int, [_P(MulDesc), C.c_void_p]),
     "ruyb200_plan_create": (C.c_int, [C.c_void_p, _P(MulDesc), C.c_int, _P(C.c_void_p)]),
     "ruyb200_plan_run": (C.c_int, [C.c_void_p]),

@@ -494,7 +494,8 @@ int choose_kernel(const ruyb200_ctx* ctx, const ruyb200_mul_desc& d) {
   return RUYB200_KERNEL_GENERIC;
 }
 
-int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous) {
+int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, void* const* mirrors = nullptr,
+            int n_mirrors = 0) {
   int rc = validate_desc(desc);
   if (rc) return rc;
   const ruyb200_mul_desc& d = *desc;
@@ -523,6 +524,9 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous) {
   }
   if (kernel == RUYB200_KERNEL_SGEMM && !is_float) kernel = RUYB200_KERNEL_GENERIC;
   const bool tc = kernel == RUYB200_KERNEL_TC_I8;
+  if (n_mirrors > 0 && (!tc || !dst_on_device || n_mirrors > 7)) {
+    return fail(RUYB200_ERR_UNSUPPORTED, "mirrored destinations need 8-bit operands, a device destination and at most 7 mirrors");
+  }
 
   // ruy/create_trmul_params.h:294-319: ruy re-allocates per-channel buffers that are shorter
   // than the padded width and says so; here nothing is read past the logical size, the
@@ -634,6 +638,8 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous) {
     L.status = ctx->d_status;
     L.allow_pair = !ctx->no_pair;
     L.fuse_sums_m = true;
+    L.n_mirrors = n_mirrors;
+    for (int i = 0; i < 7; i++) L.mirrors[i] = i < n_mirrors ? mirrors[i] : nullptr;
     ce = launch_tc_i8(L, ctx->stream);
   } else if (kernel == RUYB200_KERNEL_SGEMM) {
     ce = launch_sgemm(r.m_side, r.n_side, r.dst, r.ep, ctx->stream);
@@ -814,6 +820,12 @@ int ruyb200_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc) {
 int ruyb200_mul_async(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc) {
   if (!ctx) return fail(RUYB200_ERR_INVALID, "null context");
   return run_mul(ctx, desc, false);
+}
+
+int ruyb200_mul_async_mirrored(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, void* const* mirror_dst, int n_mirrors) {
+  if (!ctx) return fail(RUYB200_ERR_INVALID, "null context");
+  if (n_mirrors < 0 || (n_mirrors > 0 && !mirror_dst)) return fail(RUYB200_ERR_INVALID, "bad mirror list");
+  return run_mul(ctx, desc, false, mirror_dst, n_mirrors);
 }
 
 int ruyb200_pack(ruyb200_ctx* ctx, const ruyb200_matrix* src, int side, void* packed, size_t packed_capacity,

@@ -138,6 +138,8 @@ struct TcI8Launch {
   int sm_count;
   int* status;
   bool allow_pair;   // permit the two-CTA (cta_group::2) variant
+  void* mirrors[7];  // addresses in peers' buffers that correspond to dst.data; every destination store is repeated there
+  int n_mirrors;
   bool fuse_sums_m;  // if ep.zp_n != 0 and ep.sums_m == nullptr, let the kernel produce the m-side sums itself
 };
 cudaError_t launch_tc_i8(const TcI8Launch& args, cudaStream_t stream);

@@ -183,6 +183,7 @@ extern "C" int ruyb200_mul_noalloc(const ruyb200_mul_desc* desc, void* cuda_stre
   L.status = status;
   L.allow_pair = true;
   L.fuse_sums_m = false;
+  L.n_mirrors = 0;
   ce = launch_tc_i8(L, stream);
   if (ce != cudaSuccess) return ctx_fail(RUYB200_ERR_CUDA, cudaGetErrorString(ce));
 

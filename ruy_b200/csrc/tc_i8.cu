@@ -38,11 +38,14 @@ constexpr int kStages = 4;
 constexpr int kABytes = kBlockM * kBlockKBytes;        // 16 KiB
 constexpr int kBBytes = kMaxBlockN * kBlockKBytes;     // 32 KiB
 constexpr int kStageBytes = kABytes + kBBytes;         // 48 KiB
-constexpr int kSmemBytes = kStages * kStageBytes + 1024;  // + alignment slack
+// staging area used when the destination is mirrored into peers' memory: 128 rows x 128 bytes, pitch 144
+constexpr int kMirrorPitch = 144;
+constexpr int kMirrorStagingBytes = 128 * kMirrorPitch;
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 + kMirrorStagingBytes;  // + alignment slack
 // two-CTA variant: each CTA stages 128 rows of each operand per stage
 constexpr int kPairStages = 6;
 constexpr int kPairStageBytes = kABytes + 128 * kBlockKBytes;   // 32 KiB
-constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + 1024;
+constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + 1024 + kMirrorStagingBytes;
 constexpr int kEpilogueWarps = 8;
 constexpr int kEpilogueGroups = kEpilogueWarps / 4;   // a group covers the four TMEM lane quarters and drains whole tiles
 constexpr int kThreads = 64 + 32 * kEpilogueWarps;   // producer warp + MMA warp + epilogue warps
@@ -69,6 +72,8 @@ struct KernelArgs {
   int sums_col;    // >= 0: accumulator column that receives sum_k of the m-side row (an all-ones row of the n operand); -1: none
   int mma_n;       // N of the MMA: block_n, plus 16 when the sums column is appended
   int* status;
+  void* mirror[7]; // peers' copies of the destination: same layout, every store is repeated there
+  int n_mirror;
   int debug;       // profiling knobs (0 in production): 1 = epilogue skips its math and stores, 2 = producer skips the loads
 };
 
@@ -291,8 +296,8 @@ struct NTerms {
 
 // Narrow and store 32 consecutive destination elements n0..n0+31 of row m.
 template <int kDstBytes>
-__device__ __forceinline__ void store_run32(const KernelArgs& a, int m, int n0, int n_end, const int32_t* v) {
-  char* base = (char*)a.dst.data + ((int64_t)m * a.dst.stride_m + n0) * kDstBytes;
+__device__ __forceinline__ void store_run32_at(char* dst_base, const KernelArgs& a, int m, int n0, int n_end, const int32_t* v) {
+  char* base = dst_base + ((int64_t)m * a.dst.stride_m + n0) * kDstBytes;
   const bool full = n0 + 32 <= n_end;   // n_end: end of this tile's columns (and of the destination)
   if (full && (((uintptr_t)base) & 15) == 0) {
     uint4* out = (uint4*)base;
@@ -323,9 +328,19 @@ __device__ __forceinline__ void store_run32(const KernelArgs& a, int m, int n0, 
     }
     return;
   }
+  DstView d = a.dst;
+  d.data = dst_base;
   for (int q = 0; q < 32; q++) {
-    if (n0 + q < n_end) store_int(a.dst, a.ep.dst_dtype, m, n0 + q, v[q]);
+    if (n0 + q < n_end) store_int(d, a.ep.dst_dtype, m, n0 + q, v[q]);
   }
+}
+
+// Narrow and store 32 consecutive destination elements n0..n0+31 of row m: locally and, when the destination is
+// mirrored into peer GPUs' memory, at the same place of every mirror.
+template <int kDstBytes>
+__device__ __forceinline__ void store_run32(const KernelArgs& a, int m, int n0, int n_end, const int32_t* v) {
+  store_run32_at<kDstBytes>((char*)a.dst.data, a, m, n0, n_end, v);
+  for (int i = 0; i < a.n_mirror; i++) store_run32_at<kDstBytes>((char*)a.mirror[i], a, m, n0, n_end, v);
 }
 
 // ---- helpers for the two-CTA (cta_group::2) variant -------------------------------------------
@@ -689,40 +704,96 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
       const bool mul_varies_with_n = ch_n && (ep.mfp_pc != nullptr || ep.mexp_pc != nullptr);
       const int sh_c = 31 - exp_m;
       const long long rnd_c = 1ll << (sh_c - 1);
-      for (int c = c_first; c < args.block_n; c += c_step) {
-        const int n0 = tn * args.block_n + c;
-        if (n0 >= args.size_n || (args.debug & 1)) break;   // uniform across the warp
-        if (c != c_first) {
-          tmem_ld_32(taddr + c, r);
-          tmem_ld_wait();
-        }
-        if (m_ok) {
-          int32_t v[32];
-          if (kDstBytes != 4 && !kX86 && !mul_varies_with_n) {
+      // bias / zero-point terms, fixed-point multiplier, destination zero point and clamp for the 32 accumulators in r[]
+      auto finish_chunk = [&](int c, int32_t (&v)[32]) {
+        if (kDstBytes != 4 && !kX86 && !mul_varies_with_n) {
 #pragma unroll
-            for (int q = 0; q < 32; q++) {
-              const int32_t x = (int32_t)(r[q] + (uint32_t)nt[c + q].add + (uint32_t)add_m);
-              const int32_t y = (int32_t)(((long long)x * (long long)mul_m + rnd_c) >> sh_c);
-              v[q] = max(min((int32_t)((uint32_t)y + (uint32_t)ep.dst_zp), ep.clamp_max), ep.clamp_min);
+          for (int q = 0; q < 32; q++) {
+            const int32_t x = (int32_t)(r[q] + (uint32_t)nt[c + q].add + (uint32_t)add_m);
+            const int32_t y = (int32_t)(((long long)x * (long long)mul_m + rnd_c) >> sh_c);
+            v[q] = max(min((int32_t)((uint32_t)y + (uint32_t)ep.dst_zp), ep.clamp_max), ep.clamp_min);
+          }
+        } else {
+#pragma unroll
+          for (int q = 0; q < 32; q++) {
+            const NTerms t = nt[c + q];
+            int32_t x = (int32_t)(r[q] + (uint32_t)t.add + (uint32_t)add_m);
+            if (kDstBytes != 4) {
+              const int32_t mul = ch_n ? t.mul : mul_m;
+              const int e = ch_n ? t.exp : exp_m;
+              x = kX86 ? requant_x86(x, mul, e) : requant_reference(x, mul, e);
+              x = (int32_t)((uint32_t)x + (uint32_t)ep.dst_zp);
+              x = max(min(x, ep.clamp_max), ep.clamp_min);
+            } else {
+              x = (int32_t)((uint32_t)x + (uint32_t)ep.dst_zp);
             }
-          } else {
+            v[q] = x;
+          }
+        }
+      };
+      if (kDstBytes == 1 && args.n_mirror > 0 && groups == 1) {
+        // Mirrored 8-bit destination.  A thread owns 32 bytes of one destination column; written directly, a warp's
+        // store would be 32 separate 32-byte pieces, which NVLink moves poorly.  So the tile is staged through
+        // shared memory 128 columns at a time and written out with every warp instruction covering 128 contiguous
+        // bytes, locally and to every peer.
+        uint8_t* stg = smem + kNumStages * kStageSize;
+        const int ml = lane_group * 32 + lane;
+        const int halves = (args.block_n + 127) / 128;
+        for (int h = 0; h < halves; h++) {
+          const int nh0 = tn * args.block_n + h * 128;       // first destination index of this half
+          if (nh0 >= n_end) break;                           // uniform over the CTA
+          for (int j = 0; j < 2; j++) {
+            const int c = h * 128 + j * 64 + c_first;
+            if (c >= args.block_n || tn * args.block_n + c >= args.size_n) continue;   // uniform across the warp
+            if (c != c_first) {
+              tmem_ld_32(taddr + c, r);
+              tmem_ld_wait();
+            }
+            int32_t v[32];
+            finish_chunk(c, v);
+            uint32_t w[8];
 #pragma unroll
-            for (int q = 0; q < 32; q++) {
-              const NTerms t = nt[c + q];
-              int32_t x = (int32_t)(r[q] + (uint32_t)t.add + (uint32_t)add_m);
-              if (kDstBytes != 4) {
-                const int32_t mul = ch_n ? t.mul : mul_m;
-                const int e = ch_n ? t.exp : exp_m;
-                x = kX86 ? requant_x86(x, mul, e) : requant_reference(x, mul, e);
-                x = (int32_t)((uint32_t)x + (uint32_t)ep.dst_zp);
-                x = max(min(x, ep.clamp_max), ep.clamp_min);
-              } else {
-                x = (int32_t)((uint32_t)x + (uint32_t)ep.dst_zp);
+            for (int q = 0; q < 8; q++) {
+              w[q] = (uint32_t)(v[4 * q] & 0xff) | ((uint32_t)(v[4 * q + 1] & 0xff) << 8) |
+                     ((uint32_t)(v[4 * q + 2] & 0xff) << 16) | ((uint32_t)(v[4 * q + 3] & 0xff) << 24);
+            }
+            uint4* sp = reinterpret_cast<uint4*>(stg + ml * kMirrorPitch + (c - h * 128));
+            sp[0] = make_uint4(w[0], w[1], w[2], w[3]);
+            sp[1] = make_uint4(w[4], w[5], w[6], w[7]);
+          }
+          epilogue_all(true, group, group_threads);          // the half tile is staged
+          const int nb = min(128, n_end - nh0);
+          for (int rr = ew; rr < kBlockM; rr += kEpilogueWarps) {
+            const int mm = tm * kUnitM + (int)rank * kBlockM + rr;
+            if (mm >= args.size_m) break;                    // uniform across the warp
+            if (lane * 4 < nb) {
+              const uint32_t val = *reinterpret_cast<const uint32_t*>(stg + rr * kMirrorPitch + lane * 4);
+              const int64_t off = (int64_t)mm * args.dst.stride_m + nh0 + lane * 4;
+              for (int t = -1; t < args.n_mirror; t++) {
+                uint8_t* base = (uint8_t*)(t < 0 ? args.dst.data : args.mirror[t]) + off;
+                if (lane * 4 + 4 <= nb && (((uintptr_t)base) & 3) == 0) {
+                  *reinterpret_cast<uint32_t*>(base) = val;
+                } else {
+                  for (int b = 0; b < 4 && lane * 4 + b < nb; b++) base[b] = (uint8_t)(val >> (8 * b));
+                }
               }
-              v[q] = x;
             }
           }
-          store_run32<kDstBytes>(args, m, n0, n_end, v);
+          epilogue_all(true, group, group_threads);          // the staging area may be overwritten
+        }
+      } else {
+        for (int c = c_first; c < args.block_n; c += c_step) {
+          const int n0 = tn * args.block_n + c;
+          if (n0 >= args.size_n || (args.debug & 1)) break;   // uniform across the warp
+          if (c != c_first) {
+            tmem_ld_32(taddr + c, r);
+            tmem_ld_wait();
+          }
+          if (m_ok) {
+            int32_t v[32];
+            finish_chunk(c, v);
+            store_run32<kDstBytes>(args, m, n0, n_end, v);
+          }
         }
       }
       tc_fence_before();
@@ -886,6 +957,8 @@ cudaError_t launch_tc_i8(const TcI8Launch& L, cudaStream_t stream) {
   a.size_n = L.n_side.width;
   a.depth = L.depth;
   a.status = L.status;
+  a.n_mirror = L.n_mirrors < 0 ? 0 : (L.n_mirrors > 7 ? 7 : L.n_mirrors);
+  for (int i = 0; i < 7; i++) a.mirror[i] = i < a.n_mirror ? L.mirrors[i] : nullptr;
   a.debug = 0;
 #ifdef RUYB200_DEBUG_KNOBS
   if (getenv("RUYB200_DEBUG")) a.debug = atoi(getenv("RUYB200_DEBUG"));
@@ -908,7 +981,7 @@ cudaError_t launch_tc_i8(const TcI8Launch& L, cudaStream_t stream) {
   a.tiles_n = (a.size_n + bn - 1) / bn;
   a.acc_shift = a.mma_n <= 64 ? 3 : (a.mma_n <= 128 ? 2 : 1);
   a.acc_bufs = 1 << a.acc_shift;
-  a.epi_groups = L.depth <= 512 ? 2 : 1;
+  a.epi_groups = (L.depth <= 512 && L.n_mirrors <= 0) ? 2 : 1;
   // instruction descriptor: int32 accumulate, operand signedness, both operands depth-major,
   // N/8 at bit 17, M/16 at bit 24 (M spans both CTAs of a pair)
   a.idesc = (2u << 4) | (fmt_m << 7) | (fmt_n << 10) | ((uint32_t)(a.mma_n >> 3) << 17) | ((uint32_t)(unit_m >> 4) << 24);

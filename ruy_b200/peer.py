@@ -1,0 +1,76 @@
+"""Host side of the mirrored-destination path (see ruyb200_mul_async_mirrored): buffers that every rank of a
+torch.distributed job can store into, and the flag exchange that ends a step.
+
+One process per GPU.  `PeerBuffer(nbytes)` allocates the same-sized buffer on every rank, exchanges the IPC
+handles through the process group (an object all-gather on the host), and maps every peer's buffer into this
+process.  Only stores go to a peer's memory (the kernel's epilogue and the flag writes); nothing loads from it."""
+import ctypes as C
+
+import torch
+import torch.distributed as dist
+
+from . import _abi
+from ._lib import lib
+from .api import _check, make_desc
+
+
+class _RawCuda:
+    def __init__(self, ptr, nbytes):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+
+class PeerBuffer:
+    def __init__(self, nbytes, device):
+        self.rank, self.world = dist.get_rank(), dist.get_world_size()
+        self.nbytes = nbytes
+        p = C.c_void_p()
+        _check(lib().ruyb200_peer_alloc(nbytes, C.byref(p)), "ruyb200_peer_alloc")
+        self.local_ptr = p.value
+        handle = C.create_string_buffer(64)
+        _check(lib().ruyb200_peer_export(self.local_ptr, handle), "ruyb200_peer_export")
+        handles = [None] * self.world
+        dist.all_gather_object(handles, handle.raw)
+        self.ptrs = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                self.ptrs.append(self.local_ptr)
+            else:
+                q = C.c_void_p()
+                _check(lib().ruyb200_peer_open(h, C.byref(q)), "ruyb200_peer_open")
+                self.ptrs.append(q.value)
+        self.tensor = torch.as_tensor(_RawCuda(self.local_ptr, nbytes), device=device)   # uint8 view of the local buffer
+
+    def close(self):
+        torch.cuda.synchronize()
+        dist.barrier()
+        for r, p in enumerate(self.ptrs):
+            if r != self.rank and p:
+                lib().ruyb200_peer_close(p)
+        dist.barrier()
+        if self.local_ptr:
+            lib().ruyb200_peer_free(self.local_ptr)
+            self.local_ptr = None
+
+
+class StepFlags:
+    """flags[r] on every rank is raised by rank r at the end of its step; a rank's step is over when all are up."""
+
+    def __init__(self, device):
+        self.buf = PeerBuffer(256, device)
+        w, r = self.buf.world, self.buf.rank
+        targets = torch.tensor([p + 4 * r for p in self.buf.ptrs], dtype=torch.int64, device=device)
+        self.targets = targets          # device array of addresses: flags[r] in every rank's buffer (own included)
+        self.world = w
+
+    def signal_and_wait(self, ctx, value):
+        _check(lib().ruyb200_peer_signal(ctx._h, C.c_void_p(self.targets.data_ptr()), self.world, value), "ruyb200_peer_signal")
+        _check(lib().ruyb200_peer_wait(ctx._h, C.c_void_p(self.buf.local_ptr), self.world, value), "ruyb200_peer_wait")
+
+    def close(self):
+        self.buf.close()
+
+
+def mul_async_mirrored(lhs, rhs, mul_params, context, dst, mirror_ptrs):
+    d = make_desc(lhs, rhs, mul_params, dst)
+    arr = (C.c_void_p * max(1, len(mirror_ptrs)))(*mirror_ptrs)
+    _check(lib().ruyb200_mul_async_mirrored(context._h, C.byref(d), arr, len(mirror_ptrs)), "ruyb200_mul_async_mirrored")

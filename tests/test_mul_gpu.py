@@ -440,6 +440,40 @@ def test_config2_plan(gpu_ctx):
     plan.close()
 
 
+def test_mirrored_destination_and_step_flags(gpu_ctx):
+    """ruyb200_mul_async_mirrored on one GPU: the mirrors are two more buffers on the same device, so they must end
+    up byte-identical to the destination (one-CTA and two-CTA tiles, ragged edges).  The flag pair is exercised in
+    stream order: the signal precedes the wait, which therefore returns at once (a peer that never signals is a
+    host-side concern and is not provoked on a GPU)."""
+    import ctypes as C
+    from ruy_b200 import peer
+    from ruy_b200._lib import lib
+    dev = torch.device("cuda", 0)
+    for shape in ((300, 208, 700), (64, 96, 40)):
+        c = cases.random_case(*shape, "uint8", "int8", "uint8", orders="RCC", perchannel=True, symmetric=False, seed=77)
+        want = util.run_oracle(c, Rounding.kReference)
+        bufs = [torch.full((c.dst_storage_elems(),), 9, dtype=torch.uint8, device=dev) for _ in range(3)]
+        lhs, rhs, p, d, keep = c.bind(bufs[0], device=dev, rounding=Rounding.kReference)
+        torch.cuda.synchronize()
+        peer.mul_async_mirrored(lhs, rhs, p, gpu_ctx, d, [bufs[1].data_ptr(), bufs[2].data_ptr()])
+        gpu_ctx.sync()
+        for b in bufs:
+            assert np.array_equal(c.dst_view(b.cpu().numpy()), want)
+    flag_words = torch.zeros(8, dtype=torch.int32, device=dev)
+    targets = torch.tensor([flag_words.data_ptr(), flag_words.data_ptr() + 4], dtype=torch.int64, device=dev)
+    torch.cuda.synchronize()
+    assert lib().ruyb200_peer_signal(gpu_ctx._h, C.c_void_p(targets.data_ptr()), 2, 5) == 0
+    assert lib().ruyb200_peer_wait(gpu_ctx._h, C.c_void_p(flag_words.data_ptr()), 2, 5) == 0
+    gpu_ctx.sync()
+    assert flag_words.cpu().tolist()[:3] == [5, 5, 0]
+    # float muls cannot be mirrored
+    fc = cases.config1((50, 50, 50))
+    dst = torch.zeros(fc.dst_storage_elems(), dtype=torch.float32, device=dev)
+    lhs, rhs, p, d, keep = fc.bind(dst, device=dev)
+    with pytest.raises(ruy_b200.RuyError):
+        peer.mul_async_mirrored(lhs, rhs, p, gpu_ctx, d, [dst.data_ptr()])
+
+
 def test_plan_mixed_items(gpu_ctx):
     """A plan with every kind of item: asymmetric uint8 (both zero-point sums computed while packing), int16 and
     int32 destinations, row-major destinations, per-column channels, depths that are not multiples of 8 or 32,
