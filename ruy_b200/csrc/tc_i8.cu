@@ -74,6 +74,7 @@ struct KernelArgs {
   int* status;
   void* mirror[7]; // peers' copies of the destination: same layout, every store is repeated there
   int n_mirror;
+  int mirror_wide; // every destination base and the destination stride are multiples of 16 bytes
   int debug;       // profiling knobs (0 in production): 1 = epilogue skips its math and stores, 2 = producer skips the loads
 };
 
@@ -763,18 +764,40 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
           }
           epilogue_all(true, group, group_threads);          // the half tile is staged
           const int nb = min(128, n_end - nh0);
-          for (int rr = ew; rr < kBlockM; rr += kEpilogueWarps) {
-            const int mm = tm * kUnitM + (int)rank * kBlockM + rr;
-            if (mm >= args.size_m) break;                    // uniform across the warp
-            if (lane * 4 < nb) {
-              const uint32_t val = *reinterpret_cast<const uint32_t*>(stg + rr * kMirrorPitch + lane * 4);
-              const int64_t off = (int64_t)mm * args.dst.stride_m + nh0 + lane * 4;
-              for (int t = -1; t < args.n_mirror; t++) {
-                uint8_t* base = (uint8_t*)(t < 0 ? args.dst.data : args.mirror[t]) + off;
-                if (lane * 4 + 4 <= nb && (((uintptr_t)base) & 3) == 0) {
-                  *reinterpret_cast<uint32_t*>(base) = val;
-                } else {
-                  for (int b = 0; b < 4 && lane * 4 + b < nb; b++) base[b] = (uint8_t)(val >> (8 * b));
+          if (args.mirror_wide && (nb & 15) == 0) {
+            // 16 bytes per lane: one warp instruction moves four rows of 128 bytes
+            const int c16 = (lane & 7) * 16;
+            int rr = ew * 4 + (lane >> 3);
+            int mm = tm * kUnitM + (int)rank * kBlockM + rr;
+            int64_t off = (int64_t)mm * args.dst.stride_m + nh0 + c16;
+            const uint8_t* sp = stg + rr * kMirrorPitch + c16;
+            if (c16 < nb) {
+#pragma unroll
+              for (int it = 0; it < kBlockM / (4 * kEpilogueWarps); it++) {
+                if (mm < args.size_m) {
+                  const uint4 val = *reinterpret_cast<const uint4*>(sp);
+                  *reinterpret_cast<uint4*>((uint8_t*)args.dst.data + off) = val;
+                  for (int t = 0; t < args.n_mirror; t++) *reinterpret_cast<uint4*>((uint8_t*)args.mirror[t] + off) = val;
+                }
+                mm += 4 * kEpilogueWarps;
+                off += (int64_t)(4 * kEpilogueWarps) * args.dst.stride_m;
+                sp += 4 * kEpilogueWarps * kMirrorPitch;
+              }
+            }
+          } else {
+            for (int rr = ew; rr < kBlockM; rr += kEpilogueWarps) {
+              const int mm = tm * kUnitM + (int)rank * kBlockM + rr;
+              if (mm >= args.size_m) break;                    // uniform across the warp
+              if (lane * 4 < nb) {
+                const uint32_t val = *reinterpret_cast<const uint32_t*>(stg + rr * kMirrorPitch + lane * 4);
+                const int64_t off = (int64_t)mm * args.dst.stride_m + nh0 + lane * 4;
+                for (int t = -1; t < args.n_mirror; t++) {
+                  uint8_t* base = (uint8_t*)(t < 0 ? args.dst.data : args.mirror[t]) + off;
+                  if (lane * 4 + 4 <= nb && (((uintptr_t)base) & 3) == 0) {
+                    *reinterpret_cast<uint32_t*>(base) = val;
+                  } else {
+                    for (int b = 0; b < 4 && lane * 4 + b < nb; b++) base[b] = (uint8_t)(val >> (8 * b));
+                  }
                 }
               }
             }
@@ -959,6 +982,8 @@ cudaError_t launch_tc_i8(const TcI8Launch& L, cudaStream_t stream) {
   a.status = L.status;
   a.n_mirror = L.n_mirrors < 0 ? 0 : (L.n_mirrors > 7 ? 7 : L.n_mirrors);
   for (int i = 0; i < 7; i++) a.mirror[i] = i < a.n_mirror ? L.mirrors[i] : nullptr;
+  a.mirror_wide = (((uintptr_t)L.dst.data | (uintptr_t)L.dst.stride_m) & 15) == 0;
+  for (int i = 0; i < a.n_mirror; i++) a.mirror_wide = a.mirror_wide && ((uintptr_t)L.mirrors[i] & 15) == 0;
   a.debug = 0;
 #ifdef RUYB200_DEBUG_KNOBS
   if (getenv("RUYB200_DEBUG")) a.debug = atoi(getenv("RUYB200_DEBUG"));

@@ -449,8 +449,10 @@ def test_mirrored_destination_and_step_flags(gpu_ctx):
     from ruy_b200 import peer
     from ruy_b200._lib import lib
     dev = torch.device("cuda", 0)
-    for shape in ((300, 208, 700), (64, 96, 40)):
-        c = cases.random_case(*shape, "uint8", "int8", "uint8", orders="RCC", perchannel=True, symmetric=False, seed=77)
+    # destination strides that are / are not multiples of 16 bytes, ragged ends in both dimensions
+    for shape, extra in (((300, 208, 700), 0), ((64, 96, 40), 0), ((512, 128, 520), 0), ((300, 60, 270), 4)):
+        c = cases.random_case(*shape, "uint8", "int8", "uint8", orders="RCC", perchannel=True, symmetric=False, seed=77,
+                              extra_stride=extra)
         want = util.run_oracle(c, Rounding.kReference)
         bufs = [torch.full((c.dst_storage_elems(),), 9, dtype=torch.uint8, device=dev) for _ in range(3)]
         lhs, rhs, p, d, keep = c.bind(bufs[0], device=dev, rounding=Rounding.kReference)
