@@ -890,6 +890,7 @@ int ctx_plan_item(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, BatchItem* out
   DeviceGuard guard(ctx->device);
   const int depth = d.lhs.cols;
   SideView views[2];
+  const int32_t* cached_sums[2] = {nullptr, nullptr};
   const ruyb200_matrix* mats[2] = {&d.lhs, &d.rhs};
   for (int side = 0; side < 2; side++) {
     const ruyb200_matrix& m = *mats[side];
@@ -899,6 +900,7 @@ int ctx_plan_item(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, BatchItem* out
       ctx->arena.reset(false);
       int rc = prepare_side(ctx, m, side, depth, true, false, true, &views[side], &sums);
       if (rc) return rc;
+      cached_sums[side] = sums;
       SideView src = side_view(m, side, m.data);
       CacheKey key(m.data, src.width, depth, src.stride_w, src.stride_k, m.zero_point, (int)m.dtype, side);
       auto it = ctx->cache.find(key);
@@ -943,6 +945,16 @@ int ctx_plan_item(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, BatchItem* out
   if (ns.dtype == RUYB200_I8) flags |= kItemNSigned;
   if (ctx_rounding_is_x86(ctx, d.params.rounding_mode)) flags |= kItemX86;
   flags |= (uint32_t)d.dst.dtype << kItemDstShift;
+  // the cache's sums stay valid as long as the entry is pinned by the plan
+  out->sums_m = ns.zero_point != 0 ? cached_sums[dst_col_major ? 0 : 1] : nullptr;
+  auto tma_ok = [](const SideView& v) { return (((uintptr_t)v.data | (uintptr_t)v.stride_w) & 15) == 0; };
+  if (tma_ok(ms)) flags |= kItemMTma;
+  if (tma_ok(ns)) flags |= kItemNTma;
+  const int nch = channel_on_m ? ms.width : ns.width;
+  bool vec_bulk = (nch & 3) == 0 && (ms.width & 3) == 0;
+  const void* vec_ptrs[4] = {out->bias, out->mfp_pc, out->mexp_pc, out->sums_m};
+  for (const void* p : vec_ptrs) vec_bulk = vec_bulk && ((uintptr_t)p & 15) == 0;
+  if (vec_bulk) flags |= kItemVecBulk;
   out->flags = flags;
   *fits = true;
   return RUYB200_OK;

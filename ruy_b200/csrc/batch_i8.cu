@@ -5,14 +5,16 @@
 // Every SM runs one persistent CTA that walks a static, size-balanced list of items through a ring of
 // shared-memory slots:
 //
-//   * warps 0-5  : pack (ruy/pack.h:105-132).  Each warp owns one slot and one item at a time: it issues
-//                  asynchronous copies (cp.async, 8 or 16 bytes each, never waiting for them) that take
-//                  both operands from HBM straight into the slot in the tensor core's depth-major
-//                  core-matrix layout, zero-filling depth up to a multiple of 32, plus the item's
-//                  per-channel vectors.  Six whole items are in flight per SM, which is what keeps
-//                  enough bytes outstanding to use the HBM bandwidth.
-//   * warp 6     : one elected lane issues the item's tcgen05.mma kind::i8 (M=128, N<=128, K=32) into one
-//                  of four tensor-memory accumulators.
+//   * warps 0-5  : pack (ruy/pack.h:105-132).  Each warp owns one slot and one item at a time and never waits
+//                  for its copies.  An operand whose rows are 16-byte aligned is fetched by ONE tensor-map
+//                  copy (the plan holds a map per operand) that lands as 128-byte rows with the 128-byte
+//                  swizzle, zero-filled past depth; any other operand is scattered by cp.async (8 or 16
+//                  bytes each) into the unswizzled core-matrix layout.  The per-channel vectors and the
+//                  cached zero-point sums ride along as bulk copies (or cp.async).  Six whole items are in
+//                  flight per SM, which is what keeps enough bytes outstanding to use the HBM bandwidth.
+//   * warps 6-7  : alternate items; one elected lane issues the item's tcgen05.mma kind::i8 (M=128, N<=128,
+//                  K=32) into one of four tensor-memory accumulators, from descriptors the pack warp left
+//                  in the slot.
 //   * warps 8-23 : epilogue, four groups of four warps; group g drains accumulator g.  Zero-point sums
 //                  are taken from the packed tile, per-column terms are staged in shared memory, then
 //                  tcgen05.ld, bias, zero-point terms, fixed-point multiplier, zero point, clamp
@@ -42,11 +44,18 @@ constexpr int kTmemCols = 512;                     // allocation must be a power
 constexpr int kPackWarps = kSlots;
 constexpr int kEpiGroups = kAccBuffers;
 constexpr int kEpiWarps = 4 * kEpiGroups;         // each group covers the four TMEM lane quarters
-constexpr int kMmaWarp = kPackWarps;
+constexpr int kMmaWarp = kPackWarps;                // warps 6 and 7 issue the MMAs of alternate items
+constexpr int kMmaWarps = 2;
 constexpr int kFirstEpiWarp = 8;                  // a multiple of 4, so that (warp % 4) is the lane quarter within a group
 constexpr int kThreads = 32 * (kFirstEpiWarp + kEpiWarps);
 constexpr int kSmemBytes = kSlots * kSlotBytes + 1024;
-constexpr uint32_t kSpinLimit = 4u << 20;
+constexpr uint32_t kSpinLimit = 1u << 19;
+
+// What the MMA warp needs for one item, prepared by the pack warp: descriptor halves and K steps of both tiles.
+struct alignas(16) MmaCmd {
+  uint32_t lo_m, hi_m, lo_n, hi_n;
+  uint32_t kstep_m, kstep_n, idesc, nk_fence;   // nk_fence: K=32 steps, bit 31 = a tile was written by cp.async
+};
 
 struct NTerm {
   int32_t add;
@@ -63,28 +72,29 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One potentially blocking probe: the hardware suspends the thread until the phase completes or about
+// kSuspendNs have passed, so a waiting warp issues almost nothing while it waits.
+constexpr uint32_t kSuspendNs = 4000;
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendNs)
       : "memory");
   return ok != 0;
 }
-// Bounded wait by one lane, result broadcast to the (converged) warp.
+// Bounded wait by one lane (kSpinLimit probes of up to kSuspendNs each: about two seconds), result broadcast
+// to the (converged) warp.
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   int ok = 1;
   if ((threadIdx.x & 31) == 0) {
     ok = 0;
     for (uint32_t i = 0; i < kSpinLimit; i++) {
       if (mbar_try_wait(bar, parity)) { ok = 1; break; }
-      if (i >= 64) {
-        if (*abort_flag) break;
-        __nanosleep(64);
-      }
+      if (*abort_flag) break;
     }
   }
   return __shfl_sync(0xffffffffu, ok, 0) != 0;
@@ -124,19 +134,53 @@ __device__ __forceinline__ bool group_all(bool ok, int group) {
   return res != 0;
 }
 
-// One K=32 MMA on core-matrix (no swizzle) depth-major tiles: 8 rows x 16 bytes per core matrix, the two
-// 16-byte depth chunks of an MMA 128 bytes apart (leading byte offset), 8-row groups `sbo` bytes apart.
-__device__ __forceinline__ void mma_i8_nosw(uint32_t tmem_d, uint32_t addr_a, uint32_t addr_b, uint32_t sbo, uint32_t idesc,
-                                            uint32_t accumulate) {
-  const uint32_t hi = (sbo >> 4) | (1u << 14);   // stride byte offset at bits 32..45, descriptor version 1 at bit 46
-  const uint32_t lo_a = ((addr_a & 0x3FFFF) >> 4) | ((128u >> 4) << 16);
-  const uint32_t lo_b = ((addr_b & 0x3FFFF) >> 4) | ((128u >> 4) << 16);
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_load_tile(uint32_t smem_dst, const CUtensorMap* map, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %2}], [%3];"
+      ::"r"(smem_dst), "l"(map), "r"(0), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void prefetch_map(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+// Untiled bulk copy global -> shared; both addresses 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_load(uint32_t smem_dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_dst), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+// Shared-memory matrix descriptor halves for the two tile layouts.  Swizzled rows of 128 bytes: 8-row groups
+// 1024 bytes apart, swizzle mode 2 at bits 61..63, one K=32 step = 32 bytes.  Unswizzled core matrices (8 rows x
+// 16 bytes): the two 16-byte depth chunks of an MMA 128 bytes apart (leading byte offset), 8-row groups `sbo`
+// bytes apart, one K=32 step = 256 bytes.  Version 1 at bit 46 in both.
+struct TileDesc {
+  uint32_t lo, hi, kstep;
+};
+__device__ __forceinline__ TileDesc tile_desc(bool swizzled, uint32_t addr, uint32_t sbo) {
+  TileDesc d;
+  if (swizzled) {
+    d.lo = ((addr & 0x3FFFF) >> 4) | (1u << 16);
+    d.hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+    d.kstep = 32 >> 4;
+  } else {
+    d.lo = ((addr & 0x3FFFF) >> 4) | ((128u >> 4) << 16);
+    d.hi = (sbo >> 4) | (1u << 14);
+    d.kstep = 256 >> 4;
+  }
+  return d;
+}
+__device__ __forceinline__ void mma_i8(uint32_t tmem_d, uint32_t lo_a, uint32_t hi_a, uint32_t lo_b, uint32_t hi_b, uint32_t idesc,
+                                       uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
       "setp.ne.u32 p, %4, 0;\n\t"
-      "mov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %5};\n\t"
+      "mov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %6};\n\t"
       "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %3, p;\n\t}"
-      ::"r"(tmem_d), "r"(lo_a), "r"(lo_b), "r"(idesc), "r"(accumulate), "r"(hi)
+      ::"r"(tmem_d), "r"(lo_a), "r"(lo_b), "r"(idesc), "r"(accumulate), "r"(hi_a), "r"(hi_b)
       : "memory");
 }
 
@@ -197,6 +241,27 @@ __device__ __forceinline__ int32_t tile_row_sum(const uint8_t* tile, int tr, int
   return s;
 }
 
+// The same for a swizzled tile: row tr is 128 bytes at tr * 128, its 16-byte chunk c stored at position c ^ (tr & 7).
+__device__ __forceinline__ int32_t tile_row_sum_swizzled(const uint8_t* tile, int tr, int kpad, bool is_signed) {
+  const uint8_t* p = tile + tr * 128;
+  int s = 0;
+  for (int q = 0; q < (kpad >> 4); q++) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p + ((q ^ (tr & 7)) << 4));
+    if (is_signed) {
+      s = __dp4a((int)v.x, 0x01010101, s);
+      s = __dp4a((int)v.y, 0x01010101, s);
+      s = __dp4a((int)v.z, 0x01010101, s);
+      s = __dp4a((int)v.w, 0x01010101, s);
+    } else {
+      s = (int)__dp4a(v.x, 0x01010101u, (unsigned)s);
+      s = (int)__dp4a(v.y, 0x01010101u, (unsigned)s);
+      s = (int)__dp4a(v.z, 0x01010101u, (unsigned)s);
+      s = (int)__dp4a(v.w, 0x01010101u, (unsigned)s);
+    }
+  }
+  return s;
+}
+
 // Requantize with per-call constants hoisted: rnd = 2^(30-e) (64 bit), sh = 31-e.
 __device__ __forceinline__ int32_t requant_ref_fast(int32_t x, int32_t mul, long long rnd, int sh) {
   const long long p = (long long)x * (long long)mul + rnd;
@@ -204,14 +269,15 @@ __device__ __forceinline__ int32_t requant_ref_fast(int32_t x, int32_t mul, long
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
-batch_i8_kernel(const BatchItem* __restrict__ items, int num_items, int* status) {
+batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restrict__ maps, int num_items, int* status) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kSlots];     // packed data of a slot is in place
   __shared__ __align__(8) uint64_t empty_bar[kSlots];    // MMAs have read the slot and the epilogue has read its header
   __shared__ __align__(8) uint64_t acc_full_bar[kAccBuffers];
   __shared__ __align__(8) uint64_t acc_empty_bar[kAccBuffers];
   __shared__ __align__(16) BatchItem slot_item[kSlots];
-  __shared__ __align__(16) int32_t slot_vec[kSlots][3][128];   // the item's bias / multiplier / exponent vectors
+  __shared__ MmaCmd slot_cmd[kSlots];
+  __shared__ __align__(16) int32_t slot_vec[kSlots][4][128];   // the item's bias / multiplier / exponent vectors and cached m-side sums
   __shared__ __align__(16) NTerm n_terms[kAccBuffers][kAccCols];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
@@ -258,7 +324,8 @@ batch_i8_kernel(const BatchItem* __restrict__ items, int num_items, int* status)
     const bool piece_lane = lane < (int)(sizeof(BatchItem) / 16);
     if (s < my_count && piece_lane) next_piece = reinterpret_cast<const uint4*>(items + blockIdx.x + s * gridDim.x)[lane];
 #ifdef RUYB200_DEBUG_KNOBS
-    long long dbg_wait = 0, dbg_work = 0, dbg_t0 = clock64();
+    long long dbg_wait = 0, dbg_work = 0, dbg_tma = 0, dbg_scatter = 0, dbg_t0 = clock64();
+    int dbg_ntma = 0;
 #endif
     for (int k = s; k < my_count; k += kSlots, ph ^= 1) {
       const uint4 piece = next_piece;
@@ -286,48 +353,90 @@ batch_i8_kernel(const BatchItem* __restrict__ items, int num_items, int* status)
       const uint8_t* n_ptr = item.n_ptr;
       const int size_m = item.size_m, size_n = item.size_n, depth = item.depth, stride_m = item.stride_m,
                 stride_n = item.stride_n, m_off = item.m_off;
-      if ((((uintptr_t)m_ptr | (uint32_t)stride_m) & 15) == 0) {
+      const uint32_t flags = item.flags;
+      const CUtensorMap* item_maps = maps + 2 * (size_t)(blockIdx.x + k * gridDim.x);
+      uint32_t tx = 0;     // bytes the bulk / tensor copies will report on full_bar[s] (the same value in every lane)
+#ifdef RUYB200_DEBUG_KNOBS
+      long long dbg_c = clock64();
+#endif
+      if (flags & kItemMTma) {
+        if (lane == 0) tma_load_tile(tile_m + (uint32_t)m_off * 128, item_maps, &full_bar[s]);
+        tx += 128u * (uint32_t)((size_m + 7) & ~7);
+      } else if ((((uintptr_t)m_ptr | (uint32_t)stride_m) & 15) == 0) {
         issue_pack<16>(m_ptr, size_m, depth, stride_m, kpad, tile_m, m_off, lane);
       } else {
         issue_pack<8>(m_ptr, size_m, depth, stride_m, kpad, tile_m, m_off, lane);
       }
-      if ((((uintptr_t)n_ptr | (uint32_t)stride_n) & 15) == 0) {
+      if (flags & kItemNTma) {
+        if (lane == 0) tma_load_tile(tile_n, item_maps + 1, &full_bar[s]);
+        tx += 128u * (uint32_t)((size_n + 15) & ~15);
+      } else if ((((uintptr_t)n_ptr | (uint32_t)stride_n) & 15) == 0) {
         issue_pack<16>(n_ptr, size_n, depth, stride_n, kpad, tile_n, 0, lane);
       } else {
         issue_pack<8>(n_ptr, size_n, depth, stride_n, kpad, tile_n, 0, lane);
       }
-      // per-channel vectors (indexed along m or along n) ride along
-      const int nch = (item.flags & kItemChannelOnN) ? size_n : size_m;
-      const int32_t* vecs[3] = {item.bias, item.mfp_pc, item.mexp_pc};
-#pragma unroll
-      for (int v = 0; v < 3; v++) {
-        if (vecs[v]) {
-          for (int i = lane; i < nch; i += 32) cp_async_zfill<4>(smem_u32(&slot_vec[s][v][i]), vecs[v] + i, 4);
-        }
+#ifdef RUYB200_DEBUG_KNOBS
+      if ((flags & (kItemMTma | kItemNTma)) == (kItemMTma | kItemNTma)) { dbg_tma += clock64() - dbg_c; dbg_ntma++; }
+      else { dbg_scatter += clock64() - dbg_c; }
+#endif
+      // the next item's maps are on their way while this one's data moves
+      if (k + kSlots < my_count && lane < 2) prefetch_map(item_maps + 2 * (size_t)kSlots * gridDim.x + lane);
+      // per-channel vectors (indexed along m or along n) and the cached m-side sums ride along
+      const int nch = (flags & kItemChannelOnN) ? size_n : size_m;
+      const int32_t* v0 = item.bias;
+      const int32_t* v1 = item.mfp_pc;
+      const int32_t* v2 = item.mexp_pc;
+      const int32_t* v3 = item.sums_m;
+      if (flags & kItemVecBulk) {
+        const int32_t* vp = lane == 0 ? v0 : (lane == 1 ? v1 : (lane == 2 ? v2 : v3));
+        const uint32_t vbytes = 4u * (uint32_t)(lane == 3 ? size_m : nch);
+        if (lane < 4 && vp) bulk_load(smem_u32(&slot_vec[s][lane][0]), vp, vbytes, &full_bar[s]);
+        tx += 4u * (uint32_t)nch * ((v0 ? 1u : 0u) + (v1 ? 1u : 0u) + (v2 ? 1u : 0u)) + (v3 ? 4u * (uint32_t)size_m : 0u);
+      } else {
+        if (v0) for (int i = lane; i < nch; i += 32) cp_async_zfill<4>(smem_u32(&slot_vec[s][0][i]), v0 + i, 4);
+        if (v1) for (int i = lane; i < nch; i += 32) cp_async_zfill<4>(smem_u32(&slot_vec[s][1][i]), v1 + i, 4);
+        if (v2) for (int i = lane; i < nch; i += 32) cp_async_zfill<4>(smem_u32(&slot_vec[s][2][i]), v2 + i, 4);
+        if (v3) for (int i = lane; i < size_m; i += 32) cp_async_zfill<4>(smem_u32(&slot_vec[s][3][i]), v3 + i, 4);
       }
-      // full_bar[s] completes when every lane's copies have landed (33 arrivals: 32 deferred ones plus
-      // lane 0's ordinary arrive, which publishes the header written above)
+      // full_bar[s] completes when every lane's cp.async copies have landed (32 deferred arrivals), lane 0 has
+      // arrived (which publishes the header written above) and the bulk / tensor copies have delivered `tx` bytes
       asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&full_bar[s])) : "memory");
+      if (lane == 0) {
+        const uint32_t sbo = (uint32_t)(kpad >> 4) * 128;
+        const TileDesc dm = tile_desc((flags & kItemMTma) != 0, tile_m, sbo);
+        const TileDesc dn = tile_desc((flags & kItemNTma) != 0, tile_n, sbo);
+        MmaCmd cmd;
+        cmd.lo_m = dm.lo; cmd.hi_m = dm.hi; cmd.kstep_m = dm.kstep;
+        cmd.lo_n = dn.lo; cmd.hi_n = dn.hi; cmd.kstep_n = dn.kstep;
+        cmd.idesc = (2u << 4) | ((flags & kItemMSigned ? 1u : 0u) << 7) | ((flags & kItemNSigned ? 1u : 0u) << 10) |
+                    ((uint32_t)(((size_n + 15) & ~15) >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+        cmd.nk_fence = (uint32_t)(kpad >> 5) | (((flags & (kItemMTma | kItemNTma)) != (kItemMTma | kItemNTma)) ? 0x80000000u : 0u);
+        slot_cmd[s] = cmd;
+      }
       __syncwarp();
-      if (lane == 0) mbar_arrive(&full_bar[s]);
+      if (lane == 0) {
+        if (tx) mbar_arrive_expect_tx(&full_bar[s], tx); else mbar_arrive(&full_bar[s]);
+      }
 #ifdef RUYB200_DEBUG_KNOBS
       dbg_work += clock64() - dbg_b;
 #endif
     }
 #ifdef RUYB200_DEBUG_KNOBS
     if (blockIdx.x == 0 && threadIdx.x == 0)
-      printf("pack warp 0: total %lld cycles, waiting for its slot %lld, issuing copies %lld, items %d\n", clock64() - dbg_t0,
-             dbg_wait, dbg_work, (my_count + kSlots - 1) / kSlots);
+      printf("pack warp 0: total %lld cycles, waiting for its slot %lld, issuing copies %lld (operands: %lld in %d items by tensor map, %lld otherwise), items %d\n",
+             clock64() - dbg_t0, dbg_wait, dbg_work, dbg_tma, dbg_ntma, dbg_scatter, (my_count + kSlots - 1) / kSlots);
 #endif
-  } else if (warp == kMmaWarp) {
-    // ---------------- MMA issue ----------------
-    uint32_t s = 0, ph = 0;
+  } else if (warp < kMmaWarp + kMmaWarps) {
+    // ---------------- MMA issue: this warp takes items mw, mw + 2, ... ----------------
+    const int mw = warp - kMmaWarp;
 #ifdef RUYB200_DEBUG_KNOBS
     long long dbg_acc = 0, dbg_full = 0, dbg_t0 = clock64();
 #endif
-    for (int it = 0; it < my_count; it++) {
+    for (int it = mw; it < my_count; it += kMmaWarps) {
       const int buf = it % kAccBuffers;
       const uint32_t aph = (it / kAccBuffers) & 1;
+      const int s = it % kSlots;
+      const uint32_t ph = (it / kSlots) & 1;
 #ifdef RUYB200_DEBUG_KNOBS
       long long dbg_a = clock64();
 #endif
@@ -344,33 +453,25 @@ batch_i8_kernel(const BatchItem* __restrict__ items, int num_items, int* status)
         if (lane == 0) { if (!*abortp) atomicCAS(status, 0, 2); *abortp = 1; }
         break;
       }
-      // the slot was filled by cp.async (generic proxy); the tensor core reads it through the async proxy
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      const uint4 c0 = reinterpret_cast<const uint4*>(&slot_cmd[s])[0];   // lo_m, hi_m, lo_n, hi_n
+      const uint4 c1 = reinterpret_cast<const uint4*>(&slot_cmd[s])[1];   // kstep_m, kstep_n, idesc, nk_fence
+      // a tile filled by cp.async was written through the generic proxy; the tensor core reads through the async proxy
+      if (c1.w & 0x80000000u) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tc_fence_after();
-      const int depth = slot_item[s].depth;
-      const int size_n = slot_item[s].size_n;
-      const uint32_t flags = slot_item[s].flags;
-      const int kpad = (depth + 31) & ~31;
-      const int nmma = (size_n + 15) & ~15;
-      const uint32_t idesc = (2u << 4) | ((flags & kItemMSigned ? 1u : 0u) << 7) | ((flags & kItemNSigned ? 1u : 0u) << 10) |
-                             ((uint32_t)(nmma >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-      const uint32_t sbo = (uint32_t)(kpad / 16) * 128;
-      const uint32_t addr_m = smem_u32(smem + s * kSlotBytes);
-      const uint32_t addr_n = addr_m + kTileBytes;
       const uint32_t tmem_d = tmem_base + (uint32_t)(buf * kAccCols);
+      const int nk = (int)(c1.w & 0xffu);
       if (elect_one()) {
-        for (int k = 0; k < kpad / 32; k++) {
-          mma_i8_nosw(tmem_d, addr_m + k * 256, addr_n + k * 256, sbo, idesc, k != 0);
+        for (int k = 0; k < nk; k++) {
+          mma_i8(tmem_d, c0.x + k * c1.x, c0.y, c0.z + k * c1.y, c0.w, c1.z, k != 0);
         }
         mma_commit(&empty_bar[s]);
         mma_commit(&acc_full_bar[buf]);
       }
       __syncwarp();
-      if (++s == kSlots) { s = 0; ph ^= 1; }
     }
 #ifdef RUYB200_DEBUG_KNOBS
     if (blockIdx.x == 0 && lane == 0)
-      printf("mma warp: total %lld cycles, waiting for an accumulator %lld, waiting for packed data %lld, items %d\n",
+      printf("mma warp %d: total %lld cycles, waiting for an accumulator %lld, waiting for packed data %lld, items %d\n", mw,
              clock64() - dbg_t0, dbg_acc, dbg_full, my_count);
 #endif
   } else if (warp >= kFirstEpiWarp) {
@@ -418,7 +519,10 @@ batch_i8_kernel(const BatchItem* __restrict__ items, int num_items, int* status)
         t.pad = 0;
         if (n < item.size_n) {
           // zero-point term of this destination column: the sum over depth of the n-side row, taken from the packed tile
-          if (item.zp_m) t.add -= item.zp_m * tile_row_sum(tile_n, n, kpad, (item.flags & kItemNSigned) != 0);
+          if (item.zp_m) {
+            const bool sg = (item.flags & kItemNSigned) != 0;
+            t.add -= item.zp_m * ((item.flags & kItemNTma) ? tile_row_sum_swizzled(tile_n, n, kpad, sg) : tile_row_sum(tile_n, n, kpad, sg));
+          }
           if (ch_n) {
             if (vbias) t.add += vbias[n];
             if (vmfp) t.mul = vmfp[n];
@@ -431,7 +535,14 @@ batch_i8_kernel(const BatchItem* __restrict__ items, int num_items, int* status)
       const bool m_ok = m >= 0 && m < item.size_m;
       int32_t add_m = 0, mul_m = item.mfp, exp_m = item.mexp;
       if (m_ok) {
-        if (item.zp_n) add_m -= item.zp_n * tile_row_sum(tile_m, quarter * 32 + lane, kpad, (item.flags & kItemMSigned) != 0);
+        if (item.zp_n) {
+          const bool sg = (item.flags & kItemMSigned) != 0;
+          const int tr = quarter * 32 + lane;
+          const int32_t sum = item.sums_m ? slot_vec[s][3][m]
+                                          : ((item.flags & kItemMTma) ? tile_row_sum_swizzled(tile_m, tr, kpad, sg)
+                                                                      : tile_row_sum(tile_m, tr, kpad, sg));
+          add_m -= item.zp_n * sum;
+        }
         if (!ch_n) {
           if (vbias) add_m += vbias[m];
           if (vmfp) mul_m = vmfp[m];
@@ -458,43 +569,66 @@ batch_i8_kernel(const BatchItem* __restrict__ items, int num_items, int* status)
         const bool fast = !per_n && !x86 && dst_dtype != RUYB200_I32;
         const int sh = 31 - exp_m;
         const long long rnd = 1ll << (sh - 1);
-        auto process = [&](const uint32_t (&rr)[16], int c) {
+        // With every shift of the warp at least 32, the result is the high word of the product shifted on.
+        // With every shift of the warp at least 33, the rounding term has no low word, so the result is
+        // (mulhi(x, multiplier) + 2^(shift-33)) >> (shift-32): one multiply-add-high and one shift.  The destination
+        // zero point joins the addend when it cannot overflow there.
+        const bool high_word = fast && esz == 1 && __all_sync(0xffffffffu, sh >= 33);
+        const int sh_hi = sh - 32;
+        const bool fold_zp = __all_sync(0xffffffffu, sh_hi <= 20) && dzp >= -256 && dzp <= 255;
+        const int32_t rnd_hi = (int32_t)(rnd >> 32) + (fold_zp ? dzp * (1 << (sh_hi & 31)) : 0);
+        const int32_t dzp_late = fold_zp ? 0 : dzp;
+        // 16 columns: all values first (branch-free, so the sixteen dependency chains interleave), then the stores
+        auto process = [&](uint32_t (&rr)[16], int c) {   // results replace the accumulators in rr[]
           const int lim = size_n - c;
-          if (fast) {
+          if (high_word) {
 #pragma unroll
             for (int q = 0; q < 16; q++) {
-              if (q < lim) {
-                int32_t x = requant_ref_fast((int32_t)(rr[q] + (uint32_t)add_m), mul_m, rnd, sh);
-                x = max(min(x + dzp, cmax), cmin);
-                if (esz == 1) *out = (uint8_t)x; else *reinterpret_cast<int16_t*>(out) = (int16_t)x;
-                out += step;
-              }
+              const int32_t h = __mulhi((int32_t)(rr[q] + (uint32_t)add_m), mul_m) + rnd_hi;
+              rr[q] = (uint32_t)max(min((h >> sh_hi) + dzp_late, cmax), cmin);
+            }
+          } else if (fast) {
+#pragma unroll
+            for (int q = 0; q < 16; q++) {
+              const int32_t x = requant_ref_fast((int32_t)(rr[q] + (uint32_t)add_m), mul_m, rnd, sh);
+              rr[q] = (uint32_t)max(min(x + dzp, cmax), cmin);
             }
           } else {
 #pragma unroll
             for (int q = 0; q < 16; q++) {
-              if (q < lim) {
-                int32_t x = (int32_t)(rr[q] + (uint32_t)add_m);
-                int32_t mul = mul_m;
-                int e = exp_m;
-                if (per_n) {
-                  const NTerm t = nt[c + q];
-                  x = (int32_t)((uint32_t)x + (uint32_t)t.add);
-                  if (ch_n) { mul = t.mul; e = t.exp; }
-                }
-                if (dst_dtype != RUYB200_I32) {
-                  x = x86 ? requant_x86(x, mul, e) : requant_reference(x, mul, e);
-                  x = (int32_t)((uint32_t)x + (uint32_t)dzp);
-                  x = max(min(x, cmax), cmin);
-                } else {
-                  x = (int32_t)((uint32_t)x + (uint32_t)dzp);
-                }
-                if (esz == 1) *out = (uint8_t)x;
-                else if (esz == 2) *reinterpret_cast<int16_t*>(out) = (int16_t)x;
-                else *reinterpret_cast<int32_t*>(out) = x;
-                out += step;
+              int32_t x = (int32_t)(rr[q] + (uint32_t)add_m);
+              int32_t mul = mul_m;
+              int e = exp_m;
+              if (per_n) {
+                const NTerm t = nt[(c + q) & (kAccCols - 1)];
+                x = (int32_t)((uint32_t)x + (uint32_t)t.add);
+                if (ch_n) { mul = t.mul; e = t.exp; }
               }
+              if (dst_dtype != RUYB200_I32) {
+                x = x86 ? requant_x86(x, mul, e) : requant_reference(x, mul, e);
+                x = (int32_t)((uint32_t)x + (uint32_t)dzp);
+                x = max(min(x, cmax), cmin);
+              } else {
+                x = (int32_t)((uint32_t)x + (uint32_t)dzp);
+              }
+              rr[q] = (uint32_t)x;
             }
+          }
+          uint8_t* o = out + (int64_t)c * step;
+          if (esz == 1) {
+            if (lim >= 16) {
+#pragma unroll
+              for (int q = 0; q < 16; q++) o[q * step] = (uint8_t)rr[q];
+            } else {
+#pragma unroll
+              for (int q = 0; q < 16; q++) if (q < lim) o[q * step] = (uint8_t)rr[q];
+            }
+          } else if (esz == 2) {
+#pragma unroll
+            for (int q = 0; q < 16; q++) if (q < lim) *reinterpret_cast<int16_t*>(o + q * step) = (int16_t)rr[q];
+          } else {
+#pragma unroll
+            for (int q = 0; q < 16; q++) if (q < lim) *reinterpret_cast<int32_t*>(o + q * step) = (int32_t)rr[q];
           }
         };
         // two register buffers: the load of the next 16 columns is in flight while 16 are processed
@@ -546,7 +680,8 @@ bool batch_i8_fits(const SideView& m_side, const SideView& n_side, int depth) {
   return depth >= 1 && depth <= 128;
 }
 
-cudaError_t launch_batch_i8(const BatchItem* items, int num_items, int grid, int* status, cudaStream_t stream) {
+cudaError_t launch_batch_i8(const BatchItem* items, const CUtensorMap* maps, int num_items, int grid, int* status,
+                            cudaStream_t stream) {
   if (num_items <= 0) return cudaSuccess;
   static bool attr_set = false;
   if (!attr_set) {
@@ -554,7 +689,7 @@ cudaError_t launch_batch_i8(const BatchItem* items, int num_items, int grid, int
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
-  batch_i8_kernel<<<grid, kThreads, kSmemBytes, stream>>>(items, num_items, status);
+  batch_i8_kernel<<<grid, kThreads, kSmemBytes, stream>>>(items, maps, num_items, status);
   return cudaGetLastError();
 }
 

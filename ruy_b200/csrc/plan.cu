@@ -4,6 +4,7 @@
 // kernel (batch_i8.cu): one launch per replay, whatever their number.  The others are replayed through
 // the ordinary single-mul dispatch.
 #include <algorithm>
+#include <cstring>
 #include <vector>
 
 #include "batch_i8.h"
@@ -17,6 +18,7 @@ struct ruyb200_plan {
   std::vector<ruyb200_mul_desc> single;     // muls replayed one launch at a time
   std::vector<const void*> pinned;          // prepacked-cache entries this plan reads
   BatchItem* d_items = nullptr;   // in schedule order
+  CUtensorMap* d_maps = nullptr;  // two per item (m side, n side), same order
   int num_items = 0;
   int grid = 0;
   uint64_t bytes = 0;
@@ -30,6 +32,7 @@ size_t esize(int dtype) { return dtype == RUYB200_I8 || dtype == RUYB200_U8 ? 1 
 void free_plan(ruyb200_plan* plan) {
   if (!plan) return;
   if (plan->d_items) cudaFree(plan->d_items);
+  if (plan->d_maps) cudaFree(plan->d_maps);
   ctx_unpin(plan->ctx, plan->pinned);
   delete plan;
 }
@@ -109,12 +112,28 @@ int ruyb200_plan_create(ruyb200_ctx* ctx, const ruyb200_mul_desc* descs, int n, 
       }
       scheduled[pos] = it;
     }
-    if (cudaMalloc(&plan->d_items, scheduled.size() * sizeof(BatchItem)) != cudaSuccess) {
+    // Operands with 16-byte aligned rows are fetched by one tensor-map copy each: encode the maps now.
+    std::vector<CUtensorMap> maps(2 * scheduled.size());
+    memset(maps.data(), 0, maps.size() * sizeof(CUtensorMap));
+    for (size_t pos = 0; pos < scheduled.size(); pos++) {
+      BatchItem& it = scheduled[pos];
+      if ((it.flags & kItemMTma) &&
+          !make_i8_tile_map(&maps[2 * pos], it.m_ptr, it.depth, it.size_m, it.stride_m, batch_box_rows_m(it.size_m))) {
+        it.flags &= ~kItemMTma;
+      }
+      if ((it.flags & kItemNTma) &&
+          !make_i8_tile_map(&maps[2 * pos + 1], it.n_ptr, it.depth, it.size_n, it.stride_n, batch_box_rows_n(it.size_n))) {
+        it.flags &= ~kItemNTma;
+      }
+    }
+    if (cudaMalloc(&plan->d_items, scheduled.size() * sizeof(BatchItem)) != cudaSuccess ||
+        cudaMalloc(&plan->d_maps, maps.size() * sizeof(CUtensorMap)) != cudaSuccess) {
       cudaGetLastError();
       free_plan(plan);
       return ctx_fail(RUYB200_ERR_OOM, "plan allocation failed");
     }
     cudaMemcpy(plan->d_items, scheduled.data(), scheduled.size() * sizeof(BatchItem), cudaMemcpyHostToDevice);
+    cudaMemcpy(plan->d_maps, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice);
   }
   // packing launched for cache misses has finished before the plan is used
   int rc = ruyb200_ctx_sync(ctx);
@@ -129,7 +148,7 @@ int ruyb200_plan_create(ruyb200_ctx* ctx, const ruyb200_mul_desc* descs, int n, 
 int ruyb200_plan_run(ruyb200_plan* plan) {
   if (!plan) return ctx_fail(RUYB200_ERR_INVALID, "null plan");
   if (plan->num_items > 0) {
-    cudaError_t ce = launch_batch_i8(plan->d_items, plan->num_items, plan->grid, ctx_status_word(plan->ctx),
+    cudaError_t ce = launch_batch_i8(plan->d_items, plan->d_maps, plan->num_items, plan->grid, ctx_status_word(plan->ctx),
                                      ctx_stream(plan->ctx));
     ctx_count_launch(plan->ctx, RUYB200_KERNEL_BATCH_I8);
     if (ce != cudaSuccess) return ctx_fail(RUYB200_ERR_CUDA, cudaGetErrorString(ce));

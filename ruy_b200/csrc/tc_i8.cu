@@ -25,6 +25,7 @@
 #include <cstdlib>
 #include <cstring>
 
+#include "batch_i8.h"
 #include "common.cuh"
 
 namespace ruyb200 {
@@ -883,6 +884,21 @@ bool make_map(CUtensorMap* map, const SideView& s, int depth, int box_rows) {
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
+
+}  // namespace
+
+bool make_i8_tile_map(CUtensorMap* map, const void* base, int depth, int width, int64_t stride_w, int box_rows) {
+  SideView s;
+  s.data = base;
+  s.stride_w = stride_w;
+  s.stride_k = 1;
+  s.width = width;
+  s.zero_point = 0;
+  s.dtype = RUYB200_U8;
+  return make_map(map, s, depth, box_rows);
+}
+
+namespace {
 
 bool is_8bit(uint8_t dtype) { return dtype == RUYB200_I8 || dtype == RUYB200_U8; }
 
