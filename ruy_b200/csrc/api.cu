@@ -161,6 +161,8 @@ struct CacheEntry {
 
 }  // namespace
 
+constexpr int kMaxChunks = 16;
+
 struct ruyb200_ctx {
   int device = 0;
   cudaStream_t stream = nullptr;
@@ -180,6 +182,14 @@ struct ruyb200_ctx {
   uint64_t counters[6] = {0, 0, 0, 0, 0, 0};
   int force_kernel = 0;  // RUYB200_KERNEL_* or 0
   bool no_pair = false;  // RUYB200_NO_PAIR=1: keep the tensor-core kernel on one CTA per tile
+  // synchronous muls with large host operands are cut into chunks that move on these two streams while the
+  // kernel of another chunk runs on `stream` (created on first use)
+  cudaStream_t copy_in = nullptr;
+  cudaStream_t copy_out = nullptr;
+  cudaEvent_t chunk_in[kMaxChunks] = {};
+  cudaEvent_t chunk_done[kMaxChunks] = {};
+  cudaEvent_t chunk_start = nullptr;
+  bool no_chunks = false;   // RUYB200_NO_CHUNKS=1: one copy in, one kernel, one copy out
 };
 
 namespace {
@@ -494,6 +504,70 @@ int choose_kernel(const ruyb200_ctx* ctx, const ruyb200_mul_desc& d) {
   return RUYB200_KERNEL_GENERIC;
 }
 
+// The chunked path of a synchronous tensor-core mul whose m-side operand and destination live on the host.
+// `L` describes the whole mul with device addresses (the m-side buffer is still empty); chunk c covers m
+// indices [c * step, ...): its operand rows are copied in on `copy_in`, its kernel runs on the context's
+// stream once they have arrived, and its destination rows leave on `copy_out` once the kernel is done.
+int run_chunks(ruyb200_ctx* ctx, const ruyb200_mul_desc& d, const TcI8Launch& L, const char* m_host, size_t dst_esz) {
+  if (!ctx->copy_in) {
+    CUDA_TRY(cudaStreamCreateWithFlags(&ctx->copy_in, cudaStreamNonBlocking));
+    CUDA_TRY(cudaStreamCreateWithFlags(&ctx->copy_out, cudaStreamNonBlocking));
+    CUDA_TRY(cudaEventCreateWithFlags(&ctx->chunk_start, cudaEventDisableTiming));
+    for (int i = 0; i < kMaxChunks; i++) {
+      CUDA_TRY(cudaEventCreateWithFlags(&ctx->chunk_in[i], cudaEventDisableTiming));
+      CUDA_TRY(cudaEventCreateWithFlags(&ctx->chunk_done[i], cudaEventDisableTiming));
+    }
+  }
+  const int width = L.m_side.width;
+  const int64_t stride_w = L.m_side.stride_w;            // bytes: the operand is 8-bit
+  // chunks of a multiple of 256 m indices (whole two-CTA tiles), about eight of them, at least 1 MiB each
+  int step = ((width + 7) / 8 + 255) / 256 * 256;
+  while ((int64_t)step * stride_w < (1 << 20) && step < width) step *= 2;
+  int chunks = (width + step - 1) / step;
+  if (chunks > kMaxChunks) {
+    step = ((width + kMaxChunks - 1) / kMaxChunks + 255) / 256 * 256;
+    chunks = (width + step - 1) / step;
+  }
+  const size_t dst_pitch = (size_t)d.dst.stride * dst_esz;
+  const size_t dst_row_bytes = (size_t)L.dst.size_n * dst_esz;
+  // the copy streams start after whatever the context's stream has queued (operand staging, packing)
+  CUDA_TRY(cudaEventRecord(ctx->chunk_start, ctx->stream));
+  CUDA_TRY(cudaStreamWaitEvent(ctx->copy_in, ctx->chunk_start, 0));
+  CUDA_TRY(cudaStreamWaitEvent(ctx->copy_out, ctx->chunk_start, 0));
+  for (int c = 0; c < chunks; c++) {
+    const int w0 = c * step;
+    const int w = std::min(step, width - w0);
+    const size_t off = (size_t)w0 * (size_t)stride_w;
+    const size_t span = (size_t)(w - 1) * (size_t)stride_w + (size_t)L.depth;
+    CUDA_TRY(cudaMemcpyAsync((char*)L.m_side.data + off, m_host + off, span, cudaMemcpyHostToDevice, ctx->copy_in));
+    ctx->counters[3] += span;
+    CUDA_TRY(cudaEventRecord(ctx->chunk_in[c], ctx->copy_in));
+    CUDA_TRY(cudaStreamWaitEvent(ctx->stream, ctx->chunk_in[c], 0));
+    TcI8Launch part = L;
+    part.m_side.data = (const char*)L.m_side.data + off;
+    part.m_side.width = w;
+    part.dst.data = (char*)L.dst.data + (size_t)w0 * dst_pitch;
+    part.dst.size_m = w;
+    if (part.ep.sums_m) part.ep.sums_m += w0;
+    // per-channel buffers indexed along m move with the chunk
+    if (!part.ep.channel_on_n) {
+      if (part.ep.bias) part.ep.bias = (const char*)part.ep.bias + (size_t)w0 * 4;
+      if (part.ep.mfp_pc) part.ep.mfp_pc += w0;
+      if (part.ep.mexp_pc) part.ep.mexp_pc += w0;
+    }
+    cudaError_t ce = launch_tc_i8(part, ctx->stream);
+    ctx->counters[0]++;
+    if (ce != cudaSuccess) return fail(RUYB200_ERR_CUDA, "kernel launch: %s", cudaGetErrorString(ce));
+    CUDA_TRY(cudaEventRecord(ctx->chunk_done[c], ctx->stream));
+    CUDA_TRY(cudaStreamWaitEvent(ctx->copy_out, ctx->chunk_done[c], 0));
+    CUDA_TRY(cudaMemcpy2DAsync((char*)d.dst.data + (size_t)w0 * dst_pitch, dst_pitch, part.dst.data, dst_pitch, dst_row_bytes, w,
+                               cudaMemcpyDeviceToHost, ctx->copy_out));
+    ctx->counters[4] += dst_row_bytes * (size_t)w;
+  }
+  CUDA_TRY(cudaStreamSynchronize(ctx->copy_out));
+  return RUYB200_OK;
+}
+
 int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, void* const* mirrors = nullptr,
             int n_mirrors = 0) {
   int rc = validate_desc(desc);
@@ -550,12 +624,35 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
   // The tensor-core kernel can produce the sums of its m-side operand (the RHS for a column-major destination,
   // the LHS otherwise) itself, so no separate pass over that operand is requested for it.
   const bool m_is_rhs = d.dst.order == RUYB200_COL_MAJOR;
-  rc = prepare_side(ctx, d.lhs, 0, depth, should_cache(d.lhs, d.rhs.cols), need_lhs_sums && !(tc && !m_is_rhs), tc, &lhs_v,
-                    &lhs_sums);
-  if (rc) return rc;
-  rc = prepare_side(ctx, d.rhs, 1, depth, should_cache(d.rhs, d.lhs.rows), need_rhs_sums && !(tc && m_is_rhs), tc, &rhs_v,
-                    &rhs_sums);
-  if (rc) return rc;
+  // Host-resident m-side operand and destination of a large synchronous mul: instead of copy-in, kernel,
+  // copy-out one after the other, the m dimension is cut into chunks whose copies (both directions, on two
+  // copy streams) overlap each other and the kernels of other chunks.  The m-side operand then goes to the
+  // device chunk by chunk, below, not through prepare_side.
+  const ruyb200_matrix& m_mat = m_is_rhs ? d.rhs : d.lhs;
+  const SideView m_host = side_view(m_mat, m_is_rhs ? 1 : 0, m_mat.data);
+  const size_t m_span = storage_span_bytes(m_mat);
+  const bool streamed = synchronous && tc && n_mirrors == 0 && !ctx->no_chunks && !dst_on_device &&
+                        !is_device_pointer(m_mat.data) && !should_cache(m_mat, m_is_rhs ? d.lhs.rows : d.rhs.cols) &&
+                        m_host.stride_k == 1 && (m_host.stride_w & 15) == 0 && m_host.width >= 2048 && m_span >= (size_t(4) << 20);
+  void* m_dev = nullptr;
+  if (streamed) {
+    m_dev = ctx->arena.alloc(m_span);
+    if (!m_dev) return fail(RUYB200_ERR_OOM, "arena allocation of %zu bytes failed", m_span);
+  }
+  if (streamed && !m_is_rhs) {
+    lhs_v = side_view(d.lhs, 0, m_dev);
+  } else {
+    rc = prepare_side(ctx, d.lhs, 0, depth, should_cache(d.lhs, d.rhs.cols), need_lhs_sums && !(tc && !m_is_rhs), tc, &lhs_v,
+                      &lhs_sums);
+    if (rc) return rc;
+  }
+  if (streamed && m_is_rhs) {
+    rhs_v = side_view(d.rhs, 1, m_dev);
+  } else {
+    rc = prepare_side(ctx, d.rhs, 1, depth, should_cache(d.rhs, d.lhs.rows), need_rhs_sums && !(tc && m_is_rhs), tc, &rhs_v,
+                      &rhs_sums);
+    if (rc) return rc;
+  }
 
   Epilogue ep;
   memset(&ep, 0, sizeof(ep));
@@ -640,6 +737,12 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
     L.fuse_sums_m = true;
     L.n_mirrors = n_mirrors;
     for (int i = 0; i < 7; i++) L.mirrors[i] = i < n_mirrors ? mirrors[i] : nullptr;
+    if (streamed) {
+      rc = run_chunks(ctx, d, L, (const char*)m_mat.data, dst_esz);
+      if (rc) return rc;
+      ctx->counters[5] = kernel;
+      return ruyb200_ctx_sync(ctx);
+    }
     ce = launch_tc_i8(L, ctx->stream);
   } else if (kernel == RUYB200_KERNEL_SGEMM) {
     ce = launch_sgemm(r.m_side, r.n_side, r.dst, r.ep, ctx->stream);
@@ -718,6 +821,8 @@ int ruyb200_ctx_create_on_stream(int device, void* cuda_stream, ruyb200_ctx** ou
   if (fk && !strcmp(fk, "generic")) ctx->force_kernel = RUYB200_KERNEL_GENERIC;
   const char* np = getenv("RUYB200_NO_PAIR");
   ctx->no_pair = np && *np && *np != '0';
+  const char* nc = getenv("RUYB200_NO_CHUNKS");
+  ctx->no_chunks = nc && *nc && *nc != '0';
   *out = ctx;
   return RUYB200_OK;
 }
@@ -733,6 +838,13 @@ int ruyb200_ctx_destroy(ruyb200_ctx* ctx) {
   ctx->arena.release();
   if (ctx->d_status) cudaFree(ctx->d_status);
   if (ctx->h_status) cudaFreeHost(ctx->h_status);
+  if (ctx->copy_in) cudaStreamDestroy(ctx->copy_in);
+  if (ctx->copy_out) cudaStreamDestroy(ctx->copy_out);
+  for (int i = 0; i < kMaxChunks; i++) {
+    if (ctx->chunk_in[i]) cudaEventDestroy(ctx->chunk_in[i]);
+    if (ctx->chunk_done[i]) cudaEventDestroy(ctx->chunk_done[i]);
+  }
+  if (ctx->chunk_start) cudaEventDestroy(ctx->chunk_start);
   if (ctx->own_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
   cudaGetLastError();
   delete ctx;

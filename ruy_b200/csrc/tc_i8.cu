@@ -75,6 +75,7 @@ struct KernelArgs {
   int* status;
   void* mirror[7]; // peers' copies of the destination: same layout, every store is repeated there
   int n_mirror;
+  int tight_wait;  // shallow main loops: the epilogue probes its barrier without backing off
   int mirror_wide; // every destination base and the destination stride are multiples of 16 bytes
   int debug;       // profiling knobs (0 in production): 1 = epilogue skips its math and stores, 2 = producer skips the loads
 };
@@ -155,6 +156,17 @@ __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, v
   if ((threadIdx.x & 31) == 0) ok = mbar_wait_relaxed(bar, parity, abort_flag) ? 1 : 0;
   ok = __shfl_sync(0xffffffffu, ok, 0);
   return ok != 0;
+}
+
+// Bounded wait with every lane probing and no sleep: the shortest wake-up (about 125 cycles against several
+// hundred with back-off).  Used by the epilogue when tiles are shallow, where every tile's hand-offs are exposed.
+__device__ __forceinline__ bool mbar_wait_warp_tight(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  int ok = 0;
+  for (uint32_t i = 0; i < kSpinLimit; i++) {
+    if (mbar_try_wait(bar, parity)) { ok = 1; break; }
+    if ((i & 15) == 15 && *abort_flag) break;
+  }
+  return __all_sync(0xffffffffu, ok) != 0;
 }
 
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
@@ -674,7 +686,7 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
       long long dbg_b = clock64();
       dbg_stage += dbg_b - dbg_a;
 #endif
-      if (!mbar_wait_warp(&acc_full_bar[buf], aph, abortp)) {
+      if (!(args.tight_wait ? mbar_wait_warp_tight(&acc_full_bar[buf], aph, abortp) : mbar_wait_warp(&acc_full_bar[buf], aph, abortp))) {
         if (!*abortp) atomicCAS(args.status, 0, kTimeoutEpilogue);
         *abortp = 1;
         ok = false;
@@ -1023,6 +1035,10 @@ cudaError_t launch_tc_i8(const TcI8Launch& L, cudaStream_t stream) {
   a.acc_shift = a.mma_n <= 64 ? 3 : (a.mma_n <= 128 ? 2 : 1);
   a.acc_bufs = 1 << a.acc_shift;
   a.epi_groups = (L.depth <= 512 && L.n_mirrors <= 0) ? 2 : 1;
+  a.tight_wait = L.depth <= 512 ? 1 : 0;
+#ifdef RUYB200_DEBUG_KNOBS
+  if (getenv("RUYB200_TIGHT")) a.tight_wait = atoi(getenv("RUYB200_TIGHT"));
+#endif
   // instruction descriptor: int32 accumulate, operand signedness, both operands depth-major,
   // N/8 at bit 17, M/16 at bit 24 (M spans both CTAs of a pair)
   a.idesc = (2u << 4) | (fmt_m << 7) | (fmt_n << 10) | ((uint32_t)(a.mma_n >> 3) << 17) | ((uint32_t)(unit_m >> 4) << 24);

@@ -173,6 +173,23 @@ def test_host_pointers_are_staged_and_padding_preserved(gpu_ctx):
     assert after["h2d_bytes"] > before["h2d_bytes"] and after["d2h_bytes"] > before["d2h_bytes"]
 
 
+def test_large_host_operands_take_the_chunked_path(gpu_ctx):
+    """Synchronous muls whose wide operand and destination are host memory are cut into chunks along the destination's
+    outer dimension (copies in both directions overlapping the kernels): more launches than one, same results, padding
+    untouched.  Column-major destination (the RHS is chunked, channels on the other dimension) and row-major destination
+    (the LHS is chunked and the per-channel buffers move with the chunks)."""
+    for shape, orders, lhs, rhs, dst in (((64, 2048, 2176), "RCC", "uint8", "uint8", "uint8"),
+                                         ((2176, 2048, 40), "RCR", "int8", "int8", "int8")):
+        c = cases.random_case(*shape, lhs, rhs, dst, orders=orders, extra_stride=16, perchannel=True,
+                              symmetric=False if lhs == "uint8" else None, seed=5)
+        before = gpu_ctx.counters()["launches"]
+        got, storage = util.run_gpu(c, gpu_ctx, where="host", rounding=Rounding.kReference, sentinel=55)
+        assert gpu_ctx.counters()["launches"] - before >= 4
+        want = util.run_oracle(c, Rounding.kReference)
+        assert np.array_equal(got, want), f"{c.name}: {(got != want).sum()} mismatches"
+        assert util.padding_untouched(c, storage, 55)
+
+
 def test_mul_async_on_device_operands(gpu_ctx):
     c = cases.config0(exps=(-17, -13))
     got, _ = util.run_gpu(c, gpu_ctx, rounding=Rounding.kReference, use_async=True)
