@@ -75,6 +75,8 @@ struct KernelArgs {
   int* status;
   void* mirror[7]; // peers' copies of the destination: same layout, every store is repeated there
   int n_mirror;
+  int pack_clamps; // 8-bit destination with a clamp range inside int16: values are clamped two at a time while being narrowed
+  uint32_t clamp_lo2, clamp_hi2;   // the clamp bounds replicated in both 16-bit halves
   int tight_wait;  // shallow main loops: the epilogue probes its barrier without backing off
   int mirror_wide; // every destination base and the destination stride are multiples of 16 bytes
   int debug;       // profiling knobs (0 in production): 1 = epilogue skips its math and stores, 2 = producer skips the loads
@@ -308,6 +310,29 @@ struct NTerms {
   int32_t pad;
 };
 
+// Narrows 32 int32 values to bytes (8 words).  With `clamp`, the values are first saturated to 16 bits two at a
+// time, clamped to [lo2, hi2] per 16-bit half (bounds replicated in both halves) and then reduced to their low bytes:
+// 7 instructions per 4 values instead of 14 for clamping and masking them one by one.
+__device__ __forceinline__ void narrow_u8x32(const int32_t* v, bool clamp, uint32_t lo2, uint32_t hi2, uint32_t* w) {
+  if (clamp) {
+#pragma unroll
+    for (int q = 0; q < 8; q++) {
+      uint32_t a, b;
+      asm("cvt.pack.sat.s16.s32 %0, %1, %2;" : "=r"(a) : "r"(v[4 * q + 1]), "r"(v[4 * q]));
+      asm("cvt.pack.sat.s16.s32 %0, %1, %2;" : "=r"(b) : "r"(v[4 * q + 3]), "r"(v[4 * q + 2]));
+      a = __vmaxs2(__vmins2(a, hi2), lo2);
+      b = __vmaxs2(__vmins2(b, hi2), lo2);
+      w[q] = __byte_perm(a, b, 0x6420);
+    }
+  } else {
+#pragma unroll
+    for (int q = 0; q < 8; q++) {
+      w[q] = (uint32_t)(v[4 * q] & 0xff) | ((uint32_t)(v[4 * q + 1] & 0xff) << 8) |
+             ((uint32_t)(v[4 * q + 2] & 0xff) << 16) | ((uint32_t)(v[4 * q + 3] & 0xff) << 24);
+    }
+  }
+}
+
 // Narrow and store 32 consecutive destination elements n0..n0+31 of row m.
 template <int kDstBytes>
 __device__ __forceinline__ void store_run32_at(char* dst_base, const KernelArgs& a, int m, int n0, int n_end, const int32_t* v) {
@@ -317,11 +342,7 @@ __device__ __forceinline__ void store_run32_at(char* dst_base, const KernelArgs&
     uint4* out = (uint4*)base;
     if (kDstBytes == 1) {
       uint32_t w[8];
-#pragma unroll
-      for (int q = 0; q < 8; q++) {
-        w[q] = (uint32_t)(v[4 * q] & 0xff) | ((uint32_t)(v[4 * q + 1] & 0xff) << 8) |
-               ((uint32_t)(v[4 * q + 2] & 0xff) << 16) | ((uint32_t)(v[4 * q + 3] & 0xff) << 24);
-      }
+      narrow_u8x32(v, a.pack_clamps != 0, a.clamp_lo2, a.clamp_hi2, w);
       out[0] = make_uint4(w[0], w[1], w[2], w[3]);
       out[1] = make_uint4(w[4], w[5], w[6], w[7]);
     } else if (kDstBytes == 2) {
@@ -344,8 +365,10 @@ __device__ __forceinline__ void store_run32_at(char* dst_base, const KernelArgs&
   }
   DstView d = a.dst;
   d.data = dst_base;
-  for (int q = 0; q < 32; q++) {
-    if (n0 + q < n_end) store_int(d, a.ep.dst_dtype, m, n0 + q, v[q]);
+#pragma unroll
+  for (int q = 0; q < 32; q++) {   // unrolled: v[] stays in registers
+    const int32_t x = (kDstBytes == 1 && a.pack_clamps) ? max(min(v[q], a.ep.clamp_max), a.ep.clamp_min) : v[q];
+    if (n0 + q < n_end) store_int(d, a.ep.dst_dtype, m, n0 + q, x);
   }
 }
 
@@ -422,7 +445,10 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
   __shared__ __align__(8) uint64_t empty_bar[kNumStages];
   __shared__ __align__(8) uint64_t acc_full_bar[kMaxAccBufs];
   __shared__ __align__(8) uint64_t acc_empty_bar[kMaxAccBufs];
-  __shared__ __align__(16) NTerms n_terms[kEpilogueGroups][kMaxBlockN];
+  // per-n terms of the tile being drained, one array per field so that the common paths fetch four addends per load
+  __shared__ __align__(16) int32_t nt_add_s[kEpilogueGroups][kMaxBlockN];
+  __shared__ __align__(16) int32_t nt_mul_s[kEpilogueGroups][kMaxBlockN];
+  __shared__ __align__(16) int32_t nt_exp_s[kEpilogueGroups][kMaxBlockN];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -646,7 +672,9 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
       if (groups == 2 && (int)(tcount & 1) != group) continue;   // the other group's tile
       // stage the per-n terms of this tile (overlaps the tile's main loop) unless the group's buffer already holds
       // them (there is one n tile, or it did not change)
-      NTerms* nt = n_terms[group];
+      int32_t* nt_add = nt_add_s[group];
+      int32_t* nt_mul = nt_mul_s[group];
+      int32_t* nt_exp = nt_exp_s[group];
       const bool restage = staged_tn != tn;
       if (restage) {
         // warps of this group may still be reading the buffer for the previous tile
@@ -667,7 +695,9 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
               if (ep.mexp_pc) t.exp = ep.mexp_pc[n];
             }
           }
-          nt[i] = t;
+          nt_add[i] = t.add;
+          nt_mul[i] = t.mul;
+          nt_exp[i] = t.exp;
         }
       }
       // per-m terms of this thread's row
@@ -718,26 +748,46 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
       const bool mul_varies_with_n = ch_n && (ep.mfp_pc != nullptr || ep.mexp_pc != nullptr);
       const int sh_c = 31 - exp_m;
       const long long rnd_c = 1ll << (sh_c - 1);
+      // With every shift of the warp at least 32 the result is the high word of the 64-bit product shifted on, and the
+      // destination zero point can ride in the rounding term when it cannot overflow there.
+      const bool high_word = kDstBytes != 4 && !kX86 && !mul_varies_with_n && __all_sync(0xffffffffu, sh_c >= 32);
+      const bool fold_zp = sh_c <= 45 && ep.dst_zp > -32768 && ep.dst_zp < 32768;
+      const long long rnd_hw = rnd_c + (fold_zp ? (long long)ep.dst_zp * (1ll << (sh_c & 63)) : 0ll);
+      const int32_t zp_late = fold_zp ? 0 : ep.dst_zp;
+      const int sh_hi = (sh_c - 32) & 31;
       // bias / zero-point terms, fixed-point multiplier, destination zero point and clamp for the 32 accumulators in r[]
+      // 8-bit destinations leave the clamp to the narrowing step (two values per instruction there)
+      const bool late_clamp = kDstBytes == 1 && args.pack_clamps;
       auto finish_chunk = [&](int c, int32_t (&v)[32]) {
-        if (kDstBytes != 4 && !kX86 && !mul_varies_with_n) {
+        if (high_word || (kDstBytes != 4 && !kX86 && !mul_varies_with_n)) {
 #pragma unroll
-          for (int q = 0; q < 32; q++) {
-            const int32_t x = (int32_t)(r[q] + (uint32_t)nt[c + q].add + (uint32_t)add_m);
-            const int32_t y = (int32_t)(((long long)x * (long long)mul_m + rnd_c) >> sh_c);
-            v[q] = max(min((int32_t)((uint32_t)y + (uint32_t)ep.dst_zp), ep.clamp_max), ep.clamp_min);
+          for (int q4 = 0; q4 < 8; q4++) {
+            const int4 ad = *reinterpret_cast<const int4*>(&nt_add[c + 4 * q4]);   // c is a multiple of 32
+            const int32_t adds[4] = {ad.x, ad.y, ad.z, ad.w};
+#pragma unroll
+            for (int t = 0; t < 4; t++) {
+              const int q = 4 * q4 + t;
+              const int32_t x = (int32_t)(r[q] + (uint32_t)adds[t] + (uint32_t)add_m);
+              int32_t y;
+              if (high_word) {
+                const long long p = (long long)x * (long long)mul_m + rnd_hw;
+                y = (int32_t)((uint32_t)((int32_t)(p >> 32) >> sh_hi) + (uint32_t)zp_late);
+              } else {
+                y = (int32_t)((uint32_t)(int32_t)(((long long)x * (long long)mul_m + rnd_c) >> sh_c) + (uint32_t)ep.dst_zp);
+              }
+              v[q] = late_clamp ? y : max(min(y, ep.clamp_max), ep.clamp_min);
+            }
           }
         } else {
 #pragma unroll
           for (int q = 0; q < 32; q++) {
-            const NTerms t = nt[c + q];
-            int32_t x = (int32_t)(r[q] + (uint32_t)t.add + (uint32_t)add_m);
+            int32_t x = (int32_t)(r[q] + (uint32_t)nt_add[c + q] + (uint32_t)add_m);
             if (kDstBytes != 4) {
-              const int32_t mul = ch_n ? t.mul : mul_m;
-              const int e = ch_n ? t.exp : exp_m;
+              const int32_t mul = ch_n ? nt_mul[c + q] : mul_m;
+              const int e = ch_n ? nt_exp[c + q] : exp_m;
               x = kX86 ? requant_x86(x, mul, e) : requant_reference(x, mul, e);
               x = (int32_t)((uint32_t)x + (uint32_t)ep.dst_zp);
-              x = max(min(x, ep.clamp_max), ep.clamp_min);
+              if (!late_clamp) x = max(min(x, ep.clamp_max), ep.clamp_min);
             } else {
               x = (int32_t)((uint32_t)x + (uint32_t)ep.dst_zp);
             }
@@ -766,11 +816,7 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
             int32_t v[32];
             finish_chunk(c, v);
             uint32_t w[8];
-#pragma unroll
-            for (int q = 0; q < 8; q++) {
-              w[q] = (uint32_t)(v[4 * q] & 0xff) | ((uint32_t)(v[4 * q + 1] & 0xff) << 8) |
-                     ((uint32_t)(v[4 * q + 2] & 0xff) << 16) | ((uint32_t)(v[4 * q + 3] & 0xff) << 24);
-            }
+            narrow_u8x32(v, late_clamp, args.clamp_lo2, args.clamp_hi2, w);
             uint4* sp = reinterpret_cast<uint4*>(stg + ml * kMirrorPitch + (c - h * 128));
             sp[0] = make_uint4(w[0], w[1], w[2], w[3]);
             sp[1] = make_uint4(w[4], w[5], w[6], w[7]);
@@ -1023,9 +1069,11 @@ cudaError_t launch_tc_i8(const TcI8Launch& L, cudaStream_t stream) {
   const bool fuse = L.fuse_sums_m && L.ep.zp_n != 0 && L.ep.sums_m == nullptr;
   // Two-CTA tiles (256 x 256) when both destination dimensions are large enough to fill them.
   const bool pair = !fuse && L.allow_pair && a.size_m >= 256 && a.size_n >= 256 && L.sm_count >= 2;
-  int bn = (a.size_n + 15) / 16 * 16;
+  // n tiles of equal width (a multiple of 16), as few as the MMA's N limit allows: 256 columns split as 128 + 128
+  // rather than 240 + 16 when the all-ones rows take 16 of the 256
   const int bn_cap = fuse ? kMaxBlockN - 16 : kMaxBlockN;
-  if (bn > bn_cap) bn = bn_cap;
+  const int n_tiles = (a.size_n + bn_cap - 1) / bn_cap;
+  const int bn = ((a.size_n + n_tiles - 1) / n_tiles + 15) / 16 * 16;
   a.block_n = bn;
   a.sums_col = fuse ? bn : -1;
   a.mma_n = fuse ? bn + 16 : bn;
@@ -1035,6 +1083,10 @@ cudaError_t launch_tc_i8(const TcI8Launch& L, cudaStream_t stream) {
   a.acc_shift = a.mma_n <= 64 ? 3 : (a.mma_n <= 128 ? 2 : 1);
   a.acc_bufs = 1 << a.acc_shift;
   a.epi_groups = (L.depth <= 512 && L.n_mirrors <= 0) ? 2 : 1;
+  const bool dst8 = L.ep.dst_dtype == RUYB200_I8 || L.ep.dst_dtype == RUYB200_U8;
+  a.pack_clamps = dst8 && L.ep.clamp_min >= -32768 && L.ep.clamp_max <= 32767 && L.ep.clamp_min <= L.ep.clamp_max;
+  a.clamp_lo2 = ((uint32_t)L.ep.clamp_min & 0xffffu) * 0x10001u;
+  a.clamp_hi2 = ((uint32_t)L.ep.clamp_max & 0xffffu) * 0x10001u;
   a.tight_wait = L.depth <= 512 ? 1 : 0;
 #ifdef RUYB200_DEBUG_KNOBS
   if (getenv("RUYB200_TIGHT")) a.tight_wait = atoi(getenv("RUYB200_TIGHT"));
