@@ -75,6 +75,8 @@ struct KernelArgs {
   int* status;
   void* mirror[7]; // peers' copies of the destination: same layout, every store is repeated there
   int n_mirror;
+  int row_pitch;   // bytes per tile row in shared memory = width of the swizzle pattern: 128, or 64 / 32 for depth <= 64 / 32
+  uint32_t desc_hi; // high word of the shared-memory matrix descriptors for that pattern
   int pack_clamps; // 8-bit destination with a clamp range inside int16: values are clamped two at a time while being narrowed
   uint32_t clamp_lo2, clamp_hi2;   // the clamp bounds replicated in both 16-bit halves
   int tight_wait;  // shallow main loops: the epilogue probes its barrier without backing off
@@ -193,7 +195,7 @@ __device__ __forceinline__ uint32_t desc_lo(uint32_t smem_addr) { return ((smem_
 // inside a single asm block.  `first_accumulates` is 0 only for the first stage of a tile.
 template <bool kPair>
 __device__ __forceinline__ void mma_stage4(uint32_t tmem_d, uint32_t lo_a, uint32_t lo_b, uint32_t idesc,
-                                           uint32_t first_accumulates) {
+                                           uint32_t first_accumulates, uint32_t desc_hi = kDescHi) {
   if (kPair) {
     asm volatile(
         "{\n\t.reg .pred p, t;\n\t.reg .b64 da, db;\n\t.reg .b32 la, lb;\n\t"
@@ -229,14 +231,15 @@ __device__ __forceinline__ void mma_stage4(uint32_t tmem_d, uint32_t lo_a, uint3
 
 // One K=32 MMA (used for a ragged last stage).
 template <bool kPair>
-__device__ __forceinline__ void mma_one(uint32_t tmem_d, uint32_t lo_a, uint32_t lo_b, uint32_t idesc, uint32_t accumulate) {
+__device__ __forceinline__ void mma_one(uint32_t tmem_d, uint32_t lo_a, uint32_t lo_b, uint32_t idesc, uint32_t accumulate,
+                                        uint32_t desc_hi) {
   if (kPair) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
         "setp.ne.u32 p, %4, 0;\n\t"
         "mov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %5};\n\t"
         "tcgen05.mma.cta_group::2.kind::i8 [%0], da, db, %3, p;\n\t}"
-        ::"r"(tmem_d), "r"(lo_a), "r"(lo_b), "r"(idesc), "r"(accumulate), "r"(kDescHi)
+        ::"r"(tmem_d), "r"(lo_a), "r"(lo_b), "r"(idesc), "r"(accumulate), "r"(desc_hi)
         : "memory");
   } else {
     asm volatile(
@@ -244,7 +247,7 @@ __device__ __forceinline__ void mma_one(uint32_t tmem_d, uint32_t lo_a, uint32_t
         "setp.ne.u32 p, %4, 0;\n\t"
         "mov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %5};\n\t"
         "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %3, p;\n\t}"
-        ::"r"(tmem_d), "r"(lo_a), "r"(lo_b), "r"(idesc), "r"(accumulate), "r"(kDescHi)
+        ::"r"(tmem_d), "r"(lo_a), "r"(lo_b), "r"(idesc), "r"(accumulate), "r"(desc_hi)
         : "memory");
   }
 }
@@ -491,8 +494,8 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
     // are filled with 0x01 once, so accumulator column sums_col becomes sum_k m[.,k] (ruy/pack.h:117-129 computes
     // these sums while packing).  All bytes are equal, so the swizzle does not matter.
     for (int st = 0; st < kNumStages; st++) {
-      uint32_t* ones = reinterpret_cast<uint32_t*>(smem + st * kStageSize + kABytes + args.sums_col * kBlockKBytes);
-      for (int i = threadIdx.x; i < 16 * kBlockKBytes / 4; i += kThreads) ones[i] = 0x01010101u;
+      uint32_t* ones = reinterpret_cast<uint32_t*>(smem + st * kStageSize + kABytes + args.sums_col * args.row_pitch);
+      for (int i = threadIdx.x; i < 16 * args.row_pitch / 4; i += kThreads) ones[i] = 0x01010101u;
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -512,7 +515,7 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
     if (lane == 0) {
       uint32_t s = 0, ph = 0;
       uint32_t issued = 0;
-      const uint32_t stage_tx = (uint32_t)(kABytes + n_rows_per_cta * kBlockKBytes);
+      const uint32_t stage_tx = (uint32_t)((kBlockM + n_rows_per_cta) * args.row_pitch);
       const uint32_t full0_cluster = kPair ? map_to_rank(smem_u32(&full_bar[0]), 0) : 0;
       bool ok = true;
       for (int tile = unit; tile < num_tiles && ok; tile += units) {
@@ -618,7 +621,7 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
               mma_stage4<kPair>(tmem_d, lo_a, lo_b, idesc, kb != 0);
             } else {
               const int ksteps = (args.depth - kb * kBlockKBytes + 31) / 32;
-              for (int k = 0; k < ksteps; k++) mma_one<kPair>(tmem_d, lo_a + 2 * k, lo_b + 2 * k, idesc, (kb | k) != 0);
+              for (int k = 0; k < ksteps; k++) mma_one<kPair>(tmem_d, lo_a + 2 * k, lo_b + 2 * k, idesc, (kb | k) != 0, args.desc_hi);
             }
             // frees the stage (in both CTAs of a pair) once these MMAs have read it
             if (kPair) mma_commit_pair(&empty_bar[s]); else mma_commit(&empty_bar[s]);
@@ -931,15 +934,18 @@ EncodeTiledFn get_encode_fn() {
 }
 
 // 2-D map over a width x depth byte matrix: dim0 = depth (contiguous), dim1 = width.
-bool make_map(CUtensorMap* map, const SideView& s, int depth, int box_rows) {
+// `pitch` (128, 64 or 32) is the box's depth extent in bytes and selects the matching swizzle pattern.
+bool make_map(CUtensorMap* map, const SideView& s, int depth, int box_rows, int pitch = kBlockKBytes) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return false;
   cuuint64_t dims[2] = {(cuuint64_t)depth, (cuuint64_t)s.width};
   cuuint64_t strides[1] = {(cuuint64_t)s.stride_w};
-  cuuint32_t box[2] = {(cuuint32_t)kBlockKBytes, (cuuint32_t)box_rows};
+  cuuint32_t box[2] = {(cuuint32_t)pitch, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapSwizzle sw = pitch == 32 ? CU_TENSOR_MAP_SWIZZLE_32B
+                                            : (pitch == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B);
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(s.data), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -1094,8 +1100,16 @@ cudaError_t launch_tc_i8(const TcI8Launch& L, cudaStream_t stream) {
   // instruction descriptor: int32 accumulate, operand signedness, both operands depth-major,
   // N/8 at bit 17, M/16 at bit 24 (M spans both CTAs of a pair)
   a.idesc = (2u << 4) | (fmt_m << 7) | (fmt_n << 10) | ((uint32_t)(a.mma_n >> 3) << 17) | ((uint32_t)(unit_m >> 4) << 24);
+  // Shallow operands use a narrower swizzle pattern: the copy engine then moves 32 or 64 bytes per row instead of
+  // 128 (mostly out-of-range zero fill), which is what bounds tiles whose depth is a single MMA step or two.
+  a.row_pitch = L.depth <= 32 ? 32 : (L.depth <= 64 ? 64 : 128);
+  const char* np_env = getenv("RUYB200_WIDE_ROWS");
+  if (np_env && *np_env == '1') a.row_pitch = 128;
+  // stride byte offset (8 rows) at bits 32..45, descriptor version 1 at bit 46, swizzle mode at bits 61..63 (2: 128 B, 4: 64 B, 6: 32 B)
+  a.desc_hi = ((uint32_t)(8 * a.row_pitch) >> 4) | (1u << 14) | ((a.row_pitch == 128 ? 2u : (a.row_pitch == 64 ? 4u : 6u)) << 29);
   CUtensorMap map_m, map_n;
-  if (!make_map(&map_m, L.m_side, L.depth, kBlockM) || !make_map(&map_n, L.n_side, L.depth, pair ? bn / 2 : bn)) {
+  if (!make_map(&map_m, L.m_side, L.depth, kBlockM, a.row_pitch) ||
+      !make_map(&map_n, L.n_side, L.depth, pair ? bn / 2 : bn, a.row_pitch)) {
     return cudaErrorInvalidValue;
   }
   const long long tiles = (long long)a.tiles_m * a.tiles_n;
