@@ -20,6 +20,8 @@
 #include <vector>
 
 #include "common.cuh"
+#include <nvtx3/nvToolsExt.h>
+
 #include "batch_i8.h"
 #include "plan.h"
 
@@ -190,6 +192,7 @@ struct ruyb200_ctx {
   cudaEvent_t chunk_done[kMaxChunks] = {};
   cudaEvent_t chunk_start = nullptr;
   bool no_chunks = false;   // RUYB200_NO_CHUNKS=1: one copy in, one kernel, one copy out
+  bool trace = false;       // RUYB200_TRACE=1: one line per mul on stderr with the decisions taken (cf. ruy/trace.h)
 };
 
 namespace {
@@ -737,6 +740,18 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
     L.fuse_sums_m = true;
     L.n_mirrors = n_mirrors;
     for (int i = 0; i < 7; i++) L.mirrors[i] = i < n_mirrors ? mirrors[i] : nullptr;
+    TcI8Info info = {};
+    if (ctx->trace) L.info = &info;
+    struct TraceAtExit {   // prints after the launch has filled `info`
+      ruyb200_ctx* ctx; const ruyb200_mul_desc& d; const TcI8Info& info; bool x86, streamed; int mirrors;
+      ~TraceAtExit() {
+        if (!ctx->trace) return;
+        fprintf(stderr, "ruy_b200: mul %dx%dx%d kernel=tc_i8 tiles=%d of %s x %d, %d-byte tile rows, m-side sums %s, rounding=%s%s, mirrors=%d\n",
+                d.lhs.rows, d.lhs.cols, d.rhs.cols, info.tiles, info.pair ? "256 (two CTAs)" : "128", info.block_n, info.row_pitch,
+                info.fused_sums ? "from the tensor core" : "not fused", x86 ? "x86" : "reference",
+                streamed ? ", host operands in chunks" : "", mirrors);
+      }
+    } trace_at_exit{ctx, d, info, ep.rounding_x86 != 0, streamed, n_mirrors};
     if (streamed) {
       rc = run_chunks(ctx, d, L, (const char*)m_mat.data, dst_esz);
       if (rc) return rc;
@@ -746,8 +761,10 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
     ce = launch_tc_i8(L, ctx->stream);
   } else if (kernel == RUYB200_KERNEL_SGEMM) {
     ce = launch_sgemm(r.m_side, r.n_side, r.dst, r.ep, ctx->stream);
+    if (ctx->trace) fprintf(stderr, "ruy_b200: mul %dx%dx%d kernel=sgemm (fp32 FFMA, compensated)\n", d.lhs.rows, d.lhs.cols, d.rhs.cols);
   } else {
     ce = launch_generic(r.m_side, r.n_side, r.dst, r.ep, ctx->stream);
+    if (ctx->trace) fprintf(stderr, "ruy_b200: mul %dx%dx%d kernel=generic (CUDA cores, any type/layout)\n", d.lhs.rows, d.lhs.cols, d.rhs.cols);
   }
   ctx->counters[0]++;
   ctx->counters[5] = kernel;
@@ -823,6 +840,8 @@ int ruyb200_ctx_create_on_stream(int device, void* cuda_stream, ruyb200_ctx** ou
   ctx->no_pair = np && *np && *np != '0';
   const char* nc = getenv("RUYB200_NO_CHUNKS");
   ctx->no_chunks = nc && *nc && *nc != '0';
+  const char* tr = getenv("RUYB200_TRACE");
+  ctx->trace = tr && *tr && *tr != '0';
   *out = ctx;
   return RUYB200_OK;
 }
@@ -926,7 +945,17 @@ int ruyb200_validate(const ruyb200_mul_desc* desc) { return validate_desc(desc);
 
 int ruyb200_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc) {
   if (!ctx) return fail(RUYB200_ERR_INVALID, "null context");
-  return run_mul(ctx, desc, true);
+  // the labels ruy's own profiler uses (ruy/frontend.h:86-89), as NVTX ranges
+  nvtxRangePushA("Mul");
+  if (desc) {
+    char label[64];
+    snprintf(label, sizeof(label), "matmul shape: %dx%dx%d", desc->lhs.rows, desc->lhs.cols, desc->rhs.cols);
+    nvtxRangePushA(label);
+  }
+  const int rc = run_mul(ctx, desc, true);
+  if (desc) nvtxRangePop();
+  nvtxRangePop();
+  return rc;
 }
 
 int ruyb200_mul_async(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc) {

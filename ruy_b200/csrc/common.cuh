@@ -129,6 +129,10 @@ cudaError_t launch_pack(const SideView& side, int depth, int packed_depth, void*
 // tcgen05 kind::i8 GEMM.  Both sides must be 8-bit, depth-contiguous, with 16-byte aligned
 // base and stride_w (bytes).  `status` is a device word that receives a non-zero code if a
 // bounded wait gives up.
+// What launch_tc_i8 decided, for the decision log.
+struct TcI8Info {
+  int pair, block_n, tiles, fused_sums, row_pitch, grid;
+};
 struct TcI8Launch {
   SideView m_side;
   SideView n_side;
@@ -140,6 +144,7 @@ struct TcI8Launch {
   bool allow_pair;   // permit the two-CTA (cta_group::2) variant
   void* mirrors[7];  // addresses in peers' buffers that correspond to dst.data; every destination store is repeated there
   int n_mirrors;
+  TcI8Info* info = nullptr;   // filled in when not null
   bool fuse_sums_m;  // if ep.zp_n != 0 and ep.sums_m == nullptr, let the kernel produce the m-side sums itself
 };
 cudaError_t launch_tc_i8(const TcI8Launch& args, cudaStream_t stream);

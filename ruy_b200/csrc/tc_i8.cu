@@ -1113,6 +1113,14 @@ cudaError_t launch_tc_i8(const TcI8Launch& L, cudaStream_t stream) {
     return cudaErrorInvalidValue;
   }
   const long long tiles = (long long)a.tiles_m * a.tiles_n;
+  if (L.info) {
+    L.info->pair = pair;
+    L.info->block_n = bn;
+    L.info->tiles = (int)tiles;
+    L.info->fused_sums = fuse;
+    L.info->row_pitch = a.row_pitch;
+    L.info->grid = 0;
+  }
   if (pair) {
     // The tile schedule is static, so every pair must be resident from the start: size the grid
     // by the number of 2-CTA clusters the device can hold at once.

@@ -598,3 +598,48 @@ def test_config3_full_size_properties(gpu_ctx):
     m, e = c8.mfp.astype(np.int64)[:, None], c8.mexp.astype(np.int64)[:, None]
     want = np.clip(((acc * m + (1 << (30 - e))) >> (31 - e)) + c8.dst_zp, -128, 127).astype(np.int8)
     assert np.array_equal(out8, want)
+
+
+def test_decision_trace_line(capfd, monkeypatch):
+    """RUYB200_TRACE=1 (read when the context is created) logs one line per mul with the decisions taken, in the spirit
+    of ruy's RUY_TRACE (ruy/trace.h)."""
+    monkeypatch.setenv("RUYB200_TRACE", "1")
+    with ruy_b200.Context(0) as ctx:
+        c = cases.config0()
+        got, _ = util.run_gpu(c, ctx, rounding=Rounding.kReference)
+        assert np.array_equal(got, util.run_oracle(c))
+    err = capfd.readouterr().err
+    assert "ruy_b200: mul 256x512x128 kernel=tc_i8" in err and "rounding=reference" in err
+
+
+def test_plan_replay_inside_a_cuda_graph():
+    """A plan whose muls all fit the batched kernel is one kernel launch per replay with no allocation, so it can be
+    captured into a CUDA graph by a caller that keeps activations on the device (the library itself does not capture)."""
+    dev = torch.device("cuda", 0)
+    stream = torch.cuda.Stream(device=dev)
+    with ruy_b200.Context(0, stream=stream.cuda_stream) as ctx:
+        cs = [cases.random_case(r, d, c, "int8", "int8", "int8", perchannel=True, seed=11 + i)
+              for i, (r, d, c) in enumerate(((16, 32, 48), (64, 64, 64), (128, 96, 24), (24, 128, 128)))]
+        bound, descs = [], []
+        for c in cs:
+            dst = torch.zeros(c.dst_storage_elems(), dtype=torch.int8, device=dev)
+            lhs, rhs, p, d, keep = c.bind(dst, device=dev, rounding=Rounding.kReference)
+            bound.append((c, dst, keep))
+            descs.append(ruy_b200.make_desc(lhs, rhs, p, d))
+        plan = ruy_b200.Plan(ctx, descs)
+        with torch.cuda.stream(stream):
+            plan.run()                      # warm-up outside the capture (sets the kernel's attributes)
+            stream.synchronize()
+            for _, dst, _ in bound:
+                dst.zero_()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                plan.run()
+            stream.synchronize()
+            for _, dst, _ in bound:
+                assert not dst.any()        # capture records, it does not execute
+            graph.replay()
+            torch.cuda.synchronize()
+        for c, dst, _ in bound:
+            assert np.array_equal(c.dst_view(dst.cpu().numpy()), util.run_oracle(c)), c.name
+        plan.close()
