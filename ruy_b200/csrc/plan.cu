@@ -4,6 +4,8 @@
 // kernel (batch_i8.cu): one launch per replay, whatever their number.  The others are replayed through
 // the ordinary single-mul dispatch.
 #include <algorithm>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -78,8 +80,12 @@ int ruyb200_plan_create(ruyb200_ctx* ctx, const ruyb200_mul_desc* descs, int n, 
     }
     if (fits) {
       items.push_back(item);
-      // packing bytes dominate; epilogue work follows the destination size
-      cost.push_back((long long)(r + c) * ((k + 31) / 32 * 32) + 4ll * r * c);
+      // estimated cycles of an item on its SM: a fixed hand-off cost, the epilogue's columns (its rows sit on
+      // parallel lanes, so they count little) and the bytes to fetch; coefficients fitted on the 16..128 mix
+      const int quarters = (item.size_m + 31) / 32;
+      const long long est = 1000 + 40ll * item.size_n + 4ll * item.size_n * quarters +
+                            ((long long)(item.size_m + item.size_n) * item.depth) / 64;
+      cost.push_back(est);
     } else {
       plan->single.push_back(d);
     }
