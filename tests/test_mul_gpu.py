@@ -643,3 +643,12 @@ def test_plan_replay_inside_a_cuda_graph():
         for c, dst, _ in bound:
             assert np.array_equal(c.dst_view(dst.cpu().numpy()), util.run_oracle(c)), c.name
         plan.close()
+
+
+@pytest.mark.parametrize("orders", ["RCC", "CRC", "RCR", "CCR"])
+def test_float_few_outputs_long_depth(orders, gpu_ctx):
+    """Few destination elements with a long depth take the warp-per-element fp32 kernel: every storage order and
+    padded strides, within 1e-5 of a double-accumulated reference (assert_float_close)."""
+    for shape in ((9, 200, 7), (1, 1000, 1), (31, 128, 33)):
+        c = cases.random_case(*shape, "float32", "float32", "float32", orders=orders, extra_stride=3, seed=21)
+        check_case(c, gpu_ctx)
