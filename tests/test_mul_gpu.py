@@ -9,7 +9,7 @@ import torch
 
 import ruy_b200
 import util
-from golden_cases import golden_cases
+from golden_cases import golden_cases, requant_extreme_cases
 from ruy_b200 import cases
 from ruy_b200.api import CachePolicy, ChannelDimension, Order, Path, PerformanceAdvisory, Rounding
 
@@ -654,51 +654,8 @@ def test_float_few_outputs_long_depth(orders, gpu_ctx):
         check_case(c, gpu_ctx)
 
 
-def _requant_extreme_cases():
-    """Multiplier exponents on both sides of every fast-path boundary of the epilogues (total shift 24..61), multipliers
-    at the ends of their range, biases large enough to wrap or to leave the small-addend path, degenerate clamps and
-    extreme destination zero points; per-tensor and per-channel along either destination dimension."""
-    exps = (7, 1, 0, -1, -2, -13, -14, -15, -19, -20, -21, -30)
-    mfps = (1 << 30, (1 << 31) - 1, 1518500250)
-    out = []
-    for i, e in enumerate(exps):
-        c = cases.random_case(70, 48, 90, "int8", "uint8", "int8", orders="RCC", symmetric=False, seed=100 + i)
-        c.mfp, c.mexp = mfps[i % 3], e
-        if e > -8:
-            # small accumulators, so that multipliers near and above one do not saturate every output
-            r2 = np.random.default_rng(50 + i)
-            c.lhs = (c.lhs_zp + r2.integers(-1, 1, size=c.lhs.shape, endpoint=True)).astype(c.lhs.dtype)
-            c.rhs = (c.rhs_zp + r2.integers(-2, 2, size=c.rhs.shape, endpoint=True)).clip(0, 255).astype(c.rhs.dtype)
-            c.bias = r2.integers(-3, 3, size=c.bias.shape, endpoint=True).astype(np.int32)
-        if e <= -15:
-            # large biases, so that multipliers far below one still produce a spread of outputs
-            r2 = np.random.default_rng(70 + i)
-            mag = min(1 << (6 - e), 1 << 30)
-            c.bias = r2.integers(-mag, mag, size=c.bias.shape, endpoint=True).astype(np.int32)
-        c.dst_zp = (-128, 127, 3)[i % 3]
-        c.name += f"_pt_e{e}"
-        out.append(c)
-    rng = np.random.default_rng(7)
-    for j, (orders, channel) in enumerate((("RCC", ChannelDimension.kRow), ("RCC", ChannelDimension.kCol),
-                                            ("RCR", ChannelDimension.kRow), ("RCR", ChannelDimension.kCol))):
-        c = cases.random_case(70, 48, 90, "uint8", "int8", "uint8", orders=orders, symmetric=False, perchannel=True,
-                              channel=channel, seed=200 + j)
-        nch = 70 if channel == ChannelDimension.kRow else 90
-        c.mexp = rng.choice(exps, size=nch).astype(np.int32)
-        c.mfp = rng.choice(mfps, size=nch).astype(np.int32)
-        b = rng.integers(-20000, 20000, size=nch).astype(np.int64)
-        b[::7] = (1 << 30) + 5
-        b[3::7] = -(1 << 30) - 9
-        b[5::11] = (1 << 31) - 1
-        c.bias = b.astype(np.int32)
-        c.clamp = (5, 5) if j == 3 else c.clamp
-        c.name += f"_pc{j}"
-        out.append(c)
-    return out
-
-
 def test_requantization_extremes_single_muls(gpu_ctx):
-    for c in _requant_extreme_cases():
+    for c in requant_extreme_cases():
         check_case(c, gpu_ctx)
 
 
@@ -706,7 +663,7 @@ def test_requantization_extremes_in_a_plan(gpu_ctx):
     dev = torch.device("cuda", 0)
     for rounding in (Rounding.kReference, Rounding.kX86):
         bound, descs = [], []
-        for c in _requant_extreme_cases():
+        for c in requant_extreme_cases():
             dst = torch.zeros(c.dst_storage_elems(), dtype=getattr(torch, c.dst_dtype), device=dev)
             lhs, rhs, p, d, keep = c.bind(dst, device=dev, rounding=rounding)
             bound.append((c, dst, keep))

@@ -9,7 +9,7 @@ import pytest
 
 import oracle
 import util
-from golden_cases import golden_cases
+from golden_cases import golden_cases, requant_extreme_cases
 from ruy_b200 import cases
 from ruy_b200.api import ChannelDimension, Rounding
 
@@ -123,6 +123,21 @@ def _live_cases():
 
 @pytest.mark.parametrize("case", _live_cases(), ids=lambda c: c.name)
 def test_oracle_matches_compiled_reference(case):
+    if oracle.reference() is None:
+        pytest.skip("compiled reference not built on this machine")
+    ref = util.run_reference(case, reference_mul=True)
+    assert np.array_equal(util.run_oracle(case, Rounding.kReference), ref)
+    assert np.array_equal(util.run_reference(case, path=0x1), ref)
+    simd = oracle.host_simd_path()
+    if simd in (0x20, 0x40):
+        assert np.array_equal(util.run_oracle(case, util.x86_rounding_for(case)),
+                              util.run_reference(case, path=simd, threads=2))
+
+
+@pytest.mark.parametrize("case", requant_extreme_cases(), ids=lambda c: c.name)
+def test_oracle_matches_compiled_reference_on_requantization_extremes(case):
+    """Exponents from +7 to -30, multipliers at both ends of their range, biases that wrap, degenerate clamps: the C
+    restatement against ruy's own ReferenceMul, kStandardCpp and widest x86 path, compiled from the reference."""
     if oracle.reference() is None:
         pytest.skip("compiled reference not built on this machine")
     ref = util.run_reference(case, reference_mul=True)
