@@ -255,7 +255,8 @@ RUYB200_API int ruyb200_plan_stats(const ruyb200_plan* plan, uint64_t* bytes, ui
  * ruyb200_peer_signal raises, after all earlier work of the context's stream, the flag words remote_flags[i]
  * (addresses in peers' memory; the array itself lives in device memory) to `value`; ruyb200_peer_wait makes the
  * stream wait until local_flags[0..n) have all reached `value`, giving up after 2 s with RUYB200_ERR_TIMEOUT at
- * the next ruyb200_ctx_sync.  Only stores ever cross NVLink; no load reads a peer's memory. */
+ * the next ruyb200_ctx_sync.  ruyb200_peer_exchange does both in one launch (signal, then wait).  Only stores
+ * ever cross NVLink; no load reads a peer's memory. */
 RUYB200_API int ruyb200_mul_async_mirrored(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, void* const* mirror_dst,
                                            int n_mirrors);
 RUYB200_API int ruyb200_peer_alloc(size_t bytes, void** out);
@@ -265,6 +266,8 @@ RUYB200_API int ruyb200_peer_open(const unsigned char handle[64], void** out);
 RUYB200_API int ruyb200_peer_close(void* ptr);
 RUYB200_API int ruyb200_peer_signal(ruyb200_ctx* ctx, uint32_t* const* remote_flags_device_array, int n, uint32_t value);
 RUYB200_API int ruyb200_peer_wait(ruyb200_ctx* ctx, const uint32_t* local_flags, int n, uint32_t value);
+RUYB200_API int ruyb200_peer_exchange(ruyb200_ctx* ctx, uint32_t* const* remote_flags_device_array, const uint32_t* local_flags,
+                                      int n, uint32_t value);
 
 /* ---- packing: PackImpl / RunPack (ruy/pack.h:105-151) -------------------- */
 

@@ -113,6 +113,7 @@ PROTOTYPES = {
     "ruyb200_peer_close": (C.c_int, [C.c_void_p]),
     "ruyb200_peer_signal": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_uint32]),
     "ruyb200_peer_wait": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_uint32]),
+    "ruyb200_peer_exchange": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_uint32]),
     "ruyb200_mul_noalloc": (C.c_int, [_P(MulDesc), C.c_void_p]),
     "ruyb200_plan_create": (C.c_int, [C.c_void_p, _P(MulDesc), C.c_int, _P(C.c_void_p)]),
     "ruyb200_plan_run": (C.c_int, [C.c_void_p]),

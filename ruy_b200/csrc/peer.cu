@@ -46,6 +46,32 @@ __global__ void wait_kernel(const uint32_t* local_flags, int n, uint32_t value, 
   }
 }
 
+// Both in one launch: thread i raises this rank's flag in peer i's memory, then waits (bounded) for peer i's flag
+// in local memory.  The peers run on other GPUs, so nothing here waits for another launch of the same GPU.
+__global__ void exchange_kernel(uint32_t* const* remote_flags, const uint32_t* local_flags, int n, uint32_t value, int* status) {
+  const int i = threadIdx.x;
+  if (i >= n) return;
+  if (remote_flags[i]) {
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote_flags[i]), "r"(value) : "memory");
+  }
+  unsigned long long t0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  for (unsigned it = 0;; it++) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(local_flags + i) : "memory");
+    if ((int32_t)(v - value) >= 0) return;
+    if ((it & 15) == 15) {
+      unsigned long long t;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+      if (t - t0 > kWaitLimitNs) {
+        atomicCAS(status, 0, 9);   // a peer never signalled: report, do not hang
+        return;
+      }
+    }
+  }
+}
+
 }  // namespace
 
 extern "C" {
@@ -111,6 +137,15 @@ int ruyb200_peer_signal(ruyb200_ctx* ctx, uint32_t* const* remote_flags_device_a
 int ruyb200_peer_wait(ruyb200_ctx* ctx, const uint32_t* local_flags, int n, uint32_t value) {
   if (!ctx || !local_flags || n < 1 || n > 32) return ctx_fail(RUYB200_ERR_INVALID, "bad argument");
   wait_kernel<<<1, 32, 0, ctx_stream(ctx)>>>(local_flags, n, value, ctx_status_word(ctx));
+  ctx_count_launch(ctx, RUYB200_KERNEL_NONE);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? RUYB200_OK : ctx_fail(RUYB200_ERR_CUDA, cudaGetErrorString(e));
+}
+
+int ruyb200_peer_exchange(ruyb200_ctx* ctx, uint32_t* const* remote_flags_device_array, const uint32_t* local_flags, int n,
+                          uint32_t value) {
+  if (!ctx || !remote_flags_device_array || !local_flags || n < 1 || n > 32) return ctx_fail(RUYB200_ERR_INVALID, "bad argument");
+  exchange_kernel<<<1, 32, 0, ctx_stream(ctx)>>>(remote_flags_device_array, local_flags, n, value, ctx_status_word(ctx));
   ctx_count_launch(ctx, RUYB200_KERNEL_NONE);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? RUYB200_OK : ctx_fail(RUYB200_ERR_CUDA, cudaGetErrorString(e));

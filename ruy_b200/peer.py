@@ -63,8 +63,8 @@ class StepFlags:
         self.world = w
 
     def signal_and_wait(self, ctx, value):
-        _check(lib().ruyb200_peer_signal(ctx._h, C.c_void_p(self.targets.data_ptr()), self.world, value), "ruyb200_peer_signal")
-        _check(lib().ruyb200_peer_wait(ctx._h, C.c_void_p(self.buf.local_ptr), self.world, value), "ruyb200_peer_wait")
+        _check(lib().ruyb200_peer_exchange(ctx._h, C.c_void_p(self.targets.data_ptr()), C.c_void_p(self.buf.local_ptr), self.world,
+                                           value), "ruyb200_peer_exchange")
 
     def close(self):
         self.buf.close()

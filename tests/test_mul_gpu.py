@@ -485,6 +485,10 @@ def test_mirrored_destination_and_step_flags(gpu_ctx):
     assert lib().ruyb200_peer_wait(gpu_ctx._h, C.c_void_p(flag_words.data_ptr()), 2, 5) == 0
     gpu_ctx.sync()
     assert flag_words.cpu().tolist()[:3] == [5, 5, 0]
+    # both in one launch: every thread raises its flag first and then finds it raised
+    assert lib().ruyb200_peer_exchange(gpu_ctx._h, C.c_void_p(targets.data_ptr()), C.c_void_p(flag_words.data_ptr()), 2, 6) == 0
+    gpu_ctx.sync()
+    assert flag_words.cpu().tolist()[:3] == [6, 6, 0]
     # float muls cannot be mirrored
     fc = cases.config1((50, 50, 50))
     dst = torch.zeros(fc.dst_storage_elems(), dtype=torch.float32, device=dev)
