@@ -637,12 +637,6 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
   const bool streamed = synchronous && tc && n_mirrors == 0 && !ctx->no_chunks && !dst_on_device &&
                         !is_device_pointer(m_mat.data) && !should_cache(m_mat, m_is_rhs ? d.lhs.rows : d.rhs.cols) &&
                         m_host.stride_k == 1 && (m_host.stride_w & 15) == 0 && m_host.width >= 2048 && m_span >= (size_t(4) << 20);
-  // The n-side sums (needed when the m-side zero point is not zero) cost a separate pass over that operand unless
-  // the prepacked cache has them.  When the destination's outer dimension fits one or two tiles, every n tile is
-  // visited once or twice, and the epilogue can sum its rows itself while the main loop of the tile runs.
-  const ruyb200_matrix& n_mat = m_is_rhs ? d.lhs : d.rhs;
-  const bool fuse_sums_n = tc && n_mirrors == 0 && m_host.width <= 256 && depth <= 8192 &&
-                           !should_cache(n_mat, m_is_rhs ? d.rhs.cols : d.lhs.rows);
   void* m_dev = nullptr;
   if (streamed) {
     m_dev = ctx->arena.alloc(m_span);
@@ -651,14 +645,14 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
   if (streamed && !m_is_rhs) {
     lhs_v = side_view(d.lhs, 0, m_dev);
   } else {
-    rc = prepare_side(ctx, d.lhs, 0, depth, should_cache(d.lhs, d.rhs.cols), need_lhs_sums && !(tc && !m_is_rhs) && !(fuse_sums_n && m_is_rhs), tc, &lhs_v,
+    rc = prepare_side(ctx, d.lhs, 0, depth, should_cache(d.lhs, d.rhs.cols), need_lhs_sums && !(tc && !m_is_rhs), tc, &lhs_v,
                       &lhs_sums);
     if (rc) return rc;
   }
   if (streamed && m_is_rhs) {
     rhs_v = side_view(d.rhs, 1, m_dev);
   } else {
-    rc = prepare_side(ctx, d.rhs, 1, depth, should_cache(d.rhs, d.lhs.rows), need_rhs_sums && !(tc && m_is_rhs) && !(fuse_sums_n && !m_is_rhs), tc, &rhs_v,
+    rc = prepare_side(ctx, d.rhs, 1, depth, should_cache(d.rhs, d.lhs.rows), need_rhs_sums && !(tc && m_is_rhs), tc, &rhs_v,
                       &rhs_sums);
     if (rc) return rc;
   }
@@ -744,7 +738,6 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
     L.status = ctx->d_status;
     L.allow_pair = !ctx->no_pair;
     L.fuse_sums_m = true;
-    L.fuse_sums_n = fuse_sums_n;
     L.n_mirrors = n_mirrors;
     for (int i = 0; i < 7; i++) L.mirrors[i] = i < n_mirrors ? mirrors[i] : nullptr;
     TcI8Info info = {};

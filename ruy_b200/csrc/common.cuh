@@ -145,7 +145,6 @@ struct TcI8Launch {
   void* mirrors[7];  // addresses in peers' buffers that correspond to dst.data; every destination store is repeated there
   int n_mirrors;
   TcI8Info* info = nullptr;   // filled in when not null
-  bool fuse_sums_n = false;   // if ep.zp_m != 0 and ep.sums_n == nullptr, the epilogue sums the n-side rows itself while staging (small m only)
   bool fuse_sums_m;  // if ep.zp_n != 0 and ep.sums_m == nullptr, let the kernel produce the m-side sums itself
 };
 cudaError_t launch_tc_i8(const TcI8Launch& args, cudaStream_t stream);

@@ -75,9 +75,6 @@ struct KernelArgs {
   int* status;
   void* mirror[7]; // peers' copies of the destination: same layout, every store is repeated there
   int n_mirror;
-  const uint8_t* nsum_ptr;   // when not null: the n-side operand, whose rows the epilogue sums itself (no sums_n given)
-  int64_t nsum_stride;
-  int nsum_signed;
   int row_pitch;   // bytes per tile row in shared memory = width of the swizzle pattern: 128, or 64 / 32 for depth <= 64 / 32
   uint32_t desc_hi; // high word of the shared-memory matrix descriptors for that pattern
   int pack_clamps; // 8-bit destination with a clamp range inside int16: values are clamped two at a time while being narrowed
@@ -306,28 +303,6 @@ __device__ __forceinline__ bool epilogue_all(bool ok, int group, int group_threa
       : "r"((uint32_t)ok), "r"(1 + group), "r"(group_threads)
       : "memory");
   return res != 0;
-}
-
-// Sum over depth of one operand row read from global memory (16-byte aligned rows).
-__device__ __forceinline__ int32_t row_sum_global(const uint8_t* row, int depth, bool is_signed) {
-  int s = 0;
-  int k = 0;
-  for (; k + 16 <= depth; k += 16) {
-    const uint4 v = *reinterpret_cast<const uint4*>(row + k);
-    if (is_signed) {
-      s = __dp4a((int)v.x, 0x01010101, s);
-      s = __dp4a((int)v.y, 0x01010101, s);
-      s = __dp4a((int)v.z, 0x01010101, s);
-      s = __dp4a((int)v.w, 0x01010101, s);
-    } else {
-      s = (int)__dp4a(v.x, 0x01010101u, (unsigned)s);
-      s = (int)__dp4a(v.y, 0x01010101u, (unsigned)s);
-      s = (int)__dp4a(v.z, 0x01010101u, (unsigned)s);
-      s = (int)__dp4a(v.w, 0x01010101u, (unsigned)s);
-    }
-  }
-  for (; k < depth; k++) s += is_signed ? (int)(int8_t)row[k] : (int)row[k];
-  return s;
 }
 
 // Per-destination-column (n) terms of one tile, staged in shared memory by the epilogue warps.
@@ -716,11 +691,7 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
           t.exp = ep.mexp;
           t.pad = 0;
           if (n < args.size_n) {
-            if (ep.zp_m) {
-              const int32_t sum_n = ep.sums_n ? ep.sums_n[n]
-                                              : row_sum_global(args.nsum_ptr + (int64_t)n * args.nsum_stride, args.depth, args.nsum_signed != 0);
-              t.add -= ep.zp_m * sum_n;
-            }
+            if (ep.zp_m) t.add -= ep.zp_m * ep.sums_n[n];
             if (ch_n) {
               if (ep.bias) t.add += ((const int32_t*)ep.bias)[n];
               if (ep.mfp_pc) t.mul = ep.mfp_pc[n];
@@ -1094,10 +1065,6 @@ cudaError_t launch_tc_i8(const TcI8Launch& L, cudaStream_t stream) {
   a.mirror_wide = (((uintptr_t)L.dst.data | (uintptr_t)L.dst.stride_m) & 15) == 0;
   for (int i = 0; i < a.n_mirror; i++) a.mirror_wide = a.mirror_wide && ((uintptr_t)L.mirrors[i] & 15) == 0;
   a.debug = 0;
-  const bool fuse_n = L.fuse_sums_n && L.ep.zp_m != 0 && L.ep.sums_n == nullptr;
-  a.nsum_ptr = fuse_n ? (const uint8_t*)L.n_side.data : nullptr;
-  a.nsum_stride = L.n_side.stride_w;
-  a.nsum_signed = L.n_side.dtype == RUYB200_I8;
 #ifdef RUYB200_DEBUG_KNOBS
   if (getenv("RUYB200_DEBUG")) a.debug = atoi(getenv("RUYB200_DEBUG"));
 #endif
