@@ -529,7 +529,10 @@ def run_c2_arm(args):
                    "plan_build_s": plan_build_s},
         "gpu_launches": int(launches), "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
-                     "traffic": None, "kernel": "batch_i8_kernel", "algorithmic_bytes": nbytes,
+                     # DRAM bytes per launch from the ncu capture of the full 16384-mul plan on one GPU
+                     # (profiles/batch_i8_kernel_c2_full_set.md: 152.1 MB read + 40.3 MB written); not measured elsewhere
+                     "traffic": 192.4e6 if (world == 1 and n_total == 16384) else None,
+                     "kernel": "batch_i8_kernel", "algorithmic_bytes": nbytes,
                      "peak_source": f"hbm_gbs of {peaks['source']} peaks"},
         "tops": total_ops / (ms * 1e-3) / 1e12,
     }
