@@ -284,6 +284,10 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
   const int lane = threadIdx.x % 32;
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
 
+  // the tensor maps of this CTA's first items start their way from HBM while the barriers and tensor memory are set up
+  if (warp < kPackWarps && lane < 2 && (int)blockIdx.x + warp * (int)gridDim.x < num_items) {
+    prefetch_map(maps + 2 * (size_t)(blockIdx.x + warp * gridDim.x) + lane);
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < kSlots; s++) {
       mbar_init(&full_bar[s], 32 + 1);       // every pack lane's copies + the header
