@@ -342,12 +342,13 @@ __device__ __forceinline__ void store_run32_at(char* dst_base, const KernelArgs&
   char* base = dst_base + ((int64_t)m * a.dst.stride_m + n0) * kDstBytes;
   const bool full = n0 + 32 <= n_end;   // n_end: end of this tile's columns (and of the destination)
   if (full && (((uintptr_t)base) & 15) == 0) {
+    // streaming stores: the destination is written once and never read here, it should not displace the operands in L2
     uint4* out = (uint4*)base;
     if (kDstBytes == 1) {
       uint32_t w[8];
       narrow_u8x32(v, a.pack_clamps != 0, a.clamp_lo2, a.clamp_hi2, w);
-      out[0] = make_uint4(w[0], w[1], w[2], w[3]);
-      out[1] = make_uint4(w[4], w[5], w[6], w[7]);
+      __stcs(&out[0], make_uint4(w[0], w[1], w[2], w[3]));
+      __stcs(&out[1], make_uint4(w[4], w[5], w[6], w[7]));
     } else if (kDstBytes == 2) {
 #pragma unroll
       for (int q = 0; q < 4; q++) {
@@ -356,12 +357,12 @@ __device__ __forceinline__ void store_run32_at(char* dst_base, const KernelArgs&
         for (int t = 0; t < 4; t++) {
           w[t] = (uint32_t)(v[8 * q + 2 * t] & 0xffff) | ((uint32_t)(v[8 * q + 2 * t + 1] & 0xffff) << 16);
         }
-        out[q] = make_uint4(w[0], w[1], w[2], w[3]);
+        __stcs(&out[q], make_uint4(w[0], w[1], w[2], w[3]));
       }
     } else {
 #pragma unroll
       for (int q = 0; q < 8; q++) {
-        out[q] = make_uint4((uint32_t)v[4 * q], (uint32_t)v[4 * q + 1], (uint32_t)v[4 * q + 2], (uint32_t)v[4 * q + 3]);
+        __stcs(&out[q], make_uint4((uint32_t)v[4 * q], (uint32_t)v[4 * q + 1], (uint32_t)v[4 * q + 2], (uint32_t)v[4 * q + 3]));
       }
     }
     return;
@@ -450,8 +451,9 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
   __shared__ __align__(8) uint64_t acc_empty_bar[kMaxAccBufs];
   // per-n terms of the tile being drained, one array per field so that the common paths fetch four addends per load
   __shared__ __align__(16) int32_t nt_add_s[kEpilogueGroups][kMaxBlockN];
-  __shared__ __align__(16) int32_t nt_mul_s[kEpilogueGroups][kMaxBlockN];
-  __shared__ __align__(16) int32_t nt_exp_s[kEpilogueGroups][kMaxBlockN];
+  // {addend, multiplier, high word of the rounding term (+ destination zero point), shift - 32} per n, for
+  // multipliers that vary along n: one 16-byte load per element
+  __shared__ __align__(16) int4 nt4_s[kEpilogueGroups][kMaxBlockN];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -661,6 +663,7 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
     uint32_t tcount = 0;
     bool ok = true;
     int staged_tn = -1;            // which n tile this group's staging buffer holds
+    bool tile_fast = false;        // every n of that tile allows the short requantisation with per-n multipliers
 #ifdef RUYB200_DEBUG_KNOBS
     long long dbg_wait = 0, dbg_busy = 0, dbg_stage = 0;
 #endif
@@ -676,13 +679,13 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
       // stage the per-n terms of this tile (overlaps the tile's main loop) unless the group's buffer already holds
       // them (there is one n tile, or it did not change)
       int32_t* nt_add = nt_add_s[group];
-      int32_t* nt_mul = nt_mul_s[group];
-      int32_t* nt_exp = nt_exp_s[group];
+      int4* nt4 = nt4_s[group];
       const bool restage = staged_tn != tn;
       if (restage) {
         // warps of this group may still be reading the buffer for the previous tile
         epilogue_all(true, group, group_threads);
         staged_tn = tn;
+        bool my_fast = true;
         for (int i = etid; i < args.block_n; i += group_threads) {
           const int n = tn * args.block_n + i;
           NTerms t;
@@ -699,9 +702,17 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
             }
           }
           nt_add[i] = t.add;
-          nt_mul[i] = t.mul;
-          nt_exp[i] = t.exp;
+          // total shift 33..45: the rounding term has no low word and the zero point fits beside it, so that
+          // result = (mulhi(x, mul) + rnd_hi) >> (shift - 32); other shifts take the general path
+          const int sh = 31 - t.exp;
+          const bool n_fast = n >= args.size_n || (sh >= 33 && sh <= 45 && ep.dst_zp > -32768 && ep.dst_zp < 32768);
+          my_fast = my_fast && n_fast;
+          const int sh_hi = sh - 32;
+          const int32_t rnd_hi = n_fast ? (int32_t)(1u << ((sh - 33) & 31)) + ep.dst_zp * (int32_t)(1u << (sh_hi & 31)) : 0;
+          nt4[i] = make_int4(t.add, t.mul, rnd_hi, sh_hi);
         }
+        // every n of the tile must qualify; the reduction also publishes the staged terms
+        tile_fast = epilogue_all(my_fast, group, group_threads);
       }
       // per-m terms of this thread's row
       const int m = tm * kUnitM + (int)rank * kBlockM + lane_group * 32 + lane;
@@ -762,7 +773,15 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
       // 8-bit destinations leave the clamp to the narrowing step (two values per instruction there)
       const bool late_clamp = kDstBytes == 1 && args.pack_clamps;
       auto finish_chunk = [&](int c, int32_t (&v)[32]) {
-        if (high_word || (kDstBytes != 4 && !kX86 && !mul_varies_with_n)) {
+        if (kDstBytes != 4 && !kX86 && mul_varies_with_n && tile_fast) {
+#pragma unroll
+          for (int q = 0; q < 32; q++) {
+            const int4 t = nt4[c + q];
+            const int32_t x = (int32_t)(r[q] + (uint32_t)t.x + (uint32_t)add_m);
+            const int32_t y = (__mulhi(x, t.y) + t.z) >> t.w;
+            v[q] = late_clamp ? y : max(min(y, ep.clamp_max), ep.clamp_min);
+          }
+        } else if (high_word || (kDstBytes != 4 && !kX86 && !mul_varies_with_n)) {
 #pragma unroll
           for (int q4 = 0; q4 < 8; q4++) {
             const int4 ad = *reinterpret_cast<const int4*>(&nt_add[c + 4 * q4]);   // c is a multiple of 32
@@ -786,8 +805,9 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
           for (int q = 0; q < 32; q++) {
             int32_t x = (int32_t)(r[q] + (uint32_t)nt_add[c + q] + (uint32_t)add_m);
             if (kDstBytes != 4) {
-              const int32_t mul = ch_n ? nt_mul[c + q] : mul_m;
-              const int e = ch_n ? nt_exp[c + q] : exp_m;
+              const int4 t = nt4[c + q];
+              const int32_t mul = ch_n ? t.y : mul_m;
+              const int e = ch_n ? -1 - t.w : exp_m;     // t.w holds 31 - e - 32
               x = kX86 ? requant_x86(x, mul, e) : requant_reference(x, mul, e);
               x = (int32_t)((uint32_t)x + (uint32_t)ep.dst_zp);
               if (!late_clamp) x = max(min(x, ep.clamp_max), ep.clamp_min);
