@@ -507,11 +507,13 @@ int choose_kernel(const ruyb200_ctx* ctx, const ruyb200_mul_desc& d) {
   return RUYB200_KERNEL_GENERIC;
 }
 
-// The chunked path of a synchronous tensor-core mul whose m-side operand and destination live on the host.
+// The chunked path of a synchronous tensor-core mul whose m-side operand and/or destination live on the host
+// (m_host / dst_host are null for the one that is already on the device).
 // `L` describes the whole mul with device addresses (the m-side buffer is still empty); chunk c covers m
 // indices [c * step, ...): its operand rows are copied in on `copy_in`, its kernel runs on the context's
 // stream once they have arrived, and its destination rows leave on `copy_out` once the kernel is done.
-int run_chunks(ruyb200_ctx* ctx, const ruyb200_mul_desc& d, const TcI8Launch& L, const char* m_host, size_t dst_esz) {
+int run_chunks(ruyb200_ctx* ctx, const ruyb200_mul_desc& d, const TcI8Launch& L, const char* m_host, char* dst_host,
+               size_t dst_esz) {
   if (!ctx->copy_in) {
     CUDA_TRY(cudaStreamCreateWithFlags(&ctx->copy_in, cudaStreamNonBlocking));
     CUDA_TRY(cudaStreamCreateWithFlags(&ctx->copy_out, cudaStreamNonBlocking));
@@ -524,14 +526,15 @@ int run_chunks(ruyb200_ctx* ctx, const ruyb200_mul_desc& d, const TcI8Launch& L,
   const int width = L.m_side.width;
   const int64_t stride_w = L.m_side.stride_w;            // bytes: the operand is 8-bit
   // chunks of a multiple of 256 m indices (whole two-CTA tiles), about eight of them, at least 1 MiB each
+  const size_t dst_pitch = (size_t)d.dst.stride * dst_esz;
+  const int64_t moved_per_m = (m_host ? stride_w : 0) + (dst_host ? (int64_t)dst_pitch : 0);   // bytes over PCIe per m index
   int step = ((width + 7) / 8 + 255) / 256 * 256;
-  while ((int64_t)step * stride_w < (1 << 20) && step < width) step *= 2;
+  while ((int64_t)step * moved_per_m < (1 << 20) && step < width) step *= 2;
   int chunks = (width + step - 1) / step;
   if (chunks > kMaxChunks) {
     step = ((width + kMaxChunks - 1) / kMaxChunks + 255) / 256 * 256;
     chunks = (width + step - 1) / step;
   }
-  const size_t dst_pitch = (size_t)d.dst.stride * dst_esz;
   const size_t dst_row_bytes = (size_t)L.dst.size_n * dst_esz;
   // the copy streams start after whatever the context's stream has queued (operand staging, packing)
   CUDA_TRY(cudaEventRecord(ctx->chunk_start, ctx->stream));
@@ -542,10 +545,12 @@ int run_chunks(ruyb200_ctx* ctx, const ruyb200_mul_desc& d, const TcI8Launch& L,
     const int w = std::min(step, width - w0);
     const size_t off = (size_t)w0 * (size_t)stride_w;
     const size_t span = (size_t)(w - 1) * (size_t)stride_w + (size_t)L.depth;
-    CUDA_TRY(cudaMemcpyAsync((char*)L.m_side.data + off, m_host + off, span, cudaMemcpyHostToDevice, ctx->copy_in));
-    ctx->counters[3] += span;
-    CUDA_TRY(cudaEventRecord(ctx->chunk_in[c], ctx->copy_in));
-    CUDA_TRY(cudaStreamWaitEvent(ctx->stream, ctx->chunk_in[c], 0));
+    if (m_host) {
+      CUDA_TRY(cudaMemcpyAsync((char*)L.m_side.data + off, m_host + off, span, cudaMemcpyHostToDevice, ctx->copy_in));
+      ctx->counters[3] += span;
+      CUDA_TRY(cudaEventRecord(ctx->chunk_in[c], ctx->copy_in));
+      CUDA_TRY(cudaStreamWaitEvent(ctx->stream, ctx->chunk_in[c], 0));
+    }
     TcI8Launch part = L;
     part.m_side.data = (const char*)L.m_side.data + off;
     part.m_side.width = w;
@@ -561,13 +566,15 @@ int run_chunks(ruyb200_ctx* ctx, const ruyb200_mul_desc& d, const TcI8Launch& L,
     cudaError_t ce = launch_tc_i8(part, ctx->stream);
     ctx->counters[0]++;
     if (ce != cudaSuccess) return fail(RUYB200_ERR_CUDA, "kernel launch: %s", cudaGetErrorString(ce));
-    CUDA_TRY(cudaEventRecord(ctx->chunk_done[c], ctx->stream));
-    CUDA_TRY(cudaStreamWaitEvent(ctx->copy_out, ctx->chunk_done[c], 0));
-    CUDA_TRY(cudaMemcpy2DAsync((char*)d.dst.data + (size_t)w0 * dst_pitch, dst_pitch, part.dst.data, dst_pitch, dst_row_bytes, w,
-                               cudaMemcpyDeviceToHost, ctx->copy_out));
-    ctx->counters[4] += dst_row_bytes * (size_t)w;
+    if (dst_host) {
+      CUDA_TRY(cudaEventRecord(ctx->chunk_done[c], ctx->stream));
+      CUDA_TRY(cudaStreamWaitEvent(ctx->copy_out, ctx->chunk_done[c], 0));
+      CUDA_TRY(cudaMemcpy2DAsync(dst_host + (size_t)w0 * dst_pitch, dst_pitch, part.dst.data, dst_pitch, dst_row_bytes, w,
+                                 cudaMemcpyDeviceToHost, ctx->copy_out));
+      ctx->counters[4] += dst_row_bytes * (size_t)w;
+    }
   }
-  CUDA_TRY(cudaStreamSynchronize(ctx->copy_out));
+  if (dst_host) CUDA_TRY(cudaStreamSynchronize(ctx->copy_out));
   return RUYB200_OK;
 }
 
@@ -634,22 +641,26 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
   const ruyb200_matrix& m_mat = m_is_rhs ? d.rhs : d.lhs;
   const SideView m_host = side_view(m_mat, m_is_rhs ? 1 : 0, m_mat.data);
   const size_t m_span = storage_span_bytes(m_mat);
-  const bool streamed = synchronous && tc && n_mirrors == 0 && !ctx->no_chunks && !dst_on_device &&
-                        !is_device_pointer(m_mat.data) && !should_cache(m_mat, m_is_rhs ? d.lhs.rows : d.rhs.cols) &&
-                        m_host.stride_k == 1 && (m_host.stride_w & 15) == 0 && m_host.width >= 2048 && m_span >= (size_t(4) << 20);
+  const bool m_on_host = !is_device_pointer(m_mat.data);
+  const size_t dst_span = (size_t)(m_is_rhs ? d.dst.cols : d.dst.rows) * (size_t)d.dst.stride * dtype_size(d.dst.dtype);
+  const bool streamed = synchronous && tc && n_mirrors == 0 && !ctx->no_chunks && (m_on_host || !dst_on_device) &&
+                        !should_cache(m_mat, m_is_rhs ? d.lhs.rows : d.rhs.cols) && m_host.stride_k == 1 &&
+                        (m_host.stride_w & 15) == 0 && ((uintptr_t)m_mat.data & 15) == 0 && m_host.width >= 2048 &&
+                        (m_on_host ? m_span : 0) + (dst_on_device ? 0 : dst_span) >= (size_t(4) << 20);
+  const bool m_streamed = streamed && m_on_host;   // the m-side operand itself travels in chunks
   void* m_dev = nullptr;
-  if (streamed) {
+  if (m_streamed) {
     m_dev = ctx->arena.alloc(m_span);
     if (!m_dev) return fail(RUYB200_ERR_OOM, "arena allocation of %zu bytes failed", m_span);
   }
-  if (streamed && !m_is_rhs) {
+  if (m_streamed && !m_is_rhs) {
     lhs_v = side_view(d.lhs, 0, m_dev);
   } else {
     rc = prepare_side(ctx, d.lhs, 0, depth, should_cache(d.lhs, d.rhs.cols), need_lhs_sums && !(tc && !m_is_rhs), tc, &lhs_v,
                       &lhs_sums);
     if (rc) return rc;
   }
-  if (streamed && m_is_rhs) {
+  if (m_streamed && m_is_rhs) {
     rhs_v = side_view(d.rhs, 1, m_dev);
   } else {
     rc = prepare_side(ctx, d.rhs, 1, depth, should_cache(d.rhs, d.lhs.rows), need_rhs_sums && !(tc && m_is_rhs), tc, &rhs_v,
@@ -753,7 +764,7 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
       }
     } trace_at_exit{ctx, d, info, ep.rounding_x86 != 0, streamed, n_mirrors};
     if (streamed) {
-      rc = run_chunks(ctx, d, L, (const char*)m_mat.data, dst_esz);
+      rc = run_chunks(ctx, d, L, m_streamed ? (const char*)m_mat.data : nullptr, dst_on_device ? nullptr : (char*)d.dst.data, dst_esz);
       if (rc) return rc;
       ctx->counters[5] = kernel;
       return ruyb200_ctx_sync(ctx);

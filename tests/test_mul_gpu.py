@@ -190,6 +190,32 @@ def test_large_host_operands_take_the_chunked_path(gpu_ctx):
         assert util.padding_untouched(c, storage, 55)
 
 
+def test_chunked_path_with_only_one_side_on_the_host(gpu_ctx):
+    """The same chunking when only the destination, or only the wide operand, is host memory."""
+    dev = torch.device("cuda", 0)
+    # device operands, large host destination
+    c = cases.random_case(2048, 64, 2176, "uint8", "uint8", "uint8", orders="RCC", extra_stride=16, perchannel=True,
+                          symmetric=False, seed=6)
+    lhs, rhs, p, d, keep = c.bind(torch.zeros(c.dst_storage_elems(), dtype=torch.uint8, device=dev), device=dev,
+                                  rounding=Rounding.kReference)
+    host_dst = c.new_dst()
+    d.data = host_dst
+    before = gpu_ctx.counters()["launches"]
+    ruy_b200.mul(lhs, rhs, p, gpu_ctx, d)
+    assert gpu_ctx.counters()["launches"] - before >= 4
+    assert np.array_equal(c.dst_view(host_dst), util.run_oracle(c, Rounding.kReference))
+    # large host right-hand side (the chunked operand), device destination
+    c = cases.random_case(64, 2048, 2176, "uint8", "uint8", "uint8", orders="RCC", extra_stride=16, perchannel=True,
+                          symmetric=False, seed=6)
+    dst_dev = torch.zeros(c.dst_storage_elems(), dtype=torch.uint8, device=dev)
+    lhs, rhs, p, d, keep = c.bind(dst_dev, device=dev, rounding=Rounding.kReference)
+    rhs.data = c.rhs
+    before = gpu_ctx.counters()["launches"]
+    ruy_b200.mul(lhs, rhs, p, gpu_ctx, d)
+    assert gpu_ctx.counters()["launches"] - before >= 4
+    assert np.array_equal(c.dst_view(dst_dev.cpu().numpy()), util.run_oracle(c, Rounding.kReference))
+
+
 def test_mul_async_on_device_operands(gpu_ctx):
     c = cases.config0(exps=(-17, -13))
     got, _ = util.run_gpu(c, gpu_ctx, rounding=Rounding.kReference, use_async=True)
