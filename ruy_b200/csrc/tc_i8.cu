@@ -195,7 +195,7 @@ __device__ __forceinline__ uint32_t desc_lo(uint32_t smem_addr) { return ((smem_
 // inside a single asm block.  `first_accumulates` is 0 only for the first stage of a tile.
 template <bool kPair>
 __device__ __forceinline__ void mma_stage4(uint32_t tmem_d, uint32_t lo_a, uint32_t lo_b, uint32_t idesc,
-                                           uint32_t first_accumulates, uint32_t desc_hi = kDescHi) {
+                                           uint32_t first_accumulates) {
   if (kPair) {
     asm volatile(
         "{\n\t.reg .pred p, t;\n\t.reg .b64 da, db;\n\t.reg .b32 la, lb;\n\t"
@@ -1123,8 +1123,10 @@ cudaError_t launch_tc_i8(const TcI8Launch& L, cudaStream_t stream) {
   // Shallow operands use a narrower swizzle pattern: the copy engine then moves 32 or 64 bytes per row instead of
   // 128 (mostly out-of-range zero fill), which is what bounds tiles whose depth is a single MMA step or two.
   a.row_pitch = L.depth <= 32 ? 32 : (L.depth <= 64 ? 64 : 128);
+#ifdef RUYB200_DEBUG_KNOBS
   const char* np_env = getenv("RUYB200_WIDE_ROWS");
   if (np_env && *np_env == '1') a.row_pitch = 128;
+#endif
   // stride byte offset (8 rows) at bits 32..45, descriptor version 1 at bit 46, swizzle mode at bits 61..63 (2: 128 B, 4: 64 B, 6: 32 B)
   a.desc_hi = ((uint32_t)(8 * a.row_pitch) >> 4) | (1u << 14) | ((a.row_pitch == 128 ? 2u : (a.row_pitch == 64 ? 4u : 6u)) << 29);
   CUtensorMap map_m, map_n;
@@ -1145,8 +1147,10 @@ cudaError_t launch_tc_i8(const TcI8Launch& L, cudaStream_t stream) {
     // The tile schedule is static, so every pair must be resident from the start: size the grid
     // by the number of 2-CTA clusters the device can hold at once.
     int pairs = max_resident_pairs(L.sm_count);
+#ifdef RUYB200_DEBUG_KNOBS
     const char* env = getenv("RUYB200_PAIRS");
     if (env && atoi(env) > 0 && atoi(env) < pairs) pairs = atoi(env);
+#endif
     const int grid = 2 * (int)(tiles < pairs ? tiles : pairs);
     return launch_by_type<true>(map_m, map_n, a, grid, stream);
   }
