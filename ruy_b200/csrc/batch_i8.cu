@@ -13,8 +13,9 @@
 //                  cached zero-point sums ride along as bulk copies (or cp.async).  Six whole items are in
 //                  flight per SM, which is what keeps enough bytes outstanding to use the HBM bandwidth.
 //   * warps 6-7  : alternate items; one elected lane issues the item's tcgen05.mma kind::i8 (M=128, N<=128,
-//                  K=32) into one of four tensor-memory accumulators, from descriptors the pack warp left
-//                  in the slot.
+//                  K=32) from descriptors the pack warp left in the slot, into the item's accumulator: one
+//                  or two of eight 64-column units of tensor memory, handed out by the plan as a ring, so
+//                  up to eight items can sit between MMA and epilogue.
 //   * warps 8-23 : epilogue, four groups of four warps; group g drains accumulator g.  Zero-point sums
 //                  are taken from the packed tile, per-column terms are staged in shared memory, then
 //                  tcgen05.ld, bias, zero-point terms, fixed-point multiplier, zero point, clamp
@@ -39,11 +40,12 @@ namespace {
 constexpr int kSlots = 6;                          // one per pack warp
 constexpr int kTileBytes = 16 * 1024;             // one operand: up to 128 rows x 128 bytes of depth
 constexpr int kSlotBytes = 2 * kTileBytes;
-constexpr int kAccBuffers = 4;                    // one per epilogue group
-constexpr int kAccCols = 128;
+constexpr int kAccUnits = kBatchAccUnits;        // 64-column accumulator units; an item takes one or two (assigned by the plan)
+constexpr int kUnitCols = 64;
+constexpr int kAccCols = 128;                     // most columns one item can use
 constexpr int kTmemCols = 512;                     // allocation must be a power of two
 constexpr int kPackWarps = kSlots;
-constexpr int kEpiGroups = kAccBuffers;
+constexpr int kEpiGroups = 4;
 constexpr int kEpiWarps = 4 * kEpiGroups;         // each group covers the four TMEM lane quarters
 constexpr int kMmaWarp = kPackWarps;                // warps 6 and 7 issue the MMAs of alternate items
 constexpr int kMmaWarps = 2;
@@ -55,7 +57,7 @@ constexpr uint32_t kSpinLimit = 1u << 24;   // probes per wait before it gives u
 // What the MMA warp needs for one item, prepared by the pack warp: descriptor halves and K steps of both tiles.
 struct alignas(16) MmaCmd {
   uint32_t lo_m, hi_m, lo_n, hi_n;
-  uint32_t kstep_m, kstep_n, idesc, nk_fence;   // nk_fence: K=32 steps, bit 31 = a tile was written by cp.async
+  uint32_t kstep_m, kstep_n, idesc, nk_fence;   // nk_fence: K=32 steps (bits 0-7), BatchItem::acc (bits 8-13), bit 31 = a tile was written by cp.async
 };
 
 struct NTerm {
@@ -271,12 +273,12 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kSlots];     // packed data of a slot is in place
   __shared__ __align__(8) uint64_t empty_bar[kSlots];    // MMAs have read the slot and the epilogue has read its header
-  __shared__ __align__(8) uint64_t acc_full_bar[kAccBuffers];
-  __shared__ __align__(8) uint64_t acc_empty_bar[kAccBuffers];
+  __shared__ __align__(8) uint64_t acc_full_bar[kAccUnits];
+  __shared__ __align__(8) uint64_t acc_empty_bar[kAccUnits];
   __shared__ __align__(16) BatchItem slot_item[kSlots];
   __shared__ MmaCmd slot_cmd[kSlots];
   __shared__ __align__(16) int32_t slot_vec[kSlots][4][128];   // the item's bias / multiplier / exponent vectors and cached m-side sums
-  __shared__ __align__(16) NTerm n_terms[kAccBuffers][kAccCols];
+  __shared__ __align__(16) NTerm n_terms[kEpiGroups][kAccCols];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -293,7 +295,7 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
       mbar_init(&full_bar[s], 32 + 1);       // every pack lane's copies + the header
       mbar_init(&empty_bar[s], 1 + 4);       // the MMA commit + the four warps of the epilogue group
     }
-    for (int b = 0; b < kAccBuffers; b++) {
+    for (int b = 0; b < kAccUnits; b++) {
       mbar_init(&acc_full_bar[b], 1);
       mbar_init(&acc_empty_bar[b], 4);
     }
@@ -439,7 +441,7 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
         cmd.lo_n = dn.lo; cmd.hi_n = dn.hi; cmd.kstep_n = dn.kstep;
         cmd.idesc = (2u << 4) | ((flags & kItemMSigned ? 1u : 0u) << 7) | ((flags & kItemNSigned ? 1u : 0u) << 10) |
                     ((uint32_t)(((size_n + 15) & ~15) >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-        cmd.nk_fence = (uint32_t)(kpad >> 5) | (((flags & (kItemMTma | kItemNTma)) != (kItemMTma | kItemNTma)) ? 0x80000000u : 0u);
+        cmd.nk_fence = (uint32_t)(kpad >> 5) | ((item.acc & 0x3fu) << 8) | (((flags & (kItemMTma | kItemNTma)) != (kItemMTma | kItemNTma)) ? 0x80000000u : 0u);
         slot_cmd[s] = cmd;
       }
       __syncwarp();
@@ -462,32 +464,40 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
     long long dbg_acc = 0, dbg_full = 0, dbg_t0 = clock64();
 #endif
     for (int it = mw; it < my_count; it += kMmaWarps) {
-      const int buf = it % kAccBuffers;
-      const uint32_t aph = (it / kAccBuffers) & 1;
       const int s = it % kSlots;
       const uint32_t ph = (it / kSlots) & 1;
 #ifdef RUYB200_DEBUG_CLOCKS
       long long dbg_a = clock64();
 #endif
-      bool ok = mbar_wait_warp(&acc_empty_bar[buf], aph ^ 1, abortp);
+      // the packed data first (the slot also says which accumulator units the item takes), then the units
+      bool ok = mbar_wait_warp(&full_bar[s], ph, abortp);
 #ifdef RUYB200_DEBUG_CLOCKS
       long long dbg_b = clock64();
-      dbg_acc += dbg_b - dbg_a;
+      dbg_full += dbg_b - dbg_a;
 #endif
-      ok = ok && mbar_wait_warp(&full_bar[s], ph, abortp);
+      uint4 c0 = make_uint4(0u, 0u, 0u, 0u), c1 = c0;
+      int unit = 0;
+      bool two = false;
+      if (ok) {
+        c0 = reinterpret_cast<const uint4*>(&slot_cmd[s])[0];   // lo_m, hi_m, lo_n, hi_n
+        c1 = reinterpret_cast<const uint4*>(&slot_cmd[s])[1];   // kstep_m, kstep_n, idesc, nk_fence
+        const uint32_t acc = (c1.w >> 8) & 0x3fu;
+        unit = (int)(acc & 7u);
+        two = (acc & 8u) != 0;
+        ok = mbar_wait_warp(&acc_empty_bar[unit], ((acc >> 4) & 1u) ^ 1u, abortp);
+        if (ok && two) ok = mbar_wait_warp(&acc_empty_bar[unit + 1], ((acc >> 5) & 1u) ^ 1u, abortp);
+      }
 #ifdef RUYB200_DEBUG_CLOCKS
-      dbg_full += clock64() - dbg_b;
+      dbg_acc += clock64() - dbg_b;
 #endif
       if (!ok) {
         if (lane == 0) { if (!*abortp) atomicCAS(status, 0, 2); *abortp = 1; }
         break;
       }
-      const uint4 c0 = reinterpret_cast<const uint4*>(&slot_cmd[s])[0];   // lo_m, hi_m, lo_n, hi_n
-      const uint4 c1 = reinterpret_cast<const uint4*>(&slot_cmd[s])[1];   // kstep_m, kstep_n, idesc, nk_fence
       // a tile filled by cp.async was written through the generic proxy; the tensor core reads through the async proxy
       if (c1.w & 0x80000000u) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tc_fence_after();
-      const uint32_t tmem_d = tmem_base + (uint32_t)(buf * kAccCols);
+      const uint32_t tmem_d = tmem_base + (uint32_t)(unit * kUnitCols);
       const int nk = (int)(c1.w & 0xffu);
       if (elect_one()) {
 #ifdef RUYB200_DEBUG_KNOBS
@@ -499,12 +509,14 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
 #ifdef RUYB200_DEBUG_KNOBS
         if (debug & 4096) {
           mbar_arrive(&empty_bar[s]);
-          mbar_arrive(&acc_full_bar[buf]);
+          mbar_arrive(&acc_full_bar[unit]);
+          if (two) mbar_arrive(&acc_full_bar[unit + 1]);
         } else
 #endif
         {
           mma_commit(&empty_bar[s]);
-          mma_commit(&acc_full_bar[buf]);
+          mma_commit(&acc_full_bar[unit]);
+          if (two) mma_commit(&acc_full_bar[unit + 1]);   // keeps the second unit's barrier phases in step with its use count
         }
       }
       __syncwarp();
@@ -515,23 +527,29 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
              clock64() - dbg_t0, dbg_acc, dbg_full, my_count);
 #endif
   } else if (warp >= kFirstEpiWarp) {
-    // ---------------- epilogue: group g drains accumulator g, i.e. items g, g + 4, ... ----------------
+    // ---------------- epilogue: group g drains items g, g + 4, ... from whichever accumulator units they were given ----------------
     const int group = (warp - kFirstEpiWarp) / 4;
     const int quarter = warp % 4;          // TMEM lane quarter this warp may read
     const int gtid = (warp - kFirstEpiWarp) % 4 * 32 + lane;
-    const int buf = group;
-    uint32_t aph = 0;
-    NTerm* nt = n_terms[buf];
+    NTerm* nt = n_terms[group];
 #ifdef RUYB200_DEBUG_CLOCKS
     long long dbg_wait = 0, dbg_stage = 0, dbg_work = 0, dbg_t0 = clock64();
 #endif
-    for (int it = group; it < my_count; it += kEpiGroups, aph ^= 1) {
+    for (int it = group; it < my_count; it += kEpiGroups) {
       const int s = it % kSlots;
 #ifdef RUYB200_DEBUG_CLOCKS
       long long dbg_a = clock64();
 #endif
-      // only the group's first warp probes the barrier; the group barrier below releases the others
-      bool ok = quarter != 0 ? true : mbar_wait_warp(&acc_full_bar[buf], aph, abortp);
+      // Only the group's first warp probes barriers; the group barrier below releases the others.  It waits for the
+      // slot's data first, because the slot's header says which accumulator unit (and which of its phases) to wait for.
+      bool ok = true;
+      if (quarter == 0) {
+        ok = mbar_wait_warp(&full_bar[s], (uint32_t)(it / kSlots) & 1u, abortp);
+        if (ok) {
+          const uint32_t a = slot_item[s].acc;
+          ok = mbar_wait_warp(&acc_full_bar[a & 7u], (a >> 4) & 1u, abortp);
+        }
+      }
 #ifdef RUYB200_DEBUG_CLOCKS
       long long dbg_b = clock64();
       dbg_wait += dbg_b - dbg_a;
@@ -543,11 +561,20 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
 #ifdef RUYB200_DEBUG_KNOBS
       if (debug & 8192) {
         __syncwarp();
-        if (lane == 0) { mbar_arrive(&empty_bar[s]); mbar_arrive(&acc_empty_bar[buf]); }
+        const uint32_t a = slot_item[s].acc;
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&empty_bar[s]);
+          mbar_arrive(&acc_empty_bar[a & 7u]);
+          if (a & 8u) mbar_arrive(&acc_empty_bar[(a & 7u) + 1]);
+        }
         continue;
       }
 #endif
       const BatchItem& item = slot_item[s];   // valid until this group has arrived on empty_bar[s]
+      const uint32_t acc = item.acc;
+      const int unit = (int)(acc & 7u);
+      const bool two_units = (acc & 8u) != 0;
       const bool ch_n = (item.flags & kItemChannelOnN) != 0;
       const bool x86 = (item.flags & kItemX86) != 0;
       const int dst_dtype = (int)((item.flags >> kItemDstShift) & 7u);
@@ -610,7 +637,7 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
 #endif
       const bool quarter_used = quarter * 32 + 32 > m_off && quarter * 32 < m_off + size_m;
       if (quarter_used) {
-        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * kAccCols);
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(unit * kUnitCols);
         const int esz = dst_dtype == RUYB200_I32 ? 4 : (dst_dtype == RUYB200_I16 ? 2 : 1);
         const int64_t step = (int64_t)dst_stride * esz;
         uint8_t* out = dst_base + (int64_t)m * esz;
@@ -711,7 +738,10 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty_bar[buf]);
+      if (lane == 0) {
+        mbar_arrive(&acc_empty_bar[unit]);
+        if (two_units) mbar_arrive(&acc_empty_bar[unit + 1]);
+      }
 #ifdef RUYB200_DEBUG_CLOCKS
       dbg_work += clock64() - dbg_c;
 #endif

@@ -46,7 +46,11 @@ struct alignas(16) BatchItem {
   int32_t mexp;
   uint32_t flags;
   int32_t m_off;       // first tile row (TMEM lane) used by this item: 0, 32, 64 or 96; spreads small items over the lane quarters
-  int32_t reserved[3];
+  // Tensor-memory columns of this item's accumulator, assigned by the plan in schedule order: bits 0-2 first
+  // 64-column unit, bit 3 set if it takes two units (more than 64 destination columns along n), bits 4 / 5 the
+  // parity of the first / second unit's use count (which phase of the unit's barriers this item sees).
+  uint32_t acc;
+  int32_t reserved[2];
 };
 static_assert(sizeof(BatchItem) == 128, "BatchItem is copied as eight 16-byte pieces");
 
@@ -63,6 +67,10 @@ cudaError_t launch_batch_i8(const BatchItem* items, const CUtensorMap* maps, int
 // Tensor map over a width x depth byte matrix (depth contiguous, rows stride_w bytes apart) whose copies land
 // as rows of 128 bytes with the 128-byte swizzle, zero-filled past depth and width: `box_rows` rows per copy.
 bool make_i8_tile_map(CUtensorMap* map, const void* base, int depth, int width, int64_t stride_w, int box_rows);
+
+// Accumulator units (64 tensor-memory columns each) per SM and what an item takes.
+constexpr int kBatchAccUnits = 8;
+inline int batch_acc_units(int size_n) { return size_n > 64 ? 2 : 1; }
 
 // Rows copied for an item's sides (also the byte count the copy reports: 128 bytes per row).
 inline int batch_box_rows_m(int size_m) { return (size_m + 7) & ~7; }

@@ -106,6 +106,10 @@ int ruyb200_plan_create(ruyb200_ctx* ctx, const ruyb200_mul_desc* descs, int n, 
     // that the epilogue work spreads evenly over the SM's four schedulers.
     std::vector<BatchItem> scheduled(items.size());
     std::vector<int> rot32(grid, 0), rot64(grid, 0);
+    // Accumulator units are handed out per CTA as a ring, in the order the CTA will meet its items; the parity of a
+    // unit's use count tells the kernel which phase of that unit's barriers the item waits for.
+    struct AccRing { int next = 0; int uses[kBatchAccUnits] = {}; };
+    std::vector<AccRing> rings(grid);
     for (size_t pos = 0; pos < order.size(); pos++) {
       BatchItem it = items[order[pos]];
       const int cta = (int)(pos % grid);
@@ -116,6 +120,14 @@ int ruyb200_plan_create(ruyb200_ctx* ctx, const ruyb200_mul_desc* descs, int n, 
       } else {
         it.m_off = 0;
       }
+      AccRing& ring = rings[cta];
+      const int units = batch_acc_units(it.size_n);
+      if (units == 2 && ring.next == kBatchAccUnits - 1) ring.next = 0;   // two units never wrap around
+      const int u = ring.next;
+      uint32_t acc = (uint32_t)u | ((uint32_t)(ring.uses[u]++ & 1) << 4);
+      if (units == 2) acc |= (1u << 3) | ((uint32_t)(ring.uses[u + 1]++ & 1) << 5);
+      ring.next = (u + units) % kBatchAccUnits;
+      it.acc = acc;
       scheduled[pos] = it;
     }
     // Operands with 16-byte aligned rows are fetched by one tensor-map copy each: encode the maps now.
