@@ -777,11 +777,14 @@ bool batch_i8_fits(const SideView& m_side, const SideView& n_side, int depth) {
 cudaError_t launch_batch_i8(const BatchItem* items, const CUtensorMap* maps, int num_items, int grid, int* status,
                             cudaStream_t stream) {
   if (num_items <= 0) return cudaSuccess;
-  static bool attr_set = false;
-  if (!attr_set) {
+  // the opt-in to more than 48 KB of dynamic shared memory is per device
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !attr_set[dev]) {
     cudaError_t e = cudaFuncSetAttribute(batch_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return e;
-    attr_set = true;
+    if (dev >= 0 && dev < 64) attr_set[dev] = true;
   }
   int debug = 0;
 #ifdef RUYB200_DEBUG_KNOBS

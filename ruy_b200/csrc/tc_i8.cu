@@ -990,12 +990,15 @@ template <int kDstBytes, bool kX86, bool kPair>
 cudaError_t launch_variant(const CUtensorMap& map_m, const CUtensorMap& map_n, const KernelArgs& a, int grid,
                            cudaStream_t stream) {
   constexpr int smem = kPair ? kPairSmemBytes : kSmemBytes;
-  static bool attr_set = false;
-  if (!attr_set) {
+  // the opt-in to more than 48 KB of dynamic shared memory is per device
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !attr_set[dev]) {
     cudaError_t e = cudaFuncSetAttribute(tc_i8_kernel<kDstBytes, kX86, kPair>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return e;
-    attr_set = true;
+    if (dev >= 0 && dev < 64) attr_set[dev] = true;
   }
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));

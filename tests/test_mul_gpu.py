@@ -707,3 +707,35 @@ def test_requantization_extremes_in_a_plan(gpu_ctx):
             got = c.dst_view(dst.cpu().numpy())
             assert np.array_equal(got, want), f"{c.name} ({rounding.name}): {(got != want).sum()} mismatches"
         plan.close()
+
+
+def test_one_context_per_thread_runs_concurrently():
+    """ruy's threading contract (ruy/ruy.h:84-87): a Context belongs to one thread, several threads may multiply at the same
+    time each with its own.  Four host threads, four contexts (each with its own stream), mixed kernels."""
+    import threading
+    todo = [cases.config0(), cases.config1((100, 100, 100)),
+            cases.random_case(70, 200, 90, "uint8", "uint8", "uint8", symmetric=False, perchannel=True, seed=31),
+            cases.random_case(33, 65, 17, "int8", "int16", "int16", seed=32)]
+    want = [util.run_oracle(c, wide_float=True) if c.accum == "float32" else util.run_oracle(c, Rounding.kReference) for c in todo]
+    errors = []
+
+    def work(i):
+        try:
+            with ruy_b200.Context(0) as ctx:
+                for rep in range(10):
+                    got, _ = util.run_gpu(todo[i], ctx, where="host" if rep % 2 else "device", rounding=Rounding.kReference)
+                    if todo[i].accum == "float32":
+                        ok = np.all(np.abs(got.astype(np.float64) - want[i]) <= FLOAT_RTOL * np.maximum(np.abs(want[i]), 1.0))
+                    else:
+                        ok = np.array_equal(got, want[i])
+                    if not ok:
+                        errors.append((todo[i].name, rep))
+        except Exception as e:   # noqa: BLE001 - reported through the list
+            errors.append((todo[i].name, repr(e)))
+
+    threads = [threading.Thread(target=work, args=(i,)) for i in range(len(todo))]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
