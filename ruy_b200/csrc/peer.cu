@@ -128,6 +128,7 @@ int ruyb200_peer_close(void* ptr) {
 
 int ruyb200_peer_signal(ruyb200_ctx* ctx, uint32_t* const* remote_flags_device_array, int n, uint32_t value) {
   if (!ctx || !remote_flags_device_array || n < 1 || n > 32) return ctx_fail(RUYB200_ERR_INVALID, "bad argument");
+  ScopedDevice on_device(ctx_device(ctx));
   signal_kernel<<<1, 32, 0, ctx_stream(ctx)>>>(remote_flags_device_array, n, value);
   ctx_count_launch(ctx, RUYB200_KERNEL_NONE);
   cudaError_t e = cudaGetLastError();
@@ -136,6 +137,7 @@ int ruyb200_peer_signal(ruyb200_ctx* ctx, uint32_t* const* remote_flags_device_a
 
 int ruyb200_peer_wait(ruyb200_ctx* ctx, const uint32_t* local_flags, int n, uint32_t value) {
   if (!ctx || !local_flags || n < 1 || n > 32) return ctx_fail(RUYB200_ERR_INVALID, "bad argument");
+  ScopedDevice on_device(ctx_device(ctx));
   wait_kernel<<<1, 32, 0, ctx_stream(ctx)>>>(local_flags, n, value, ctx_status_word(ctx));
   ctx_count_launch(ctx, RUYB200_KERNEL_NONE);
   cudaError_t e = cudaGetLastError();
@@ -145,6 +147,7 @@ int ruyb200_peer_wait(ruyb200_ctx* ctx, const uint32_t* local_flags, int n, uint
 int ruyb200_peer_exchange(ruyb200_ctx* ctx, uint32_t* const* remote_flags_device_array, const uint32_t* local_flags, int n,
                           uint32_t value) {
   if (!ctx || !remote_flags_device_array || !local_flags || n < 1 || n > 32) return ctx_fail(RUYB200_ERR_INVALID, "bad argument");
+  ScopedDevice on_device(ctx_device(ctx));
   exchange_kernel<<<1, 32, 0, ctx_stream(ctx)>>>(remote_flags_device_array, local_flags, n, value, ctx_status_word(ctx));
   ctx_count_launch(ctx, RUYB200_KERNEL_NONE);
   cudaError_t e = cudaGetLastError();

@@ -33,6 +33,7 @@ size_t esize(int dtype) { return dtype == RUYB200_I8 || dtype == RUYB200_U8 ? 1 
 
 void free_plan(ruyb200_plan* plan) {
   if (!plan) return;
+  ScopedDevice on_device(ctx_device(plan->ctx));
   if (plan->d_items) cudaFree(plan->d_items);
   if (plan->d_maps) cudaFree(plan->d_maps);
   ctx_unpin(plan->ctx, plan->pinned);
@@ -46,6 +47,7 @@ extern "C" {
 int ruyb200_plan_create(ruyb200_ctx* ctx, const ruyb200_mul_desc* descs, int n, ruyb200_plan** out) {
   if (!ctx || !out || n < 0 || (n > 0 && !descs)) return ctx_fail(RUYB200_ERR_INVALID, "bad argument");
   *out = nullptr;
+  ScopedDevice on_device(ctx_device(ctx));
   ruyb200_plan* plan = new ruyb200_plan;
   plan->ctx = ctx;
   std::vector<BatchItem> items;
@@ -165,6 +167,7 @@ int ruyb200_plan_create(ruyb200_ctx* ctx, const ruyb200_mul_desc* descs, int n, 
 
 int ruyb200_plan_run(ruyb200_plan* plan) {
   if (!plan) return ctx_fail(RUYB200_ERR_INVALID, "null plan");
+  ScopedDevice on_device(ctx_device(plan->ctx));
   if (plan->num_items > 0) {
     cudaError_t ce = launch_batch_i8(plan->d_items, plan->d_maps, plan->num_items, plan->grid, ctx_status_word(plan->ctx),
                                      ctx_stream(plan->ctx));

@@ -10,6 +10,20 @@
 
 namespace ruyb200 {
 
+// Makes `dev` the current device for the scope of a call and restores the caller's device afterwards.
+struct ScopedDevice {
+  int prev = -1;
+  explicit ScopedDevice(int dev) {
+    cudaGetDevice(&prev);
+    if (prev != dev) cudaSetDevice(dev);
+  }
+  ~ScopedDevice() {
+    int cur = -1;
+    cudaGetDevice(&cur);
+    if (prev >= 0 && cur != prev) cudaSetDevice(prev);
+  }
+};
+
 cudaStream_t ctx_stream(ruyb200_ctx* ctx);
 int ctx_device(ruyb200_ctx* ctx);
 int ctx_sm_count(ruyb200_ctx* ctx);

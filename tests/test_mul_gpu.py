@@ -739,3 +739,31 @@ def test_one_context_per_thread_runs_concurrently():
     for t in threads:
         t.join()
     assert not errors, errors
+
+
+def test_two_devices_in_one_process():
+    """Contexts on two GPUs of one process: each kernel's shared-memory opt-in, caches and plans are per device."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    for dev_index in (1, 0, 1):
+        dev = torch.device("cuda", dev_index)
+        with ruy_b200.Context(dev_index) as ctx:
+            for c in (cases.config0(), cases.random_case(300, 208, 700, "uint8", "int8", "uint8", symmetric=False, seed=41)):
+                dst = torch.zeros(c.dst_storage_elems(), dtype=getattr(torch, c.dst_dtype), device=dev)
+                lhs, rhs, p, d, keep = c.bind(dst, device=dev, rounding=Rounding.kReference)
+                ruy_b200.mul(lhs, rhs, p, ctx, d)
+                assert np.array_equal(c.dst_view(dst.cpu().numpy()), util.run_oracle(c, Rounding.kReference)), (dev_index, c.name)
+            small = [cases.random_case(r, k, n, "int8", "int8", "int8", perchannel=True, seed=50 + i)
+                     for i, (r, k, n) in enumerate(((16, 32, 48), (64, 64, 64), (128, 96, 24)))]
+            bound, descs = [], []
+            for c in small:
+                dst = torch.zeros(c.dst_storage_elems(), dtype=torch.int8, device=dev)
+                lhs, rhs, p, d, keep = c.bind(dst, device=dev, rounding=Rounding.kReference)
+                bound.append((c, dst, keep))
+                descs.append(ruy_b200.make_desc(lhs, rhs, p, d))
+            plan = ruy_b200.Plan(ctx, descs)
+            plan.run()
+            ctx.sync()
+            for c, dst, _ in bound:
+                assert np.array_equal(c.dst_view(dst.cpu().numpy()), util.run_oracle(c)), (dev_index, c.name)
+            plan.close()
