@@ -114,6 +114,29 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(inside), "window": window}
 
 
+def host_cpu():
+    """Model name, logical CPUs and physical cores of this host, from /proc/cpuinfo."""
+    model, cores, logical = "unknown", set(), 0
+    try:
+        phys = core = None
+        for line in open("/proc/cpuinfo"):
+            key, _, val = line.partition(":")
+            key, val = key.strip(), val.strip()
+            if key == "processor":
+                logical += 1
+            elif key == "model name":
+                model = val
+            elif key == "physical id":
+                phys = val
+            elif key == "core id":
+                core = val
+                cores.add((phys, core))
+    except OSError:
+        pass
+    logical = logical or (os.cpu_count() or 1)
+    return {"cpu_model": model, "logical_cpus": logical, "physical_cores": len(cores) or logical}
+
+
 def dist_env():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -126,9 +149,9 @@ def dist_env():
 # ------------------------------------------------------------------------------------------
 
 class CpuArm:
-    """ruy's own CPU implementation of the workload on the host cores, on a bounded sample: the first
-    1024 of the 8192 columns (the weights are the full 4096 x 4096 and stay in ruy's prepacked cache).
-    Uses the compiled reference when oracle/_ref holds it, else the scalar C port on a smaller slice."""
+    """ruy's own CPU implementation of the workload on the host cores: the compiled reference (oracle/_ref) runs the
+    FULL 4096 x 4096 x 8192 mul with the weights in ruy's prepacked cache, on every logical CPU.  Without the
+    compiled reference the scalar C port of the oracle runs a small slice on one thread."""
 
     def __init__(self, workload):
         import oracle
@@ -136,17 +159,20 @@ class CpuArm:
         from ruy_b200.api import make_desc
         self.oracle = oracle
         self.ref = oracle.reference()
+        self.host = host_cpu()
         dst = "int32" if workload == "c3_i32" else "int8"
         if self.ref is not None:
-            self.case = cases.config3(dst=dst, col_begin=0, col_count=1024)
-            self.cores = os.cpu_count() or 1
+            self.case = cases.config3(dst=dst)
+            self.cores = self.host["logical_cpus"]
             self.kind = "reference"
             self.ctx = self.ref.ruy_ref_ctx_create(oracle.host_simd_path(), self.cores)
+            self.same_config = True
         else:
             self.case = cases.config3(rows=512, depth=4096, cols=64, dst=dst)
             self.cores = 1
             self.kind = "port"
             self.ctx = None
+            self.same_config = False
         self.dst = self.case.new_dst()
         self.bound = self.case.bind(self.dst)
         self.desc = make_desc(self.bound[0], self.bound[1], self.bound[2], self.bound[3])
@@ -164,8 +190,13 @@ class CpuArm:
         if self.ref is not None:
             used = {0x40: "kAvx512", 0x20: "kAvx2Fma", 0x10: "kAvx", 0x1: "kStandardCpp"}.get(
                 self.ref.ruy_ref_last_used_path(self.ctx), "?")
-            return f"{self.sample}; ruy::Mul on {used}, {self.cores} threads, weights in the prepacked cache"
+            return (f"{self.sample} (the whole mul); ruy::Mul on {used}, {self.cores} threads on {self.host['physical_cores']} "
+                    f"physical cores of {self.host['cpu_model']}, weights in the prepacked cache")
         return f"{self.sample}; scalar C port of the oracle, 1 thread"
+
+    def baseline(self, value, unit=UNIT):
+        return {"value": value, "unit": unit, "cores": self.cores, "physical_cores": self.host["physical_cores"],
+                "cpu_model": self.host["cpu_model"], "kind": self.kind, "sample": self.describe()}
 
     def tops(self, secs):
         return self.case.ops / secs / 1e12
@@ -191,8 +222,10 @@ def run_reference_arm(args):
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "int8", "data": "synthetic",
         "config": {"workload": args.workload, "rows": 4096, "depth": 4096, "cols": 8192,
-                   "note": "each step times one bounded sample of the workload on the host cores"},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": arm.cores, "kind": arm.kind, "sample": arm.describe()},
+                   "same_config": arm.same_config,
+                   "note": "each step is the whole mul on the host cores" if arm.same_config else
+                           "each step times one bounded sample of the workload on the host cores"},
+        "cpu_baseline": arm.baseline(value),
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     arm.close()

@@ -89,7 +89,7 @@ enum {
   RUYB200_KERNEL_GENERIC = 1,   /* CUDA-core kernel, any type / layout / stride */
   RUYB200_KERNEL_TC_I8 = 2,     /* tcgen05 kind::i8, TMA-staged, fused epilogue */
   RUYB200_KERNEL_SGEMM = 3,     /* fp32 FFMA tiled kernel */
-  RUYB200_KERNEL_GEMV = 4,      /* one-column bandwidth kernel */
+  RUYB200_KERNEL_GEMV = 4,      /* narrow muls (at most 8 destination rows or columns): one pass over the wide operand */
   RUYB200_KERNEL_BATCH_I8 = 5   /* persistent many-small-muls kernel (plans) */
 };
 
@@ -254,11 +254,22 @@ RUYB200_API int ruyb200_plan_stats(const ruyb200_plan* plan, uint64_t* bytes, ui
  * cudaIpcMemHandle_t to be sent to the other processes by any means) and mapped with ruyb200_peer_open.
  * ruyb200_peer_signal raises, after all earlier work of the context's stream, the flag words remote_flags[i]
  * (addresses in peers' memory; the array itself lives in device memory) to `value`; ruyb200_peer_wait makes the
- * stream wait until local_flags[0..n) have all reached `value`, giving up after 2 s with RUYB200_ERR_TIMEOUT at
- * the next ruyb200_ctx_sync.  ruyb200_peer_exchange does both in one launch (signal, then wait).  Only stores
+ * stream wait until local_flags[0..n) have all reached `value`, giving up after the context's wait limit (2 s unless
+ * changed) with RUYB200_ERR_TIMEOUT at the next ruyb200_ctx_sync.  ruyb200_peer_exchange does both in one launch (signal, then wait).  Only stores
  * ever cross NVLink; no load reads a peer's memory. */
 RUYB200_API int ruyb200_mul_async_mirrored(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, void* const* mirror_dst,
                                            int n_mirrors);
+/* The same mul with the step's flag exchange folded into the launch: the CTA that finishes last does what
+ * ruyb200_peer_exchange does (raise remote_flags[i] to `value`, then wait, within the context's wait limit, until
+ * local_flags[0..n_flags) have reached it), which saves a launch per step.
+ * Reuse rule for mirrored destinations: the exchange tells a rank that every peer's tiles of this step have landed
+ * in its buffer; it does not tell a rank that its peers are done READING their copies.  A rank that mirrors step s+1
+ * into the same buffers may therefore overwrite data a slower peer is still consuming.  Alternate between two sets
+ * of buffers (step parity): a rank can only reach step s+2 after every peer has signalled step s+1, and a peer
+ * signals step s+1 after, in its stream, everything that read step s. */
+RUYB200_API int ruyb200_mul_async_mirrored_exchange(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, void* const* mirror_dst,
+                                                    int n_mirrors, uint32_t* const* remote_flags_device_array,
+                                                    const uint32_t* local_flags, int n_flags, uint32_t value);
 RUYB200_API int ruyb200_peer_alloc(size_t bytes, void** out);
 RUYB200_API int ruyb200_peer_free(void* ptr);
 RUYB200_API int ruyb200_peer_export(void* ptr, unsigned char handle[64]);
@@ -268,6 +279,43 @@ RUYB200_API int ruyb200_peer_signal(ruyb200_ctx* ctx, uint32_t* const* remote_fl
 RUYB200_API int ruyb200_peer_wait(ruyb200_ctx* ctx, const uint32_t* local_flags, int n, uint32_t value);
 RUYB200_API int ruyb200_peer_exchange(ruyb200_ctx* ctx, uint32_t* const* remote_flags_device_array, const uint32_t* local_flags,
                                       int n, uint32_t value);
+/* How long ruyb200_peer_wait / ruyb200_peer_exchange of this context wait before they give up (default 2000 ms).
+ * A wait that runs out returns by itself; the next ruyb200_ctx_sync reports RUYB200_ERR_TIMEOUT and the context
+ * stays usable. */
+RUYB200_API int ruyb200_ctx_set_peer_wait_ms(ruyb200_ctx* ctx, uint32_t ms);
+
+/* ---- prepacked-cache persistence --------------------------------------------------------------- */
+
+/* Additive.  ruy's PrepackedCache lives and dies with its process: an entry is identified by (source pointer,
+ * packed layout, zero point) (ruy/prepacked_cache.h:68-80) and holds the packed data plus the sums
+ * (ruy/prepacked_cache.cc:29-45,79-127); there is no serialised form.  These calls take an entry of the device
+ * cache out as a self-describing, versioned blob and put one back, so that weights are packed once per model
+ * rather than once per process.  Blob layout (little endian): a 64-byte header -- bytes 0-7 "RUYB2PCK", 8-11 ABI
+ * version, 12-15 tile-format id, 16 dtype, 17 side, 18 has_sums, 19 zero, 20-23 width, 24-27 depth, 28-31 packed
+ * depth, 32-35 zero point, 36-39 zero, 40-47 data bytes, 48-55 sums bytes, 56-63 FNV-1a (64 bit) of header bytes
+ * 0-55 followed by the payload -- then the packed data, then the int32 sums.
+ * `src` + `side` (0 = LHS, 1 = RHS) name the entry exactly as a later ruyb200_mul will look it up; import never
+ * reads src->data, it only uses the pointer as the key.  After a successful import the next mul with that
+ * operand is a cache hit and launches no packing kernel. */
+#define RUYB200_CACHE_FORMAT_ROWS16 1u   /* [width][depth rounded up to 16 bytes] depth-contiguous rows, int32 sums[width] */
+typedef struct ruyb200_cache_blob {
+  uint32_t abi_version;
+  uint32_t format;
+  uint8_t dtype, side, has_sums, reserved;
+  int32_t width, depth, packed_depth, zero_point;
+  uint64_t data_bytes, sums_bytes;
+} ruyb200_cache_blob;
+/* Validates a blob on the host (magic, version, tile format, sizes, checksum) and describes it; needs no device.
+ * RUYB200_ERR_INVALID for anything this library version cannot use. */
+RUYB200_API int ruyb200_cache_blob_info(const void* blob, size_t n, ruyb200_cache_blob* out);
+/* Copies the cached form of `src` out of the context's cache.  With blob == NULL only *n (bytes needed) is
+ * returned; otherwise *n is the capacity on entry and the size written on return.  RUYB200_ERR_INVALID when
+ * the matrix is not cached or the buffer is too small. */
+RUYB200_API int ruyb200_cache_export(ruyb200_ctx* ctx, const ruyb200_matrix* src, int side, void* blob, size_t* n);
+/* Installs a blob as the cache entry of `src`.  The blob must describe a matrix of the same side, type, shape
+ * and zero point and come from the same ABI version and tile format; anything else is RUYB200_ERR_INVALID and
+ * leaves the cache unchanged.  The cache budget applies (older unpinned entries are evicted to make room). */
+RUYB200_API int ruyb200_cache_import(ruyb200_ctx* ctx, const ruyb200_matrix* src, int side, const void* blob, size_t n);
 
 /* ---- packing: PackImpl / RunPack (ruy/pack.h:105-151) -------------------- */
 

@@ -79,6 +79,26 @@ class MulDesc(C.Structure):
     ]
 
 
+class CacheBlob(C.Structure):
+    """ruyb200_cache_blob."""
+    _fields_ = [
+        ("abi_version", C.c_uint32),
+        ("format", C.c_uint32),
+        ("dtype", C.c_uint8),
+        ("side", C.c_uint8),
+        ("has_sums", C.c_uint8),
+        ("reserved", C.c_uint8),
+        ("width", C.c_int32),
+        ("depth", C.c_int32),
+        ("packed_depth", C.c_int32),
+        ("zero_point", C.c_int32),
+        ("data_bytes", C.c_uint64),
+        ("sums_bytes", C.c_uint64),
+    ]
+
+
+CACHE_FORMAT_ROWS16 = 1
+
 _P = C.POINTER
 
 # name -> (restype, argtypes); the authoritative list of exported entry points.
@@ -106,6 +126,8 @@ PROTOTYPES = {
     "ruyb200_mul_async": (C.c_int, [C.c_void_p, _P(MulDesc)]),
     "ruyb200_validate": (C.c_int, [_P(MulDesc)]),
     "ruyb200_mul_async_mirrored": (C.c_int, [C.c_void_p, _P(MulDesc), _P(C.c_void_p), C.c_int]),
+    "ruyb200_mul_async_mirrored_exchange": (C.c_int, [C.c_void_p, _P(MulDesc), _P(C.c_void_p), C.c_int, C.c_void_p, C.c_void_p,
+                                                      C.c_int, C.c_uint32]),
     "ruyb200_peer_alloc": (C.c_int, [C.c_size_t, _P(C.c_void_p)]),
     "ruyb200_peer_free": (C.c_int, [C.c_void_p]),
     "ruyb200_peer_export": (C.c_int, [C.c_void_p, C.c_char_p]),
@@ -114,6 +136,10 @@ PROTOTYPES = {
     "ruyb200_peer_signal": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_uint32]),
     "ruyb200_peer_wait": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_uint32]),
     "ruyb200_peer_exchange": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_uint32]),
+    "ruyb200_ctx_set_peer_wait_ms": (C.c_int, [C.c_void_p, C.c_uint32]),
+    "ruyb200_cache_blob_info": (C.c_int, [C.c_void_p, C.c_size_t, _P(CacheBlob)]),
+    "ruyb200_cache_export": (C.c_int, [C.c_void_p, _P(MatrixDesc), C.c_int, C.c_void_p, _P(C.c_size_t)]),
+    "ruyb200_cache_import": (C.c_int, [C.c_void_p, _P(MatrixDesc), C.c_int, C.c_void_p, C.c_size_t]),
     "ruyb200_mul_noalloc": (C.c_int, [_P(MulDesc), C.c_void_p]),
     "ruyb200_plan_create": (C.c_int, [C.c_void_p, _P(MulDesc), C.c_int, _P(C.c_void_p)]),
     "ruyb200_plan_run": (C.c_int, [C.c_void_p]),

@@ -245,6 +245,23 @@ class Context:
     def stream(self):
         return lib().ruyb200_ctx_stream(self._h)
 
+    def set_peer_wait_ms(self, ms):
+        _check(lib().ruyb200_ctx_set_peer_wait_ms(self._h, int(ms)), "ruyb200_ctx_set_peer_wait_ms")
+
+    def cache_export(self, matrix, side):
+        """The cached (prepacked) form of `matrix` as a bytes blob (see ruyb200_cache_export).  side: 0 = LHS, 1 = RHS."""
+        m = matrix.to_desc()
+        n = C.c_size_t(0)
+        _check(lib().ruyb200_cache_export(self._h, C.byref(m), side, None, C.byref(n)), "ruyb200_cache_export")
+        buf = C.create_string_buffer(n.value)
+        _check(lib().ruyb200_cache_export(self._h, C.byref(m), side, buf, C.byref(n)), "ruyb200_cache_export")
+        return buf.raw[:n.value]
+
+    def cache_import(self, matrix, side, blob):
+        """Installs a blob made by cache_export as the cache entry of `matrix` (see ruyb200_cache_import)."""
+        m = matrix.to_desc()
+        _check(lib().ruyb200_cache_import(self._h, C.byref(m), side, blob, len(blob)), "ruyb200_cache_import")
+
     def sync(self):
         _check(lib().ruyb200_ctx_sync(self._h), "ruyb200_ctx_sync")
 
@@ -266,6 +283,13 @@ def mul_noalloc(lhs, rhs, mul_params, dst, stream=None):
     device-resident depth-contiguous operands, at most 16384 x 16384 destinations).  Synchronous."""
     d = make_desc(lhs, rhs, mul_params, dst)
     _check(lib().ruyb200_mul_noalloc(C.byref(d), C.c_void_p(stream) if stream else None), "ruyb200_mul_noalloc")
+
+
+def cache_blob_info(blob):
+    """Host-side validation and description of a prepacked-cache blob (no device needed); raises RuyError if unusable."""
+    info = _abi.CacheBlob()
+    _check(lib().ruyb200_cache_blob_info(blob, len(blob), C.byref(info)), "ruyb200_cache_blob_info")
+    return {name: getattr(info, name) for name, _ in _abi.CacheBlob._fields_ if name != "reserved"}
 
 
 def validate(lhs, rhs, mul_params, dst):

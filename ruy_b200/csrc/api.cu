@@ -11,6 +11,7 @@
 
 #include <algorithm>
 #include <cstdarg>
+#include <cstddef>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -148,10 +149,6 @@ struct Arena {
   }
 };
 
-// Key of the prepacked cache: the source pointer, the layout of the TrMul view and the zero
-// point (ruy/prepacked_cache.h:68-80), plus the side and element type.
-typedef std::tuple<const void*, int, int, int64_t, int64_t, int, int, int> CacheKey;
-
 struct CacheEntry {
   void* packed = nullptr;
   int32_t* sums = nullptr;
@@ -159,7 +156,20 @@ struct CacheEntry {
   size_t bytes = 0;
   uint64_t stamp = 0;
   int pins = 0;   // plans that hold pointers into this entry; pinned entries are never evicted or cleared
+  int slab = -1;  // which CacheSlab the entry was carved from
 };
+
+// Cache entries are carved out of large device blocks instead of one cudaMalloc each (a plan over thousands of
+// small cached weights would otherwise pay thousands of allocations).  A block is a bump allocator with a
+// count of live entries; it is returned to the driver when its last entry dies (the block being filled is
+// rewound instead).  Entries of a quarter block or more get a block of their own.
+struct CacheSlab {
+  char* base = nullptr;
+  size_t cap = 0;
+  size_t used = 0;
+  int live = 0;
+};
+constexpr size_t kCacheSlabBytes = size_t(32) << 20;
 
 }  // namespace
 
@@ -176,14 +186,20 @@ struct ruyb200_ctx {
   int advisory = RUYB200_ADVISORY_NONE;
   Arena arena;
   std::map<CacheKey, CacheEntry> cache;
+  std::vector<CacheSlab> cache_slabs;
+  int cache_open_slab = -1;   // the block new small entries are carved from
   size_t cache_bytes = 0;
   size_t cache_budget = size_t(8) << 30;
   uint64_t cache_clock = 0;
   int* d_status = nullptr;
   int* h_status = nullptr;  // pinned
+  unsigned long long peer_wait_ns = 2000000000ull;   // limit of ruyb200_peer_wait / _exchange
   uint64_t counters[6] = {0, 0, 0, 0, 0, 0};
   int force_kernel = 0;  // RUYB200_KERNEL_* or 0
   bool no_pair = false;  // RUYB200_NO_PAIR=1: keep the tensor-core kernel on one CTA per tile
+  // RUYB200_TILE=[pair|single][:columns] overrides the tile-shape choice of the tensor-core kernel (tests, measurements)
+  int force_pair = -1;
+  int force_block_n = 0;
   // synchronous muls with large host operands are cut into chunks that move on these two streams while the
   // kernel of another chunk runs on `stream` (created on first use)
   cudaStream_t copy_in = nullptr;
@@ -335,6 +351,63 @@ size_t storage_span_bytes(const ruyb200_matrix& m) {
   return ((size_t)(outer - 1) * (size_t)m.stride + (size_t)inner) * dtype_size(m.dtype);
 }
 
+// Device memory for one cache entry (`bytes` is a multiple of 256).  Returns nullptr when the device is out of memory.
+void* cache_alloc(ruyb200_ctx* ctx, size_t bytes, int* slab_out) {
+  auto new_slab = [&](size_t cap) -> int {
+    char* p = nullptr;
+    if (cudaMalloc(&p, cap) != cudaSuccess) {
+      cudaGetLastError();
+      return -1;
+    }
+    for (size_t i = 0; i < ctx->cache_slabs.size(); i++) {
+      if (!ctx->cache_slabs[i].base) {
+        ctx->cache_slabs[i] = CacheSlab{p, cap, 0, 0};
+        return (int)i;
+      }
+    }
+    ctx->cache_slabs.push_back(CacheSlab{p, cap, 0, 0});
+    return (int)ctx->cache_slabs.size() - 1;
+  };
+  int idx;
+  if (bytes >= kCacheSlabBytes / 4) {
+    idx = new_slab(bytes);
+    if (idx < 0) return nullptr;
+  } else {
+    idx = ctx->cache_open_slab;
+    if (idx < 0 || ctx->cache_slabs[idx].used + bytes > ctx->cache_slabs[idx].cap) {
+      // the block being left keeps its entries; if it has none it can go at once
+      if (idx >= 0 && ctx->cache_slabs[idx].live == 0) {
+        cudaFree(ctx->cache_slabs[idx].base);
+        ctx->cache_slabs[idx] = CacheSlab();
+      }
+      idx = new_slab(kCacheSlabBytes);
+      if (idx < 0) {
+        ctx->cache_open_slab = -1;
+        return nullptr;
+      }
+      ctx->cache_open_slab = idx;
+    }
+  }
+  CacheSlab& sl = ctx->cache_slabs[idx];
+  void* p = sl.base + sl.used;
+  sl.used += bytes;
+  sl.live++;
+  *slab_out = idx;
+  return p;
+}
+
+void cache_free(ruyb200_ctx* ctx, const CacheEntry& e) {
+  if (e.slab < 0 || e.slab >= (int)ctx->cache_slabs.size()) return;
+  CacheSlab& sl = ctx->cache_slabs[e.slab];
+  if (--sl.live > 0) return;
+  if (e.slab == ctx->cache_open_slab) {
+    sl.used = 0;   // keep filling the same block from its start
+  } else {
+    cudaFree(sl.base);
+    sl = CacheSlab();
+  }
+}
+
 // Evicts the least recently used unpinned entry; false if there is none.
 bool cache_evict_one(ruyb200_ctx* ctx) {
   auto oldest = ctx->cache.end();
@@ -344,7 +417,7 @@ bool cache_evict_one(ruyb200_ctx* ctx) {
   }
   if (oldest == ctx->cache.end()) return false;
   ctx->cache_bytes -= oldest->second.bytes;
-  cudaFree(oldest->second.packed);
+  cache_free(ctx, oldest->second);
   ctx->cache.erase(oldest);
   return true;
 }
@@ -419,17 +492,17 @@ int prepare_side(ruyb200_ctx* ctx, const ruyb200_matrix& m, int side, int depth,
       while (!ctx->cache.empty() && ctx->cache_bytes + total > ctx->cache_budget) {
         if (!cache_evict_one(ctx)) break;
       }
-      void* buf = nullptr;
-      CUDA_TRY(cudaMalloc(&buf, total));
+      CacheEntry e;
+      void* buf = cache_alloc(ctx, total, &e.slab);
+      if (!buf) return fail(RUYB200_ERR_OOM, "prepacked cache: allocation of %zu bytes failed", total);
       SideView staged = src;
       if (!on_device) {
         int rc = stage_to_device(&staged);
         if (rc) {
-          cudaFree(buf);
+          cache_free(ctx, e);
           return rc;
         }
       }
-      CacheEntry e;
       e.packed = buf;
       e.sums = integer ? (int32_t*)((char*)buf + data_bytes) : nullptr;
       e.packed_depth = pd;
@@ -437,7 +510,7 @@ int prepare_side(ruyb200_ctx* ctx, const ruyb200_matrix& m, int side, int depth,
       cudaError_t ce = launch_pack(staged, depth, pd, e.packed, e.sums, ctx->stream);
       ctx->counters[0]++;
       if (ce != cudaSuccess) {
-        cudaFree(buf);
+        cache_free(ctx, e);
         return fail(RUYB200_ERR_CUDA, "pack launch: %s", cudaGetErrorString(ce));
       }
       ctx->cache_bytes += total;
@@ -500,7 +573,7 @@ int stage_vector(ruyb200_ctx* ctx, const void* p, size_t count, const void** out
 }
 
 int choose_kernel(const ruyb200_ctx* ctx, const ruyb200_mul_desc& d) {
-  if (ctx->force_kernel) return ctx->force_kernel;
+  if (ctx->force_kernel == RUYB200_KERNEL_GENERIC) return ctx->force_kernel;
   if (d.params.accum_dtype == RUYB200_F32) return RUYB200_KERNEL_SGEMM;
   const bool both8 = dtype_size(d.lhs.dtype) == 1 && dtype_size(d.rhs.dtype) == 1;
   if (both8 && d.lhs.cols > 0) return RUYB200_KERNEL_TC_I8;
@@ -578,8 +651,16 @@ int run_chunks(ruyb200_ctx* ctx, const ruyb200_mul_desc& d, const TcI8Launch& L,
   return RUYB200_OK;
 }
 
+// The flag exchange a mirrored mul can carry out at its end.
+struct Exchange {
+  uint32_t* const* remote = nullptr;
+  const uint32_t* local = nullptr;
+  int n = 0;
+  uint32_t value = 0;
+};
+
 int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, void* const* mirrors = nullptr,
-            int n_mirrors = 0) {
+            int n_mirrors = 0, const Exchange* xchg = nullptr) {
   int rc = validate_desc(desc);
   if (rc) return rc;
   const ruyb200_mul_desc& d = *desc;
@@ -607,8 +688,17 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
     kernel = RUYB200_KERNEL_GENERIC;
   }
   if (kernel == RUYB200_KERNEL_SGEMM && !is_float) kernel = RUYB200_KERNEL_GENERIC;
+  // Narrow muls (at most kGemvMaxNarrow destination rows or columns) are a single pass over the wide operand
+  // (ruy's single-column kernels, ruy/kernel_avx512.cc:628-870,1238-1320).  Both operands must be
+  // depth-contiguous where the kernel will read them: as stored, or in their packed form when they are cached.
+  if ((kernel == RUYB200_KERNEL_TC_I8 || kernel == RUYB200_KERNEL_SGEMM) && !ctx->force_kernel && n_mirrors == 0 && depth > 0 &&
+      std::min(d.dst.rows, d.dst.cols) <= kGemvMaxNarrow) {
+    const bool lhs_ok = side_view(d.lhs, 0, d.lhs.data).stride_k == 1 || should_cache(d.lhs, d.rhs.cols);
+    const bool rhs_ok = side_view(d.rhs, 1, d.rhs.data).stride_k == 1 || should_cache(d.rhs, d.lhs.rows);
+    if (lhs_ok && rhs_ok) kernel = RUYB200_KERNEL_GEMV;
+  }
   const bool tc = kernel == RUYB200_KERNEL_TC_I8;
-  if (n_mirrors > 0 && (!tc || !dst_on_device || n_mirrors > 7)) {
+  if ((n_mirrors > 0 || xchg) && (!tc || !dst_on_device || n_mirrors > 7)) {
     return fail(RUYB200_ERR_UNSUPPORTED, "mirrored destinations need 8-bit operands, a device destination and at most 7 mirrors");
   }
 
@@ -627,8 +717,8 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
   // operands
   SideView lhs_v, rhs_v;
   const int32_t *lhs_sums = nullptr, *rhs_sums = nullptr;
-  const bool generic = kernel == RUYB200_KERNEL_GENERIC;
-  // the generic kernel subtracts zero points while loading and needs no sums
+  // the generic kernel subtracts zero points while loading and the narrow kernel sums while it streams: neither needs sums
+  const bool generic = kernel == RUYB200_KERNEL_GENERIC || kernel == RUYB200_KERNEL_GEMV;
   const bool need_lhs_sums = !is_float && !generic && d.rhs.zero_point != 0;
   const bool need_rhs_sums = !is_float && !generic && d.lhs.zero_point != 0;
   // The tensor-core kernel can produce the sums of its m-side operand (the RHS for a column-major destination,
@@ -748,17 +838,27 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
     L.sm_count = ctx->sm_count;
     L.status = ctx->d_status;
     L.allow_pair = !ctx->no_pair;
+    L.force_pair = ctx->force_pair;
+    L.force_block_n = ctx->force_block_n;
     L.fuse_sums_m = true;
     L.n_mirrors = n_mirrors;
     for (int i = 0; i < 7; i++) L.mirrors[i] = i < n_mirrors ? mirrors[i] : nullptr;
+    if (xchg && xchg->n > 0) {
+      L.xchg_remote = xchg->remote;
+      L.xchg_local = xchg->local;
+      L.n_xchg = xchg->n;
+      L.xchg_value = xchg->value;
+      L.xchg_counter = (unsigned int*)(ctx->d_status + 1);
+      L.xchg_limit_ns = ctx->peer_wait_ns;
+    }
     TcI8Info info = {};
     if (ctx->trace) L.info = &info;
     struct TraceAtExit {   // prints after the launch has filled `info`
       ruyb200_ctx* ctx; const ruyb200_mul_desc& d; const TcI8Info& info; bool x86, streamed; int mirrors;
       ~TraceAtExit() {
         if (!ctx->trace) return;
-        fprintf(stderr, "ruy_b200: mul %dx%dx%d kernel=tc_i8 tiles=%d of %s x %d, %d-byte tile rows, m-side sums %s, rounding=%s%s, mirrors=%d\n",
-                d.lhs.rows, d.lhs.cols, d.rhs.cols, info.tiles, info.pair ? "256 (two CTAs)" : "128", info.block_n, info.row_pitch,
+        fprintf(stderr, "ruy_b200: mul %dx%dx%d kernel=tc_i8 tiles=%d of %s x %d (estimated %.0f cycles), %d-byte tile rows, m-side sums %s, rounding=%s%s, mirrors=%d\n",
+                d.lhs.rows, d.lhs.cols, d.rhs.cols, info.tiles, info.pair ? "256 (two CTAs)" : "128", info.block_n, info.est_cycles, info.row_pitch,
                 info.fused_sums ? "from the tensor core" : "not fused", x86 ? "x86" : "reference",
                 streamed ? ", host operands in chunks" : "", mirrors);
       }
@@ -770,10 +870,16 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
       return ruyb200_ctx_sync(ctx);
     }
     ce = launch_tc_i8(L, ctx->stream);
-  } else if (kernel == RUYB200_KERNEL_SGEMM) {
+  } else if (kernel == RUYB200_KERNEL_GEMV && gemv_eligible(r.m_side, r.n_side, is_float)) {
+    ce = launch_gemv(r.m_side, r.n_side, r.dst, r.ep, ctx->stream);
+    if (ctx->trace) fprintf(stderr, "ruy_b200: mul %dx%dx%d kernel=gemv (one pass over the wide operand, %s)\n", d.lhs.rows, d.lhs.cols, d.rhs.cols,
+                            is_float ? "fp32 FFMA, compensated" : "dp4a, sums on the way");
+  } else if (is_float) {
+    kernel = RUYB200_KERNEL_SGEMM;
     ce = launch_sgemm(r.m_side, r.n_side, r.dst, r.ep, ctx->stream);
     if (ctx->trace) fprintf(stderr, "ruy_b200: mul %dx%dx%d kernel=sgemm (fp32 FFMA, compensated)\n", d.lhs.rows, d.lhs.cols, d.rhs.cols);
   } else {
+    kernel = RUYB200_KERNEL_GENERIC;
     ce = launch_generic(r.m_side, r.n_side, r.dst, r.ep, ctx->stream);
     if (ctx->trace) fprintf(stderr, "ruy_b200: mul %dx%dx%d kernel=generic (CUDA cores, any type/layout)\n", d.lhs.rows, d.lhs.cols, d.rhs.cols);
   }
@@ -787,6 +893,62 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
     ctx->counters[4] += (size_t)dst_inner * dst_esz * dst_outer;
   }
   if (synchronous) return ruyb200_ctx_sync(ctx);
+  return RUYB200_OK;
+}
+
+
+// ---- prepacked-cache persistence ---------------------------------------------------------------
+//
+// ruy packs a cached operand once per process and has no on-disk format (ruy/prepacked_cache.cc:79-127).  Here an
+// entry can be taken out of the device cache as a self-describing blob and put back later (another process,
+// another run), so that weights are packed once per model.  Blob = 64-byte header, packed data, sums.
+
+struct BlobHeader {
+  char magic[8];           // "RUYB2PCK"
+  uint32_t abi_version;    // RUYB200_ABI_VERSION of the writer
+  uint32_t format;         // RUYB200_CACHE_FORMAT_ROWS16: [width][packed_depth] depth-contiguous rows + int32 sums[width]
+  uint8_t dtype, side, has_sums, reserved;
+  int32_t width, depth, packed_depth, zero_point;
+  uint64_t data_bytes, sums_bytes;
+  uint64_t checksum;       // FNV-1a of the header up to here and of the payload
+};
+static_assert(sizeof(BlobHeader) == 64, "blob header is 64 bytes");
+const char kBlobMagic[8] = {'R', 'U', 'Y', 'B', '2', 'P', 'C', 'K'};
+
+uint64_t fnv1a(const void* p, size_t n, uint64_t h) {
+  const unsigned char* b = (const unsigned char*)p;
+  for (size_t i = 0; i < n; i++) {
+    h ^= b[i];
+    h *= 1099511628211ull;
+  }
+  return h;
+}
+
+uint64_t blob_checksum(const BlobHeader& h, const void* payload, size_t payload_bytes) {
+  uint64_t c = fnv1a(&h, offsetof(BlobHeader, checksum), 14695981039346656037ull);
+  return fnv1a(payload, payload_bytes, c);
+}
+
+// Checks everything that can be checked without a device.
+int parse_blob(const void* blob, size_t n, BlobHeader* out) {
+  if (!blob || n < sizeof(BlobHeader)) return fail(RUYB200_ERR_INVALID, "cache blob: shorter than its header");
+  BlobHeader h;
+  memcpy(&h, blob, sizeof(h));
+  if (memcmp(h.magic, kBlobMagic, 8) != 0) return fail(RUYB200_ERR_INVALID, "cache blob: bad magic");
+  if (h.abi_version != RUYB200_ABI_VERSION)
+    return fail(RUYB200_ERR_INVALID, "cache blob: written by ABI version %u, this library is version %d", h.abi_version, RUYB200_ABI_VERSION);
+  if (h.format != RUYB200_CACHE_FORMAT_ROWS16) return fail(RUYB200_ERR_INVALID, "cache blob: unknown tile format %u", h.format);
+  if (h.dtype > RUYB200_F32 || h.dtype == RUYB200_I32 || h.side > 1 || h.width <= 0 || h.depth <= 0)
+    return fail(RUYB200_ERR_INVALID, "cache blob: bad field");
+  if (h.packed_depth != packed_depth_for(h.depth, h.dtype)) return fail(RUYB200_ERR_INVALID, "cache blob: packed depth does not match this library's layout");
+  const uint64_t want_data = (uint64_t)h.width * h.packed_depth * dtype_size(h.dtype);
+  const uint64_t want_sums = h.has_sums ? (uint64_t)h.width * 4 : 0;
+  if ((h.has_sums != 0) != (h.dtype != RUYB200_F32) || h.data_bytes != want_data || h.sums_bytes != want_sums ||
+      n != sizeof(BlobHeader) + want_data + want_sums)
+    return fail(RUYB200_ERR_INVALID, "cache blob: sizes do not add up");
+  if (blob_checksum(h, (const char*)blob + sizeof(BlobHeader), n - sizeof(BlobHeader)) != h.checksum)
+    return fail(RUYB200_ERR_INVALID, "cache blob: checksum mismatch");
+  *out = h;
   return RUYB200_OK;
 }
 
@@ -838,7 +1000,8 @@ int ruyb200_ctx_create_on_stream(int device, void* cuda_stream, ruyb200_ctx** ou
     }
     ctx->own_stream = true;
   }
-  if (cudaMalloc(&ctx->d_status, sizeof(int)) != cudaSuccess || cudaMemset(ctx->d_status, 0, sizeof(int)) != cudaSuccess ||
+  // word 0: status of bounded waits; word 1: finished-CTA counter of launches that end with a flag exchange
+  if (cudaMalloc(&ctx->d_status, 4 * sizeof(int)) != cudaSuccess || cudaMemset(ctx->d_status, 0, 4 * sizeof(int)) != cudaSuccess ||
       cudaMallocHost(&ctx->h_status, sizeof(int)) != cudaSuccess) {
     cudaGetLastError();
     ruyb200_ctx_destroy(ctx);
@@ -847,8 +1010,16 @@ int ruyb200_ctx_create_on_stream(int device, void* cuda_stream, ruyb200_ctx** ou
   *ctx->h_status = 0;
   const char* fk = getenv("RUYB200_FORCE_KERNEL");
   if (fk && !strcmp(fk, "generic")) ctx->force_kernel = RUYB200_KERNEL_GENERIC;
+  if (fk && !strcmp(fk, "tc_i8")) ctx->force_kernel = RUYB200_KERNEL_TC_I8;   // keeps narrow 8-bit muls on the tensor-core kernel
   const char* np = getenv("RUYB200_NO_PAIR");
   ctx->no_pair = np && *np && *np != '0';
+  const char* tile = getenv("RUYB200_TILE");
+  if (tile && *tile) {
+    if (!strncmp(tile, "pair", 4)) ctx->force_pair = 1;
+    if (!strncmp(tile, "single", 6)) ctx->force_pair = 0;
+    const char* colon = strchr(tile, ':');
+    if (colon && atoi(colon + 1) > 0) ctx->force_block_n = atoi(colon + 1);
+  }
   const char* nc = getenv("RUYB200_NO_CHUNKS");
   ctx->no_chunks = nc && *nc && *nc != '0';
   const char* tr = getenv("RUYB200_TRACE");
@@ -863,8 +1034,11 @@ int ruyb200_ctx_destroy(ruyb200_ctx* ctx) {
   if (!ctx) return RUYB200_OK;
   DeviceGuard guard(ctx->device);
   if (ctx->stream) cudaStreamSynchronize(ctx->stream);
-  for (auto& kv : ctx->cache) cudaFree(kv.second.packed);
   ctx->cache.clear();
+  for (CacheSlab& sl : ctx->cache_slabs) {
+    if (sl.base) cudaFree(sl.base);
+  }
+  ctx->cache_slabs.clear();
   ctx->arena.release();
   if (ctx->d_status) cudaFree(ctx->d_status);
   if (ctx->h_status) cudaFreeHost(ctx->h_status);
@@ -913,7 +1087,7 @@ int ruyb200_ctx_clear_prepacked_cache(ruyb200_ctx* ctx) {
       continue;
     }
     ctx->cache_bytes -= it->second.bytes;
-    cudaFree(it->second.packed);
+    cache_free(ctx, it->second);
     it = ctx->cache.erase(it);
   }
   return RUYB200_OK;
@@ -980,6 +1154,20 @@ int ruyb200_mul_async_mirrored(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, v
   return run_mul(ctx, desc, false, mirror_dst, n_mirrors);
 }
 
+int ruyb200_mul_async_mirrored_exchange(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, void* const* mirror_dst, int n_mirrors,
+                                        uint32_t* const* remote_flags_device_array, const uint32_t* local_flags, int n_flags,
+                                        uint32_t value) {
+  if (!ctx) return fail(RUYB200_ERR_INVALID, "null context");
+  if (n_mirrors < 0 || (n_mirrors > 0 && !mirror_dst)) return fail(RUYB200_ERR_INVALID, "bad mirror list");
+  if (!remote_flags_device_array || !local_flags || n_flags < 1 || n_flags > 32) return fail(RUYB200_ERR_INVALID, "bad flag arguments");
+  Exchange x;
+  x.remote = remote_flags_device_array;
+  x.local = local_flags;
+  x.n = n_flags;
+  x.value = value;
+  return run_mul(ctx, desc, false, mirror_dst, n_mirrors, &x);
+}
+
 int ruyb200_pack(ruyb200_ctx* ctx, const ruyb200_matrix* src, int side, void* packed, size_t packed_capacity,
                  int32_t* sums, int32_t* packed_depth) {
   if (!ctx || !src || !packed || side < 0 || side > 1) return fail(RUYB200_ERR_INVALID, "bad argument");
@@ -1003,6 +1191,116 @@ int ruyb200_pack(ruyb200_ctx* ctx, const ruyb200_matrix* src, int side, void* pa
   ctx->counters[0]++;
   if (ce != cudaSuccess) return fail(RUYB200_ERR_CUDA, "pack launch: %s", cudaGetErrorString(ce));
   return ruyb200_ctx_sync(ctx);
+}
+
+int ruyb200_ctx_set_peer_wait_ms(ruyb200_ctx* ctx, uint32_t ms) {
+  if (!ctx || ms == 0) return fail(RUYB200_ERR_INVALID, "bad argument");
+  ctx->peer_wait_ns = (unsigned long long)ms * 1000000ull;
+  return RUYB200_OK;
+}
+
+int ruyb200_cache_blob_info(const void* blob, size_t n, ruyb200_cache_blob* out) {
+  BlobHeader h;
+  int rc = parse_blob(blob, n, &h);
+  if (rc) return rc;
+  if (out) {
+    out->abi_version = h.abi_version;
+    out->format = h.format;
+    out->dtype = h.dtype;
+    out->side = h.side;
+    out->has_sums = h.has_sums;
+    out->reserved = 0;
+    out->width = h.width;
+    out->depth = h.depth;
+    out->packed_depth = h.packed_depth;
+    out->zero_point = h.zero_point;
+    out->data_bytes = h.data_bytes;
+    out->sums_bytes = h.sums_bytes;
+  }
+  return RUYB200_OK;
+}
+
+int ruyb200_cache_export(ruyb200_ctx* ctx, const ruyb200_matrix* src, int side, void* blob, size_t* n) {
+  if (!ctx || !src || !n || side < 0 || side > 1) return fail(RUYB200_ERR_INVALID, "bad argument");
+  const int depth = side == 0 ? src->cols : src->rows;
+  SideView v = side_view(*src, side, src->data);
+  CacheKey key(src->data, v.width, depth, v.stride_w, v.stride_k, src->zero_point, (int)src->dtype, side);
+  auto it = ctx->cache.find(key);
+  if (it == ctx->cache.end()) return fail(RUYB200_ERR_INVALID, "ruyb200_cache_export: this matrix is not in the prepacked cache");
+  const CacheEntry& e = it->second;
+  BlobHeader h;
+  memset(&h, 0, sizeof(h));
+  memcpy(h.magic, kBlobMagic, 8);
+  h.abi_version = RUYB200_ABI_VERSION;
+  h.format = RUYB200_CACHE_FORMAT_ROWS16;
+  h.dtype = src->dtype;
+  h.side = (uint8_t)side;
+  h.has_sums = e.sums != nullptr;
+  h.width = v.width;
+  h.depth = depth;
+  h.packed_depth = e.packed_depth;
+  h.zero_point = src->zero_point;
+  h.data_bytes = (uint64_t)v.width * e.packed_depth * dtype_size(src->dtype);
+  h.sums_bytes = e.sums ? (uint64_t)v.width * 4 : 0;
+  const size_t need = sizeof(BlobHeader) + h.data_bytes + h.sums_bytes;
+  if (!blob) {   // size query
+    *n = need;
+    return RUYB200_OK;
+  }
+  if (*n < need) {
+    *n = need;
+    return fail(RUYB200_ERR_INVALID, "ruyb200_cache_export: the buffer is too small (%zu bytes needed)", need);
+  }
+  DeviceGuard guard(ctx->device);
+  char* payload = (char*)blob + sizeof(BlobHeader);
+  CUDA_TRY(cudaStreamSynchronize(ctx->stream));   // the entry may still be being packed
+  CUDA_TRY(cudaMemcpy(payload, e.packed, h.data_bytes, cudaMemcpyDeviceToHost));
+  if (e.sums) CUDA_TRY(cudaMemcpy(payload + h.data_bytes, e.sums, h.sums_bytes, cudaMemcpyDeviceToHost));
+  h.checksum = blob_checksum(h, payload, h.data_bytes + h.sums_bytes);
+  memcpy(blob, &h, sizeof(h));
+  *n = need;
+  return RUYB200_OK;
+}
+
+int ruyb200_cache_import(ruyb200_ctx* ctx, const ruyb200_matrix* src, int side, const void* blob, size_t n) {
+  if (!ctx || !src || side < 0 || side > 1) return fail(RUYB200_ERR_INVALID, "bad argument");
+  BlobHeader h;
+  int rc = parse_blob(blob, n, &h);
+  if (rc) return rc;
+  const int depth = side == 0 ? src->cols : src->rows;
+  SideView v = side_view(*src, side, src->data);
+  if (h.side != side || h.dtype != src->dtype || h.width != v.width || h.depth != depth || h.zero_point != src->zero_point)
+    return fail(RUYB200_ERR_INVALID, "ruyb200_cache_import: the blob describes another matrix (side %d, dtype %d, %d x %d, zero point %d)",
+                h.side, h.dtype, h.width, h.depth, h.zero_point);
+  CacheKey key(src->data, v.width, depth, v.stride_w, v.stride_k, src->zero_point, (int)src->dtype, side);
+  if (ctx->cache.count(key)) return RUYB200_OK;   // already resident
+  DeviceGuard guard(ctx->device);
+  const size_t data_bytes = ((size_t)h.data_bytes + 255) & ~size_t(255);
+  const size_t sums_bytes = h.has_sums ? (((size_t)h.sums_bytes + 255) & ~size_t(255)) : 0;
+  const size_t total = data_bytes + sums_bytes;
+  while (!ctx->cache.empty() && ctx->cache_bytes + total > ctx->cache_budget) {
+    if (!cache_evict_one(ctx)) break;
+  }
+  CacheEntry e;
+  void* buf = cache_alloc(ctx, total, &e.slab);
+  if (!buf) return fail(RUYB200_ERR_OOM, "prepacked cache: allocation of %zu bytes failed", total);
+  e.packed = buf;
+  e.sums = h.has_sums ? (int32_t*)((char*)buf + data_bytes) : nullptr;
+  e.packed_depth = h.packed_depth;
+  e.bytes = total;
+  e.stamp = ++ctx->cache_clock;
+  const char* payload = (const char*)blob + sizeof(BlobHeader);
+  cudaError_t ce = cudaMemcpyAsync(e.packed, payload, h.data_bytes, cudaMemcpyHostToDevice, ctx->stream);
+  if (ce == cudaSuccess && e.sums) ce = cudaMemcpyAsync(e.sums, payload + h.data_bytes, h.sums_bytes, cudaMemcpyHostToDevice, ctx->stream);
+  if (ce == cudaSuccess) ce = cudaStreamSynchronize(ctx->stream);   // the caller may free the blob on return
+  if (ce != cudaSuccess) {
+    cache_free(ctx, e);
+    return fail(RUYB200_ERR_CUDA, "ruyb200_cache_import: %s", cudaGetErrorString(ce));
+  }
+  ctx->counters[3] += h.data_bytes + h.sums_bytes;
+  ctx->cache_bytes += total;
+  ctx->cache.emplace(key, e);
+  return RUYB200_OK;
 }
 
 }  // extern "C"
@@ -1034,7 +1332,7 @@ int ctx_run_mul_async(ruyb200_ctx* ctx, const ruyb200_mul_desc* d) { return run_
 // it are taken from the prepacked cache (packed now on a miss) and pinned there; `pinned` receives the
 // entries to unpin when the plan dies.  *fits tells whether the mul can be an item of the batched kernel.
 int ctx_plan_item(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, BatchItem* out, bool* fits,
-                  std::vector<const void*>* pinned_sources) {
+                  std::vector<CacheKey>* pinned) {
   const ruyb200_mul_desc& d = *desc;
   *fits = false;
   memset(out, 0, sizeof(*out));
@@ -1058,7 +1356,7 @@ int ctx_plan_item(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, BatchItem* out
       auto it = ctx->cache.find(key);
       if (it != ctx->cache.end()) {
         it->second.pins++;
-        pinned_sources->push_back(m.data);
+        pinned->push_back(key);
       }
     } else {
       views[side] = side_view(m, side, m.data);
@@ -1112,15 +1410,15 @@ int ctx_plan_item(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, BatchItem* out
   return RUYB200_OK;
 }
 
-void ctx_unpin(ruyb200_ctx* ctx, const std::vector<const void*>& sources) {
-  for (const void* p : sources) {
-    for (auto& kv : ctx->cache) {
-      if (std::get<0>(kv.first) == p && kv.second.pins > 0) {
-        kv.second.pins--;
-        break;
-      }
-    }
+// Releases exactly the entries a plan pinned (the full key: the same source pointer may be cached more than once,
+// e.g. as LHS of one mul and RHS of another, or with two zero points).
+void ctx_unpin(ruyb200_ctx* ctx, const std::vector<CacheKey>& pinned) {
+  for (const CacheKey& key : pinned) {
+    auto it = ctx->cache.find(key);
+    if (it != ctx->cache.end() && it->second.pins > 0) it->second.pins--;
   }
 }
+
+unsigned long long ctx_peer_wait_ns(ruyb200_ctx* ctx) { return ctx->peer_wait_ns; }
 
 }  // namespace ruyb200

@@ -29,6 +29,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 
 #include "batch_i8.h"
 #include "common.cuh"
@@ -777,14 +778,18 @@ bool batch_i8_fits(const SideView& m_side, const SideView& n_side, int depth) {
 cudaError_t launch_batch_i8(const BatchItem* items, const CUtensorMap* maps, int num_items, int grid, int* status,
                             cudaStream_t stream) {
   if (num_items <= 0) return cudaSuccess;
-  // the opt-in to more than 48 KB of dynamic shared memory is per device
+  // the opt-in to more than 48 KB of dynamic shared memory is per device; contexts on several threads may get here together
+  static std::mutex mu;
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(batch_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    if (e != cudaSuccess) return e;
-    if (dev >= 0 && dev < 64) attr_set[dev] = true;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+      cudaError_t e = cudaFuncSetAttribute(batch_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+      if (e != cudaSuccess) return e;
+      if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
   }
   int debug = 0;
 #ifdef RUYB200_DEBUG_KNOBS

@@ -132,6 +132,7 @@ cudaError_t launch_pack(const SideView& side, int depth, int packed_depth, void*
 // What launch_tc_i8 decided, for the decision log.
 struct TcI8Info {
   int pair, block_n, tiles, fused_sums, row_pitch, grid;
+  double est_cycles;   // the tile-shape choice's estimate for the launch, in SM cycles
 };
 struct TcI8Launch {
   SideView m_side;
@@ -146,10 +147,28 @@ struct TcI8Launch {
   int n_mirrors;
   TcI8Info* info = nullptr;   // filled in when not null
   bool fuse_sums_m;  // if ep.zp_n != 0 and ep.sums_m == nullptr, let the kernel produce the m-side sums itself
+  // Overrides of the tile-shape choice (tests and measurements): force_pair -1 = free, 0 = one-CTA tiles only,
+  // 1 = two-CTA tiles when possible; force_block_n 0 = free, else the widest n tile of at most that many columns.
+  int force_pair = -1;
+  int force_block_n = 0;
+  // Optional step-end flag exchange done by the launch itself (see ruyb200_mul_async_mirrored_exchange).
+  uint32_t* const* xchg_remote = nullptr;
+  const uint32_t* xchg_local = nullptr;
+  int n_xchg = 0;
+  uint32_t xchg_value = 0;
+  unsigned int* xchg_counter = nullptr;
+  unsigned long long xchg_limit_ns = 0;
 };
 cudaError_t launch_tc_i8(const TcI8Launch& args, cudaStream_t stream);
 // True when the operands satisfy launch_tc_i8's requirements.
 bool tc_i8_eligible(const SideView& m_side, const SideView& n_side);
+
+// Narrow muls (one side has at most kGemvMaxNarrow rows): one pass over the wide operand, no packing, no sums
+// needed from the caller.  Both sides must be depth-contiguous; 8-bit x 8-bit or fp32.
+constexpr int kGemvMaxNarrow = 8;
+bool gemv_eligible(const SideView& m_side, const SideView& n_side, bool is_float);
+cudaError_t launch_gemv(const SideView& m_side, const SideView& n_side, const DstView& dst, const Epilogue& ep,
+                        cudaStream_t stream);
 
 // fp32 kernels.
 cudaError_t launch_sgemm(const SideView& m_side, const SideView& n_side, const DstView& dst,

@@ -1,0 +1,275 @@
+// Narrow muls: one side of the product has at most eight rows (matrix times vector, or times a handful of
+// vectors).  ruy has dedicated kernels for the single-column case, Kernel8bitAvx512SingleCol
+// (ruy/kernel_avx512.cc:628-870) and KernelFloatAvx512SingleCol (ruy/kernel_avx512.cc:1238-1320), because a
+// 16-wide kernel wastes fifteen sixteenths of its work there; a 128-lane tensor-core tile would waste even more.
+// Such a mul is a stream over the wide operand: HBM-bound, one pass, no packing, no tensor core.
+//
+// One warp per row of the wide side.  The lanes stride over 16-byte pieces of the depth; every piece of the wide
+// row is multiplied (dp4a for 8-bit, FFMA for fp32) with the same piece of each narrow row, which the whole grid
+// shares through L1/L2.  The zero-point sums of both sides (ruy/pack.h:117-129) come out of the same pass.  A
+// butterfly reduction leaves the totals in every lane and lane j finishes and stores output j with the epilogue
+// of ruy/kernel.h:213-237.
+#include "common.cuh"
+
+namespace ruyb200 {
+
+namespace {
+
+constexpr int kWarpsPerBlock = 8;
+
+template <bool kASigned, bool kBSigned>
+__device__ __forceinline__ int32_t dot4(uint32_t a, uint32_t b, int32_t c) {
+  int32_t d;
+  if (kASigned && kBSigned) {
+    asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  } else if (kASigned) {
+    asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  } else if (kBSigned) {
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  } else {
+    asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  }
+  return d;
+}
+
+template <bool kSigned>
+__device__ __forceinline__ int32_t sum4(uint32_t a, int32_t c) {
+  return dot4<kSigned, false>(a, 0x01010101u, c);
+}
+
+template <bool kSigned>
+__device__ __forceinline__ int32_t load8(const uint8_t* p) {
+  return kSigned ? (int32_t)(int8_t)*p : (int32_t)*p;
+}
+
+struct GemvArgs {
+  SideView wide;      // one warp per row of this side
+  SideView narrow;    // at most kGemvMaxNarrow rows
+  DstView dst;
+  Epilogue ep;
+  int wide_is_m;      // 1: the wide side indexes the destination's m dimension, 0: its n (contiguous) dimension
+  int vec;            // both sides: 16-byte aligned base and row stride
+};
+
+// Finishes one output from its raw dot product and the two sums over depth (ruy/kernel.h:213-237).
+__device__ __forceinline__ int32_t finish_with_sums(int32_t raw, int32_t sum_m, int32_t sum_n, int m, int n, const Epilogue& ep) {
+  uint32_t acc = (uint32_t)raw;
+  const int ch = ep.channel_on_n ? n : m;
+  if (ep.bias) acc += (uint32_t)((const int32_t*)ep.bias)[ch];
+  acc -= (uint32_t)ep.zp_m * (uint32_t)sum_n;
+  acc -= (uint32_t)ep.zp_n * (uint32_t)sum_m;
+  acc += (uint32_t)ep.zp_m * (uint32_t)ep.zp_n * (uint32_t)ep.depth;
+  int32_t v = (int32_t)acc;
+  if (ep.dst_dtype != RUYB200_I32) {
+    const int32_t mult = ep.mfp_pc ? ep.mfp_pc[ch] : ep.mfp;
+    const int e = ep.mexp_pc ? ep.mexp_pc[ch] : ep.mexp;
+    v = ep.rounding_x86 ? requant_x86(v, mult, e) : requant_reference(v, mult, e);
+  }
+  v = (int32_t)((uint32_t)v + (uint32_t)ep.dst_zp);
+  if (ep.dst_dtype != RUYB200_I32) {
+    v = min(v, ep.clamp_max);
+    v = max(v, ep.clamp_min);
+  }
+  return v;
+}
+
+template <int kNarrow, bool kWideSigned, bool kNarrowSigned>
+__global__ void __launch_bounds__(32 * kWarpsPerBlock) gemv_i8_kernel(const GemvArgs a) {
+  const int lane = threadIdx.x % 32;
+  const long long w = (long long)blockIdx.x * kWarpsPerBlock + threadIdx.x / 32;
+  if (w >= a.wide.width) return;
+  const int depth = a.ep.depth;
+  const uint8_t* wrow = (const uint8_t*)a.wide.data + w * a.wide.stride_w;
+  const uint8_t* nbase = (const uint8_t*)a.narrow.data;
+  const int64_t nstride = a.narrow.stride_w;
+  int32_t acc[kNarrow], nsum[kNarrow];
+#pragma unroll
+  for (int j = 0; j < kNarrow; j++) acc[j] = nsum[j] = 0;
+  int32_t wsum = 0;
+  int k = 0;
+  if (a.vec) {
+    const int pieces = depth / 16;
+    for (int c = lane; c < pieces; c += 32) {
+      const uint4 x = __ldcs(reinterpret_cast<const uint4*>(wrow) + c);   // streamed: read exactly once
+      wsum = sum4<kWideSigned>(x.x, wsum);
+      wsum = sum4<kWideSigned>(x.y, wsum);
+      wsum = sum4<kWideSigned>(x.z, wsum);
+      wsum = sum4<kWideSigned>(x.w, wsum);
+#pragma unroll
+      for (int j = 0; j < kNarrow; j++) {
+        if (j < a.narrow.width) {
+          const uint4 y = __ldg(reinterpret_cast<const uint4*>(nbase + j * nstride) + c);
+          acc[j] = dot4<kWideSigned, kNarrowSigned>(x.x, y.x, acc[j]);
+          acc[j] = dot4<kWideSigned, kNarrowSigned>(x.y, y.y, acc[j]);
+          acc[j] = dot4<kWideSigned, kNarrowSigned>(x.z, y.z, acc[j]);
+          acc[j] = dot4<kWideSigned, kNarrowSigned>(x.w, y.w, acc[j]);
+          nsum[j] = sum4<kNarrowSigned>(y.x, nsum[j]);
+          nsum[j] = sum4<kNarrowSigned>(y.y, nsum[j]);
+          nsum[j] = sum4<kNarrowSigned>(y.z, nsum[j]);
+          nsum[j] = sum4<kNarrowSigned>(y.w, nsum[j]);
+        }
+      }
+    }
+    k = pieces * 16;
+  }
+  // what the 16-byte pieces do not cover (all of it for unaligned operands), one byte per lane and step
+  for (int kk = k + lane; kk < depth; kk += 32) {
+    const int32_t x = load8<kWideSigned>(wrow + kk);
+    wsum += x;
+#pragma unroll
+    for (int j = 0; j < kNarrow; j++) {
+      if (j < a.narrow.width) {
+        const int32_t y = load8<kNarrowSigned>(nbase + j * nstride + kk);
+        acc[j] = (int32_t)((uint32_t)acc[j] + (uint32_t)(x * y));   // accumulators wrap, as ruy's do
+        nsum[j] += y;
+      }
+    }
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) {
+    wsum += __shfl_xor_sync(0xffffffffu, wsum, d);
+#pragma unroll
+    for (int j = 0; j < kNarrow; j++) {
+      acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], d);
+      nsum[j] += __shfl_xor_sync(0xffffffffu, nsum[j], d);
+    }
+  }
+  int32_t my_acc = 0, my_nsum = 0;
+#pragma unroll
+  for (int j = 0; j < kNarrow; j++) {
+    if (lane == j) {
+      my_acc = acc[j];
+      my_nsum = nsum[j];
+    }
+  }
+  if (lane < a.narrow.width) {
+    const int m = a.wide_is_m ? (int)w : lane;
+    const int n = a.wide_is_m ? lane : (int)w;
+    const int32_t sum_m = a.wide_is_m ? wsum : my_nsum;
+    const int32_t sum_n = a.wide_is_m ? my_nsum : wsum;
+    store_int(a.dst, a.ep.dst_dtype, m, n, finish_with_sums(my_acc, sum_m, sum_n, m, n, a.ep));
+  }
+}
+
+// Compensated (Kahan) running sum: folds y into (sum, comp).
+__device__ __forceinline__ void kahan_add(float& sum, float& comp, float y) {
+  const float yy = y - comp;
+  const float t = sum + yy;
+  comp = (t - sum) - yy;
+  sum = t;
+}
+
+// fp32: the same walk with FFMA.  Each lane folds four products at a time into a compensated sum and the lane tree
+// is compensated as well, so that a long depth with cancellation stays within 1e-5 of a double-precision sum.
+template <int kNarrow>
+__global__ void __launch_bounds__(32 * kWarpsPerBlock) gemv_f32_kernel(const GemvArgs a) {
+  const int lane = threadIdx.x % 32;
+  const long long w = (long long)blockIdx.x * kWarpsPerBlock + threadIdx.x / 32;
+  if (w >= a.wide.width) return;
+  const int depth = a.ep.depth;
+  const float* wrow = (const float*)a.wide.data + w * a.wide.stride_w;
+  const float* nbase = (const float*)a.narrow.data;
+  const int64_t nstride = a.narrow.stride_w;
+  float sum[kNarrow], comp[kNarrow];
+#pragma unroll
+  for (int j = 0; j < kNarrow; j++) sum[j] = comp[j] = 0.f;
+  int k = 0;
+  if (a.vec) {
+    const int pieces = depth / 4;
+    for (int c = lane; c < pieces; c += 32) {
+      const float4 x = __ldcs(reinterpret_cast<const float4*>(wrow) + c);
+#pragma unroll
+      for (int j = 0; j < kNarrow; j++) {
+        if (j < a.narrow.width) {
+          const float4 y = __ldg(reinterpret_cast<const float4*>(nbase + j * nstride) + c);
+          float part = x.x * y.x;
+          part = fmaf(x.y, y.y, part);
+          part = fmaf(x.z, y.z, part);
+          part = fmaf(x.w, y.w, part);
+          kahan_add(sum[j], comp[j], part);
+        }
+      }
+    }
+    k = pieces * 4;
+  }
+  for (int kk = k + lane; kk < depth; kk += 32) {
+    const float x = wrow[kk];
+#pragma unroll
+    for (int j = 0; j < kNarrow; j++) {
+      if (j < a.narrow.width) kahan_add(sum[j], comp[j], x * nbase[j * nstride + kk]);
+    }
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) {
+#pragma unroll
+    for (int j = 0; j < kNarrow; j++) {
+      const float other = __shfl_xor_sync(0xffffffffu, sum[j], d);
+      const float other_c = __shfl_xor_sync(0xffffffffu, comp[j], d);
+      const float y = other - (comp[j] + other_c);
+      const float t = sum[j] + y;
+      comp[j] = (t - sum[j]) - y;
+      sum[j] = t;
+    }
+  }
+  float mine = 0.f;
+#pragma unroll
+  for (int j = 0; j < kNarrow; j++) {
+    if (lane == j) mine = sum[j];
+  }
+  if (lane < a.narrow.width) {
+    const int m = a.wide_is_m ? (int)w : lane;
+    const int n = a.wide_is_m ? lane : (int)w;
+    ((float*)a.dst.data)[(int64_t)m * a.dst.stride_m + n] = finish_float(mine, m, n, a.ep);
+  }
+}
+
+template <int kNarrow>
+cudaError_t launch_i8(const GemvArgs& a, unsigned grid, cudaStream_t stream) {
+  const bool ws = a.wide.dtype == RUYB200_I8, ns = a.narrow.dtype == RUYB200_I8;
+  if (ws && ns) gemv_i8_kernel<kNarrow, true, true><<<grid, 32 * kWarpsPerBlock, 0, stream>>>(a);
+  else if (ws) gemv_i8_kernel<kNarrow, true, false><<<grid, 32 * kWarpsPerBlock, 0, stream>>>(a);
+  else if (ns) gemv_i8_kernel<kNarrow, false, true><<<grid, 32 * kWarpsPerBlock, 0, stream>>>(a);
+  else gemv_i8_kernel<kNarrow, false, false><<<grid, 32 * kWarpsPerBlock, 0, stream>>>(a);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool gemv_eligible(const SideView& m_side, const SideView& n_side, bool is_float) {
+  const int narrow = m_side.width < n_side.width ? m_side.width : n_side.width;
+  if (narrow < 1 || narrow > kGemvMaxNarrow) return false;
+  if (m_side.stride_k != 1 || n_side.stride_k != 1) return false;
+  const long long wide = m_side.width < n_side.width ? n_side.width : m_side.width;
+  if ((wide + kWarpsPerBlock - 1) / kWarpsPerBlock > 0x7fffffffLL) return false;
+  if (is_float) return m_side.dtype == RUYB200_F32 && n_side.dtype == RUYB200_F32;
+  const bool m8 = m_side.dtype == RUYB200_I8 || m_side.dtype == RUYB200_U8;
+  const bool n8 = n_side.dtype == RUYB200_I8 || n_side.dtype == RUYB200_U8;
+  return m8 && n8;
+}
+
+cudaError_t launch_gemv(const SideView& m_side, const SideView& n_side, const DstView& dst, const Epilogue& ep,
+                        cudaStream_t stream) {
+  if (dst.size_m <= 0 || dst.size_n <= 0) return cudaSuccess;
+  GemvArgs a;
+  a.wide_is_m = m_side.width >= n_side.width ? 1 : 0;
+  a.wide = a.wide_is_m ? m_side : n_side;
+  a.narrow = a.wide_is_m ? n_side : m_side;
+  a.dst = dst;
+  a.ep = ep;
+  const size_t esz = ep.is_float ? 4 : 1;
+  a.vec = (((uintptr_t)a.wide.data | (uintptr_t)a.narrow.data | (uintptr_t)(a.wide.stride_w * esz) |
+            (uintptr_t)(a.narrow.stride_w * esz)) & 15) == 0;
+  const unsigned grid = (unsigned)(((long long)a.wide.width + kWarpsPerBlock - 1) / kWarpsPerBlock);
+  const int narrow = a.narrow.width;
+  if (ep.is_float) {
+    if (narrow <= 1) gemv_f32_kernel<1><<<grid, 32 * kWarpsPerBlock, 0, stream>>>(a);
+    else if (narrow <= 4) gemv_f32_kernel<4><<<grid, 32 * kWarpsPerBlock, 0, stream>>>(a);
+    else gemv_f32_kernel<kGemvMaxNarrow><<<grid, 32 * kWarpsPerBlock, 0, stream>>>(a);
+    return cudaGetLastError();
+  }
+  if (narrow <= 1) return launch_i8<1>(a, grid, stream);
+  if (narrow <= 4) return launch_i8<4>(a, grid, stream);
+  return launch_i8<kGemvMaxNarrow>(a, grid, stream);
+}
+
+}  // namespace ruyb200

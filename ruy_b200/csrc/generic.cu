@@ -140,7 +140,6 @@ __global__ void sums_kernel(SideView s, int depth, int32_t* sums) {
 template <typename T>
 __global__ void __launch_bounds__(256) pack_kernel(SideView s, int depth, int packed_depth, T* out, int32_t* sums) {
   __shared__ T tile[32][33];
-  __shared__ uint32_t part[32][9];
   const int tx = threadIdx.x % 32;
   const int ty = threadIdx.x / 32;
   const int w0 = blockIdx.x * 32;
@@ -175,7 +174,6 @@ __global__ void __launch_bounds__(256) pack_kernel(SideView s, int depth, int pa
       if (tx == 0 && w0 + ty + 8 * r < s.width) sums[w0 + ty + 8 * r] = (int32_t)t;
     }
   }
-  (void)part;
 }
 
 }  // namespace

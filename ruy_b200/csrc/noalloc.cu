@@ -16,6 +16,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <mutex>
 
 #include "common.cuh"
 #include "plan.h"
@@ -40,10 +41,12 @@ struct DeviceSetup {
   int sm_count = 0;
 };
 DeviceSetup g_setup[kMaxDevices];
+std::mutex g_setup_mutex;   // two threads may make their first call on a device at the same time
 
 // Runs once per device, with that device current.
 int setup_device(int device, DeviceSetup** out) {
   if (device < 0 || device >= kMaxDevices) return ctx_fail(RUYB200_ERR_INVALID, "device index out of range");
+  std::lock_guard<std::mutex> lock(g_setup_mutex);
   DeviceSetup& s = g_setup[device];
   if (!s.ready) {
     void* ptr = nullptr;

@@ -14,7 +14,6 @@ using namespace ruyb200;
 
 namespace {
 
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // 2 s: then the wait gives up and reports
 
 // One thread per peer: everything this GPU wrote before (the previous kernels of the stream) is made visible
 // system-wide, then the peer's flag word is raised to `value`.
@@ -27,7 +26,7 @@ __global__ void signal_kernel(uint32_t* const* remote_flags, int n, uint32_t val
 }
 
 // One thread per peer spins, with a time limit, until that peer's flag in local memory reaches `value`.
-__global__ void wait_kernel(const uint32_t* local_flags, int n, uint32_t value, int* status) {
+__global__ void wait_kernel(const uint32_t* local_flags, int n, uint32_t value, int* status, unsigned long long limit_ns) {
   const int i = threadIdx.x;
   if (i >= n) return;
   unsigned long long t0;
@@ -38,7 +37,7 @@ __global__ void wait_kernel(const uint32_t* local_flags, int n, uint32_t value, 
     if ((int32_t)(v - value) >= 0) return;
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    if (t - t0 > kWaitLimitNs) {
+    if (t - t0 > limit_ns) {
       atomicCAS(status, 0, 9);   // a peer never signalled: report, do not hang
       return;
     }
@@ -48,7 +47,8 @@ __global__ void wait_kernel(const uint32_t* local_flags, int n, uint32_t value, 
 
 // Both in one launch: thread i raises this rank's flag in peer i's memory, then waits (bounded) for peer i's flag
 // in local memory.  The peers run on other GPUs, so nothing here waits for another launch of the same GPU.
-__global__ void exchange_kernel(uint32_t* const* remote_flags, const uint32_t* local_flags, int n, uint32_t value, int* status) {
+__global__ void exchange_kernel(uint32_t* const* remote_flags, const uint32_t* local_flags, int n, uint32_t value, int* status,
+                                unsigned long long limit_ns) {
   const int i = threadIdx.x;
   if (i >= n) return;
   if (remote_flags[i]) {
@@ -64,7 +64,7 @@ __global__ void exchange_kernel(uint32_t* const* remote_flags, const uint32_t* l
     if ((it & 15) == 15) {
       unsigned long long t;
       asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-      if (t - t0 > kWaitLimitNs) {
+      if (t - t0 > limit_ns) {
         atomicCAS(status, 0, 9);   // a peer never signalled: report, do not hang
         return;
       }
@@ -138,7 +138,7 @@ int ruyb200_peer_signal(ruyb200_ctx* ctx, uint32_t* const* remote_flags_device_a
 int ruyb200_peer_wait(ruyb200_ctx* ctx, const uint32_t* local_flags, int n, uint32_t value) {
   if (!ctx || !local_flags || n < 1 || n > 32) return ctx_fail(RUYB200_ERR_INVALID, "bad argument");
   ScopedDevice on_device(ctx_device(ctx));
-  wait_kernel<<<1, 32, 0, ctx_stream(ctx)>>>(local_flags, n, value, ctx_status_word(ctx));
+  wait_kernel<<<1, 32, 0, ctx_stream(ctx)>>>(local_flags, n, value, ctx_status_word(ctx), ctx_peer_wait_ns(ctx));
   ctx_count_launch(ctx, RUYB200_KERNEL_NONE);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? RUYB200_OK : ctx_fail(RUYB200_ERR_CUDA, cudaGetErrorString(e));
@@ -148,7 +148,8 @@ int ruyb200_peer_exchange(ruyb200_ctx* ctx, uint32_t* const* remote_flags_device
                           uint32_t value) {
   if (!ctx || !remote_flags_device_array || !local_flags || n < 1 || n > 32) return ctx_fail(RUYB200_ERR_INVALID, "bad argument");
   ScopedDevice on_device(ctx_device(ctx));
-  exchange_kernel<<<1, 32, 0, ctx_stream(ctx)>>>(remote_flags_device_array, local_flags, n, value, ctx_status_word(ctx));
+  exchange_kernel<<<1, 32, 0, ctx_stream(ctx)>>>(remote_flags_device_array, local_flags, n, value, ctx_status_word(ctx),
+                                                ctx_peer_wait_ns(ctx));
   ctx_count_launch(ctx, RUYB200_KERNEL_NONE);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? RUYB200_OK : ctx_fail(RUYB200_ERR_CUDA, cudaGetErrorString(e));

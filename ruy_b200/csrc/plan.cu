@@ -18,7 +18,7 @@ using namespace ruyb200;
 struct ruyb200_plan {
   ruyb200_ctx* ctx = nullptr;
   std::vector<ruyb200_mul_desc> single;     // muls replayed one launch at a time
-  std::vector<const void*> pinned;          // prepacked-cache entries this plan reads
+  std::vector<CacheKey> pinned;             // prepacked-cache entries this plan reads
   BatchItem* d_items = nullptr;   // in schedule order
   CUtensorMap* d_maps = nullptr;  // two per item (m side, n side), same order
   int num_items = 0;

@@ -24,6 +24,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 
 #include "batch_i8.h"
 #include "common.cuh"
@@ -32,6 +33,7 @@ namespace ruyb200 {
 
 namespace {
 
+constexpr int kMaxDevices = 64;
 constexpr int kBlockM = 128;          // TMEM lanes per tile
 constexpr int kMaxBlockN = 256;       // accumulator columns per tile
 constexpr int kBlockKBytes = 128;     // one swizzle atom of depth per stage
@@ -82,6 +84,15 @@ struct KernelArgs {
   int tight_wait;  // shallow main loops: the epilogue probes its barrier without backing off
   int mirror_wide; // every destination base and the destination stride are multiples of 16 bytes
   int debug;       // profiling knobs (0 in production): 1 = epilogue skips its math and stores, 2 = producer skips the loads
+  // Step-end flag exchange folded into this launch (mirrored destinations): the CTA that finishes last raises
+  // xchg_remote[i] (one word per rank, in that rank's memory) to xchg_value and then waits, for at most
+  // xchg_limit_ns, until xchg_local[i] (this rank's words) have all reached it.  n_xchg == 0: no exchange.
+  uint32_t* const* xchg_remote;
+  const uint32_t* xchg_local;
+  int n_xchg;
+  uint32_t xchg_value;
+  unsigned int* xchg_counter;   // CTAs that have finished; zero between launches
+  unsigned long long xchg_limit_ns;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -456,6 +467,7 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
   __shared__ __align__(16) int4 nt4_s[kEpilogueGroups][kMaxBlockN];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
+  __shared__ int last_cta;
 
   const int warp = threadIdx.x / 32;
   const int lane = threadIdx.x % 32;
@@ -919,6 +931,8 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
       printf("epilogue warp: staging %lld, waiting for a tile %lld, working %lld cycles over %u tiles\n", dbg_stage,
              dbg_wait, dbg_busy, tcount);
 #endif
+    // this thread's stores into peers' memory are visible system-wide before the CTA counts itself as finished
+    if (args.n_xchg > 0) __threadfence_system();
   }
 
   tc_fence_before();
@@ -932,6 +946,43 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
       asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }
   }
+  if (args.n_xchg > 0) {
+    // The CTA that finishes last tells every rank that this rank's tiles have landed and waits (bounded) for the same
+    // news from the others: the step's flag exchange without a launch of its own.  The peers run on other GPUs;
+    // nothing here waits for another launch on this GPU.
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      const unsigned int prev = atomicAdd(args.xchg_counter, 1u);
+      last_cta = prev == gridDim.x - 1 ? 1 : 0;
+      if (last_cta) {
+        __threadfence();
+        *args.xchg_counter = 0u;   // for the next launch, which follows in stream order
+      }
+    }
+    __syncthreads();
+    if (last_cta && (int)threadIdx.x < args.n_xchg) {
+      const int i = threadIdx.x;
+      if (args.xchg_remote[i]) {
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(args.xchg_remote[i]), "r"(args.xchg_value) : "memory");
+      }
+      unsigned long long t0;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+      for (unsigned it = 0;; it++) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(args.xchg_local + i) : "memory");
+        if ((int32_t)(v - args.xchg_value) >= 0) break;
+        if ((it & 15) == 15) {
+          unsigned long long t;
+          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+          if (t - t0 > args.xchg_limit_ns) {
+            atomicCAS(args.status, 0, 9);   // a peer never signalled: report, do not hang
+            break;
+          }
+        }
+      }
+    }
+  }
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -939,17 +990,16 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
+  // looked up once per process; initialisation of a function-local static is thread-safe
+  static const EncodeTiledFn fn = []() -> EncodeTiledFn {
     void* p = nullptr;
     cudaDriverEntryPointQueryResult q;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
         q == cudaDriverEntryPointSuccess) {
-      fn = (EncodeTiledFn)p;
+      return (EncodeTiledFn)p;
     }
-  }
+    return nullptr;
+  }();
   return fn;
 }
 
@@ -990,15 +1040,20 @@ template <int kDstBytes, bool kX86, bool kPair>
 cudaError_t launch_variant(const CUtensorMap& map_m, const CUtensorMap& map_n, const KernelArgs& a, int grid,
                            cudaStream_t stream) {
   constexpr int smem = kPair ? kPairSmemBytes : kSmemBytes;
-  // the opt-in to more than 48 KB of dynamic shared memory is per device
-  static bool attr_set[64] = {};
+  // the opt-in to more than 48 KB of dynamic shared memory is per device and per kernel variant; contexts on
+  // several threads may get here at the same time
+  static std::mutex mu;
+  static bool attr_set[kMaxDevices] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(tc_i8_kernel<kDstBytes, kX86, kPair>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return e;
-    if (dev >= 0 && dev < 64) attr_set[dev] = true;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev < 0 || dev >= kMaxDevices || !attr_set[dev]) {
+      cudaError_t e = cudaFuncSetAttribute(tc_i8_kernel<kDstBytes, kX86, kPair>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (e != cudaSuccess) return e;
+      if (dev >= 0 && dev < kMaxDevices) attr_set[dev] = true;
+    }
   }
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
@@ -1016,10 +1071,14 @@ cudaError_t launch_variant(const CUtensorMap& map_m, const CUtensorMap& map_n, c
   return cudaLaunchKernelEx(&cfg, tc_i8_kernel<kDstBytes, kX86, kPair>, map_m, map_n, a);
 }
 
-// How many 2-CTA clusters of this kernel can be resident at the same time.
+// How many 2-CTA clusters of this kernel can be resident at the same time on the current device.
 int max_resident_pairs(int sm_count) {
-  static int cached = 0;
-  if (cached) return cached;
+  static std::mutex mu;
+  static int cached[kMaxDevices] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (dev >= 0 && dev < kMaxDevices && cached[dev]) return cached[dev];
   int n = 0;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
@@ -1040,7 +1099,7 @@ int max_resident_pairs(int sm_count) {
   }
   if (n > sm_count / 2) n = sm_count / 2;
   if (getenv("RUYB200_VERBOSE")) fprintf(stderr, "ruy_b200: %d resident CTA pairs on %d SMs\n", n, sm_count);
-  cached = n;
+  if (dev >= 0 && dev < kMaxDevices) cached[dev] = n;
   return n;
 }
 
@@ -1059,6 +1118,75 @@ cudaError_t launch_by_type(const CUtensorMap& map_m, const CUtensorMap& map_n, c
     default:
       return launch_variant<4, false, kPair>(map_m, map_n, a, grid, stream);
   }
+}
+
+// ---- tile-shape choice ---------------------------------------------------------------------------
+//
+// The part of ruy's MakeBlockMap that matters on this machine (ruy/block_map.cc:217-245 "multithreading
+// score", :289-317 "kernel amortization score", :339-471 the choice): ruy scores power-of-two block sizes by
+// how many blocks each thread gets and how well a block amortises the kernel's fixed costs, and takes the
+// best.  Here a "thread" is a persistent CTA (or CTA pair) and the schedule is static, so a launch takes
+// ceil(tiles / units) rounds of one tile each: the candidates are one-CTA tiles of 128 x bn and two-CTA tiles of
+// 256 x bn for every bn that splits the n dimension evenly (a multiple of 16, at most 256), and the score is the
+// estimated duration rounds x cycles per tile.  Smaller tiles waste less of the last round but cost more
+// operand traffic per multiply-add and more hand-offs; the estimate weighs the two.
+struct TileShape {
+  bool pair;
+  int block_n;
+  double cycles;   // estimated SM cycles of the whole launch
+};
+
+// Constants of the estimate, in SM cycles (fitted to measured launches of this kernel).
+constexpr double kFeedBytesPerCycle = 72.0;   // shared-memory fill one SM sustains from L2 while the other SMs do the same
+constexpr double kChunkCycles = 330.0;        // one epilogue warp: 32 accumulator columns loaded, requantised, narrowed, stored
+constexpr double kHandoffCycles = 700.0;      // per tile: barrier round trips between producer, issuer and epilogue
+constexpr double kStageCycles = 36.0;         // per 128-byte stage: what the issuing warp spends outside the MMAs
+
+double tile_cycles(int bn, bool pair, int depth, bool fuse) {
+  const int mma_n = bn + (fuse ? 16 : 0);
+  const int ksteps = (depth + 31) / 32;
+  const int k_blocks = (depth + kBlockKBytes - 1) / kBlockKBytes;
+  const int row_pitch = depth <= 32 ? 32 : (depth <= 64 ? 64 : 128);
+  const double mma = ksteps * (mma_n / 2.0);   // M=128 (or 256 over two SMs) x N x K=32 takes N/2 cycles
+  const double fill = (double)k_blocks * (kBlockM + (pair ? bn / 2 : bn)) * row_pitch / kFeedBytesPerCycle;
+  const double main_loop = (mma > fill ? mma : fill) + k_blocks * kStageCycles;
+  const double epilogue = ((bn + 31) / 32) * kChunkCycles / 2.0;   // eight warps, two per lane quarter (or two tiles in flight)
+  return (main_loop > epilogue ? main_loop : epilogue) + kHandoffCycles;
+}
+
+// force_pair: -1 = free choice, 0 = one-CTA tiles only, 1 = two-CTA tiles when the shape allows them.
+// force_block_n: 0 = free choice, otherwise the widest candidate of at most that many columns is taken.
+TileShape choose_tile_shape(int size_m, int size_n, int depth, bool fuse, bool pair_possible, int sm_count, int pairs_resident,
+                            int force_pair, int force_block_n) {
+  TileShape best = {false, 0, 0.0};
+  const int bn_cap = fuse ? kMaxBlockN - 16 : kMaxBlockN;
+  const bool want_pair_only = force_pair > 0 && pair_possible;
+  for (int p = 0; p < 2; p++) {
+    const bool pair = p == 1;
+    if (pair && (!pair_possible || force_pair == 0)) continue;
+    if (!pair && want_pair_only) continue;
+    const int units = pair ? pairs_resident : sm_count;
+    const int unit_m = pair ? 2 * kBlockM : kBlockM;
+    const long long tiles_m = (size_m + unit_m - 1) / unit_m;
+    int last_bn = 0;
+    for (int n_tiles = (size_n + bn_cap - 1) / bn_cap;; n_tiles++) {
+      // n tiles of equal width: 256 columns split as 128 + 128 rather than 240 + 16
+      const int bn = ((size_n + n_tiles - 1) / n_tiles + 15) / 16 * 16;
+      if (bn == last_bn) continue;   // n_tiles grew without a narrower tile
+      last_bn = bn;
+      const bool forced_out = force_block_n > 0 && bn > force_block_n && bn > 16;
+      if (!forced_out) {
+        const long long tiles = tiles_m * ((size_n + bn - 1) / bn);
+        const long long rounds = (tiles + units - 1) / units;
+        const double cycles = rounds * tile_cycles(bn, pair, depth, fuse);
+        // ties go to the larger tile, as in ruy (ruy/block_map.cc:410)
+        if (best.block_n == 0 || cycles < best.cycles * 0.999) best = {pair, bn, cycles};
+        if (force_block_n > 0) break;   // the widest admissible candidate of this kind
+      }
+      if (bn <= 32) break;
+    }
+  }
+  return best;
 }
 
 }  // namespace
@@ -1091,18 +1219,23 @@ cudaError_t launch_tc_i8(const TcI8Launch& L, cudaStream_t stream) {
 #ifdef RUYB200_DEBUG_KNOBS
   if (getenv("RUYB200_DEBUG")) a.debug = atoi(getenv("RUYB200_DEBUG"));
 #endif
+  a.n_xchg = L.n_xchg > 0 && L.xchg_remote && L.xchg_local && L.xchg_counter ? (L.n_xchg > 32 ? 32 : L.n_xchg) : 0;
+  a.xchg_remote = L.xchg_remote;
+  a.xchg_local = L.xchg_local;
+  a.xchg_value = L.xchg_value;
+  a.xchg_counter = L.xchg_counter;
+  a.xchg_limit_ns = L.xchg_limit_ns;
   const uint32_t fmt_m = L.m_side.dtype == RUYB200_I8 ? 1u : 0u;
   const uint32_t fmt_n = L.n_side.dtype == RUYB200_I8 ? 1u : 0u;
   // The m-side zero-point sums can come out of the tensor core itself (an all-ones row appended to the n tile)
   // instead of a separate pass over the m operand; that variant runs with one CTA per tile.
   const bool fuse = L.fuse_sums_m && L.ep.zp_n != 0 && L.ep.sums_m == nullptr;
-  // Two-CTA tiles (256 x 256) when both destination dimensions are large enough to fill them.
-  const bool pair = !fuse && L.allow_pair && a.size_m >= 256 && a.size_n >= 256 && L.sm_count >= 2;
-  // n tiles of equal width (a multiple of 16), as few as the MMA's N limit allows: 256 columns split as 128 + 128
-  // rather than 240 + 16 when the all-ones rows take 16 of the 256
-  const int bn_cap = fuse ? kMaxBlockN - 16 : kMaxBlockN;
-  const int n_tiles = (a.size_n + bn_cap - 1) / bn_cap;
-  const int bn = ((a.size_n + n_tiles - 1) / n_tiles + 15) / 16 * 16;
+  const bool pair_possible = !fuse && L.allow_pair && a.size_m >= 256 && a.size_n >= 256 && L.sm_count >= 2;
+  const int pairs_resident = pair_possible ? max_resident_pairs(L.sm_count) : 0;
+  const TileShape shape = choose_tile_shape(a.size_m, a.size_n, L.depth, fuse, pair_possible, L.sm_count, pairs_resident,
+                                            L.force_pair, L.force_block_n);
+  const bool pair = shape.pair;
+  const int bn = shape.block_n;
   a.block_n = bn;
   a.sums_col = fuse ? bn : -1;
   a.mma_n = fuse ? bn + 16 : bn;
@@ -1145,11 +1278,12 @@ cudaError_t launch_tc_i8(const TcI8Launch& L, cudaStream_t stream) {
     L.info->fused_sums = fuse;
     L.info->row_pitch = a.row_pitch;
     L.info->grid = 0;
+    L.info->est_cycles = shape.cycles;
   }
   if (pair) {
     // The tile schedule is static, so every pair must be resident from the start: size the grid
     // by the number of 2-CTA clusters the device can hold at once.
-    int pairs = max_resident_pairs(L.sm_count);
+    int pairs = pairs_resident;
 #ifdef RUYB200_DEBUG_KNOBS
     const char* env = getenv("RUYB200_PAIRS");
     if (env && atoi(env) > 0 && atoi(env) < pairs) pairs = atoi(env);

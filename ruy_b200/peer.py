@@ -70,7 +70,14 @@ class StepFlags:
         self.buf.close()
 
 
-def mul_async_mirrored(lhs, rhs, mul_params, context, dst, mirror_ptrs):
+def mul_async_mirrored(lhs, rhs, mul_params, context, dst, mirror_ptrs, flags=None, value=0):
+    """The mul whose epilogue also stores into `mirror_ptrs`; with `flags` (a StepFlags) the launch ends with the
+    step's flag exchange (raise this rank's flag on every rank to `value`, wait for everybody's)."""
     d = make_desc(lhs, rhs, mul_params, dst)
     arr = (C.c_void_p * max(1, len(mirror_ptrs)))(*mirror_ptrs)
-    _check(lib().ruyb200_mul_async_mirrored(context._h, C.byref(d), arr, len(mirror_ptrs)), "ruyb200_mul_async_mirrored")
+    if flags is None:
+        _check(lib().ruyb200_mul_async_mirrored(context._h, C.byref(d), arr, len(mirror_ptrs)), "ruyb200_mul_async_mirrored")
+    else:
+        _check(lib().ruyb200_mul_async_mirrored_exchange(context._h, C.byref(d), arr, len(mirror_ptrs),
+                                                         C.c_void_p(flags.targets.data_ptr()), C.c_void_p(flags.buf.local_ptr),
+                                                         flags.world, value), "ruyb200_mul_async_mirrored_exchange")
