@@ -49,6 +49,8 @@ struct GemvArgs {
   Epilogue ep;
   int wide_is_m;      // 1: the wide side indexes the destination's m dimension, 0: its n (contiguous) dimension
   int vec;            // both sides: 16-byte aligned base and row stride
+  int need_wsum;      // the narrow side's zero point is not 0: the sums over depth of the wide rows are needed
+  int need_nsum;      // the wide side's zero point is not 0: the sums of the narrow rows are needed
 };
 
 // Finishes one output from its raw dot product and the two sums over depth (ruy/kernel.h:213-237).
@@ -91,10 +93,12 @@ __global__ void __launch_bounds__(32 * kWarpsPerBlock) gemv_i8_kernel(const Gemv
     const int pieces = depth / 16;
     for (int c = lane; c < pieces; c += 32) {
       const uint4 x = __ldcs(reinterpret_cast<const uint4*>(wrow) + c);   // streamed: read exactly once
-      wsum = sum4<kWideSigned>(x.x, wsum);
-      wsum = sum4<kWideSigned>(x.y, wsum);
-      wsum = sum4<kWideSigned>(x.z, wsum);
-      wsum = sum4<kWideSigned>(x.w, wsum);
+      if (a.need_wsum) {
+        wsum = sum4<kWideSigned>(x.x, wsum);
+        wsum = sum4<kWideSigned>(x.y, wsum);
+        wsum = sum4<kWideSigned>(x.z, wsum);
+        wsum = sum4<kWideSigned>(x.w, wsum);
+      }
 #pragma unroll
       for (int j = 0; j < kNarrow; j++) {
         if (j < a.narrow.width) {
@@ -103,10 +107,12 @@ __global__ void __launch_bounds__(32 * kWarpsPerBlock) gemv_i8_kernel(const Gemv
           acc[j] = dot4<kWideSigned, kNarrowSigned>(x.y, y.y, acc[j]);
           acc[j] = dot4<kWideSigned, kNarrowSigned>(x.z, y.z, acc[j]);
           acc[j] = dot4<kWideSigned, kNarrowSigned>(x.w, y.w, acc[j]);
-          nsum[j] = sum4<kNarrowSigned>(y.x, nsum[j]);
-          nsum[j] = sum4<kNarrowSigned>(y.y, nsum[j]);
-          nsum[j] = sum4<kNarrowSigned>(y.z, nsum[j]);
-          nsum[j] = sum4<kNarrowSigned>(y.w, nsum[j]);
+          if (a.need_nsum) {
+            nsum[j] = sum4<kNarrowSigned>(y.x, nsum[j]);
+            nsum[j] = sum4<kNarrowSigned>(y.y, nsum[j]);
+            nsum[j] = sum4<kNarrowSigned>(y.z, nsum[j]);
+            nsum[j] = sum4<kNarrowSigned>(y.w, nsum[j]);
+          }
         }
       }
     }
@@ -259,6 +265,8 @@ cudaError_t launch_gemv(const SideView& m_side, const SideView& n_side, const Ds
   const size_t esz = ep.is_float ? 4 : 1;
   a.vec = (((uintptr_t)a.wide.data | (uintptr_t)a.narrow.data | (uintptr_t)(a.wide.stride_w * esz) |
             (uintptr_t)(a.narrow.stride_w * esz)) & 15) == 0;
+  a.need_wsum = a.narrow.zero_point != 0;
+  a.need_nsum = a.wide.zero_point != 0;
   const unsigned grid = (unsigned)(((long long)a.wide.width + kWarpsPerBlock - 1) / kWarpsPerBlock);
   const int narrow = a.narrow.width;
   if (ep.is_float) {

@@ -1127,29 +1127,33 @@ cudaError_t launch_by_type(const CUtensorMap& map_m, const CUtensorMap& map_n, c
 // how many blocks each thread gets and how well a block amortises the kernel's fixed costs, and takes the
 // best.  Here a "thread" is a persistent CTA (or CTA pair) and the schedule is static, so a launch takes
 // ceil(tiles / units) rounds of one tile each: the candidates are one-CTA tiles of 128 x bn and two-CTA tiles of
-// 256 x bn for every bn that splits the n dimension evenly (a multiple of 16, at most 256), and the score is the
-// estimated duration rounds x cycles per tile.  Smaller tiles waste less of the last round but cost more
-// operand traffic per multiply-add and more hand-offs; the estimate weighs the two.
+// 256 x bn for a handful of widths bn (multiples of 16, at most 256), and the score is the estimated duration
+// rounds x cycles per tile.  Smaller tiles waste less of the last round and occupy more SMs when tiles are few,
+// but cost more per multiply-add; the estimate weighs the two.
 struct TileShape {
   bool pair;
   int block_n;
   double cycles;   // estimated SM cycles of the whole launch
 };
 
-// Constants of the estimate, in SM cycles (fitted to measured launches of this kernel).
-constexpr double kFeedBytesPerCycle = 72.0;   // shared-memory fill one SM sustains from L2 while the other SMs do the same
+// Constants of the estimate, in SM cycles, fitted to launches of this kernel on 4096-deep shards of 1024 to 8192
+// columns with every candidate forced in turn.  A 128-byte stage takes the longer of its four MMAs (N / 2 cycles
+// each) and of a fill time that is mostly latency: about 330 cycles plus 0.8 (two-CTA) or 1.05 (one-CTA) cycles per
+// tile column.  Narrow tiles therefore cost almost as much per stage as wide ones, and a deep mul wants the widest
+// tile; only when tiles are few or shallow does a narrower shape win, by occupying more SMs.
+constexpr double kStageBaseCycles = 330.0;
+constexpr double kStageCyclesPerColumnPair = 0.8;
+constexpr double kStageCyclesPerColumnSingle = 1.05;
 constexpr double kChunkCycles = 330.0;        // one epilogue warp: 32 accumulator columns loaded, requantised, narrowed, stored
 constexpr double kHandoffCycles = 700.0;      // per tile: barrier round trips between producer, issuer and epilogue
-constexpr double kStageCycles = 36.0;         // per 128-byte stage: what the issuing warp spends outside the MMAs
 
 double tile_cycles(int bn, bool pair, int depth, bool fuse) {
   const int mma_n = bn + (fuse ? 16 : 0);
-  const int ksteps = (depth + 31) / 32;
   const int k_blocks = (depth + kBlockKBytes - 1) / kBlockKBytes;
-  const int row_pitch = depth <= 32 ? 32 : (depth <= 64 ? 64 : 128);
-  const double mma = ksteps * (mma_n / 2.0);   // M=128 (or 256 over two SMs) x N x K=32 takes N/2 cycles
-  const double fill = (double)k_blocks * (kBlockM + (pair ? bn / 2 : bn)) * row_pitch / kFeedBytesPerCycle;
-  const double main_loop = (mma > fill ? mma : fill) + k_blocks * kStageCycles;
+  const int last_steps = ((depth - (k_blocks - 1) * kBlockKBytes) + 31) / 32;   // K=32 steps of the last stage
+  const double fill = kStageBaseCycles + (pair ? kStageCyclesPerColumnPair : kStageCyclesPerColumnSingle) * mma_n;
+  const double mma_full = 4 * (mma_n / 2.0), mma_last = last_steps * (mma_n / 2.0);
+  const double main_loop = (k_blocks - 1) * (mma_full > fill ? mma_full : fill) + (mma_last > fill ? mma_last : fill);
   const double epilogue = ((bn + 31) / 32) * kChunkCycles / 2.0;   // eight warps, two per lane quarter (or two tiles in flight)
   return (main_loop > epilogue ? main_loop : epilogue) + kHandoffCycles;
 }
@@ -1161,6 +1165,11 @@ TileShape choose_tile_shape(int size_m, int size_n, int depth, bool fuse, bool p
   TileShape best = {false, 0, 0.0};
   const int bn_cap = fuse ? kMaxBlockN - 16 : kMaxBlockN;
   const bool want_pair_only = force_pair > 0 && pair_possible;
+  // widths tried: the cap, a few fixed steps below it, and the even split of the n dimension (256 columns as
+  // 128 + 128 rather than 240 + 16 when the all-ones rows take 16 of the 256)
+  const int even_tiles = (size_n + bn_cap - 1) / bn_cap;
+  const int even_bn = ((size_n + even_tiles - 1) / even_tiles + 15) / 16 * 16;
+  const int widths[] = {even_bn, 192, 128, 96, 64, 48, 32, 16};
   for (int p = 0; p < 2; p++) {
     const bool pair = p == 1;
     if (pair && (!pair_possible || force_pair == 0)) continue;
@@ -1168,22 +1177,16 @@ TileShape choose_tile_shape(int size_m, int size_n, int depth, bool fuse, bool p
     const int units = pair ? pairs_resident : sm_count;
     const int unit_m = pair ? 2 * kBlockM : kBlockM;
     const long long tiles_m = (size_m + unit_m - 1) / unit_m;
-    int last_bn = 0;
-    for (int n_tiles = (size_n + bn_cap - 1) / bn_cap;; n_tiles++) {
-      // n tiles of equal width: 256 columns split as 128 + 128 rather than 240 + 16
-      const int bn = ((size_n + n_tiles - 1) / n_tiles + 15) / 16 * 16;
-      if (bn == last_bn) continue;   // n_tiles grew without a narrower tile
-      last_bn = bn;
-      const bool forced_out = force_block_n > 0 && bn > force_block_n && bn > 16;
-      if (!forced_out) {
-        const long long tiles = tiles_m * ((size_n + bn - 1) / bn);
-        const long long rounds = (tiles + units - 1) / units;
-        const double cycles = rounds * tile_cycles(bn, pair, depth, fuse);
-        // ties go to the larger tile, as in ruy (ruy/block_map.cc:410)
-        if (best.block_n == 0 || cycles < best.cycles * 0.999) best = {pair, bn, cycles};
-        if (force_block_n > 0) break;   // the widest admissible candidate of this kind
-      }
-      if (bn <= 32) break;
+    for (int bn : widths) {
+      if (bn > even_bn) continue;                              // wider than the dimension needs
+      if (pair && bn < 64) continue;                           // each CTA of a pair stages at least 32 rows
+      if (force_block_n > 0 && bn > force_block_n && bn > 16) continue;
+      const long long tiles = tiles_m * ((size_n + bn - 1) / bn);
+      const long long rounds = (tiles + units - 1) / units;
+      const double cycles = rounds * tile_cycles(bn, pair, depth, fuse);
+      // ties go to the larger tile, as in ruy (ruy/block_map.cc:410)
+      if (best.block_n == 0 || cycles < best.cycles * 0.999) best = {pair, bn, cycles};
+      if (force_block_n > 0) break;   // the widest admissible candidate of this kind
     }
   }
   return best;
