@@ -88,9 +88,10 @@ enum {
   RUYB200_KERNEL_NONE = 0,
   RUYB200_KERNEL_GENERIC = 1,   /* CUDA-core kernel, any type / layout / stride */
   RUYB200_KERNEL_TC_I8 = 2,     /* tcgen05 kind::i8, TMA-staged, fused epilogue */
-  RUYB200_KERNEL_SGEMM = 3,     /* fp32 FFMA tiled kernel */
+  RUYB200_KERNEL_SGEMM = 3,     /* fp32 FFMA tiled kernel (small shapes) */
   RUYB200_KERNEL_GEMV = 4,      /* narrow muls (at most 8 destination rows or columns): one pass over the wide operand */
-  RUYB200_KERNEL_BATCH_I8 = 5   /* persistent many-small-muls kernel (plans) */
+  RUYB200_KERNEL_BATCH_I8 = 5,  /* persistent many-small-muls kernel (plans) */
+  RUYB200_KERNEL_TC_F32 = 6     /* fp32 on tcgen05 kind::tf32: hi/lo split operands, three products, short accumulation chains */
 };
 
 /* A non-owning matrix view: ruy::Matrix<T> / ruy::Mat<T> (ruy/matrix.h:132-165,

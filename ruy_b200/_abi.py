@@ -28,8 +28,8 @@ PATH_NONE, PATH_STANDARD_CPP = 0, 0x1
 PATH_INTERNAL_VARIANT1, PATH_INTERNAL_VARIANT2, PATH_INTERNAL_VARIANT3 = 0x2, 0x4, 0x8
 PATH_AVX, PATH_AVX2_FMA, PATH_AVX512 = 0x10, 0x20, 0x40
 ADVISORY_NONE, ADVISORY_REALLOCATED_PERCHANNEL_BUFFER = 0, 1
-KERNEL_NONE, KERNEL_GENERIC, KERNEL_TC_I8, KERNEL_SGEMM, KERNEL_GEMV, KERNEL_BATCH_I8 = 0, 1, 2, 3, 4, 5
-KERNEL_NAMES = {0: "none", 1: "generic", 2: "tc_i8", 3: "sgemm", 4: "gemv", 5: "batch_i8"}
+KERNEL_NONE, KERNEL_GENERIC, KERNEL_TC_I8, KERNEL_SGEMM, KERNEL_GEMV, KERNEL_BATCH_I8, KERNEL_TC_F32 = 0, 1, 2, 3, 4, 5, 6
+KERNEL_NAMES = {0: "none", 1: "generic", 2: "tc_i8", 3: "sgemm", 4: "gemv", 5: "batch_i8", 6: "tc_f32"}
 
 
 class MatrixDesc(C.Structure):

@@ -6,7 +6,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libruy_b200.so")
-SOURCES = ["api.cu", "plan.cu", "generic.cu", "sgemm.cu", "gemv.cu", "tc_i8.cu", "batch_i8.cu", "noalloc.cu", "peer.cu"]
+SOURCES = ["api.cu", "plan.cu", "generic.cu", "sgemm.cu", "gemv.cu", "tc_i8.cu", "tc_f32.cu", "shallow_i8.cu", "batch_i8.cu", "noalloc.cu", "peer.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr",

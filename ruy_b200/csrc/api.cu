@@ -200,6 +200,7 @@ struct ruyb200_ctx {
   // RUYB200_TILE=[pair|single][:columns] overrides the tile-shape choice of the tensor-core kernel (tests, measurements)
   int force_pair = -1;
   int force_block_n = 0;
+  bool no_shallow = false;   // RUYB200_NO_SHALLOW=1: keep shallow-depth muls on the general tensor-core kernel
   // synchronous muls with large host operands are cut into chunks that move on these two streams while the
   // kernel of another chunk runs on `stream` (created on first use)
   cudaStream_t copy_in = nullptr;
@@ -598,10 +599,11 @@ int run_chunks(ruyb200_ctx* ctx, const ruyb200_mul_desc& d, const TcI8Launch& L,
   }
   const int width = L.m_side.width;
   const int64_t stride_w = L.m_side.stride_w;            // bytes: the operand is 8-bit
-  // chunks of a multiple of 256 m indices (whole two-CTA tiles), about eight of them, at least 1 MiB each
+  // chunks of a multiple of 256 m indices (whole two-CTA tiles), about sixteen of them (the first copy in and the last
+  // copy out are not overlapped with anything, so they should be short), at least 1 MiB each
   const size_t dst_pitch = (size_t)d.dst.stride * dst_esz;
   const int64_t moved_per_m = (m_host ? stride_w : 0) + (dst_host ? (int64_t)dst_pitch : 0);   // bytes over PCIe per m index
-  int step = ((width + 7) / 8 + 255) / 256 * 256;
+  int step = ((width + 15) / 16 + 255) / 256 * 256;
   while ((int64_t)step * moved_per_m < (1 << 20) && step < width) step *= 2;
   int chunks = (width + step - 1) / step;
   if (chunks > kMaxChunks) {
@@ -642,8 +644,13 @@ int run_chunks(ruyb200_ctx* ctx, const ruyb200_mul_desc& d, const TcI8Launch& L,
     if (dst_host) {
       CUDA_TRY(cudaEventRecord(ctx->chunk_done[c], ctx->stream));
       CUDA_TRY(cudaStreamWaitEvent(ctx->copy_out, ctx->chunk_done[c], 0));
-      CUDA_TRY(cudaMemcpy2DAsync(dst_host + (size_t)w0 * dst_pitch, dst_pitch, part.dst.data, dst_pitch, dst_row_bytes, w,
-                                 cudaMemcpyDeviceToHost, ctx->copy_out));
+      if (dst_row_bytes == dst_pitch) {   // a dense destination leaves as one linear copy
+        CUDA_TRY(cudaMemcpyAsync(dst_host + (size_t)w0 * dst_pitch, part.dst.data, dst_pitch * (size_t)w, cudaMemcpyDeviceToHost,
+                                 ctx->copy_out));
+      } else {
+        CUDA_TRY(cudaMemcpy2DAsync(dst_host + (size_t)w0 * dst_pitch, dst_pitch, part.dst.data, dst_pitch, dst_row_bytes, w,
+                                   cudaMemcpyDeviceToHost, ctx->copy_out));
+      }
       ctx->counters[4] += dst_row_bytes * (size_t)w;
     }
   }
@@ -696,6 +703,12 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
     const bool lhs_ok = side_view(d.lhs, 0, d.lhs.data).stride_k == 1 || should_cache(d.lhs, d.rhs.cols);
     const bool rhs_ok = side_view(d.rhs, 1, d.rhs.data).stride_k == 1 || should_cache(d.rhs, d.lhs.rows);
     if (lhs_ok && rhs_ok) kernel = RUYB200_KERNEL_GEMV;
+  }
+  // fp32 muls that fill tensor-core tiles go to the 3 x TF32 kernel; small ones stay on the FFMA kernel, whose single
+  // launch costs less than the split pre-pass
+  if (kernel == RUYB200_KERNEL_SGEMM && ctx->force_kernel != RUYB200_KERNEL_SGEMM && std::min(d.dst.rows, d.dst.cols) >= 64 &&
+      depth >= 32 && (double)d.dst.rows * d.dst.cols * depth >= (double)(1 << 21)) {
+    kernel = RUYB200_KERNEL_TC_F32;
   }
   const bool tc = kernel == RUYB200_KERNEL_TC_I8;
   if ((n_mirrors > 0 || xchg) && (!tc || !dst_on_device || n_mirrors > 7)) {
@@ -838,6 +851,7 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
     L.sm_count = ctx->sm_count;
     L.status = ctx->d_status;
     L.allow_pair = !ctx->no_pair;
+    L.allow_shallow = !ctx->no_shallow;
     L.force_pair = ctx->force_pair;
     L.force_block_n = ctx->force_block_n;
     L.fuse_sums_m = true;
@@ -857,6 +871,12 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
       ruyb200_ctx* ctx; const ruyb200_mul_desc& d; const TcI8Info& info; bool x86, streamed; int mirrors;
       ~TraceAtExit() {
         if (!ctx->trace) return;
+        if (info.shallow) {
+          fprintf(stderr, "ruy_b200: mul %dx%dx%d kernel=tc_i8 (shallow depth: %d activation rows per 128-byte line, %d tiles of %d rows x %d, "
+                  "row sums from shared memory), rounding=%s\n", d.lhs.rows, d.lhs.cols, d.rhs.cols, info.shallow, info.tiles, 128 * info.shallow,
+                  info.block_n, x86 ? "x86" : "reference");
+          return;
+        }
         fprintf(stderr, "ruy_b200: mul %dx%dx%d kernel=tc_i8 tiles=%d of %s x %d (estimated %.0f cycles), %d-byte tile rows, m-side sums %s, rounding=%s%s, mirrors=%d\n",
                 d.lhs.rows, d.lhs.cols, d.rhs.cols, info.tiles, info.pair ? "256 (two CTAs)" : "128", info.block_n, info.est_cycles, info.row_pitch,
                 info.fused_sums ? "from the tensor core" : "not fused", x86 ? "x86" : "reference",
@@ -870,6 +890,14 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
       return ruyb200_ctx_sync(ctx);
     }
     ce = launch_tc_i8(L, ctx->stream);
+  } else if (kernel == RUYB200_KERNEL_TC_F32) {
+    void* sm_ = ctx->arena.alloc(tc_f32_scratch_bytes(r.m_side.width, depth));
+    void* sn_ = ctx->arena.alloc(tc_f32_scratch_bytes(r.n_side.width, depth));
+    if (!sm_ || !sn_) return fail(RUYB200_ERR_OOM, "arena allocation failed");
+    ce = launch_tc_f32(r.m_side, r.n_side, r.dst, r.ep, sm_, sn_, ctx->sm_count, ctx->d_status, ctx->stream);
+    ctx->counters[0] += 2;   // the two split launches
+    if (ctx->trace) fprintf(stderr, "ruy_b200: mul %dx%dx%d kernel=tc_f32 (tcgen05 kind::tf32, hi/lo split, three products, 32-deep accumulation chains)\n",
+                            d.lhs.rows, d.lhs.cols, d.rhs.cols);
   } else if (kernel == RUYB200_KERNEL_GEMV && gemv_eligible(r.m_side, r.n_side, is_float)) {
     ce = launch_gemv(r.m_side, r.n_side, r.dst, r.ep, ctx->stream);
     if (ctx->trace) fprintf(stderr, "ruy_b200: mul %dx%dx%d kernel=gemv (one pass over the wide operand, %s)\n", d.lhs.rows, d.lhs.cols, d.rhs.cols,
@@ -1010,7 +1038,8 @@ int ruyb200_ctx_create_on_stream(int device, void* cuda_stream, ruyb200_ctx** ou
   *ctx->h_status = 0;
   const char* fk = getenv("RUYB200_FORCE_KERNEL");
   if (fk && !strcmp(fk, "generic")) ctx->force_kernel = RUYB200_KERNEL_GENERIC;
-  if (fk && !strcmp(fk, "tc_i8")) ctx->force_kernel = RUYB200_KERNEL_TC_I8;   // keeps narrow 8-bit muls on the tensor-core kernel
+  if (fk && !strcmp(fk, "tc_i8")) ctx->force_kernel = RUYB200_KERNEL_TC_I8;
+  if (fk && !strcmp(fk, "sgemm")) ctx->force_kernel = RUYB200_KERNEL_SGEMM;   // keeps fp32 muls on the FFMA kernel   // keeps narrow 8-bit muls on the tensor-core kernel
   const char* np = getenv("RUYB200_NO_PAIR");
   ctx->no_pair = np && *np && *np != '0';
   const char* tile = getenv("RUYB200_TILE");
@@ -1020,6 +1049,8 @@ int ruyb200_ctx_create_on_stream(int device, void* cuda_stream, ruyb200_ctx** ou
     const char* colon = strchr(tile, ':');
     if (colon && atoi(colon + 1) > 0) ctx->force_block_n = atoi(colon + 1);
   }
+  const char* ns = getenv("RUYB200_NO_SHALLOW");
+  ctx->no_shallow = ns && *ns && *ns != '0';
   const char* nc = getenv("RUYB200_NO_CHUNKS");
   ctx->no_chunks = nc && *nc && *nc != '0';
   const char* tr = getenv("RUYB200_TRACE");

@@ -133,6 +133,7 @@ cudaError_t launch_pack(const SideView& side, int depth, int packed_depth, void*
 struct TcI8Info {
   int pair, block_n, tiles, fused_sums, row_pitch, grid;
   double est_cycles;   // the tile-shape choice's estimate for the launch, in SM cycles
+  int shallow;         // > 0: served by the shallow-depth kernel, that many activation rows per 128-byte line
 };
 struct TcI8Launch {
   SideView m_side;
@@ -151,6 +152,7 @@ struct TcI8Launch {
   // 1 = two-CTA tiles when possible; force_block_n 0 = free, else the widest n tile of at most that many columns.
   int force_pair = -1;
   int force_block_n = 0;
+  bool allow_shallow = true;   // permit the shallow-depth kernel (depth 32 or 64, contiguous activation rows)
   // Optional step-end flag exchange done by the launch itself (see ruyb200_mul_async_mirrored_exchange).
   uint32_t* const* xchg_remote = nullptr;
   const uint32_t* xchg_local = nullptr;
@@ -162,6 +164,9 @@ struct TcI8Launch {
 cudaError_t launch_tc_i8(const TcI8Launch& args, cudaStream_t stream);
 // True when the operands satisfy launch_tc_i8's requirements.
 bool tc_i8_eligible(const SideView& m_side, const SideView& n_side);
+// The shallow-depth variant (shallow_i8.cu); launch_tc_i8 hands eligible launches over to it.
+bool shallow_i8_eligible(const TcI8Launch& args);
+cudaError_t launch_shallow_i8(const TcI8Launch& args, cudaStream_t stream);
 
 // Narrow muls (one side has at most kGemvMaxNarrow rows): one pass over the wide operand, no packing, no sums
 // needed from the caller.  Both sides must be depth-contiguous; 8-bit x 8-bit or fp32.
@@ -169,6 +174,12 @@ constexpr int kGemvMaxNarrow = 8;
 bool gemv_eligible(const SideView& m_side, const SideView& n_side, bool is_float);
 cudaError_t launch_gemv(const SideView& m_side, const SideView& n_side, const DstView& dst, const Epilogue& ep,
                         cudaStream_t stream);
+
+// fp32 on the tensor core (3 x TF32 with short accumulation chains, see tc_f32.cu).  scratch_m / scratch_n receive
+// the hi/lo split of each side: tc_f32_scratch_bytes(width, depth) bytes each, 256-byte aligned.
+size_t tc_f32_scratch_bytes(int width, int depth);
+cudaError_t launch_tc_f32(const SideView& m_side, const SideView& n_side, const DstView& dst, const Epilogue& ep, void* scratch_m,
+                          void* scratch_n, int sm_count, int* status, cudaStream_t stream);
 
 // fp32 kernels.
 cudaError_t launch_sgemm(const SideView& m_side, const SideView& n_side, const DstView& dst,

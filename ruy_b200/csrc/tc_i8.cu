@@ -1207,6 +1207,7 @@ bool tc_i8_eligible(const SideView& m_side, const SideView& n_side) {
 }
 
 cudaError_t launch_tc_i8(const TcI8Launch& L, cudaStream_t stream) {
+  if (shallow_i8_eligible(L)) return launch_shallow_i8(L, stream);
   KernelArgs a;
   a.dst = L.dst;
   a.ep = L.ep;
@@ -1282,6 +1283,7 @@ cudaError_t launch_tc_i8(const TcI8Launch& L, cudaStream_t stream) {
     L.info->row_pitch = a.row_pitch;
     L.info->grid = 0;
     L.info->est_cycles = shape.cycles;
+    L.info->shallow = 0;
   }
   if (pair) {
     // The tile schedule is static, so every pair must be resident from the start: size the grid

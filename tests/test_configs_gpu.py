@@ -156,3 +156,43 @@ def test_config3_full_against_compiled_reference(gpu_ctx):
     gr, _ = util.run_gpu(c, gpu_ctx, rounding=Rounding.kReference)
     diff = np.abs(gr.astype(np.int32) - gx.astype(np.int32))
     assert diff.max() <= 1 and 0 < (diff != 0).mean() < 0.02
+
+
+SHALLOW = [  # (rows, depth, cols, lhs, rhs, dst, per-channel, channel dimension)
+    (64, 32, 151552 + 4 * 37, "uint8", "uint8", "uint8", False, "row"),     # ragged last tile
+    (40, 32, 160000, "int8", "uint8", "int8", True, "row"),                 # n not a multiple of 16, per-row multipliers
+    (128, 64, 75776 + 2 * 51, "uint8", "int8", "uint8", True, "col"),       # depth 64, per-column (activation side) channels
+    (100, 64, 80000, "int8", "int8", "int8", False, "row"),
+]
+
+
+@pytest.mark.parametrize("spec", SHALLOW, ids=lambda s: "x".join(map(str, s[:3])) + "_" + s[7])
+def test_shallow_depth_kernel(spec, capfd):
+    """Depth 32 / 64 with contiguous activation rows takes the kernel that fetches 128-byte lines of several rows;
+    the same cases on the general kernel (RUYB200_NO_SHALLOW=1) must give the same bits."""
+    from ruy_b200.api import ChannelDimension
+    rows, depth, cols, lt, rt, dt, pc, ch = spec
+    c = cases.random_case(rows, depth, cols, lt, rt, dt, orders="RCC", perchannel=pc, symmetric=False, seed=rows + depth,
+                          channel=ChannelDimension.kRow if ch == "row" else ChannelDimension.kCol,
+                          lhs_cache=CachePolicy.kAlwaysCache)
+    os.environ["RUYB200_TRACE"] = "1"
+    try:
+        ctx = ruy_b200.Context(0)
+    finally:
+        del os.environ["RUYB200_TRACE"]
+    try:
+        check_against_reference(c, ctx, sample_seed=rows)
+        assert "shallow depth" in capfd.readouterr().err
+        got, _ = util.run_gpu(c, ctx, rounding=Rounding.kReference)
+    finally:
+        ctx.close()
+    os.environ["RUYB200_NO_SHALLOW"] = "1"
+    try:
+        plain = ruy_b200.Context(0)
+    finally:
+        del os.environ["RUYB200_NO_SHALLOW"]
+    try:
+        want, _ = util.run_gpu(c, plain, rounding=Rounding.kReference)
+    finally:
+        plain.close()
+    assert np.array_equal(got, want)

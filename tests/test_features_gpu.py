@@ -278,3 +278,44 @@ def test_mirrored_mul_with_the_exchange_folded_in():
                                                          C.c_void_p(words.data_ptr()), 2, 8) == 0
         ctx.sync()
         assert words.cpu().tolist()[:2] == [8, 8]
+
+
+# ---- fp32 on the tensor core ------------------------------------------------------------------------------
+
+TF32_SHAPES = [(1024, 1024, 1024), (200, 333, 130), (64, 512, 64), (129, 4100, 96), (640, 32, 257), (96, 16384, 72)]
+
+
+@pytest.mark.parametrize("shape", TF32_SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_float_muls_on_the_tensor_core(shape, gpu_ctx):
+    """3 x TF32 with 32-deep accumulation chains must meet the same bound as the FFMA kernel:
+    |gpu - ref64| <= 1e-5 * max(|ref64|, 1) against a double-accumulated reference, for every storage order."""
+    for orders, ch in (("RCC", ChannelDimension.kRow), ("CRC", ChannelDimension.kRow), ("RCR", ChannelDimension.kCol),
+                       ("CCR", ChannelDimension.kRow)):
+        c = cases.random_case(*shape, "float32", "float32", "float32", orders=orders, channel=ch, seed=sum(shape),
+                              extra_stride=0 if orders != "CCR" else 3)
+        got, _ = util.run_gpu(c, gpu_ctx)
+        assert gpu_ctx.counters()["last_kernel"] == "tc_f32"
+        wide = util.run_oracle(c, wide_float=True).astype(np.float64)
+        err = np.abs(got.astype(np.float64) - wide)
+        assert np.all(err <= 1e-5 * np.maximum(np.abs(wide), 1.0)), (orders, float(err.max()))
+
+
+def test_float_tensor_core_and_ffma_kernels_agree():
+    """Benchmark config 1's large shape on both fp32 kernels: each within 1e-5 of the double-precision reference, hence
+    within 2e-5 of each other; small shapes stay on the FFMA kernel."""
+    c = cases.config1((1024, 1024, 1024))
+    wide = util.run_oracle(c, wide_float=True).astype(np.float64)
+    ffma = ctx_with_env(RUYB200_FORCE_KERNEL="sgemm")
+    try:
+        a, _ = util.run_gpu(c, ffma)
+        assert ffma.counters()["last_kernel"] == "sgemm"
+    finally:
+        ffma.close()
+    with ruy_b200.Context(0) as ctx:
+        b, _ = util.run_gpu(c, ctx)
+        assert ctx.counters()["last_kernel"] == "tc_f32"
+        small = cases.config1((100, 100, 100))
+        util.run_gpu(small, ctx)
+        assert ctx.counters()["last_kernel"] == "sgemm"
+    for got in (a, b):
+        assert np.all(np.abs(got - wide) <= 1e-5 * np.maximum(np.abs(wide), 1.0))
