@@ -902,7 +902,7 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
     ce = launch_gemv(r.m_side, r.n_side, r.dst, r.ep, ctx->stream);
     if (ctx->trace) fprintf(stderr, "ruy_b200: mul %dx%dx%d kernel=gemv (one pass over the wide operand, %s)\n", d.lhs.rows, d.lhs.cols, d.rhs.cols,
                             is_float ? "fp32 FFMA, compensated" : "dp4a, sums on the way");
-  } else if (is_float) {
+  } else if (is_float && kernel != RUYB200_KERNEL_GENERIC) {
     kernel = RUYB200_KERNEL_SGEMM;
     ce = launch_sgemm(r.m_side, r.n_side, r.dst, r.ep, ctx->stream);
     if (ctx->trace) fprintf(stderr, "ruy_b200: mul %dx%dx%d kernel=sgemm (fp32 FFMA, compensated)\n", d.lhs.rows, d.lhs.cols, d.rhs.cols);

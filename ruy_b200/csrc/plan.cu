@@ -108,10 +108,14 @@ int ruyb200_plan_create(ruyb200_ctx* ctx, const ruyb200_mul_desc* descs, int n, 
     // that the epilogue work spreads evenly over the SM's four schedulers.
     std::vector<BatchItem> scheduled(items.size());
     std::vector<int> rot32(grid, 0), rot64(grid, 0);
-    // Accumulator units are handed out per CTA as a ring, in the order the CTA will meet its items; the parity of a
-    // unit's use count tells the kernel which phase of that unit's barriers the item waits for.
-    struct AccRing { int next = 0; int uses[kBatchAccUnits] = {}; };
-    std::vector<AccRing> rings(grid);
+    // Accumulator units are handed out per CTA in the order the CTA will meet its items; the parity of a unit's use
+    // count tells the kernel which phase of that unit's barriers the item waits for.  A parity wait is only sound
+    // when the successive users of a unit are waited for by the same warp, in order; the kernel's two MMA warps
+    // take the even and the odd items of a CTA independently of each other, so each of them gets its own half
+    // of the units (a ring of four): a unit never passes from one warp's items to the other's.
+    constexpr int kHalf = kBatchAccUnits / 2;
+    struct AccRing { int next = 0; int uses[kHalf] = {}; };
+    std::vector<AccRing> rings(2 * (size_t)grid);
     for (size_t pos = 0; pos < order.size(); pos++) {
       BatchItem it = items[order[pos]];
       const int cta = (int)(pos % grid);
@@ -122,13 +126,15 @@ int ruyb200_plan_create(ruyb200_ctx* ctx, const ruyb200_mul_desc* descs, int n, 
       } else {
         it.m_off = 0;
       }
-      AccRing& ring = rings[cta];
+      const int stream_of_item = (int)((pos / grid) & 1);   // which MMA warp will issue it
+      AccRing& ring = rings[2 * (size_t)cta + stream_of_item];
       const int units = batch_acc_units(it.size_n);
-      if (units == 2 && ring.next == kBatchAccUnits - 1) ring.next = 0;   // two units never wrap around
+      if (units == 2 && ring.next == kHalf - 1) ring.next = 0;   // two units never wrap around
       const int u = ring.next;
-      uint32_t acc = (uint32_t)u | ((uint32_t)(ring.uses[u]++ & 1) << 4);
+      const int base = stream_of_item * kHalf;
+      uint32_t acc = (uint32_t)(base + u) | ((uint32_t)(ring.uses[u]++ & 1) << 4);
       if (units == 2) acc |= (1u << 3) | ((uint32_t)(ring.uses[u + 1]++ & 1) << 5);
-      ring.next = (u + units) % kBatchAccUnits;
+      ring.next = (u + units) % kHalf;
       it.acc = acc;
       scheduled[pos] = it;
     }

@@ -280,6 +280,7 @@ tc_f32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constan
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       const int tm = tile / args.tiles_n, tn = tile % args.tiles_n;
       const int n_tile0 = tn * args.block_n;
+      const int n_end = min(args.size_n, n_tile0 + args.block_n);   // a 32-column chunk may reach past the tile's columns
       float sum[2][32], comp[2][32];
 #pragma unroll
       for (int c = 0; c < 2; c++)
@@ -327,21 +328,21 @@ tc_f32_kernel(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constan
         for (int c = 0; c < 2; c++) {
           const int col = (2 * c + half) * 32;
           const int n0 = n_tile0 + col;
-          if (col >= args.block_n || n0 >= args.size_n) continue;
+          if (col >= args.block_n || n0 >= n_end) continue;
           float v[32];
 #pragma unroll
           for (int j = 0; j < 32; j++) {
             float x = sum[c][j] + bias_m;
-            if (ch_n && ep.bias && n0 + j < args.size_n) x += ((const float*)ep.bias)[n0 + j];
+            if (ch_n && ep.bias && n0 + j < n_end) x += ((const float*)ep.bias)[n0 + j];
             v[j] = fmaxf(fminf(x, cmax), cmin);
           }
           float* out = (float*)args.dst.data + (int64_t)m * args.dst.stride_m + n0;
-          if (n0 + 32 <= args.size_n && (((uintptr_t)out) & 15) == 0) {
+          if (n0 + 32 <= n_end && (((uintptr_t)out) & 15) == 0) {
 #pragma unroll
             for (int q = 0; q < 8; q++) __stcs(reinterpret_cast<float4*>(out) + q, make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
           } else {
 #pragma unroll
-            for (int j = 0; j < 32; j++) if (n0 + j < args.size_n) out[j] = v[j];
+            for (int j = 0; j < 32; j++) if (n0 + j < n_end) out[j] = v[j];
           }
         }
       }

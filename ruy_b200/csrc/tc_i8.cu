@@ -1136,32 +1136,39 @@ struct TileShape {
   double cycles;   // estimated SM cycles of the whole launch
 };
 
-// Constants of the estimate, in SM cycles, fitted to launches of this kernel on 4096-deep shards of 1024 to 8192
-// columns with every candidate forced in turn.  A 128-byte stage takes the longer of its four MMAs (N / 2 cycles
-// each) and of a fill time that is mostly latency: about 330 cycles plus 0.8 (two-CTA) or 1.05 (one-CTA) cycles per
-// tile column.  Narrow tiles therefore cost almost as much per stage as wide ones, and a deep mul wants the widest
-// tile; only when tiles are few or shallow does a narrower shape win, by occupying more SMs.
+// Constants of the estimate, in SM cycles, fitted to launches of this kernel with every candidate forced in turn
+// (4096-deep shards of 1024 to 8192 columns; depth 128 to 1024 with 3136 to 50176 columns).  A 128-byte stage takes the
+// longer of its four MMAs (N / 2 cycles each) and of a fill time that is mostly latency: about 330 cycles plus 0.8
+// (two-CTA) or 1.05 (one-CTA) cycles per tile column, so narrow tiles cost almost as much per stage as wide ones and a
+// deep mul wants the widest tile.  A 32-column chunk of the epilogue takes one warp about 900 cycles; with two warps
+// per lane quarter a tile drains twice as fast, and with two epilogue groups (shallow depths) two tiles drain at once.
+// The last tile's epilogue is not overlapped with anything, which is what makes narrower tiles win when a launch has
+// only one or two rounds.
 constexpr double kStageBaseCycles = 330.0;
 constexpr double kStageCyclesPerColumnPair = 0.8;
 constexpr double kStageCyclesPerColumnSingle = 1.05;
-constexpr double kChunkCycles = 330.0;        // one epilogue warp: 32 accumulator columns loaded, requantised, narrowed, stored
+constexpr double kChunkCycles = 900.0;
 constexpr double kHandoffCycles = 700.0;      // per tile: barrier round trips between producer, issuer and epilogue
 
-double tile_cycles(int bn, bool pair, int depth, bool fuse) {
+// Estimated cycles of a launch that gives every unit `rounds` tiles of this shape.
+double launch_cycles(long long rounds, int bn, bool pair, int depth, bool fuse, bool two_groups) {
   const int mma_n = bn + (fuse ? 16 : 0);
   const int k_blocks = (depth + kBlockKBytes - 1) / kBlockKBytes;
   const int last_steps = ((depth - (k_blocks - 1) * kBlockKBytes) + 31) / 32;   // K=32 steps of the last stage
   const double fill = kStageBaseCycles + (pair ? kStageCyclesPerColumnPair : kStageCyclesPerColumnSingle) * mma_n;
   const double mma_full = 4 * (mma_n / 2.0), mma_last = last_steps * (mma_n / 2.0);
   const double main_loop = (k_blocks - 1) * (mma_full > fill ? mma_full : fill) + (mma_last > fill ? mma_last : fill);
-  const double epilogue = ((bn + 31) / 32) * kChunkCycles / 2.0;   // eight warps, two per lane quarter (or two tiles in flight)
-  return (main_loop > epilogue ? main_loop : epilogue) + kHandoffCycles;
+  const int chunks = (bn + 31) / 32;
+  const double drain = two_groups ? chunks * kChunkCycles : chunks * kChunkCycles / 2.0;   // one tile, start to end
+  const double drain_rate = two_groups ? drain / 2.0 : drain;                              // per tile in steady state
+  const double steady = main_loop > drain_rate ? main_loop : drain_rate;
+  return rounds * (steady + kHandoffCycles) + drain;
 }
 
 // force_pair: -1 = free choice, 0 = one-CTA tiles only, 1 = two-CTA tiles when the shape allows them.
 // force_block_n: 0 = free choice, otherwise the widest candidate of at most that many columns is taken.
 TileShape choose_tile_shape(int size_m, int size_n, int depth, bool fuse, bool pair_possible, int sm_count, int pairs_resident,
-                            int force_pair, int force_block_n) {
+                            int force_pair, int force_block_n, bool two_groups) {
   TileShape best = {false, 0, 0.0};
   const int bn_cap = fuse ? kMaxBlockN - 16 : kMaxBlockN;
   const bool want_pair_only = force_pair > 0 && pair_possible;
@@ -1183,7 +1190,7 @@ TileShape choose_tile_shape(int size_m, int size_n, int depth, bool fuse, bool p
       if (force_block_n > 0 && bn > force_block_n && bn > 16) continue;
       const long long tiles = tiles_m * ((size_n + bn - 1) / bn);
       const long long rounds = (tiles + units - 1) / units;
-      const double cycles = rounds * tile_cycles(bn, pair, depth, fuse);
+      const double cycles = launch_cycles(rounds, bn, pair, depth, fuse, two_groups);
       // ties go to the larger tile, as in ruy (ruy/block_map.cc:410)
       if (best.block_n == 0 || cycles < best.cycles * 0.999) best = {pair, bn, cycles};
       if (force_block_n > 0) break;   // the widest admissible candidate of this kind
@@ -1236,8 +1243,9 @@ cudaError_t launch_tc_i8(const TcI8Launch& L, cudaStream_t stream) {
   const bool fuse = L.fuse_sums_m && L.ep.zp_n != 0 && L.ep.sums_m == nullptr;
   const bool pair_possible = !fuse && L.allow_pair && a.size_m >= 256 && a.size_n >= 256 && L.sm_count >= 2;
   const int pairs_resident = pair_possible ? max_resident_pairs(L.sm_count) : 0;
+  a.epi_groups = (L.depth <= 512 && L.n_mirrors <= 0) ? 2 : 1;
   const TileShape shape = choose_tile_shape(a.size_m, a.size_n, L.depth, fuse, pair_possible, L.sm_count, pairs_resident,
-                                            L.force_pair, L.force_block_n);
+                                            L.force_pair, L.force_block_n, a.epi_groups == 2);
   const bool pair = shape.pair;
   const int bn = shape.block_n;
   a.block_n = bn;
@@ -1248,7 +1256,6 @@ cudaError_t launch_tc_i8(const TcI8Launch& L, cudaStream_t stream) {
   a.tiles_n = (a.size_n + bn - 1) / bn;
   a.acc_shift = a.mma_n <= 64 ? 3 : (a.mma_n <= 128 ? 2 : 1);
   a.acc_bufs = 1 << a.acc_shift;
-  a.epi_groups = (L.depth <= 512 && L.n_mirrors <= 0) ? 2 : 1;
   const bool dst8 = L.ep.dst_dtype == RUYB200_I8 || L.ep.dst_dtype == RUYB200_U8;
   a.pack_clamps = dst8 && L.ep.clamp_min >= -32768 && L.ep.clamp_max <= 32767 && L.ep.clamp_min <= L.ep.clamp_max;
   a.clamp_lo2 = ((uint32_t)L.ep.clamp_min & 0xffffu) * 0x10001u;
