@@ -705,9 +705,11 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
     if (lhs_ok && rhs_ok) kernel = RUYB200_KERNEL_GEMV;
   }
   // fp32 muls that fill tensor-core tiles go to the 3 x TF32 kernel; small ones stay on the FFMA kernel, whose single
-  // launch costs less than the split pre-pass
+  // launch costs less than the split pre-pass, and so do very deep ones: the tensor core truncates when it adds, each
+  // 32-deep chain leaves an error of a few 1e-7, and over more than 2048 of depth their sum (measured 1.5e-5 at depth
+  // 16384) would pass the 1e-5 this library promises, which the FFMA kernel's compensated sums keep at any depth
   if (kernel == RUYB200_KERNEL_SGEMM && ctx->force_kernel != RUYB200_KERNEL_SGEMM && std::min(d.dst.rows, d.dst.cols) >= 64 &&
-      depth >= 32 && (double)d.dst.rows * d.dst.cols * depth >= (double)(1 << 21)) {
+      depth >= 32 && depth <= 2048 && (double)d.dst.rows * d.dst.cols * depth >= (double)(1 << 21)) {
     kernel = RUYB200_KERNEL_TC_F32;
   }
   const bool tc = kernel == RUYB200_KERNEL_TC_I8;

@@ -13,9 +13,9 @@
 //
 //   warp 0     : TMA producer: the weights once, then one 16 KB stage of activation lines per tile
 //   warp 1     : F x (depth / 32) tcgen05.mma kind::i8 per tile into F accumulators (M = 128 lines, N = weight rows)
-//   warps 2-9  : two epilogue groups that take tiles in turn.  The zero-point sums of the activation rows
-//                (ruy/pack.h:117-129) are taken from the stage in shared memory (each thread sums its own line),
-//                which is why the epilogue, not the MMA, releases the stage.
+//   warps 2-17 : two epilogue groups of eight warps that take tiles in turn.  The zero-point sums of the activation
+//                rows (ruy/pack.h:117-129) are taken from the stage in shared memory (each thread sums its own
+//                line), which is why the epilogue, not the MMA, releases the stage.
 //
 // No cluster multicast; all mbarrier waits are bounded as in the general kernel.
 #include <cuda.h>
@@ -34,7 +34,7 @@ constexpr int kStageBytes = kLines * 128;      // 16 KiB
 constexpr int kStages = 8;
 constexpr int kWeightBytes = 128 * 64;         // at most 128 weight rows x 64 bytes
 constexpr int kSmemBytes = kStages * kStageBytes + kWeightBytes + 1024;
-constexpr int kEpilogueWarps = 8;
+constexpr int kEpilogueWarps = 16;
 constexpr int kThreads = 64 + 32 * kEpilogueWarps;
 constexpr int kTmemCols = 512;                 // two buffers of 256 columns: F accumulators of N columns each
 constexpr int kMaxN = 128;
@@ -138,13 +138,13 @@ __device__ __forceinline__ bool elect_one() {
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-// AND-reduction of `ok` over the 128 threads of one epilogue group (named barrier 1 + group).
+// AND-reduction of `ok` over the 256 threads of one epilogue group (named barrier 1 + group).
 __device__ __forceinline__ bool group_all(bool ok, int group) {
   uint32_t res;
   asm volatile(
       "{\n\t.reg .pred p, q;\n\t"
       "setp.ne.u32 q, %1, 0;\n\t"
-      "bar.red.and.pred p, %2, 128, q;\n\t"
+      "bar.red.and.pred p, %2, 256, q;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(res)
       : "r"((uint32_t)ok), "r"(1 + group)
@@ -182,8 +182,11 @@ shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_co
   __shared__ __align__(8) uint64_t acc_full_bar[2];
   __shared__ __align__(8) uint64_t acc_empty_bar[2];
   __shared__ __align__(8) uint64_t weights_bar;
-  // per-n (weight row) terms: {addend, multiplier, exponent, 0}
-  __shared__ __align__(16) int4 n_terms[kMaxN];
+  // per-n (weight row) terms: the addends alone (four per load on the common path), and {addend, multiplier, rounding
+  // term of the short form (+ destination zero point), total shift - 32} for multipliers that vary along n
+  __shared__ __align__(16) int32_t nt_add[kMaxN];
+  __shared__ __align__(16) int4 nt4[kMaxN];
+  __shared__ int all_n_fast;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -197,11 +200,11 @@ shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_co
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; s++) {
       mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], 4);     // the four warps of the epilogue group that drained the tile
+      mbar_init(&empty_bar[s], 8);     // the eight warps of the epilogue group that drained the tile
     }
     for (int b = 0; b < 2; b++) {
       mbar_init(&acc_full_bar[b], 1);
-      mbar_init(&acc_empty_bar[b], 4);
+      mbar_init(&acc_empty_bar[b], 8);
     }
     mbar_init(&weights_bar, 1);
     abort_flag = 0;
@@ -214,17 +217,23 @@ shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_co
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   // the per-n terms are the same for every tile (there is one n tile): stage them once
+  if (threadIdx.x == 0) all_n_fast = 1;
+  __syncthreads();
   for (int n = threadIdx.x; n < kMaxN; n += kThreads) {
-    int4 t = make_int4(ep.zp_m * ep.zp_n * ep.depth, ep.mfp, ep.mexp, 0);
+    int32_t add = ep.zp_m * ep.zp_n * ep.depth, mul = ep.mfp, e = ep.mexp;
     if (n < args.size_n) {
-      if (ep.zp_m) t.x -= ep.zp_m * ep.sums_n[n];
+      if (ep.zp_m) add -= ep.zp_m * ep.sums_n[n];
       if (ch_n) {
-        if (ep.bias) t.x += ((const int32_t*)ep.bias)[n];
-        if (ep.mfp_pc) t.y = ep.mfp_pc[n];
-        if (ep.mexp_pc) t.z = ep.mexp_pc[n];
+        if (ep.bias) add += ((const int32_t*)ep.bias)[n];
+        if (ep.mfp_pc) mul = ep.mfp_pc[n];
+        if (ep.mexp_pc) e = ep.mexp_pc[n];
       }
     }
-    n_terms[n] = t;
+    const int sh = 31 - e;
+    const bool fast = sh >= 33 && sh <= 45 && ep.dst_zp > -32768 && ep.dst_zp < 32768;
+    if (!fast && n < args.size_n) all_n_fast = 0;
+    nt_add[n] = add;
+    nt4[n] = make_int4(add, mul, (int32_t)(1u << ((sh - 33) & 31)) + ep.dst_zp * (int32_t)(1u << ((sh - 32) & 31)), sh - 32);
   }
   tc_fence_before();
   __syncthreads();
@@ -295,21 +304,20 @@ shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_co
       if (++s == kStages) { s = 0; ph ^= 1; }
     }
   } else {
-    // ---------------- epilogue: two groups of four warps take tiles in turn ----------------
+    // ---------------- epilogue: two groups of eight warps take tiles in turn ----------------
+    // A warp of the epilogue is bound by the latency of its own instruction stream (about 900 cycles per 32 columns), not
+    // by any pipe, so the kernel runs sixteen of them: within a group two warps share each lane quarter and take
+    // every other (row-of-line, 32-column chunk) piece of the tile.
     const int ew = warp - 2;
-    const int group = ew / 4;
+    const int group = ew / 8;
     const int quarter = warp % 4;             // TMEM lane quarter this warp may read
+    const int half = (ew % 8) / 4;            // which of the two warps of this quarter in the group
     const int line_in_tile = quarter * 32 + lane;
     const int32_t cmin = ep.clamp_min, cmax = ep.clamp_max;
     const bool late_clamp = args.pack_clamps != 0;
     const bool mul_per_n = ch_n && (ep.mfp_pc != nullptr || ep.mexp_pc != nullptr);
-    const bool mul_per_m = !ch_n && (ep.mfp_pc != nullptr || ep.mexp_pc != nullptr);
-    // one multiplier for the whole matrix and a total shift of 32..45 bits: the result is the high word of a 64-bit
-    // multiply-add shifted on, with the destination zero point riding in the rounding term
-    const int sh_u = 31 - ep.mexp;
-    const bool uniform_fast = !kX86 && !mul_per_n && !mul_per_m && sh_u >= 32 && sh_u <= 45 && ep.dst_zp > -32768 && ep.dst_zp < 32768;
-    const long long rnd_hw = (1ll << ((sh_u - 1) & 63)) + (long long)ep.dst_zp * (1ll << (sh_u & 63));
-    const int sh_hi = (sh_u - 32) & 31;
+    const bool zp_small = ep.dst_zp > -32768 && ep.dst_zp < 32768;
+    const int chunks = (args.size_n + 31) / 32;
     uint32_t tcount = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, tcount++) {
@@ -330,63 +338,100 @@ shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_co
       mbar_try_wait(&full_bar[s], sph);
       const long long line = (long long)tile * kLines + line_in_tile;
       const int m0 = (int)(line * fold);
-      // zero-point sums of this thread's rows, from its own line in shared memory (16-byte piece j of line r sits at j ^ (r & 7))
-      int32_t add_m[4] = {0, 0, 0, 0};
-      if (ep.zp_n) {
+      // Per-row terms of this thread's rows: the zero-point sum comes from the thread's own line in shared memory
+      // (16-byte piece j of line r sits at j ^ (r & 7)); the multiplier is reduced to the constants of the short form
+      // result = (mulhi(x, mul) + rnd) >> sh, valid for a total shift of 33..45 bits, where it is exact:
+      // (x * mul + 2^(s-1)) >> s == (hi32(x * mul) + 2^(s-33)) >> (s - 32), and the zero point rides in rnd.
+      int32_t add_q[4], mul_q[4], exp_q[4], rnd_q[4];
+      bool fast_lane = !kX86 && zp_small;
+      {
         const uint8_t* lp = smem + s * kStageBytes + line_in_tile * 128;
         const int per_row = pitch / 16;
-        for (int q = 0; q < fold; q++) {
-          int32_t sum = 0;
-          for (int j = 0; j < per_row; j++) {
-            const uint4 v = *reinterpret_cast<const uint4*>(lp + (((q * per_row + j) ^ (line_in_tile & 7)) << 4));
-            if (args.m_signed) {
-              sum = __dp4a((int)v.x, 0x01010101, sum);
-              sum = __dp4a((int)v.y, 0x01010101, sum);
-              sum = __dp4a((int)v.z, 0x01010101, sum);
-              sum = __dp4a((int)v.w, 0x01010101, sum);
-            } else {
-              sum = (int)__dp4a(v.x, 0x01010101u, (unsigned)sum);
-              sum = (int)__dp4a(v.y, 0x01010101u, (unsigned)sum);
-              sum = (int)__dp4a(v.z, 0x01010101u, (unsigned)sum);
-              sum = (int)__dp4a(v.w, 0x01010101u, (unsigned)sum);
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          add_q[q] = 0;
+          mul_q[q] = ep.mfp;
+          exp_q[q] = ep.mexp;
+          if (q < fold) {
+            const int m = m0 + q;
+            if (ep.zp_n) {
+              int32_t sum = 0;
+              for (int j = 0; j < per_row; j++) {
+                const uint4 v = *reinterpret_cast<const uint4*>(lp + (((q * per_row + j) ^ (line_in_tile & 7)) << 4));
+                if (args.m_signed) {
+                  sum = __dp4a((int)v.x, 0x01010101, sum);
+                  sum = __dp4a((int)v.y, 0x01010101, sum);
+                  sum = __dp4a((int)v.z, 0x01010101, sum);
+                  sum = __dp4a((int)v.w, 0x01010101, sum);
+                } else {
+                  sum = (int)__dp4a(v.x, 0x01010101u, (unsigned)sum);
+                  sum = (int)__dp4a(v.y, 0x01010101u, (unsigned)sum);
+                  sum = (int)__dp4a(v.z, 0x01010101u, (unsigned)sum);
+                  sum = (int)__dp4a(v.w, 0x01010101u, (unsigned)sum);
+                }
+              }
+              add_q[q] = -ep.zp_n * sum;
+            }
+            if (!ch_n && m < args.size_m) {
+              if (ep.bias) add_q[q] += ((const int32_t*)ep.bias)[m];
+              if (ep.mfp_pc) mul_q[q] = ep.mfp_pc[m];
+              if (ep.mexp_pc) exp_q[q] = ep.mexp_pc[m];
             }
           }
-          add_m[q] = -ep.zp_n * sum;
+          const int sh = 31 - exp_q[q];
+          fast_lane = fast_lane && sh >= 33 && sh <= 45;
+          rnd_q[q] = (int32_t)(1u << ((sh - 33) & 31)) + ep.dst_zp * (int32_t)(1u << ((sh - 32) & 31));
         }
       }
+      const bool fast_m = __all_sync(0xffffffffu, fast_lane) != 0;
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty_bar[s]);       // the stage may be refilled
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256u;
-      for (int q = 0; q < fold; q++) {
+      for (int piece = half; piece < fold * chunks; piece += 2) {
+        const int q = piece / chunks;
+        const int c = (piece - q * chunks) * 32;
         const int m = m0 + q;
         const bool m_ok = m < args.size_m;
-        int32_t mul_m = ep.mfp, exp_m = ep.mexp, addm = add_m[q];
-        if (m_ok && !ch_n) {
-          if (ep.bias) addm += ((const int32_t*)ep.bias)[m];
-          if (ep.mfp_pc) mul_m = ep.mfp_pc[m];
-          if (ep.mexp_pc) exp_m = ep.mexp_pc[m];
-        }
-        for (int c = 0; c < args.size_n; c += 32) {
-          uint32_t r[32];
-          tmem_ld_32(taddr + (uint32_t)(q * n_cols + c), r);
-          tmem_ld_wait();
-          if (m_ok) {
-          int32_t v[32];
-          if (uniform_fast) {
+        int32_t addm = add_q[0], mulm = mul_q[0], expm = exp_q[0], rndm = rnd_q[0];
 #pragma unroll
-            for (int j = 0; j < 32; j++) {
-              const int32_t x = (int32_t)(r[j] + (uint32_t)n_terms[c + j].x + (uint32_t)addm);
-              const long long p = (long long)x * (long long)mul_m + rnd_hw;
-              const int32_t y = (int32_t)(p >> 32) >> sh_hi;
-              v[j] = late_clamp ? y : max(min(y, cmax), cmin);
+        for (int t = 1; t < 4; t++) {
+          if (q == t) { addm = add_q[t]; mulm = mul_q[t]; expm = exp_q[t]; rndm = rnd_q[t]; }
+        }
+        uint32_t r[32];
+        tmem_ld_32(taddr + (uint32_t)(q * n_cols + c), r);
+        tmem_ld_wait();
+        if (m_ok) {
+          int32_t v[32];
+          if (mul_per_n ? all_n_fast != 0 : fast_m) {
+            const int sh_hi = (31 - expm - 32) & 31;
+#pragma unroll
+            for (int j4 = 0; j4 < 8; j4++) {
+              if (mul_per_n) {
+#pragma unroll
+                for (int t = 0; t < 4; t++) {
+                  const int4 nt = nt4[c + 4 * j4 + t];
+                  const int32_t x = (int32_t)(r[4 * j4 + t] + (uint32_t)nt.x + (uint32_t)addm);
+                  const int32_t y = (__mulhi(x, nt.y) + nt.z) >> nt.w;
+                  v[4 * j4 + t] = late_clamp ? y : max(min(y, cmax), cmin);
+                }
+              } else {
+                const int4 ad = *reinterpret_cast<const int4*>(&nt_add[c + 4 * j4]);
+                const int32_t adds[4] = {ad.x, ad.y, ad.z, ad.w};
+#pragma unroll
+                for (int t = 0; t < 4; t++) {
+                  const int32_t x = (int32_t)(r[4 * j4 + t] + (uint32_t)adds[t] + (uint32_t)addm);
+                  const int32_t y = (__mulhi(x, mulm) + rndm) >> sh_hi;
+                  v[4 * j4 + t] = late_clamp ? y : max(min(y, cmax), cmin);
+                }
+              }
             }
           } else {
 #pragma unroll
             for (int j = 0; j < 32; j++) {
-              const int4 t = n_terms[c + j];
-              int32_t x = (int32_t)(r[j] + (uint32_t)t.x + (uint32_t)addm);
-              const int32_t mul = mul_per_n ? t.y : mul_m;
-              const int e = mul_per_n ? t.z : exp_m;
+              const int4 nt = nt4[c + j];
+              int32_t x = (int32_t)(r[j] + (uint32_t)nt_add[c + j] + (uint32_t)addm);
+              const int32_t mul = mul_per_n ? nt.y : mulm;
+              const int e = mul_per_n ? -1 - nt.w : expm;     // nt.w holds 31 - e - 32
               x = kX86 ? requant_x86(x, mul, e) : requant_reference(x, mul, e);
               x = (int32_t)((uint32_t)x + (uint32_t)ep.dst_zp);
               v[j] = late_clamp ? x : max(min(x, cmax), cmin);
@@ -404,9 +449,8 @@ shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_co
               if (c + j < args.size_n) out[j] = (uint8_t)(late_clamp ? max(min(v[j], cmax), cmin) : v[j]);
             }
           }
-          }
-          __syncwarp();   // the next tensor-memory load is a warp-wide instruction
         }
+        __syncwarp();   // the next tensor-memory load is a warp-wide instruction
       }
       tc_fence_before();
       __syncwarp();

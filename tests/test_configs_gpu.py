@@ -161,7 +161,7 @@ def test_config3_full_against_compiled_reference(gpu_ctx):
 SHALLOW = [  # (rows, depth, cols, lhs, rhs, dst, per-channel, channel dimension)
     (64, 32, 151552 + 4 * 37, "uint8", "uint8", "uint8", False, "row"),     # ragged last tile
     (40, 32, 160000, "int8", "uint8", "int8", True, "row"),                 # n not a multiple of 16, per-row multipliers
-    (128, 64, 75776 + 2 * 51, "uint8", "int8", "uint8", True, "col"),       # depth 64, per-column (activation side) channels
+    (128, 64, 75776 + 2 * 51, "int8", "uint8", "int8", True, "col"),        # depth 64, per-column (activation side) channels
     (100, 64, 80000, "int8", "int8", "int8", False, "row"),
 ]
 

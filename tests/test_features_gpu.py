@@ -282,7 +282,7 @@ def test_mirrored_mul_with_the_exchange_folded_in():
 
 # ---- fp32 on the tensor core ------------------------------------------------------------------------------
 
-TF32_SHAPES = [(1024, 1024, 1024), (200, 333, 130), (64, 512, 64), (129, 4100, 96), (640, 32, 257), (96, 16384, 72)]
+TF32_SHAPES = [(1024, 1024, 1024), (200, 333, 130), (64, 512, 64), (129, 2048, 96), (640, 32, 257), (300, 1500, 520)]
 
 
 @pytest.mark.parametrize("shape", TF32_SHAPES, ids=lambda s: "x".join(map(str, s)))
@@ -298,6 +298,17 @@ def test_float_muls_on_the_tensor_core(shape, gpu_ctx):
         wide = util.run_oracle(c, wide_float=True).astype(np.float64)
         err = np.abs(got.astype(np.float64) - wide)
         assert np.all(err <= 1e-5 * np.maximum(np.abs(wide), 1.0)), (orders, float(err.max()))
+
+
+@pytest.mark.parametrize("shape", [(129, 4100, 96), (96, 16384, 72)], ids=lambda s: "x".join(map(str, s)))
+def test_very_deep_float_muls_stay_on_the_compensated_kernel(shape, gpu_ctx):
+    """Beyond a depth of 2048 the truncating accumulation of the tensor core would not hold 1e-5; those muls keep the
+    FFMA kernel with its compensated sums."""
+    c = cases.random_case(*shape, "float32", "float32", "float32", orders="RCC", seed=sum(shape))
+    got, _ = util.run_gpu(c, gpu_ctx)
+    assert gpu_ctx.counters()["last_kernel"] == "sgemm"
+    wide = util.run_oracle(c, wide_float=True).astype(np.float64)
+    assert np.all(np.abs(got.astype(np.float64) - wide) <= 1e-5 * np.maximum(np.abs(wide), 1.0))
 
 
 def test_float_tensor_core_and_ffma_kernels_agree():
