@@ -209,7 +209,6 @@ struct ruyb200_ctx {
   cudaEvent_t chunk_done[kMaxChunks] = {};
   cudaEvent_t chunk_start = nullptr;
   bool no_chunks = false;   // RUYB200_NO_CHUNKS=1: one copy in, one kernel, one copy out
-  int chunk_target = 16;    // RUYB200_CHUNKS=n: how many chunks a large host-operand mul is cut into (2..16)
   bool trace = false;       // RUYB200_TRACE=1: one line per mul on stderr with the decisions taken (cf. ruy/trace.h)
 };
 
@@ -604,8 +603,7 @@ int run_chunks(ruyb200_ctx* ctx, const ruyb200_mul_desc& d, const TcI8Launch& L,
   // copy out are not overlapped with anything, so they should be short), at least 1 MiB each
   const size_t dst_pitch = (size_t)d.dst.stride * dst_esz;
   const int64_t moved_per_m = (m_host ? stride_w : 0) + (dst_host ? (int64_t)dst_pitch : 0);   // bytes over PCIe per m index
-  const int target = ctx->chunk_target;
-  int step = ((width + target - 1) / target + 255) / 256 * 256;
+  int step = ((width + 15) / 16 + 255) / 256 * 256;
   while ((int64_t)step * moved_per_m < (1 << 20) && step < width) step *= 2;
   int chunks = (width + step - 1) / step;
   if (chunks > kMaxChunks) {
@@ -1057,8 +1055,6 @@ int ruyb200_ctx_create_on_stream(int device, void* cuda_stream, ruyb200_ctx** ou
   ctx->no_shallow = ns && *ns && *ns != '0';
   const char* nc = getenv("RUYB200_NO_CHUNKS");
   ctx->no_chunks = nc && *nc && *nc != '0';
-  const char* ck = getenv("RUYB200_CHUNKS");
-  if (ck && atoi(ck) >= 2 && atoi(ck) <= kMaxChunks) ctx->chunk_target = atoi(ck);
   const char* tr = getenv("RUYB200_TRACE");
   ctx->trace = tr && *tr && *tr != '0';
   *out = ctx;
@@ -1400,15 +1396,8 @@ int ctx_plan_item(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, BatchItem* out
     }
   }
   const bool dst_col_major = d.dst.order == RUYB200_COL_MAJOR;
-  // Which side sits on the tensor-memory lanes (m).  For 8-bit destinations it is the side of the destination's
-  // NON-contiguous dimension: a thread then holds consecutive destination bytes and stores them sixteen at a time.
-  // Wider destinations keep the contiguous dimension on the lanes (a warp writes 32 consecutive elements).
-  const bool n_major = d.dst.dtype == RUYB200_I8 || d.dst.dtype == RUYB200_U8;
-  const int contiguous_side = dst_col_major ? 0 : 1;      // the LHS indexes rows, the RHS columns
-  const int m_idx = n_major ? 1 - contiguous_side : contiguous_side;
-  const int n_idx = 1 - m_idx;
-  const SideView& ms = views[m_idx];
-  const SideView& ns = views[n_idx];
+  const SideView& ms = dst_col_major ? views[0] : views[1];   // the destination's contiguous dimension
+  const SideView& ns = dst_col_major ? views[1] : views[0];
   if (!batch_i8_fits(ms, ns, depth)) return RUYB200_OK;
   const bool channel_row = d.params.channel_dimension == RUYB200_CHANNEL_ROW;
   out->m_ptr = (const uint8_t*)ms.data;
@@ -1433,22 +1422,20 @@ int ctx_plan_item(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, BatchItem* out
   out->clamp_min = d.params.clamp_min.i;
   out->clamp_max = d.params.clamp_max.i;
   uint32_t flags = 0;
-  const bool channel_on_m = (channel_row ? 0 : 1) == m_idx;
+  const bool channel_on_m = dst_col_major ? channel_row : !channel_row;
   if (!channel_on_m) flags |= kItemChannelOnN;
-  if (n_major) flags |= kItemNMajor;
   if (ms.dtype == RUYB200_I8) flags |= kItemMSigned;
   if (ns.dtype == RUYB200_I8) flags |= kItemNSigned;
   if (ctx_rounding_is_x86(ctx, d.params.rounding_mode)) flags |= kItemX86;
   flags |= (uint32_t)d.dst.dtype << kItemDstShift;
   // the cache's sums stay valid as long as the entry is pinned by the plan
-  out->sums_m = ns.zero_point != 0 ? cached_sums[m_idx] : nullptr;
-  out->sums_n = ms.zero_point != 0 ? cached_sums[n_idx] : nullptr;
+  out->sums_m = ns.zero_point != 0 ? cached_sums[dst_col_major ? 0 : 1] : nullptr;
   auto tma_ok = [](const SideView& v) { return (((uintptr_t)v.data | (uintptr_t)v.stride_w) & 15) == 0; };
   if (tma_ok(ms)) flags |= kItemMTma;
   if (tma_ok(ns)) flags |= kItemNTma;
   const int nch = channel_on_m ? ms.width : ns.width;
-  bool vec_bulk = (nch & 3) == 0 && (!out->sums_m || (ms.width & 3) == 0) && (!out->sums_n || (ns.width & 3) == 0);
-  const void* vec_ptrs[5] = {out->bias, out->mfp_pc, out->mexp_pc, out->sums_m, out->sums_n};
+  bool vec_bulk = (nch & 3) == 0 && (ms.width & 3) == 0;
+  const void* vec_ptrs[4] = {out->bias, out->mfp_pc, out->mexp_pc, out->sums_m};
   for (const void* p : vec_ptrs) vec_bulk = vec_bulk && ((uintptr_t)p & 15) == 0;
   if (vec_bulk) flags |= kItemVecBulk;
   out->flags = flags;

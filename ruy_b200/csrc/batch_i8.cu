@@ -61,13 +61,11 @@ struct alignas(16) MmaCmd {
   uint32_t kstep_m, kstep_n, idesc, nk_fence;   // nk_fence: K=32 steps (bits 0-7), BatchItem::acc (bits 8-13), bit 31 = a tile was written by cp.async
 };
 
-// Per-n terms staged by the epilogue: the addend, the multiplier, and the constants of the short requantisation form
-// result = (mulhi(x, mul) + rnd) >> sh_hi with sh_hi = (31 - exponent) - 32 (the exponent is -1 - sh_hi).
 struct NTerm {
   int32_t add;
   int32_t mul;
-  int32_t rnd;
-  int32_t sh_hi;
+  int32_t exp;
+  int32_t pad;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -280,7 +278,7 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
   __shared__ __align__(8) uint64_t acc_empty_bar[kAccUnits];
   __shared__ __align__(16) BatchItem slot_item[kSlots];
   __shared__ MmaCmd slot_cmd[kSlots];
-  __shared__ __align__(16) int32_t slot_vec[kSlots][5][128];   // the item's bias / multiplier / exponent vectors and cached m-side / n-side sums
+  __shared__ __align__(16) int32_t slot_vec[kSlots][4][128];   // the item's bias / multiplier / exponent vectors and cached m-side sums
   __shared__ __align__(16) NTerm n_terms[kEpiGroups][kAccCols];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
@@ -417,23 +415,20 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
       const int32_t* v1 = item.mfp_pc;
       const int32_t* v2 = item.mexp_pc;
       const int32_t* v3 = item.sums_m;
-      const int32_t* v4 = item.sums_n;
 #ifdef RUYB200_DEBUG_KNOBS
       if (debug & 2) {
       } else
 #endif
       if (flags & kItemVecBulk) {
-        const int32_t* vp = lane == 0 ? v0 : (lane == 1 ? v1 : (lane == 2 ? v2 : (lane == 3 ? v3 : v4)));
-        const uint32_t vbytes = 4u * (uint32_t)(lane == 3 ? size_m : (lane == 4 ? size_n : nch));
-        if (lane < 5 && vp) bulk_load(smem_u32(&slot_vec[s][lane][0]), vp, vbytes, &full_bar[s]);
-        tx += 4u * (uint32_t)nch * ((v0 ? 1u : 0u) + (v1 ? 1u : 0u) + (v2 ? 1u : 0u)) + (v3 ? 4u * (uint32_t)size_m : 0u) +
-              (v4 ? 4u * (uint32_t)size_n : 0u);
+        const int32_t* vp = lane == 0 ? v0 : (lane == 1 ? v1 : (lane == 2 ? v2 : v3));
+        const uint32_t vbytes = 4u * (uint32_t)(lane == 3 ? size_m : nch);
+        if (lane < 4 && vp) bulk_load(smem_u32(&slot_vec[s][lane][0]), vp, vbytes, &full_bar[s]);
+        tx += 4u * (uint32_t)nch * ((v0 ? 1u : 0u) + (v1 ? 1u : 0u) + (v2 ? 1u : 0u)) + (v3 ? 4u * (uint32_t)size_m : 0u);
       } else {
         if (v0) for (int i = lane; i < nch; i += 32) cp_async_zfill<4>(smem_u32(&slot_vec[s][0][i]), v0 + i, 4);
         if (v1) for (int i = lane; i < nch; i += 32) cp_async_zfill<4>(smem_u32(&slot_vec[s][1][i]), v1 + i, 4);
         if (v2) for (int i = lane; i < nch; i += 32) cp_async_zfill<4>(smem_u32(&slot_vec[s][2][i]), v2 + i, 4);
         if (v3) for (int i = lane; i < size_m; i += 32) cp_async_zfill<4>(smem_u32(&slot_vec[s][3][i]), v3 + i, 4);
-        if (v4) for (int i = lane; i < size_n; i += 32) cp_async_zfill<4>(smem_u32(&slot_vec[s][4][i]), v4 + i, 4);
       }
       // full_bar[s] completes when every lane's cp.async copies have landed (32 deferred arrivals), lane 0 has
       // arrived (which publishes the header written above) and the bulk / tensor copies have delivered `tx` bytes
@@ -584,43 +579,32 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
       const bool ch_n = (item.flags & kItemChannelOnN) != 0;
       const bool x86 = (item.flags & kItemX86) != 0;
       const int dst_dtype = (int)((item.flags >> kItemDstShift) & 7u);
-      const bool n_major = (item.flags & kItemNMajor) != 0;
-      const bool per_n = n_major || ch_n || item.zp_m != 0;   // some term varies along n (or the n-major path wants them staged)
+      const bool per_n = ch_n || item.zp_m != 0;   // some term varies along n
       const int kpad = (item.depth + 31) & ~31;
       const uint8_t* tile_m = smem + s * kSlotBytes;
       const uint8_t* tile_n = tile_m + kTileBytes;
       const int32_t* vbias = item.bias ? slot_vec[s][0] : nullptr;
       const int32_t* vmfp = item.mfp_pc ? slot_vec[s][1] : nullptr;
       const int32_t* vmexp = item.mexp_pc ? slot_vec[s][2] : nullptr;
-      const bool zp_small = item.dst_zp > -32768 && item.dst_zp < 32768;
-      bool n_fast = true;      // this thread's n allows the short requantisation form
       if (per_n) {
         const int n = gtid;
         NTerm t;
         t.add = item.zp_m * item.zp_n * item.depth;
         t.mul = item.mfp;
-        int e = item.mexp;
+        t.exp = item.mexp;
+        t.pad = 0;
         if (n < item.size_n) {
-          // zero-point term of this destination column: the sum over depth of the n-side row, from the prepacked cache
-          // when it holds it, else taken from the packed tile
+          // zero-point term of this destination column: the sum over depth of the n-side row, taken from the packed tile
           if (item.zp_m) {
             const bool sg = (item.flags & kItemNSigned) != 0;
-            const int32_t sum = item.sums_n ? slot_vec[s][4][n]
-                                            : ((item.flags & kItemNTma) ? tile_row_sum_swizzled(tile_n, n, kpad, sg)
-                                                                        : tile_row_sum(tile_n, n, kpad, sg));
-            t.add -= item.zp_m * sum;
+            t.add -= item.zp_m * ((item.flags & kItemNTma) ? tile_row_sum_swizzled(tile_n, n, kpad, sg) : tile_row_sum(tile_n, n, kpad, sg));
           }
           if (ch_n) {
             if (vbias) t.add += vbias[n];
             if (vmfp) t.mul = vmfp[n];
-            if (vmexp) e = vmexp[n];
+            if (vmexp) t.exp = vmexp[n];
           }
-          const int sh = 31 - e;
-          n_fast = sh >= 33 && sh <= 45;
         }
-        const int sh = 31 - e;
-        t.sh_hi = sh - 32;
-        t.rnd = (int32_t)(1u << ((sh - 33) & 31)) + item.dst_zp * (int32_t)(1u << ((sh - 32) & 31));
         nt[n] = t;
       }
       const int m = quarter * 32 + lane - item.m_off;     // tile row -> destination index along m
@@ -645,9 +629,7 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
       const int32_t cmin = item.clamp_min, cmax = item.clamp_max, dzp = item.dst_zp;
       uint8_t* const dst_base = item.dst;
       const int dst_stride = item.dst_stride;
-      // n_terms[] staged (uniform over the group: per_n comes from the header); the same reduction tells whether
-      // every n of the item allows the short form
-      const bool all_n_fast = per_n ? group_all(n_fast, group) : true;
+      if (per_n) group_all(true, group);   // n_terms[] staged (uniform over the group: per_n comes from the header)
       __syncwarp();                        // this warp is done with the slot's header, vectors and tiles
       if (lane == 0) mbar_arrive(&empty_bar[s]);
 #ifdef RUYB200_DEBUG_CLOCKS
@@ -657,78 +639,6 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
       const bool quarter_used = quarter * 32 + 32 > m_off && quarter * 32 < m_off + size_m;
       if (quarter_used) {
         const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(unit * kUnitCols);
-        if (n_major) {
-          // The destination is contiguous along n: this thread owns row m of it and writes 16 results per store.
-          // Requantisation takes the short form (one multiply-high, an add and a shift per value) whenever every
-          // exponent involved allows it; the multiplier comes from the staged per-n terms when the channel runs along
-          // n, else from this thread's registers.
-          const int sh_m = 31 - exp_m;
-          const bool lane_fast = sh_m >= 33 && sh_m <= 45;
-          const bool short_form = !x86 && zp_small && all_n_fast && (ch_n || __all_sync(0xffffffffu, lane_fast));
-          const int32_t rnd_m = (int32_t)(1u << ((sh_m - 33) & 31)) + dzp * (int32_t)(1u << ((sh_m - 32) & 31));
-          const int sh_hi_m = (sh_m - 32) & 31;
-          const uint32_t lo2 = ((uint32_t)cmin & 0xffffu) * 0x10001u, hi2 = ((uint32_t)cmax & 0xffffu) * 0x10001u;
-          uint8_t* const row = dst_base + (int64_t)m * dst_stride;
-          auto process_n = [&](uint32_t (&rr)[16], int c) {
-            int32_t v[16];
-            if (short_form && ch_n) {
-#pragma unroll
-              for (int q = 0; q < 16; q++) {
-                const NTerm t = nt[(c + q) & (kAccCols - 1)];
-                const int32_t x = (int32_t)(rr[q] + (uint32_t)t.add + (uint32_t)add_m);
-                v[q] = (__mulhi(x, t.mul) + t.rnd) >> t.sh_hi;
-              }
-            } else if (short_form) {
-#pragma unroll
-              for (int q = 0; q < 16; q++) {
-                const int32_t x = (int32_t)(rr[q] + (uint32_t)nt[(c + q) & (kAccCols - 1)].add + (uint32_t)add_m);
-                v[q] = (__mulhi(x, mul_m) + rnd_m) >> sh_hi_m;
-              }
-            } else {
-#pragma unroll
-              for (int q = 0; q < 16; q++) {
-                const NTerm t = nt[(c + q) & (kAccCols - 1)];
-                int32_t x = (int32_t)(rr[q] + (uint32_t)t.add + (uint32_t)add_m);
-                const int32_t mul = ch_n ? t.mul : mul_m;
-                const int e = ch_n ? -1 - t.sh_hi : exp_m;
-                x = x86 ? requant_x86(x, mul, e) : requant_reference(x, mul, e);
-                v[q] = (int32_t)((uint32_t)x + (uint32_t)dzp);
-              }
-            }
-            // saturate to 16 bits two at a time, clamp both halves at once, keep the low bytes
-            uint32_t w[4];
-#pragma unroll
-            for (int q = 0; q < 4; q++) {
-              uint32_t lo, hi;
-              asm("cvt.pack.sat.s16.s32 %0, %1, %2;" : "=r"(lo) : "r"(v[4 * q + 1]), "r"(v[4 * q]));
-              asm("cvt.pack.sat.s16.s32 %0, %1, %2;" : "=r"(hi) : "r"(v[4 * q + 3]), "r"(v[4 * q + 2]));
-              lo = __vmaxs2(__vmins2(lo, hi2), lo2);
-              hi = __vmaxs2(__vmins2(hi, hi2), lo2);
-              w[q] = __byte_perm(lo, hi, 0x6420);
-            }
-            uint8_t* o = row + c;
-            const int lim = size_n - c;
-            if (lim >= 16 && (((uintptr_t)o) & 15) == 0) {
-              *reinterpret_cast<uint4*>(o) = make_uint4(w[0], w[1], w[2], w[3]);
-            } else if (lim >= 16 && (((uintptr_t)o) & 7) == 0) {
-              *reinterpret_cast<uint2*>(o) = make_uint2(w[0], w[1]);
-              *reinterpret_cast<uint2*>(o + 8) = make_uint2(w[2], w[3]);
-            } else {
-#pragma unroll
-              for (int q = 0; q < 16; q++) {
-                if (q < lim) o[q] = (uint8_t)(w[q >> 2] >> (8 * (q & 3)));
-              }
-            }
-          };
-          // one register buffer: sixteen epilogue warps hide the load latency among themselves
-          uint32_t rr[16];
-          for (int c = 0; c < size_n; c += 16) {
-            tmem_ld_16(taddr + c, rr);
-            tmem_ld_wait();
-            if (m_ok) process_n(rr, c);
-            __syncwarp();
-          }
-        } else {
         const int esz = dst_dtype == RUYB200_I32 ? 4 : (dst_dtype == RUYB200_I16 ? 2 : 1);
         const int64_t step = (int64_t)dst_stride * esz;
         uint8_t* out = dst_base + (int64_t)m * esz;
@@ -768,7 +678,7 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
               if (per_n) {
                 const NTerm t = nt[(c + q) & (kAccCols - 1)];
                 x = (int32_t)((uint32_t)x + (uint32_t)t.add);
-                if (ch_n) { mul = t.mul; e = -1 - t.sh_hi; }
+                if (ch_n) { mul = t.mul; e = t.exp; }
               }
               if (dst_dtype != RUYB200_I32) {
                 x = x86 ? requant_x86(x, mul, e) : requant_reference(x, mul, e);
@@ -825,7 +735,6 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
             if (c + 32 < size_n) tmem_ld_16(taddr + c + 32, ra);
             if (m_ok) process(rb, c + 16);
           }
-        }
         }
       }
       tc_fence_before();

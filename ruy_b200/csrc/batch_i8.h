@@ -17,14 +17,12 @@ enum : uint32_t {
   kItemDstShift = 4,           // 3 bits: ruyb200_dtype of the destination
   kItemMTma = 1u << 8,         // the m-side operand is fetched by one tensor-map copy (16-byte aligned base and row stride)
   kItemNTma = 1u << 9,         // the same for the n-side operand
-  kItemVecBulk = 1u << 10,     // every per-channel vector is 16-byte aligned with a length that is a multiple of 4
-  kItemNMajor = 1u << 11       // the destination is contiguous along n (8-bit destinations): a thread packs its results into 16-byte stores
+  kItemVecBulk = 1u << 10      // every per-channel vector is 16-byte aligned with a length that is a multiple of 4
 };
 
-// One small mul, fully resolved to device pointers.  "m" is the dimension that sits on the tensor-memory lanes, "n"
-// the one along the accumulator columns.  Without kItemNMajor m is the destination's contiguous dimension and element
-// (m, n) is stored at dst[n * dst_stride + m]; with it n is the contiguous one and the element is at
-// dst[m * dst_stride + n].  Both operands are depth-contiguous with rows stride_* bytes apart.
+// One small mul, fully resolved to device pointers.  "m" is the destination's contiguous dimension
+// (it sits on the tensor-memory lanes), "n" the other one; element (m, n) is stored at
+// dst[n * dst_stride + m].  Both operands are depth-contiguous with rows stride_* bytes apart.
 struct alignas(16) BatchItem {
   const uint8_t* m_ptr;
   const uint8_t* n_ptr;
@@ -52,7 +50,7 @@ struct alignas(16) BatchItem {
   // 64-column unit, bit 3 set if it takes two units (more than 64 destination columns along n), bits 4 / 5 the
   // parity of the first / second unit's use count (which phase of the unit's barriers this item sees).
   uint32_t acc;
-  const int32_t* sums_n;   // the same for the n-side operand (one per n)
+  int32_t reserved[2];
 };
 static_assert(sizeof(BatchItem) == 128, "BatchItem is copied as eight 16-byte pieces");
 
