@@ -209,6 +209,7 @@ struct ruyb200_ctx {
   cudaEvent_t chunk_done[kMaxChunks] = {};
   cudaEvent_t chunk_start = nullptr;
   bool no_chunks = false;   // RUYB200_NO_CHUNKS=1: one copy in, one kernel, one copy out
+  int chunk_target = 4;     // RUYB200_CHUNKS=n: how many chunks a large host-operand mul is cut into (2..16)
   bool trace = false;       // RUYB200_TRACE=1: one line per mul on stderr with the decisions taken (cf. ruy/trace.h)
 };
 
@@ -599,11 +600,13 @@ int run_chunks(ruyb200_ctx* ctx, const ruyb200_mul_desc& d, const TcI8Launch& L,
   }
   const int width = L.m_side.width;
   const int64_t stride_w = L.m_side.stride_w;            // bytes: the operand is 8-bit
-  // chunks of a multiple of 256 m indices (whole two-CTA tiles), about sixteen of them (the first copy in and the last
-  // copy out are not overlapped with anything, so they should be short), at least 1 MiB each
+  // chunks of a multiple of 256 m indices (whole two-CTA tiles), at least 1 MiB each.  Few chunks leave the first copy
+  // in and the last copy out exposed; many chunks pay a cross-stream hand-off each.  Measured on config 3 (33.6 MB each
+  // way): 4 chunks 1.02 ms, 8 1.06, 12 1.10, 16 1.19.
   const size_t dst_pitch = (size_t)d.dst.stride * dst_esz;
   const int64_t moved_per_m = (m_host ? stride_w : 0) + (dst_host ? (int64_t)dst_pitch : 0);   // bytes over PCIe per m index
-  int step = ((width + 15) / 16 + 255) / 256 * 256;
+  const int target = ctx->chunk_target;
+  int step = ((width + target - 1) / target + 255) / 256 * 256;
   while ((int64_t)step * moved_per_m < (1 << 20) && step < width) step *= 2;
   int chunks = (width + step - 1) / step;
   if (chunks > kMaxChunks) {
@@ -1055,6 +1058,8 @@ int ruyb200_ctx_create_on_stream(int device, void* cuda_stream, ruyb200_ctx** ou
   ctx->no_shallow = ns && *ns && *ns != '0';
   const char* nc = getenv("RUYB200_NO_CHUNKS");
   ctx->no_chunks = nc && *nc && *nc != '0';
+  const char* ck = getenv("RUYB200_CHUNKS");
+  if (ck && atoi(ck) >= 2 && atoi(ck) <= kMaxChunks) ctx->chunk_target = atoi(ck);
   const char* tr = getenv("RUYB200_TRACE");
   ctx->trace = tr && *tr && *tr != '0';
   *out = ctx;

@@ -13,7 +13,7 @@
 //
 //   warp 0     : TMA producer: the weights once, then one 16 KB stage of activation lines per tile
 //   warp 1     : F x (depth / 32) tcgen05.mma kind::i8 per tile into F accumulators (M = 128 lines, N = weight rows)
-//   warps 2-17 : two epilogue groups of eight warps that take tiles in turn.  The zero-point sums of the activation
+//   warps 2-9  : two epilogue groups of four warps that take tiles in turn.  The zero-point sums of the activation
 //                rows (ruy/pack.h:117-129) are taken from the stage in shared memory (each thread sums its own
 //                line), which is why the epilogue, not the MMA, releases the stage.
 //
@@ -34,7 +34,9 @@ constexpr int kStageBytes = kLines * 128;      // 16 KiB
 constexpr int kStages = 8;
 constexpr int kWeightBytes = 128 * 64;         // at most 128 weight rows x 64 bytes
 constexpr int kSmemBytes = kStages * kStageBytes + kWeightBytes + 1024;
-constexpr int kEpilogueWarps = 16;
+constexpr int kWarpsPerQuarter = 1;            // epilogue warps per lane quarter within a group (measured: 2 was slower, 67 vs 44 us on 64 x 32 x 802816)
+constexpr int kGroupWarps = 4 * kWarpsPerQuarter;
+constexpr int kEpilogueWarps = 2 * kGroupWarps;
 constexpr int kThreads = 64 + 32 * kEpilogueWarps;
 constexpr int kTmemCols = 512;                 // two buffers of 256 columns: F accumulators of N columns each
 constexpr int kMaxN = 128;
@@ -138,16 +140,16 @@ __device__ __forceinline__ bool elect_one() {
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-// AND-reduction of `ok` over the 256 threads of one epilogue group (named barrier 1 + group).
+// AND-reduction of `ok` over the threads of one epilogue group (named barrier 1 + group).
 __device__ __forceinline__ bool group_all(bool ok, int group) {
   uint32_t res;
   asm volatile(
       "{\n\t.reg .pred p, q;\n\t"
       "setp.ne.u32 q, %1, 0;\n\t"
-      "bar.red.and.pred p, %2, 256, q;\n\t"
+      "bar.red.and.pred p, %2, %3, q;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(res)
-      : "r"((uint32_t)ok), "r"(1 + group)
+      : "r"((uint32_t)ok), "r"(1 + group), "r"(32 * kGroupWarps)
       : "memory");
   return res != 0;
 }
@@ -200,11 +202,11 @@ shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_co
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; s++) {
       mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], 8);     // the eight warps of the epilogue group that drained the tile
+      mbar_init(&empty_bar[s], kGroupWarps);     // the warps of the epilogue group that drained the tile
     }
     for (int b = 0; b < 2; b++) {
       mbar_init(&acc_full_bar[b], 1);
-      mbar_init(&acc_empty_bar[b], 8);
+      mbar_init(&acc_empty_bar[b], kGroupWarps);
     }
     mbar_init(&weights_bar, 1);
     abort_flag = 0;
@@ -304,14 +306,13 @@ shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_co
       if (++s == kStages) { s = 0; ph ^= 1; }
     }
   } else {
-    // ---------------- epilogue: two groups of eight warps take tiles in turn ----------------
-    // A warp of the epilogue is bound by the latency of its own instruction stream (about 900 cycles per 32 columns), not
-    // by any pipe, so the kernel runs sixteen of them: within a group two warps share each lane quarter and take
-    // every other (row-of-line, 32-column chunk) piece of the tile.
+    // ---------------- epilogue: two groups take tiles in turn ----------------
+    // Within a group, kWarpsPerQuarter warps share each lane quarter and take the (row-of-line, 32-column chunk)
+    // pieces of the tile in turn.
     const int ew = warp - 2;
-    const int group = ew / 8;
+    const int group = ew / kGroupWarps;
     const int quarter = warp % 4;             // TMEM lane quarter this warp may read
-    const int half = (ew % 8) / 4;            // which of the two warps of this quarter in the group
+    const int half = (ew % kGroupWarps) / 4;  // which of the warps of this quarter in the group
     const int line_in_tile = quarter * 32 + lane;
     const int32_t cmin = ep.clamp_min, cmax = ep.clamp_max;
     const bool late_clamp = args.pack_clamps != 0;
@@ -387,7 +388,7 @@ shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_co
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty_bar[s]);       // the stage may be refilled
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256u;
-      for (int piece = half; piece < fold * chunks; piece += 2) {
+      for (int piece = half; piece < fold * chunks; piece += kWarpsPerQuarter) {
         const int q = piece / chunks;
         const int c = (piece - q * chunks) * 32;
         const int m = m0 + q;
@@ -402,7 +403,7 @@ shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_co
         tmem_ld_wait();
         if (m_ok) {
           int32_t v[32];
-          if (mul_per_n ? all_n_fast != 0 : fast_m) {
+          if (!kX86 && (mul_per_n ? all_n_fast != 0 : fast_m)) {
             const int sh_hi = (31 - expm - 32) & 31;
 #pragma unroll
             for (int j4 = 0; j4 < 8; j4++) {
