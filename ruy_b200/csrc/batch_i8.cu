@@ -38,13 +38,14 @@ namespace ruyb200 {
 
 namespace {
 
-constexpr int kSlots = kBatchGranules;             // 16 KB granules of shared memory, two per pack warp; an item takes one or both
-constexpr int kSlotBytes = kBatchGranuleBytes;
+constexpr int kSlots = 6;                          // one per pack warp
+constexpr int kTileBytes = 16 * 1024;             // one operand: up to 128 rows x 128 bytes of depth
+constexpr int kSlotBytes = 2 * kTileBytes;
 constexpr int kAccUnits = kBatchAccUnits;        // 64-column accumulator units; an item takes one or two (assigned by the plan)
 constexpr int kUnitCols = 64;
 constexpr int kAccCols = 128;                     // most columns one item can use
 constexpr int kTmemCols = 512;                     // allocation must be a power of two
-constexpr int kPackWarps = kBatchPackWarps;
+constexpr int kPackWarps = kSlots;
 constexpr int kEpiGroups = 4;
 constexpr int kEpiWarps = 4 * kEpiGroups;         // each group covers the four TMEM lane quarters
 constexpr int kMmaWarp = kPackWarps;                // warps 6 and 7 issue the MMAs of alternate items
@@ -64,6 +65,7 @@ struct NTerm {
   int32_t add;
   int32_t mul;
   int32_t exp;
+  int32_t pad;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -159,12 +161,11 @@ __device__ __forceinline__ void bulk_load(uint32_t smem_dst, const void* src, ui
 struct TileDesc {
   uint32_t lo, hi, kstep;
 };
-// `pitch`: row length of a swizzled tile (128, 64 or 32 bytes: swizzle mode 2, 4 or 6, 8-row groups 8 * pitch apart).
-__device__ __forceinline__ TileDesc tile_desc(bool swizzled, uint32_t addr, uint32_t sbo, uint32_t pitch) {
+__device__ __forceinline__ TileDesc tile_desc(bool swizzled, uint32_t addr, uint32_t sbo) {
   TileDesc d;
   if (swizzled) {
     d.lo = ((addr & 0x3FFFF) >> 4) | (1u << 16);
-    d.hi = ((8u * pitch) >> 4) | (1u << 14) | ((pitch == 128 ? 2u : (pitch == 64 ? 4u : 6u)) << 29);
+    d.hi = (1024u >> 4) | (1u << 14) | (2u << 29);
     d.kstep = 32 >> 4;
   } else {
     d.lo = ((addr & 0x3FFFF) >> 4) | ((128u >> 4) << 16);
@@ -241,13 +242,12 @@ __device__ __forceinline__ int32_t tile_row_sum(const uint8_t* tile, int tr, int
   return s;
 }
 
-// The same for a swizzled tile: row tr is `pitch` bytes at tr * pitch.  The swizzle only permutes the 16-byte pieces
-// within a row and the copy zero-fills the row past the depth, so the sum runs over the whole row.
-__device__ __forceinline__ int32_t tile_row_sum_swizzled(const uint8_t* tile, int tr, int pitch, bool is_signed) {
-  const uint8_t* p = tile + tr * pitch;
+// The same for a swizzled tile: row tr is 128 bytes at tr * 128, its 16-byte chunk c stored at position c ^ (tr & 7).
+__device__ __forceinline__ int32_t tile_row_sum_swizzled(const uint8_t* tile, int tr, int kpad, bool is_signed) {
+  const uint8_t* p = tile + tr * 128;
   int s = 0;
-  for (int q = 0; q < (pitch >> 4); q++) {
-    const uint4 v = *reinterpret_cast<const uint4*>(p + (q << 4));
+  for (int q = 0; q < (kpad >> 4); q++) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p + ((q ^ (tr & 7)) << 4));
     if (is_signed) {
       s = __dp4a((int)v.x, 0x01010101, s);
       s = __dp4a((int)v.y, 0x01010101, s);
@@ -319,33 +319,28 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
 
   if (warp < kPackWarps) {
     // ---------------- pack: HBM -> shared memory, zero-point sums on the way ----------------
-    // Pack warp w handles items k = w, w + 6, ... and packs them into its own two granules, which the plan hands out as
-    // a ring: small items (most of them) alternate between the two, so the warp packs the next item while the
-    // previous one is still being multiplied and drained.
-    const int pw = warp;
+    // Pack warp w owns slot w and handles items k = w, w + kSlots, ...: kSlots items are being packed at any
+    // time, each by its own warp, which is what keeps enough loads in flight.
+    const int s = warp;
+    uint32_t ph = 0;
     // The descriptor travels global -> register (one 16-byte piece in each of 8 lanes, fetched one item
     // ahead) -> the slot header in shared memory, from where every role reads the fields it needs.
     uint4 next_piece = make_uint4(0u, 0u, 0u, 0u);
     const bool piece_lane = lane < (int)(sizeof(BatchItem) / 16);
-    if (pw < my_count && piece_lane) next_piece = reinterpret_cast<const uint4*>(items + blockIdx.x + pw * gridDim.x)[lane];
+    if (s < my_count && piece_lane) next_piece = reinterpret_cast<const uint4*>(items + blockIdx.x + s * gridDim.x)[lane];
 #ifdef RUYB200_DEBUG_CLOCKS
     long long dbg_wait = 0, dbg_work = 0, dbg_tma = 0, dbg_scatter = 0, dbg_t0 = clock64();
     int dbg_ntma = 0;
 #endif
-    for (int k = pw; k < my_count; k += kPackWarps) {
+    for (int k = s; k < my_count; k += kSlots, ph ^= 1) {
       const uint4 piece = next_piece;
-      if (k + kPackWarps < my_count && piece_lane) {
-        next_piece = reinterpret_cast<const uint4*>(items + blockIdx.x + (k + kPackWarps) * gridDim.x)[lane];
+      if (k + kSlots < my_count && piece_lane) {
+        next_piece = reinterpret_cast<const uint4*>(items + blockIdx.x + (k + kSlots) * gridDim.x)[lane];
       }
-      // BatchItem::slot is the third word of the descriptor's last 16-byte piece
-      const uint32_t slot = __shfl_sync(0xffffffffu, piece.z, 7);
-      const int s = (int)(slot & 15u);
-      const bool two_granules = (slot & 16u) != 0;
 #ifdef RUYB200_DEBUG_CLOCKS
       long long dbg_a = clock64();
 #endif
-      if (!mbar_wait_warp(&empty_bar[s], ((slot >> 5) & 1u) ^ 1u, abortp) ||
-          (two_granules && !mbar_wait_warp(&empty_bar[s + 1], ((slot >> 6) & 1u) ^ 1u, abortp))) {
+      if (!mbar_wait_warp(&empty_bar[s], ph ^ 1, abortp)) {
         if (lane == 0) { if (!*abortp) atomicCAS(status, 0, 1); *abortp = 1; }
         break;
       }
@@ -357,9 +352,8 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
       __syncwarp();
       const BatchItem& item = slot_item[s];
       const int kpad = (item.depth + 31) & ~31;
-      const uint32_t pitch = item.depth <= 32 ? 32u : (item.depth <= 64 ? 64u : 128u);
       const uint32_t tile_m = smem_u32(smem + s * kSlotBytes);
-      const uint32_t tile_n = tile_m + 128u * pitch;
+      const uint32_t tile_n = tile_m + kTileBytes;
       const uint8_t* m_ptr = item.m_ptr;
       const uint8_t* n_ptr = item.n_ptr;
       const int size_m = item.size_m, size_n = item.size_n, depth = item.depth, stride_m = item.stride_m,
@@ -375,8 +369,8 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
         if (!(debug & 4))
 #endif
         {
-        if (lane == 0) tma_load_tile(tile_m + (uint32_t)m_off * pitch, item_maps, &full_bar[s]);
-        tx += pitch * (uint32_t)((size_m + 7) & ~7);
+        if (lane == 0) tma_load_tile(tile_m + (uint32_t)m_off * 128, item_maps, &full_bar[s]);
+        tx += 128u * (uint32_t)((size_m + 7) & ~7);
         }
       }
 #ifdef RUYB200_DEBUG_KNOBS
@@ -394,7 +388,7 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
 #endif
         {
         if (lane == 0) tma_load_tile(tile_n, item_maps + 1, &full_bar[s]);
-        tx += pitch * (uint32_t)((size_n + 15) & ~15);
+        tx += 128u * (uint32_t)((size_n + 15) & ~15);
         }
       }
 #ifdef RUYB200_DEBUG_KNOBS
@@ -414,7 +408,7 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
 #ifdef RUYB200_DEBUG_KNOBS
       if (!(debug & 1))
 #endif
-      if (k + kPackWarps < my_count && lane < 2) prefetch_map(item_maps + 2 * (size_t)kPackWarps * gridDim.x + lane);
+      if (k + kSlots < my_count && lane < 2) prefetch_map(item_maps + 2 * (size_t)kSlots * gridDim.x + lane);
       // per-channel vectors (indexed along m or along n) and the cached m-side sums ride along
       const int nch = (flags & kItemChannelOnN) ? size_n : size_m;
       const int32_t* v0 = item.bias;
@@ -441,15 +435,14 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
       asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&full_bar[s])) : "memory");
       if (lane == 0) {
         const uint32_t sbo = (uint32_t)(kpad >> 4) * 128;
-        const TileDesc dm = tile_desc((flags & kItemMTma) != 0, tile_m, sbo, pitch);
-        const TileDesc dn = tile_desc((flags & kItemNTma) != 0, tile_n, sbo, pitch);
+        const TileDesc dm = tile_desc((flags & kItemMTma) != 0, tile_m, sbo);
+        const TileDesc dn = tile_desc((flags & kItemNTma) != 0, tile_n, sbo);
         MmaCmd cmd;
         cmd.lo_m = dm.lo; cmd.hi_m = dm.hi; cmd.kstep_m = dm.kstep;
         cmd.lo_n = dn.lo; cmd.hi_n = dn.hi; cmd.kstep_n = dn.kstep;
         cmd.idesc = (2u << 4) | ((flags & kItemMSigned ? 1u : 0u) << 7) | ((flags & kItemNSigned ? 1u : 0u) << 10) |
                     ((uint32_t)(((size_n + 15) & ~15) >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-        cmd.nk_fence = (uint32_t)(kpad >> 5) | ((item.acc & 0x3fu) << 8) | (((flags & (kItemMTma | kItemNTma)) != (kItemMTma | kItemNTma)) ? 0x80000000u : 0u) |
-                       (two_granules ? 0x40000000u : 0u);
+        cmd.nk_fence = (uint32_t)(kpad >> 5) | ((item.acc & 0x3fu) << 8) | (((flags & (kItemMTma | kItemNTma)) != (kItemMTma | kItemNTma)) ? 0x80000000u : 0u);
         slot_cmd[s] = cmd;
       }
       __syncwarp();
@@ -463,7 +456,7 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
 #ifdef RUYB200_DEBUG_CLOCKS
     if (blockIdx.x == 0 && threadIdx.x == 0)
       printf("pack warp 0: total %lld cycles, waiting for its slot %lld, issuing copies %lld (operands: %lld in %d items by tensor map, %lld otherwise), items %d\n",
-             clock64() - dbg_t0, dbg_wait, dbg_work, dbg_tma, dbg_ntma, dbg_scatter, (my_count + kPackWarps - 1) / kPackWarps);
+             clock64() - dbg_t0, dbg_wait, dbg_work, dbg_tma, dbg_ntma, dbg_scatter, (my_count + kSlots - 1) / kSlots);
 #endif
   } else if (warp < kMmaWarp + kMmaWarps) {
     // ---------------- MMA issue: this warp takes items mw, mw + 2, ... ----------------
@@ -471,13 +464,9 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
 #ifdef RUYB200_DEBUG_CLOCKS
     long long dbg_acc = 0, dbg_full = 0, dbg_t0 = clock64();
 #endif
-    // the word that says where an item is packed comes from the item list, fetched one item ahead
-    uint32_t next_slot = mw < my_count ? items[blockIdx.x + mw * gridDim.x].slot : 0u;
     for (int it = mw; it < my_count; it += kMmaWarps) {
-      const uint32_t slot = next_slot;
-      if (it + kMmaWarps < my_count) next_slot = items[blockIdx.x + (it + kMmaWarps) * gridDim.x].slot;
-      const int s = (int)(slot & 15u);
-      const uint32_t ph = (slot >> 7) & 1u;
+      const int s = it % kSlots;
+      const uint32_t ph = (it / kSlots) & 1;
 #ifdef RUYB200_DEBUG_CLOCKS
       long long dbg_a = clock64();
 #endif
@@ -527,7 +516,6 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
 #endif
         {
           mma_commit(&empty_bar[s]);
-          if (c1.w & 0x40000000u) mma_commit(&empty_bar[s + 1]);
           mma_commit(&acc_full_bar[unit]);
           if (two) mma_commit(&acc_full_bar[unit + 1]);   // keeps the second unit's barrier phases in step with its use count
         }
@@ -548,12 +536,8 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
 #ifdef RUYB200_DEBUG_CLOCKS
     long long dbg_wait = 0, dbg_stage = 0, dbg_work = 0, dbg_t0 = clock64();
 #endif
-    uint32_t next_slot = group < my_count ? items[blockIdx.x + group * gridDim.x].slot : 0u;
     for (int it = group; it < my_count; it += kEpiGroups) {
-      const uint32_t slot = next_slot;
-      if (it + kEpiGroups < my_count) next_slot = items[blockIdx.x + (it + kEpiGroups) * gridDim.x].slot;
-      const int s = (int)(slot & 15u);
-      const bool two_granules = (slot & 16u) != 0;
+      const int s = it % kSlots;
 #ifdef RUYB200_DEBUG_CLOCKS
       long long dbg_a = clock64();
 #endif
@@ -561,7 +545,7 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
       // slot's data first, because the slot's header says which accumulator unit (and which of its phases) to wait for.
       bool ok = true;
       if (quarter == 0) {
-        ok = mbar_wait_warp(&full_bar[s], (slot >> 7) & 1u, abortp);
+        ok = mbar_wait_warp(&full_bar[s], (uint32_t)(it / kSlots) & 1u, abortp);
         if (ok) {
           const uint32_t a = slot_item[s].acc;
           ok = mbar_wait_warp(&acc_full_bar[a & 7u], (a >> 4) & 1u, abortp);
@@ -597,9 +581,8 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
       const int dst_dtype = (int)((item.flags >> kItemDstShift) & 7u);
       const bool per_n = ch_n || item.zp_m != 0;   // some term varies along n
       const int kpad = (item.depth + 31) & ~31;
-      const int pitch = item.depth <= 32 ? 32 : (item.depth <= 64 ? 64 : 128);
       const uint8_t* tile_m = smem + s * kSlotBytes;
-      const uint8_t* tile_n = tile_m + 128 * pitch;
+      const uint8_t* tile_n = tile_m + kTileBytes;
       const int32_t* vbias = item.bias ? slot_vec[s][0] : nullptr;
       const int32_t* vmfp = item.mfp_pc ? slot_vec[s][1] : nullptr;
       const int32_t* vmexp = item.mexp_pc ? slot_vec[s][2] : nullptr;
@@ -609,11 +592,12 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
         t.add = item.zp_m * item.zp_n * item.depth;
         t.mul = item.mfp;
         t.exp = item.mexp;
+        t.pad = 0;
         if (n < item.size_n) {
           // zero-point term of this destination column: the sum over depth of the n-side row, taken from the packed tile
           if (item.zp_m) {
             const bool sg = (item.flags & kItemNSigned) != 0;
-            t.add -= item.zp_m * ((item.flags & kItemNTma) ? tile_row_sum_swizzled(tile_n, n, pitch, sg) : tile_row_sum(tile_n, n, kpad, sg));
+            t.add -= item.zp_m * ((item.flags & kItemNTma) ? tile_row_sum_swizzled(tile_n, n, kpad, sg) : tile_row_sum(tile_n, n, kpad, sg));
           }
           if (ch_n) {
             if (vbias) t.add += vbias[n];
@@ -631,7 +615,7 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
           const bool sg = (item.flags & kItemMSigned) != 0;
           const int tr = quarter * 32 + lane;
           const int32_t sum = item.sums_m ? slot_vec[s][3][m]
-                                          : ((item.flags & kItemMTma) ? tile_row_sum_swizzled(tile_m, tr, pitch, sg)
+                                          : ((item.flags & kItemMTma) ? tile_row_sum_swizzled(tile_m, tr, kpad, sg)
                                                                       : tile_row_sum(tile_m, tr, kpad, sg));
           add_m -= item.zp_n * sum;
         }
@@ -647,10 +631,7 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
       const int dst_stride = item.dst_stride;
       if (per_n) group_all(true, group);   // n_terms[] staged (uniform over the group: per_n comes from the header)
       __syncwarp();                        // this warp is done with the slot's header, vectors and tiles
-      if (lane == 0) {
-        mbar_arrive(&empty_bar[s]);
-        if (two_granules) mbar_arrive(&empty_bar[s + 1]);
-      }
+      if (lane == 0) mbar_arrive(&empty_bar[s]);
 #ifdef RUYB200_DEBUG_CLOCKS
       long long dbg_c = clock64();
       dbg_stage += dbg_c - dbg_b;

@@ -50,12 +50,7 @@ struct alignas(16) BatchItem {
   // 64-column unit, bit 3 set if it takes two units (more than 64 destination columns along n), bits 4 / 5 the
   // parity of the first / second unit's use count (which phase of the unit's barriers this item sees).
   uint32_t acc;
-  // Where the item's operands are packed in shared memory, assigned by the plan: bits 0-3 first granule (16 KB each,
-  // two per pack warp), bit 4 set if the item takes both granules of its pack warp, bits 5 / 6 the parity of the
-  // first / second granule's use count (which phase of its "empty" barrier the item waits for), bit 7 the parity of
-  // the first granule's count of uses as a first granule (the phase of its "full" barrier the item completes).
-  uint32_t slot;
-  int32_t reserved;
+  int32_t reserved[2];
 };
 static_assert(sizeof(BatchItem) == 128, "BatchItem is copied as eight 16-byte pieces");
 
@@ -71,8 +66,7 @@ cudaError_t launch_batch_i8(const BatchItem* items, const CUtensorMap* maps, int
 
 // Tensor map over a width x depth byte matrix (depth contiguous, rows stride_w bytes apart) whose copies land
 // as rows of 128 bytes with the 128-byte swizzle, zero-filled past depth and width: `box_rows` rows per copy.
-// `pitch` (128, 64 or 32 bytes) is the row length of the shared-memory tile and selects the matching swizzle pattern.
-bool make_i8_tile_map(CUtensorMap* map, const void* base, int depth, int width, int64_t stride_w, int box_rows, int pitch = 128);
+bool make_i8_tile_map(CUtensorMap* map, const void* base, int depth, int width, int64_t stride_w, int box_rows);
 
 // Accumulator units (64 tensor-memory columns each) per SM and what an item takes.
 constexpr int kBatchAccUnits = 8;
@@ -81,17 +75,5 @@ inline int batch_acc_units(int size_n) { return size_n > 64 ? 2 : 1; }
 // Rows copied for an item's sides (also the byte count the copy reports: 128 bytes per row).
 inline int batch_box_rows_m(int size_m) { return (size_m + 7) & ~7; }
 inline int batch_box_rows_n(int size_n) { return (size_n + 15) & ~15; }
-
-// Shared-memory footprint of an item.  Tile rows are as long as the depth needs (32, 64 or 128 bytes); the m tile
-// always spans the 128 rows the MMA reads, the n tile the rows it copies.  The ring of a pack warp is two granules of
-// 16 KB: an item takes one, or both when it does not fit one.
-constexpr int kBatchPackWarps = 6;
-constexpr int kBatchGranuleBytes = 16 * 1024;
-constexpr int kBatchGranules = 2 * kBatchPackWarps;
-inline int batch_pitch(int depth) { return depth <= 32 ? 32 : (depth <= 64 ? 64 : 128); }
-inline int batch_granules(int depth, int size_n) {
-  const int pitch = batch_pitch(depth);
-  return (128 + batch_box_rows_n(size_n)) * pitch > kBatchGranuleBytes ? 2 : 1;
-}
 
 }  // namespace ruyb200

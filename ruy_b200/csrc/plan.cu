@@ -116,25 +116,9 @@ int ruyb200_plan_create(ruyb200_ctx* ctx, const ruyb200_mul_desc* descs, int n, 
     constexpr int kHalf = kBatchAccUnits / 2;
     struct AccRing { int next = 0; int uses[kHalf] = {}; };
     std::vector<AccRing> rings(2 * (size_t)grid);
-    // Shared-memory granules: pack warp w of a CTA packs that CTA's items w, w + 6, ... into its own two granules, used as
-    // a ring (one granule per item, or both); as for the accumulators, use counts give the barrier phases, and every
-    // wait on a granule's barriers comes from one warp in item order.
-    struct SlotRing { int next = 0; int uses[2] = {}; int first_uses[2] = {}; };
-    std::vector<SlotRing> slot_rings((size_t)grid * kBatchPackWarps);
     for (size_t pos = 0; pos < order.size(); pos++) {
       BatchItem it = items[order[pos]];
       const int cta = (int)(pos % grid);
-      {
-        const int pack_warp = (int)((pos / grid) % kBatchPackWarps);
-        SlotRing& sr = slot_rings[(size_t)cta * kBatchPackWarps + pack_warp];
-        const int granules = batch_granules(it.depth, it.size_n);
-        if (granules == 2) sr.next = 0;
-        const int u = sr.next;
-        uint32_t slot = (uint32_t)(2 * pack_warp + u) | ((uint32_t)(sr.uses[u]++ & 1) << 5) | ((uint32_t)(sr.first_uses[u]++ & 1) << 7);
-        if (granules == 2) slot |= (1u << 4) | ((uint32_t)(sr.uses[1]++ & 1) << 6);
-        sr.next = (u + granules) % 2;
-        it.slot = slot;
-      }
       if (it.size_m <= 32) {
         it.m_off = 32 * (rot32[cta]++ & 3);
       } else if (it.size_m <= 64) {
@@ -160,12 +144,11 @@ int ruyb200_plan_create(ruyb200_ctx* ctx, const ruyb200_mul_desc* descs, int n, 
     for (size_t pos = 0; pos < scheduled.size(); pos++) {
       BatchItem& it = scheduled[pos];
       if ((it.flags & kItemMTma) &&
-          !make_i8_tile_map(&maps[2 * pos], it.m_ptr, it.depth, it.size_m, it.stride_m, batch_box_rows_m(it.size_m), batch_pitch(it.depth))) {
+          !make_i8_tile_map(&maps[2 * pos], it.m_ptr, it.depth, it.size_m, it.stride_m, batch_box_rows_m(it.size_m))) {
         it.flags &= ~kItemMTma;
       }
       if ((it.flags & kItemNTma) &&
-          !make_i8_tile_map(&maps[2 * pos + 1], it.n_ptr, it.depth, it.size_n, it.stride_n, batch_box_rows_n(it.size_n),
-                            batch_pitch(it.depth))) {
+          !make_i8_tile_map(&maps[2 * pos + 1], it.n_ptr, it.depth, it.size_n, it.stride_n, batch_box_rows_n(it.size_n))) {
         it.flags &= ~kItemNTma;
       }
     }

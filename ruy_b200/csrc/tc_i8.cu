@@ -1021,7 +1021,7 @@ bool make_map(CUtensorMap* map, const SideView& s, int depth, int box_rows, int 
 
 }  // namespace
 
-bool make_i8_tile_map(CUtensorMap* map, const void* base, int depth, int width, int64_t stride_w, int box_rows, int pitch) {
+bool make_i8_tile_map(CUtensorMap* map, const void* base, int depth, int width, int64_t stride_w, int box_rows) {
   SideView s;
   s.data = base;
   s.stride_w = stride_w;
@@ -1029,7 +1029,7 @@ bool make_i8_tile_map(CUtensorMap* map, const void* base, int depth, int width, 
   s.width = width;
   s.zero_point = 0;
   s.dtype = RUYB200_U8;
-  return make_map(map, s, depth, box_rows, pitch);
+  return make_map(map, s, depth, box_rows);
 }
 
 namespace {
