@@ -219,10 +219,15 @@ RUYB200_API int ruyb200_validate(const ruyb200_mul_desc* desc);
  * are depth-contiguous (row-major LHS, column-major RHS) with 16-byte aligned base addresses and
  * strides; all pointers in `desc` device pointers.  No cudaMalloc, cudaFree or other allocating
  * call is made.  The work is enqueued on `cuda_stream` (a cudaStream_t, NULL for the default
- * stream) of the current device and the call returns after that stream has finished.  The first
- * call on each device looks up the array's device address (cudaGetSymbolAddress); make that first
- * call before starting any stream capture.  Every call shares the one array: two calls whose GPU
- * work overlaps (different streams or threads) race on it and must be serialised by the caller.
+ * stream) of the current device and the call returns after that stream has finished: it always
+ * synchronises that stream (it reads back the status word of the kernel's bounded waits), so it
+ * serves callers that may not allocate, not callers that may not block.  The first call on each
+ * device does one-time set-up under a lock: it looks up the array's device address
+ * (cudaGetSymbolAddress) and, like the first use of any kernel variant of this library, raises
+ * that kernel's dynamic shared-memory limit (cudaFuncSetAttribute) and asks how many two-CTA
+ * clusters fit the device (cudaOccupancyMaxActiveClusters); make that first call before starting
+ * any stream capture.  Every call shares the one array: two calls whose GPU work overlaps
+ * (different streams or threads) race on it and must be serialised by the caller.
  * rounding_mode RUYB200_ROUNDING_FROM_PATH means the reference rounding here. */
 RUYB200_API int ruyb200_mul_noalloc(const ruyb200_mul_desc* desc, void* cuda_stream);
 

@@ -14,7 +14,8 @@ from ruy_b200 import _abi
 _HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_SO = os.path.join(_HERE, "liboracle.so")
 REF_SO = os.path.join(_HERE, "_ref", "libruy_ref.so")
-REFERENCE_DIR = os.environ.get("RUY_REFERENCE_DIR", "/root/reference")
+# Where the reference checkout lies: RUY_REFERENCE_DIR, else a directory named "reference" beside this repository.
+REFERENCE_DIR = os.environ.get("RUY_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
 _oracle = None
 _ref = None
 
