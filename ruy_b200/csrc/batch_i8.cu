@@ -16,11 +16,10 @@
 //                  K=32) from descriptors the pack warp left in the slot, into the item's accumulator: one
 //                  or two of eight 64-column units of tensor memory, handed out by the plan as a ring, so
 //                  up to eight items can sit between MMA and epilogue.
-//   * warps 8-23 : epilogue, four warps per tensor-memory lane quarter.  An item is cut into one piece per lane quarter
-//                  it occupies; the warps of a quarter take that quarter's pieces in turn, each on its own.  Zero-point
-//                  sums are taken from the cache's vector or the packed tile, per-column terms are produced sixteen
-//                  columns at a time, then tcgen05.ld, bias, zero-point terms, fixed-point multiplier, zero point,
-//                  clamp (ruy/kernel.h:213-237) and store.  The destination's contiguous dimension sits on the
+//   * warps 8-23 : epilogue, four groups of four warps; group g drains accumulator g.  Zero-point sums
+//                  are taken from the packed tile, per-column terms are staged in shared memory, then
+//                  tcgen05.ld, bias, zero-point terms, fixed-point multiplier, zero point, clamp
+//                  (ruy/kernel.h:213-237) and store.  The destination's contiguous dimension sits on the
 //                  TMEM lanes, so the 32 lanes of a warp write 32 consecutive elements.
 //
 // All mbarrier waits are bounded; a wait that gives up sets a status word and an abort flag and every
@@ -44,6 +43,7 @@ constexpr int kTileBytes = 16 * 1024;             // one operand: up to 128 rows
 constexpr int kSlotBytes = 2 * kTileBytes;
 constexpr int kAccUnits = kBatchAccUnits;        // 64-column accumulator units; an item takes one or two (assigned by the plan)
 constexpr int kUnitCols = 64;
+constexpr int kAccCols = 128;                     // most columns one item can use
 constexpr int kTmemCols = 512;                     // allocation must be a power of two
 constexpr int kPackWarps = kSlots;
 constexpr int kEpiGroups = 4;
@@ -65,6 +65,7 @@ struct NTerm {
   int32_t add;
   int32_t mul;
   int32_t exp;
+  int32_t pad;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -74,10 +75,6 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-// `count` arrivals at once (a piece of the epilogue also arrives for the lane quarters its item does not occupy).
-__device__ __forceinline__ void mbar_arrive_n(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
 }
 // One potentially blocking probe: returns early when the phase completes, otherwise after a short
 // implementation-defined time.
@@ -103,10 +100,6 @@ __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, v
   }
   return __all_sync(0xffffffffu, ok) != 0;
 }
-// Makes a per-lane observation warp-uniform: a barrier phase that one lane has seen complete is complete, and a
-// reason to give up that one lane has seen is one for the whole warp.  Every decision of a polling loop that the
-// lanes take together goes through this.
-__device__ __forceinline__ bool warp_saw(bool mine) { return __any_sync(0xffffffffu, mine) != 0; }
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred;
   asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
@@ -128,6 +121,20 @@ __device__ __forceinline__ void tmem_ld_16(uint32_t taddr, uint32_t* r) {
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// AND-reduction over the 128 threads of one epilogue group (named barrier 1 + group).
+__device__ __forceinline__ bool group_all(bool ok, int group) {
+  uint32_t res;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %1, 0;\n\t"
+      "bar.red.and.pred p, %2, 128, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(res)
+      : "r"((uint32_t)ok), "r"(1 + group)
+      : "memory");
+  return res != 0;
+}
+
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
@@ -272,9 +279,7 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
   __shared__ __align__(16) BatchItem slot_item[kSlots];
   __shared__ MmaCmd slot_cmd[kSlots];
   __shared__ __align__(16) int32_t slot_vec[kSlots][4][128];   // the item's bias / multiplier / exponent vectors and cached m-side sums
-  __shared__ NTerm nt_warp[kEpiWarps][16];       // per-n terms of the sixteen columns an epilogue warp is working on
-  __shared__ uint32_t items_done[kMmaWarps];     // items of each MMA warp whose MMAs have completed (only grows)
-  __shared__ uint8_t pending_acc[kMmaWarps][8];  // BatchItem::acc of each MMA warp's issued items, by issue index mod 8
+  __shared__ __align__(16) NTerm n_terms[kEpiGroups][kAccCols];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
@@ -296,7 +301,6 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
       mbar_init(&acc_empty_bar[b], 4);
     }
     abort_flag = 0;
-    for (int i = 0; i < kMmaWarps; i++) items_done[i] = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == kMmaWarp) {
@@ -456,276 +460,298 @@ batch_i8_kernel(const BatchItem* __restrict__ items, const CUtensorMap* __restri
 #endif
   } else if (warp < kMmaWarp + kMmaWarps) {
     // ---------------- MMA issue: this warp takes items mw, mw + 2, ... ----------------
-    // Besides issuing, the warp publishes completions: the epilogue warps take (item, lane quarter) pieces in an order of
-    // their own, and a parity wait on an mbarrier is only sound for a waiter that follows the barrier's phases one by
-    // one.  So this warp, which meets its items in order, is the only one that waits on the accumulator-full barriers;
-    // when the MMAs of its j-th item have completed it stores j + 1 into items_done[mw], a counter that only grows and
-    // that any warp can compare against at any time.
     const int mw = warp - kMmaWarp;
-    const int my_items = (my_count - mw + kMmaWarps - 1) / kMmaWarps;   // items of this warp
-    int issued = 0, published = 0;
-    bool have_cmd = false;
-    uint4 c0 = make_uint4(0u, 0u, 0u, 0u), c1 = c0;
-    uint32_t spins = 0;
-    bool ok = true;
-    while (published < my_items && ok) {
-      bool progress = false;
-      if (published < issued) {
-        // the oldest item whose MMAs may still be running: its first unit's barrier, phase from its use count
-        const uint32_t pacc = pending_acc[mw][published & 7];
-        if (warp_saw(mbar_try_wait(&acc_full_bar[pacc & 7u], (pacc >> 4) & 1u))) {
-          published++;
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_u32(&items_done[mw])), "r"((uint32_t)published) : "memory");
-          progress = true;
-        }
+#ifdef RUYB200_DEBUG_CLOCKS
+    long long dbg_acc = 0, dbg_full = 0, dbg_t0 = clock64();
+#endif
+    for (int it = mw; it < my_count; it += kMmaWarps) {
+      const int s = it % kSlots;
+      const uint32_t ph = (it / kSlots) & 1;
+#ifdef RUYB200_DEBUG_CLOCKS
+      long long dbg_a = clock64();
+#endif
+      // the packed data first (the slot also says which accumulator units the item takes), then the units
+      bool ok = mbar_wait_warp(&full_bar[s], ph, abortp);
+#ifdef RUYB200_DEBUG_CLOCKS
+      long long dbg_b = clock64();
+      dbg_full += dbg_b - dbg_a;
+#endif
+      uint4 c0 = make_uint4(0u, 0u, 0u, 0u), c1 = c0;
+      int unit = 0;
+      bool two = false;
+      if (ok) {
+        c0 = reinterpret_cast<const uint4*>(&slot_cmd[s])[0];   // lo_m, hi_m, lo_n, hi_n
+        c1 = reinterpret_cast<const uint4*>(&slot_cmd[s])[1];   // kstep_m, kstep_n, idesc, nk_fence
+        const uint32_t acc = (c1.w >> 8) & 0x3fu;
+        unit = (int)(acc & 7u);
+        two = (acc & 8u) != 0;
+        ok = mbar_wait_warp(&acc_empty_bar[unit], ((acc >> 4) & 1u) ^ 1u, abortp);
+        if (ok && two) ok = mbar_wait_warp(&acc_empty_bar[unit + 1], ((acc >> 5) & 1u) ^ 1u, abortp);
       }
-      if (issued < my_items) {
-        const int it = mw + issued * kMmaWarps;
-        const int s = it % kSlots;
-        const uint32_t ph = (it / kSlots) & 1;
-        // the packed data first (the slot also says which accumulator units the item takes), then the units
-        if (!have_cmd && warp_saw(mbar_try_wait(&full_bar[s], ph))) {
-          c0 = reinterpret_cast<const uint4*>(&slot_cmd[s])[0];   // lo_m, hi_m, lo_n, hi_n
-          c1 = reinterpret_cast<const uint4*>(&slot_cmd[s])[1];   // kstep_m, kstep_n, idesc, nk_fence
-          have_cmd = true;
-        }
-        if (have_cmd) {
-          const uint32_t acc = (c1.w >> 8) & 0x3fu;
-          const int unit = (int)(acc & 7u);
-          const bool two = (acc & 8u) != 0;
-          if (warp_saw(mbar_try_wait(&acc_empty_bar[unit], ((acc >> 4) & 1u) ^ 1u)) &&
-              (!two || warp_saw(mbar_try_wait(&acc_empty_bar[unit + 1], ((acc >> 5) & 1u) ^ 1u)))) {
-            // a tile filled by cp.async was written through the generic proxy; the tensor core reads through the async proxy
-            if (c1.w & 0x80000000u) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            tc_fence_after();
-            const uint32_t tmem_d = tmem_base + (uint32_t)(unit * kUnitCols);
-            const int nk = (int)(c1.w & 0xffu);
-            if (lane == 0) pending_acc[mw][issued & 7] = (uint8_t)acc;
-            if (elect_one()) {
-              for (int k = 0; k < nk; k++) {
-                mma_i8(tmem_d, c0.x + k * c1.x, c0.y, c0.z + k * c1.y, c0.w, c1.z, k != 0);
-              }
-              mma_commit(&empty_bar[s]);
-              mma_commit(&acc_full_bar[unit]);
-              if (two) mma_commit(&acc_full_bar[unit + 1]);   // keeps the second unit's barrier phases in step with its use count
-            }
-            __syncwarp();
-            issued++;
-            have_cmd = false;
-            progress = true;
-          }
-        }
-      }
-      if (progress) {
-        spins = 0;
-      } else if (warp_saw(++spins > kSpinLimit || ((spins & 63u) == 63u && *abortp))) {
+#ifdef RUYB200_DEBUG_CLOCKS
+      dbg_acc += clock64() - dbg_b;
+#endif
+      if (!ok) {
         if (lane == 0) { if (!*abortp) atomicCAS(status, 0, 2); *abortp = 1; }
-        ok = false;
+        break;
       }
+      // a tile filled by cp.async was written through the generic proxy; the tensor core reads through the async proxy
+      if (c1.w & 0x80000000u) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      tc_fence_after();
+      const uint32_t tmem_d = tmem_base + (uint32_t)(unit * kUnitCols);
+      const int nk = (int)(c1.w & 0xffu);
+      if (elect_one()) {
+#ifdef RUYB200_DEBUG_KNOBS
+        if (!(debug & 32))
+#endif
+        for (int k = 0; k < nk; k++) {
+          mma_i8(tmem_d, c0.x + k * c1.x, c0.y, c0.z + k * c1.y, c0.w, c1.z, k != 0);
+        }
+#ifdef RUYB200_DEBUG_KNOBS
+        if (debug & 4096) {
+          mbar_arrive(&empty_bar[s]);
+          mbar_arrive(&acc_full_bar[unit]);
+          if (two) mbar_arrive(&acc_full_bar[unit + 1]);
+        } else
+#endif
+        {
+          mma_commit(&empty_bar[s]);
+          mma_commit(&acc_full_bar[unit]);
+          if (two) mma_commit(&acc_full_bar[unit + 1]);   // keeps the second unit's barrier phases in step with its use count
+        }
+      }
+      __syncwarp();
     }
+#ifdef RUYB200_DEBUG_CLOCKS
+    if (blockIdx.x == 0 && lane == 0)
+      printf("mma warp %d: total %lld cycles, waiting for an accumulator %lld, waiting for packed data %lld, items %d\n", mw,
+             clock64() - dbg_t0, dbg_acc, dbg_full, my_count);
+#endif
   } else if (warp >= kFirstEpiWarp) {
-    // ---------------- epilogue: sixteen warps, four per lane quarter, take (item, quarter) pieces ----------------
-    // A piece is the part of one item's accumulator that lies in one quarter of the tensor-memory lanes.  An item with at
-    // most 32 rows is one piece, a full one four.  The warps of a quarter take that quarter's pieces in turn (warp j the
-    // j-th, (j+4)-th, ...), each on its own: no warp waits for another warp's piece, and a small item occupies one warp
-    // instead of a group of four.
-    const int quarter = warp % 4;                         // TMEM lane quarter this warp may read
-    const int turn = (warp - kFirstEpiWarp) / 4;          // which of the quarter's four warps
-    NTerm* nt = nt_warp[warp - kFirstEpiWarp];
-    int pieces_seen = 0;                                  // pieces of this quarter met so far
-    bool ok = true;
-    for (int base = 0; base < my_count && ok; base += 32) {
-      // which lane quarters each of the next 32 items occupies (one word per item, from the item list)
-      const uint32_t my_word = base + lane < my_count ? items[blockIdx.x + (size_t)(base + lane) * gridDim.x].pieces : 0u;
-      for (int it = base; it < min(base + 32, my_count) && ok; it++) {
-        const uint32_t qmask = __shfl_sync(0xffffffffu, my_word, it - base);
-        if (!((qmask >> quarter) & 1u)) continue;
-        const bool mine = (pieces_seen++ & 3) == turn;
-        if (!mine) continue;
-        const int s = it % kSlots;
-        // wait until the MMAs of this item have completed (published by the MMA warp that issued them)
-        {
-          const uint32_t need = (uint32_t)(it >> 1) + 1u;
-          const uint32_t addr = smem_u32(&items_done[it & 1]);
-          uint32_t spins = 0, seen = 0;
-          for (;;) {
-            asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(seen) : "r"(addr) : "memory");
-            if (seen >= need) break;
-            if (++spins > kSpinLimit || ((spins & 63u) == 63u && *abortp)) break;
-          }
-          __syncwarp();     // the lanes may have left the loop at different times
-          if (!__all_sync(0xffffffffu, seen >= need)) {
-            if (lane == 0) { if (!*abortp) atomicCAS(status, 0, 3); *abortp = 1; }
-            ok = false;
-            break;
-          }
+    // ---------------- epilogue: group g drains items g, g + 4, ... from whichever accumulator units they were given ----------------
+    const int group = (warp - kFirstEpiWarp) / 4;
+    const int quarter = warp % 4;          // TMEM lane quarter this warp may read
+    const int gtid = (warp - kFirstEpiWarp) % 4 * 32 + lane;
+    NTerm* nt = n_terms[group];
+#ifdef RUYB200_DEBUG_CLOCKS
+    long long dbg_wait = 0, dbg_stage = 0, dbg_work = 0, dbg_t0 = clock64();
+#endif
+    for (int it = group; it < my_count; it += kEpiGroups) {
+      const int s = it % kSlots;
+#ifdef RUYB200_DEBUG_CLOCKS
+      long long dbg_a = clock64();
+#endif
+      // Only the group's first warp probes barriers; the group barrier below releases the others.  It waits for the
+      // slot's data first, because the slot's header says which accumulator unit (and which of its phases) to wait for.
+      bool ok = true;
+      if (quarter == 0) {
+        ok = mbar_wait_warp(&full_bar[s], (uint32_t)(it / kSlots) & 1u, abortp);
+        if (ok) {
+          const uint32_t a = slot_item[s].acc;
+          ok = mbar_wait_warp(&acc_full_bar[a & 7u], (a >> 4) & 1u, abortp);
         }
-        tc_fence_after();
-        const BatchItem& item = slot_item[s];   // valid until this piece has arrived on empty_bar[s]
-        const uint32_t acc = item.acc;
-        const int unit = (int)(acc & 7u);
-        const bool two_units = (acc & 8u) != 0;
-        const bool ch_n = (item.flags & kItemChannelOnN) != 0;
-        const bool x86 = (item.flags & kItemX86) != 0;
-        const int dst_dtype = (int)((item.flags >> kItemDstShift) & 7u);
-        const bool per_n = ch_n || item.zp_m != 0;   // some term varies along n
-        const int kpad = (item.depth + 31) & ~31;
-        const uint8_t* tile_m = smem + s * kSlotBytes;
-        const uint8_t* tile_n = tile_m + kTileBytes;
-        const int32_t* vbias = item.bias ? slot_vec[s][0] : nullptr;
-        const int32_t* vmfp = item.mfp_pc ? slot_vec[s][1] : nullptr;
-        const int32_t* vmexp = item.mexp_pc ? slot_vec[s][2] : nullptr;
-        // arrivals this piece owes: its own, plus those of the quarters the item does not occupy if it is the item's first piece
-        const uint32_t first_piece = (qmask & (0u - qmask)) == (1u << quarter) ? 1u : 0u;
-        const uint32_t arrivals = 1u + first_piece * (4u - (uint32_t)__popc(qmask & 15u));
-        const int m = quarter * 32 + lane - item.m_off;     // tile row -> destination index along m
-        const bool m_ok = m >= 0 && m < item.size_m;
-        int32_t add_m = 0, mul_m = item.mfp, exp_m = item.mexp;
-        if (m_ok) {
-          if (item.zp_n) {
-            const bool sg = (item.flags & kItemMSigned) != 0;
-            const int tr = quarter * 32 + lane;
-            const int32_t sum = item.sums_m ? slot_vec[s][3][m]
-                                            : ((item.flags & kItemMTma) ? tile_row_sum_swizzled(tile_m, tr, kpad, sg)
-                                                                        : tile_row_sum(tile_m, tr, kpad, sg));
-            add_m -= item.zp_n * sum;
-          }
-          if (!ch_n) {
-            if (vbias) add_m += vbias[m];
-            if (vmfp) mul_m = vmfp[m];
-            if (vmexp) exp_m = vmexp[m];
-          }
-        }
-        const int size_n = item.size_n;
-        const int32_t cmin = item.clamp_min, cmax = item.clamp_max, dzp = item.dst_zp;
-        uint8_t* const dst_base = item.dst;
-        const int dst_stride = item.dst_stride;
-        // per-n terms are produced sixteen columns at a time by the first sixteen lanes (below); they need the slot's
-        // vectors and, for the zero-point term, the packed n tile, so a piece with such terms keeps the slot to its end
-        const int32_t nt_zz = item.zp_m * item.zp_n * item.depth, nt_zp_m = item.zp_m, nt_mfp = item.mfp, nt_mexp = item.mexp;
-        const bool n_signed = (item.flags & kItemNSigned) != 0, n_tma = (item.flags & kItemNTma) != 0;
-        __syncwarp();                        // every lane has read what it needs from the slot's header and m-side data
-        if (!per_n && lane == 0) mbar_arrive_n(&empty_bar[s], arrivals);
-        {
-          const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(unit * kUnitCols);
-          const int esz = dst_dtype == RUYB200_I32 ? 4 : (dst_dtype == RUYB200_I16 ? 2 : 1);
-          const int64_t step = (int64_t)dst_stride * esz;
-          uint8_t* out = dst_base + (int64_t)m * esz;
-          const bool fast = !per_n && !x86 && dst_dtype != RUYB200_I32;
-          const int sh = 31 - exp_m;
-          const long long rnd = 1ll << (sh - 1);
-          // With every shift of the warp at least 32, the result is the high word of the product shifted on.
-          // With every shift of the warp at least 32 and the per-row addend small enough that accumulator + addend
-          // cannot wrap (|accumulator| < 2^23 for depth <= 128), the whole requantization is one 64-bit multiply-add
-          // and one shift of its high word: acc * mul + (addend * mul + rounding [+ zero point << shift]).
-          const bool high_word = fast && esz == 1 && __all_sync(0xffffffffu, sh >= 32 && add_m > -(1 << 30) && add_m < (1 << 30));
-          const int sh_hi = sh - 32;
-          const bool fold_zp = __all_sync(0xffffffffu, sh <= 50) && dzp >= -256 && dzp <= 255;
-          const long long c64 = (long long)add_m * (long long)mul_m + rnd + (fold_zp ? (long long)dzp * (1ll << (sh & 63)) : 0ll);
-          const int32_t dzp_late = fold_zp ? 0 : dzp;
-          // the per-n terms of columns c .. c + 15, one per lane of the warp's first half, into this warp's buffer
-          auto stage_n_terms = [&](int c) {
-            __syncwarp();    // the previous chunk's reads of the buffer are done
-            if (lane < 16) {
-              const int n = c + lane;
-              NTerm t;
-              t.add = nt_zz;
-              t.mul = nt_mfp;
-              t.exp = nt_mexp;
-              if (n < size_n) {
-                // zero-point term of this destination column: the sum over depth of the n-side row, taken from the packed tile
-                if (nt_zp_m) t.add -= nt_zp_m * (n_tma ? tile_row_sum_swizzled(tile_n, n, kpad, n_signed) : tile_row_sum(tile_n, n, kpad, n_signed));
-                if (ch_n) {
-                  if (vbias) t.add += vbias[n];
-                  if (vmfp) t.mul = vmfp[n];
-                  if (vmexp) t.exp = vmexp[n];
-                }
-              }
-              nt[lane] = t;
-            }
-            __syncwarp();
-          };
-          // 16 columns: all values first (branch-free, so the sixteen dependency chains interleave), then the stores
-          auto process = [&](uint32_t (&rr)[16], int c) {   // results replace the accumulators in rr[]
-            const int lim = size_n - c;
-            if (high_word) {
-#pragma unroll
-              for (int q = 0; q < 16; q++) {
-                const long long p = (long long)(int32_t)rr[q] * (long long)mul_m + c64;
-                rr[q] = (uint32_t)max(min(((int32_t)(p >> 32) >> sh_hi) + dzp_late, cmax), cmin);
-              }
-            } else if (fast) {
-#pragma unroll
-              for (int q = 0; q < 16; q++) {
-                const int32_t x = requant_ref_fast((int32_t)(rr[q] + (uint32_t)add_m), mul_m, rnd, sh);
-                rr[q] = (uint32_t)max(min(x + dzp, cmax), cmin);
-              }
-            } else {
-#pragma unroll
-              for (int q = 0; q < 16; q++) {
-                int32_t x = (int32_t)(rr[q] + (uint32_t)add_m);
-                int32_t mul = mul_m;
-                int e = exp_m;
-                if (per_n) {
-                  const NTerm t = nt[q];
-                  x = (int32_t)((uint32_t)x + (uint32_t)t.add);
-                  if (ch_n) { mul = t.mul; e = t.exp; }
-                }
-                if (dst_dtype != RUYB200_I32) {
-                  x = x86 ? requant_x86(x, mul, e) : requant_reference(x, mul, e);
-                  x = (int32_t)((uint32_t)x + (uint32_t)dzp);
-                  x = max(min(x, cmax), cmin);
-                } else {
-                  x = (int32_t)((uint32_t)x + (uint32_t)dzp);
-                }
-                rr[q] = (uint32_t)x;
-              }
-            }
-            if (!m_ok) return;     // lanes outside the item's rows computed along (the buffer reads above are warp-wide)
-            uint8_t* o = out + (int64_t)c * step;
-            if (esz == 1) {
-              if (lim >= 16) {
-#pragma unroll
-                for (int q = 0; q < 16; q++) o[q * step] = (uint8_t)rr[q];
-              } else {
-#pragma unroll
-                for (int q = 0; q < 16; q++) if (q < lim) o[q * step] = (uint8_t)rr[q];
-              }
-            } else if (esz == 2) {
-#pragma unroll
-              for (int q = 0; q < 16; q++) if (q < lim) *reinterpret_cast<int16_t*>(o + q * step) = (int16_t)rr[q];
-            } else {
-#pragma unroll
-              for (int q = 0; q < 16; q++) if (q < lim) *reinterpret_cast<int32_t*>(o + q * step) = (int32_t)rr[q];
-            }
-          };
-          // two register buffers: the load of the next 16 columns is in flight while 16 are processed
-          uint32_t ra[16], rb[16];
-          tmem_ld_16(taddr, ra);
-          for (int c = 0; c < size_n; c += 32) {
-            tmem_ld_wait();
-            if (c + 16 < size_n) tmem_ld_16(taddr + c + 16, rb);
-            if (per_n) stage_n_terms(c);
-            process(ra, c);
-            if (c + 16 < size_n) {
-              tmem_ld_wait();
-              if (c + 32 < size_n) tmem_ld_16(taddr + c + 32, ra);
-              if (per_n) stage_n_terms(c + 16);
-              process(rb, c + 16);
-            }
-          }
-        }
-        tc_fence_before();
+      }
+#ifdef RUYB200_DEBUG_CLOCKS
+      long long dbg_b = clock64();
+      dbg_wait += dbg_b - dbg_a;
+#endif
+      if (!ok && lane == 0) { if (!*abortp) atomicCAS(status, 0, 3); *abortp = 1; }
+      // collective decision; also orders the previous item's reads of n_terms[] before this item's writes
+      if (!group_all(ok, group)) break;
+      tc_fence_after();
+#ifdef RUYB200_DEBUG_KNOBS
+      if (debug & 8192) {
+        __syncwarp();
+        const uint32_t a = slot_item[s].acc;
         __syncwarp();
         if (lane == 0) {
-          if (per_n) mbar_arrive_n(&empty_bar[s], arrivals);
-          mbar_arrive_n(&acc_empty_bar[unit], arrivals);
-          if (two_units) mbar_arrive_n(&acc_empty_bar[unit + 1], arrivals);
+          mbar_arrive(&empty_bar[s]);
+          mbar_arrive(&acc_empty_bar[a & 7u]);
+          if (a & 8u) mbar_arrive(&acc_empty_bar[(a & 7u) + 1]);
+        }
+        continue;
+      }
+#endif
+      const BatchItem& item = slot_item[s];   // valid until this group has arrived on empty_bar[s]
+      const uint32_t acc = item.acc;
+      const int unit = (int)(acc & 7u);
+      const bool two_units = (acc & 8u) != 0;
+      const bool ch_n = (item.flags & kItemChannelOnN) != 0;
+      const bool x86 = (item.flags & kItemX86) != 0;
+      const int dst_dtype = (int)((item.flags >> kItemDstShift) & 7u);
+      const bool per_n = ch_n || item.zp_m != 0;   // some term varies along n
+      const int kpad = (item.depth + 31) & ~31;
+      const uint8_t* tile_m = smem + s * kSlotBytes;
+      const uint8_t* tile_n = tile_m + kTileBytes;
+      const int32_t* vbias = item.bias ? slot_vec[s][0] : nullptr;
+      const int32_t* vmfp = item.mfp_pc ? slot_vec[s][1] : nullptr;
+      const int32_t* vmexp = item.mexp_pc ? slot_vec[s][2] : nullptr;
+      if (per_n) {
+        const int n = gtid;
+        NTerm t;
+        t.add = item.zp_m * item.zp_n * item.depth;
+        t.mul = item.mfp;
+        t.exp = item.mexp;
+        t.pad = 0;
+        if (n < item.size_n) {
+          // zero-point term of this destination column: the sum over depth of the n-side row, taken from the packed tile
+          if (item.zp_m) {
+            const bool sg = (item.flags & kItemNSigned) != 0;
+            t.add -= item.zp_m * ((item.flags & kItemNTma) ? tile_row_sum_swizzled(tile_n, n, kpad, sg) : tile_row_sum(tile_n, n, kpad, sg));
+          }
+          if (ch_n) {
+            if (vbias) t.add += vbias[n];
+            if (vmfp) t.mul = vmfp[n];
+            if (vmexp) t.exp = vmexp[n];
+          }
+        }
+        nt[n] = t;
+      }
+      const int m = quarter * 32 + lane - item.m_off;     // tile row -> destination index along m
+      const bool m_ok = m >= 0 && m < item.size_m;
+      int32_t add_m = 0, mul_m = item.mfp, exp_m = item.mexp;
+      if (m_ok) {
+        if (item.zp_n) {
+          const bool sg = (item.flags & kItemMSigned) != 0;
+          const int tr = quarter * 32 + lane;
+          const int32_t sum = item.sums_m ? slot_vec[s][3][m]
+                                          : ((item.flags & kItemMTma) ? tile_row_sum_swizzled(tile_m, tr, kpad, sg)
+                                                                      : tile_row_sum(tile_m, tr, kpad, sg));
+          add_m -= item.zp_n * sum;
+        }
+        if (!ch_n) {
+          if (vbias) add_m += vbias[m];
+          if (vmfp) mul_m = vmfp[m];
+          if (vmexp) exp_m = vmexp[m];
         }
       }
+      const int size_m = item.size_m, size_n = item.size_n, m_off = item.m_off;
+      const int32_t cmin = item.clamp_min, cmax = item.clamp_max, dzp = item.dst_zp;
+      uint8_t* const dst_base = item.dst;
+      const int dst_stride = item.dst_stride;
+      if (per_n) group_all(true, group);   // n_terms[] staged (uniform over the group: per_n comes from the header)
+      __syncwarp();                        // this warp is done with the slot's header, vectors and tiles
+      if (lane == 0) mbar_arrive(&empty_bar[s]);
+#ifdef RUYB200_DEBUG_CLOCKS
+      long long dbg_c = clock64();
+      dbg_stage += dbg_c - dbg_b;
+#endif
+      const bool quarter_used = quarter * 32 + 32 > m_off && quarter * 32 < m_off + size_m;
+      if (quarter_used) {
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(unit * kUnitCols);
+        const int esz = dst_dtype == RUYB200_I32 ? 4 : (dst_dtype == RUYB200_I16 ? 2 : 1);
+        const int64_t step = (int64_t)dst_stride * esz;
+        uint8_t* out = dst_base + (int64_t)m * esz;
+        const bool fast = !per_n && !x86 && dst_dtype != RUYB200_I32;
+        const int sh = 31 - exp_m;
+        const long long rnd = 1ll << (sh - 1);
+        // With every shift of the warp at least 32, the result is the high word of the product shifted on.
+        // With every shift of the warp at least 32 and the per-row addend small enough that accumulator + addend
+        // cannot wrap (|accumulator| < 2^23 for depth <= 128), the whole requantization is one 64-bit multiply-add
+        // and one shift of its high word: acc * mul + (addend * mul + rounding [+ zero point << shift]).
+        const bool high_word = fast && esz == 1 && __all_sync(0xffffffffu, sh >= 32 && add_m > -(1 << 30) && add_m < (1 << 30));
+        const int sh_hi = sh - 32;
+        const bool fold_zp = __all_sync(0xffffffffu, sh <= 50) && dzp >= -256 && dzp <= 255;
+        const long long c64 = (long long)add_m * (long long)mul_m + rnd + (fold_zp ? (long long)dzp * (1ll << (sh & 63)) : 0ll);
+        const int32_t dzp_late = fold_zp ? 0 : dzp;
+        // 16 columns: all values first (branch-free, so the sixteen dependency chains interleave), then the stores
+        auto process = [&](uint32_t (&rr)[16], int c) {   // results replace the accumulators in rr[]
+          const int lim = size_n - c;
+          if (high_word) {
+#pragma unroll
+            for (int q = 0; q < 16; q++) {
+              const long long p = (long long)(int32_t)rr[q] * (long long)mul_m + c64;
+              rr[q] = (uint32_t)max(min(((int32_t)(p >> 32) >> sh_hi) + dzp_late, cmax), cmin);
+            }
+          } else if (fast) {
+#pragma unroll
+            for (int q = 0; q < 16; q++) {
+              const int32_t x = requant_ref_fast((int32_t)(rr[q] + (uint32_t)add_m), mul_m, rnd, sh);
+              rr[q] = (uint32_t)max(min(x + dzp, cmax), cmin);
+            }
+          } else {
+#pragma unroll
+            for (int q = 0; q < 16; q++) {
+              int32_t x = (int32_t)(rr[q] + (uint32_t)add_m);
+              int32_t mul = mul_m;
+              int e = exp_m;
+              if (per_n) {
+                const NTerm t = nt[(c + q) & (kAccCols - 1)];
+                x = (int32_t)((uint32_t)x + (uint32_t)t.add);
+                if (ch_n) { mul = t.mul; e = t.exp; }
+              }
+              if (dst_dtype != RUYB200_I32) {
+                x = x86 ? requant_x86(x, mul, e) : requant_reference(x, mul, e);
+                x = (int32_t)((uint32_t)x + (uint32_t)dzp);
+                x = max(min(x, cmax), cmin);
+              } else {
+                x = (int32_t)((uint32_t)x + (uint32_t)dzp);
+              }
+              rr[q] = (uint32_t)x;
+            }
+          }
+          uint8_t* o = out + (int64_t)c * step;
+#ifdef RUYB200_DEBUG_KNOBS
+          if (debug & 16) {
+            uint32_t acc = 0;
+#pragma unroll
+            for (int q = 0; q < 16; q++) acc ^= rr[q];
+            if (acc == 0x12345678u) o[0] = 1;
+          } else
+#endif
+          if (esz == 1) {
+            if (lim >= 16) {
+#pragma unroll
+              for (int q = 0; q < 16; q++) o[q * step] = (uint8_t)rr[q];
+            } else {
+#pragma unroll
+              for (int q = 0; q < 16; q++) if (q < lim) o[q * step] = (uint8_t)rr[q];
+            }
+          } else if (esz == 2) {
+#pragma unroll
+            for (int q = 0; q < 16; q++) if (q < lim) *reinterpret_cast<int16_t*>(o + q * step) = (int16_t)rr[q];
+          } else {
+#pragma unroll
+            for (int q = 0; q < 16; q++) if (q < lim) *reinterpret_cast<int32_t*>(o + q * step) = (int32_t)rr[q];
+          }
+        };
+        // two register buffers: the load of the next 16 columns is in flight while 16 are processed
+        uint32_t ra[16], rb[16];
+#ifdef RUYB200_DEBUG_KNOBS
+        if (!(debug & 64))
+#endif
+        tmem_ld_16(taddr, ra);
+#ifdef RUYB200_DEBUG_KNOBS
+        if (debug & 8) {
+          tmem_ld_wait();
+        } else
+#endif
+        for (int c = 0; c < size_n; c += 32) {
+          tmem_ld_wait();
+          if (c + 16 < size_n) tmem_ld_16(taddr + c + 16, rb);
+          if (m_ok) process(ra, c);
+          if (c + 16 < size_n) {
+            tmem_ld_wait();
+            if (c + 32 < size_n) tmem_ld_16(taddr + c + 32, ra);
+            if (m_ok) process(rb, c + 16);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&acc_empty_bar[unit]);
+        if (two_units) mbar_arrive(&acc_empty_bar[unit + 1]);
+      }
+#ifdef RUYB200_DEBUG_CLOCKS
+      dbg_work += clock64() - dbg_c;
+#endif
     }
+#ifdef RUYB200_DEBUG_CLOCKS
+    if (blockIdx.x == 0 && lane == 0 && group == 0)
+      printf("epilogue group 0 quarter %d: total %lld cycles, waiting for a tile %lld, staging %lld, working %lld\n", quarter,
+             clock64() - dbg_t0, dbg_wait, dbg_stage, dbg_work);
+#endif
   }
 
   tc_fence_before();

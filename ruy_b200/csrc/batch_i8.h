@@ -50,10 +50,7 @@ struct alignas(16) BatchItem {
   // 64-column unit, bit 3 set if it takes two units (more than 64 destination columns along n), bits 4 / 5 the
   // parity of the first / second unit's use count (which phase of the unit's barriers this item sees).
   uint32_t acc;
-  // Which quarters of the 128 tensor-memory lanes the item's rows occupy (bits 0-3), from m_off and size_m: the
-  // epilogue takes one piece of work per occupied quarter.
-  uint32_t pieces;
-  int32_t reserved;
+  int32_t reserved[2];
 };
 static_assert(sizeof(BatchItem) == 128, "BatchItem is copied as eight 16-byte pieces");
 

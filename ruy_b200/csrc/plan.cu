@@ -136,10 +136,6 @@ int ruyb200_plan_create(ruyb200_ctx* ctx, const ruyb200_mul_desc* descs, int n, 
       if (units == 2) acc |= (1u << 3) | ((uint32_t)(ring.uses[u + 1]++ & 1) << 5);
       ring.next = (u + units) % kHalf;
       it.acc = acc;
-      {
-        const int first_quarter = it.m_off / 32, last_quarter = (it.m_off + it.size_m - 1) / 32;
-        it.pieces = ((2u << last_quarter) - 1u) & ~((1u << first_quarter) - 1u);
-      }
       scheduled[pos] = it;
     }
     // Operands with 16-byte aligned rows are fetched by one tensor-map copy each: encode the maps now.
