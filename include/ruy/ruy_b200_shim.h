@@ -94,6 +94,7 @@ template <> struct TypeCode<std::uint8_t> { static constexpr std::uint8_t value 
 template <> struct TypeCode<std::int16_t> { static constexpr std::uint8_t value = RUYB200_I16; };
 template <> struct TypeCode<std::int32_t> { static constexpr std::uint8_t value = RUYB200_I32; };
 template <> struct TypeCode<float> { static constexpr std::uint8_t value = RUYB200_F32; };
+template <> struct TypeCode<double> { static constexpr std::uint8_t value = RUYB200_F64; };
 }  // namespace b200_detail
 
 // Same accessors and defaults as ruy's: no bias, multiplier 0 with exponent 0 (so a quantized Mul whose
@@ -233,8 +234,13 @@ ruyb200_matrix Flatten(const Matrix<T>& m) {
 }
 template <typename Accum, typename Dst>
 void FlattenClamp(const MulParams<Accum, Dst>& p, ruyb200_mul_params* out, std::true_type /*float*/) {
-  out->clamp_min.f = p.clamp_min();
-  out->clamp_max.f = p.clamp_max();
+  if (std::is_same<Accum, double>::value) {   // the mixed float/double cases carry their bounds as doubles
+    out->clamp_min.d = static_cast<double>(p.clamp_min());
+    out->clamp_max.d = static_cast<double>(p.clamp_max());
+  } else {
+    out->clamp_min.f = static_cast<float>(p.clamp_min());
+    out->clamp_max.f = static_cast<float>(p.clamp_max());
+  }
 }
 template <typename Accum, typename Dst>
 void FlattenClamp(const MulParams<Accum, Dst>& p, ruyb200_mul_params* out, std::false_type) {

@@ -25,7 +25,7 @@
 extern "C" {
 #endif
 
-#define RUYB200_ABI_VERSION 1
+#define RUYB200_ABI_VERSION 2
 
 #if defined(__GNUC__)
 #define RUYB200_API __attribute__((visibility("default")))
@@ -49,7 +49,8 @@ typedef enum ruyb200_dtype {
   RUYB200_U8 = 1,
   RUYB200_I16 = 2,
   RUYB200_I32 = 3,
-  RUYB200_F32 = 4
+  RUYB200_F32 = 4,
+  RUYB200_F64 = 5   /* only in ruy's mixed float cases: (f64, f32, f64, f32) and (f32, f64, f64, f64) */
 } ruyb200_dtype;
 
 /* ruy::Order (ruy/matrix.h:30). */
@@ -110,8 +111,9 @@ typedef struct ruyb200_matrix {
 } ruyb200_matrix;
 
 /* ruy::MulParams<Accum,Dst> (ruy/mul_params.h:102-223) with types erased.
- * accum_dtype is RUYB200_I32 or RUYB200_F32.  For the float case bias points to
- * floats and clamp_* hold float bit patterns in .f; multipliers are ignored.
+ * accum_dtype is RUYB200_I32, RUYB200_F32 or RUYB200_F64.  For the float case bias points to
+ * floats and clamp_* hold floats in .f; with a double accumulator (an operand or the destination is
+ * RUYB200_F64) bias points to doubles and clamp_* hold doubles in .d; multipliers are ignored.
  * Per-channel pointers, when non-NULL, take precedence over the scalar pair
  * (ruy/apply_multiplier.h:66-79).  Per-channel buffers hold one entry per dst
  * row (CHANNEL_ROW) or column (CHANNEL_COL); the library never reads past that
@@ -119,6 +121,7 @@ typedef struct ruyb200_matrix {
 typedef union ruyb200_scalar {
   int32_t i;
   float f;
+  double d;
 } ruyb200_scalar;
 
 typedef struct ruyb200_mul_params {

@@ -75,6 +75,16 @@ struct FillParams<float, float> {
   }
 };
 
+// ruy's mixed floating-point cases (ruy/BUILD:1195-1207): double accumulator and bias, bounds in .d
+template <typename Dst>
+struct FillParams<double, Dst> {
+  static void Run(const ruyb200_mul_params& p, ruy::MulParams<double, Dst>* out) {
+    out->set_bias(static_cast<const double*>(p.bias));
+    out->set_clamp_min(static_cast<Dst>(p.clamp_min.d));
+    out->set_clamp_max(static_cast<Dst>(p.clamp_max.d));
+  }
+};
+
 template <typename L, typename R, typename Accum, typename Dst>
 int Run(ruy::Context* ctx, const ruyb200_mul_desc& d, bool reference_mul) {
   ruy::Matrix<L> lhs = ToMatrix<L>(d.lhs, false);
@@ -104,6 +114,8 @@ int Dispatch(ruy::Context* ctx, const ruyb200_mul_desc& d, bool reference_mul) {
 #define CASE(LT, RT, DT, L, R, A, D) \
   if (l == LT && r == RT && o == DT) return Run<L, R, A, D>(ctx, d, reference_mul);
   CASE(RUYB200_F32, RUYB200_F32, RUYB200_F32, float, float, float, float)
+  CASE(RUYB200_F64, RUYB200_F32, RUYB200_F32, double, float, double, float)
+  CASE(RUYB200_F32, RUYB200_F64, RUYB200_F64, float, double, double, double)
   CASE(RUYB200_I8, RUYB200_I8, RUYB200_I8, i8, i8, i32, i8)
   CASE(RUYB200_I8, RUYB200_I8, RUYB200_U8, i8, i8, i32, u8)
   CASE(RUYB200_I8, RUYB200_I8, RUYB200_I16, i8, i8, i32, i16)

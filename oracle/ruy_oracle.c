@@ -100,6 +100,11 @@ static int dtype_lowest(int dtype) {
   }
 }
 
+static int is_fp(int dtype) { return dtype == RUYB200_F32 || dtype == RUYB200_F64; }
+static double load_fp(const ruyb200_matrix* m, int64_t off) {
+  return m->dtype == RUYB200_F64 ? ((const double*)m->data)[off] : (double)((const float*)m->data)[off];
+}
+
 /* Returns 0 when ruy would accept the arguments (its checks are debug asserts). */
 ORACLE_API int ruy_oracle_validate(const ruyb200_mul_desc* d) {
   const ruyb200_matrix* l = &d->lhs;
@@ -112,7 +117,13 @@ ORACLE_API int ruy_oracle_validate(const ruyb200_mul_desc* d) {
     if (l->zero_point || r->zero_point || o->zero_point) return -1;
     return 0;
   }
-  if (l->dtype == RUYB200_F32 || r->dtype == RUYB200_F32 || o->dtype == RUYB200_F32) return -2;
+  if (d->params.accum_dtype == RUYB200_F64) {
+    /* ruy's mixed floating-point cases: (f64, f32, f64, f32) and (f32, f64, f64, f64), ruy/BUILD:1195-1207 */
+    if (!is_fp(l->dtype) || !is_fp(r->dtype) || !is_fp(o->dtype)) return -2;
+    if (l->zero_point || r->zero_point || o->zero_point) return -1;
+    return 0;
+  }
+  if (is_fp(l->dtype) || is_fp(r->dtype) || is_fp(o->dtype)) return -2;
   if (l->dtype == RUYB200_I16 || r->dtype == RUYB200_I16) {
     if (l->zero_point || r->zero_point || o->zero_point) return -1;
   }
@@ -163,6 +174,24 @@ ORACLE_API int ruy_oracle_mul(const ruyb200_mul_desc* d, int rounding, int wide_
           out = acc;
         }
         ((float*)D->data)[offset_of(D, i, j)] = out;
+      }
+    }
+    return 0;
+  }
+
+  if (P->accum_dtype == RUYB200_F64) {
+    /* the standard C++ kernel with AccumScalar = double (ruy/kernel.h:211-237): operands widened to double,
+     * summed in depth order, double bias, bounds applied in double, then the cast to the destination type */
+    const double* bias64 = (const double*)P->bias;
+    for (int i = 0; i < rows; i++) {
+      for (int j = 0; j < cols; j++) {
+        double acc = 0;
+        for (int k = 0; k < depth; k++) acc += load_fp(L, offset_of(L, i, k)) * load_fp(R, offset_of(R, k, j));
+        if (bias64) acc += bias64[chan_row ? i : j];
+        acc = acc < P->clamp_max.d ? acc : P->clamp_max.d;
+        acc = acc > P->clamp_min.d ? acc : P->clamp_min.d;
+        if (D->dtype == RUYB200_F64) ((double*)D->data)[offset_of(D, i, j)] = acc;
+        else ((float*)D->data)[offset_of(D, i, j)] = (float)acc;
       }
     }
     return 0;

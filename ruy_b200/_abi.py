@@ -5,7 +5,7 @@ test-suite checks sizes and the exported symbol list against the header text.
 """
 import ctypes as C
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 # ruyb200_status
 OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_NO_DEVICE, ERR_CUDA, ERR_TIMEOUT, ERR_OOM = 0, -1, -2, -3, -4, -5, -6
@@ -15,9 +15,9 @@ STATUS_NAMES = {
 }
 
 # ruyb200_dtype
-I8, U8, I16, I32, F32 = 0, 1, 2, 3, 4
-DTYPE_SIZE = {I8: 1, U8: 1, I16: 2, I32: 4, F32: 4}
-NUMPY_DTYPE = {I8: "int8", U8: "uint8", I16: "int16", I32: "int32", F32: "float32"}
+I8, U8, I16, I32, F32, F64 = 0, 1, 2, 3, 4, 5
+DTYPE_SIZE = {I8: 1, U8: 1, I16: 2, I32: 4, F32: 4, F64: 8}
+NUMPY_DTYPE = {I8: "int8", U8: "uint8", I16: "int16", I32: "int32", F32: "float32", F64: "float64"}
 DTYPE_OF_NUMPY = {v: k for k, v in NUMPY_DTYPE.items()}
 
 COL_MAJOR, ROW_MAJOR = 0, 1
@@ -49,7 +49,7 @@ class MatrixDesc(C.Structure):
 
 class Scalar(C.Union):
     """ruyb200_scalar."""
-    _fields_ = [("i", C.c_int32), ("f", C.c_float)]
+    _fields_ = [("i", C.c_int32), ("f", C.c_float), ("d", C.c_double)]
 
 
 class MulParamsDesc(C.Structure):

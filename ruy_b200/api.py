@@ -97,7 +97,7 @@ def _ptr_and_dtype(data):
     if _is_torch(data):
         import torch
         names = {torch.int8: "int8", torch.uint8: "uint8", torch.int16: "int16",
-                 torch.int32: "int32", torch.float32: "float32"}
+                 torch.int32: "int32", torch.float32: "float32", torch.float64: "float64"}
         return data.data_ptr(), _abi.DTYPE_OF_NUMPY[names[data.dtype]]
     a = data
     return a.ctypes.data, _abi.DTYPE_OF_NUMPY[a.dtype.name]
@@ -140,7 +140,7 @@ class MulParams:
         self.multiplier_exponent = 0
         self.multiplier_fixedpoint_perchannel = None
         self.multiplier_exponent_perchannel = None
-        if self.accum == "float32":
+        if self.accum in ("float32", "float64"):
             self.clamp_min, self.clamp_max = -np.inf, np.inf
         else:
             info = np.iinfo(self.dst)
@@ -156,7 +156,10 @@ class MulParams:
         p.multiplier_exponent_perchannel = _ptr_and_dtype(self.multiplier_exponent_perchannel)[0]
         p.multiplier_fixedpoint = int(self.multiplier_fixedpoint)
         p.multiplier_exponent = int(self.multiplier_exponent)
-        if self.accum == "float32":
+        if self.accum == "float64":
+            p.clamp_min.d = float(self.clamp_min)
+            p.clamp_max.d = float(self.clamp_max)
+        elif self.accum == "float32":
             p.clamp_min.f = float(self.clamp_min)
             p.clamp_max.f = float(self.clamp_max)
         else:

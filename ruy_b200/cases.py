@@ -50,9 +50,12 @@ class MulCase:
         self.dst_dtype = np.dtype(dst_dtype).name
         self.dst_layout, self.dst_zp = dst_layout, dst_zp
         self.bias, self.mfp, self.mexp = bias, mfp, mexp
-        self.accum = "float32" if lhs.dtype == np.float32 else "int32"
+        if np.float64 in (lhs.dtype, rhs.dtype) or np.dtype(dst_dtype) == np.float64:
+            self.accum = "float64"      # ruy's mixed cases (f64, f32, f64, f32) and (f32, f64, f64, f64)
+        else:
+            self.accum = "float32" if lhs.dtype == np.float32 else "int32"
         if clamp is None:
-            if self.accum == "float32":
+            if self.accum in ("float32", "float64"):
                 clamp = (-np.inf, np.inf)
             else:
                 info = np.iinfo(self.dst_dtype)
@@ -286,14 +289,16 @@ def random_case(rows, depth, cols, lhs="int8", rhs="int8", dst="int8", orders="R
     o = [Order.kRowMajor if ch == "R" else Order.kColMajor for ch in orders]
     ll, rl, dl = (_layout(rows, depth, o[0], extra_stride), _layout(depth, cols, o[1], extra_stride),
                   _layout(rows, cols, o[2], extra_stride))
-    if lhs == "float32":
-        L = rng.uniform(-1, 1, size=(rows, depth)).astype(np.float32)
-        R = rng.uniform(-1, 1, size=(depth, cols)).astype(np.float32)
+    if lhs in ("float32", "float64"):
+        L = rng.uniform(-1, 1, size=(rows, depth)).astype(lhs)
+        R = rng.uniform(-1, 1, size=(depth, cols)).astype(rhs)
         nch = rows if channel == ChannelDimension.kRow else cols
-        b = rng.uniform(-1, 1, size=nch).astype(np.float32) if bias else None
+        wide = "float64" in (lhs, rhs, dst)       # the bias has the accumulator's type
+        b = rng.uniform(-1, 1, size=nch).astype(np.float64 if wide else np.float32) if bias else None
         lo = float(-0.25 * np.sqrt(depth))
-        return MulCase(f"f32_{rows}x{depth}x{cols}_{orders}", _storage(L, ll), ll, 0, _storage(R, rl), rl, 0,
-                       "float32", dl, 0, b, clamp=(lo, -lo * 0.9), channel=channel,
+        name = f"f32_{rows}x{depth}x{cols}_{orders}" if not wide else f"{lhs}x{rhs}_{dst}_{rows}x{depth}x{cols}_{orders}"
+        return MulCase(name, _storage(L, ll), ll, 0, _storage(R, rl), rl, 0,
+                       dst if wide else "float32", dl, 0, b, clamp=(lo, -lo * 0.9), channel=channel,
                        lhs_cache=lhs_cache, rhs_cache=rhs_cache)
     (llo, lhi), (rlo, rhi) = _INT_RANGE[lhs], _INT_RANGE[rhs]
     # LHS avoids the minimum value, as ruy's harness does (kOffCenterAvoidMinValue)

@@ -57,6 +57,8 @@ size_t dtype_size(int dtype) {
       return 1;
     case RUYB200_I16:
       return 2;
+    case RUYB200_F64:
+      return 8;
     default:
       return 4;
   }
@@ -174,6 +176,7 @@ constexpr size_t kCacheSlabBytes = size_t(32) << 20;
 }  // namespace
 
 constexpr int kMaxChunks = 16;
+constexpr size_t kBounceBytes = size_t(256) << 10;   // pinned staging for per-channel vectors: 3 x 16384 channels and more
 
 struct ruyb200_ctx {
   int device = 0;
@@ -207,6 +210,9 @@ struct ruyb200_ctx {
   cudaStream_t copy_out = nullptr;
   cudaEvent_t chunk_in[kMaxChunks] = {};
   cudaEvent_t chunk_done[kMaxChunks] = {};
+  char* bounce = nullptr;   // pinned staging for small host vectors (bias, multipliers), kBounceBytes
+  size_t bounce_off = 0;
+  cudaEvent_t chunk_out[kMaxChunks] = {};   // only with RUYB200_TRACE: when each chunk's destination rows have left
   cudaEvent_t chunk_start = nullptr;
   bool no_chunks = false;   // RUYB200_NO_CHUNKS=1: one copy in, one kernel, one copy out
   int chunk_target = 4;     // RUYB200_CHUNKS=n: how many chunks a large host-operand mul is cut into (2..16)
@@ -263,14 +269,14 @@ int validate_desc(const ruyb200_mul_desc* d) {
   const char* names[3] = {"lhs", "rhs", "dst"};
   for (int i = 0; i < 3; i++) {
     const ruyb200_matrix* m = ms[i];
-    if (m->dtype > RUYB200_F32) return fail(RUYB200_ERR_UNSUPPORTED, "%s: unknown dtype %d", names[i], m->dtype);
+    if (m->dtype > RUYB200_F64) return fail(RUYB200_ERR_UNSUPPORTED, "%s: unknown dtype %d", names[i], m->dtype);
     if (m->order > 1) return fail(RUYB200_ERR_INVALID, "%s: bad order", names[i]);
     if (m->rows < 0 || m->cols < 0) return fail(RUYB200_ERR_INVALID, "%s: negative dimension", names[i]);
     const int inner = m->order == RUYB200_COL_MAJOR ? m->rows : m->cols;
     if (m->stride < inner) return fail(RUYB200_ERR_INVALID, "%s: stride %d < %d", names[i], m->stride, inner);
     if (m->rows > 0 && m->cols > 0 && !m->data) return fail(RUYB200_ERR_INVALID, "%s: null data", names[i]);
     if (m->cache_policy > RUYB200_ALWAYS_CACHE) return fail(RUYB200_ERR_INVALID, "%s: bad cache policy", names[i]);
-    if (m->dtype == RUYB200_F32) {
+    if (m->dtype == RUYB200_F32 || m->dtype == RUYB200_F64) {
       if (m->zero_point) return fail(RUYB200_ERR_INVALID, "%s: float zero_point must be 0", names[i]);
     } else {
       int64_t lo, hi;
@@ -291,7 +297,17 @@ int validate_desc(const ruyb200_mul_desc* d) {
       return fail(RUYB200_ERR_UNSUPPORTED, "float accumulation needs float operands and destination");
     return RUYB200_OK;
   }
-  if (p.accum_dtype != RUYB200_I32) return fail(RUYB200_ERR_UNSUPPORTED, "accumulator must be int32 or float");
+  if (p.accum_dtype == RUYB200_F64) {
+    // ruy's mixed floating-point cases, (f64, f32, f64, f32) and (f32, f64, f64, f64) in ruy/BUILD:1195-1207, and
+    // every other mix of float and double operands with a double accumulator
+    const auto fp = [](int t) { return t == RUYB200_F32 || t == RUYB200_F64; };
+    if (!fp(L) || !fp(R) || !fp(D))
+      return fail(RUYB200_ERR_UNSUPPORTED, "double accumulation needs float or double operands and destination");
+    return RUYB200_OK;
+  }
+  if (p.accum_dtype != RUYB200_I32) return fail(RUYB200_ERR_UNSUPPORTED, "accumulator must be int32, float or double");
+  const auto wide = [](int t) { return t == RUYB200_F32 || t == RUYB200_F64; };
+  if (wide(L) || wide(R) || wide(D)) return fail(RUYB200_ERR_UNSUPPORTED, "unsupported integer type combination");
   if (L == RUYB200_F32 || R == RUYB200_F32 || D == RUYB200_F32 || L == RUYB200_I32 || R == RUYB200_I32)
     return fail(RUYB200_ERR_UNSUPPORTED, "unsupported integer type combination");
   const bool has16 = L == RUYB200_I16 || R == RUYB200_I16;
@@ -456,7 +472,7 @@ struct Resolved {
 int prepare_side(ruyb200_ctx* ctx, const ruyb200_matrix& m, int side, int depth, bool cache_it, bool need_sums,
                  bool tc_path, SideView* out, const int32_t** sums_out) {
   *sums_out = nullptr;
-  const bool integer = m.dtype != RUYB200_F32;
+  const bool integer = m.dtype != RUYB200_F32 && m.dtype != RUYB200_F64;
   SideView src = side_view(m, side, m.data);
   const size_t esz = dtype_size(m.dtype);
   const bool on_device = is_device_pointer(m.data);
@@ -563,13 +579,28 @@ int prepare_side(ruyb200_ctx* ctx, const ruyb200_matrix& m, int side, int depth,
 }
 
 // Copies a small host vector (bias / multipliers) into the arena unless it already lives on the device.
-int stage_vector(ruyb200_ctx* ctx, const void* p, size_t count, const void** out) {
+// Such vectors are usually pageable memory, from which a copy holds the calling thread for some 10 us; they go through
+// a pinned buffer of the context instead (host pointers only occur in synchronous muls, so the buffer is free again
+// when the next call starts).
+int stage_vector(ruyb200_ctx* ctx, const void* p, size_t count, const void** out, size_t elem = 4) {
   *out = p;
   if (!p || count == 0 || is_device_pointer(p)) return RUYB200_OK;
-  void* d = ctx->arena.alloc(count * 4);
+  const size_t bytes = count * elem;
+  void* d = ctx->arena.alloc(bytes);
   if (!d) return fail(RUYB200_ERR_OOM, "arena allocation failed");
-  CUDA_TRY(cudaMemcpyAsync(d, p, count * 4, cudaMemcpyHostToDevice, ctx->stream));
-  ctx->counters[3] += count * 4;
+  const void* src = p;
+  const size_t padded = (bytes + 63) & ~size_t(63);
+  if (!ctx->bounce && cudaHostAlloc(&ctx->bounce, kBounceBytes, cudaHostAllocDefault) != cudaSuccess) {
+    cudaGetLastError();
+    ctx->bounce = nullptr;
+  }
+  if (ctx->bounce && ctx->bounce_off + padded <= kBounceBytes) {
+    memcpy(ctx->bounce + ctx->bounce_off, p, bytes);
+    src = ctx->bounce + ctx->bounce_off;
+    ctx->bounce_off += padded;
+  }
+  CUDA_TRY(cudaMemcpyAsync(d, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+  ctx->counters[3] += bytes;
   *out = d;
   return RUYB200_OK;
 }
@@ -577,6 +608,7 @@ int stage_vector(ruyb200_ctx* ctx, const void* p, size_t count, const void** out
 int choose_kernel(const ruyb200_ctx* ctx, const ruyb200_mul_desc& d) {
   if (ctx->force_kernel == RUYB200_KERNEL_GENERIC) return ctx->force_kernel;
   if (d.params.accum_dtype == RUYB200_F32) return RUYB200_KERNEL_SGEMM;
+  if (d.params.accum_dtype == RUYB200_F64) return RUYB200_KERNEL_GENERIC;
   const bool both8 = dtype_size(d.lhs.dtype) == 1 && dtype_size(d.rhs.dtype) == 1;
   if (both8 && d.lhs.cols > 0) return RUYB200_KERNEL_TC_I8;
   return RUYB200_KERNEL_GENERIC;
@@ -592,10 +624,13 @@ int run_chunks(ruyb200_ctx* ctx, const ruyb200_mul_desc& d, const TcI8Launch& L,
   if (!ctx->copy_in) {
     CUDA_TRY(cudaStreamCreateWithFlags(&ctx->copy_in, cudaStreamNonBlocking));
     CUDA_TRY(cudaStreamCreateWithFlags(&ctx->copy_out, cudaStreamNonBlocking));
-    CUDA_TRY(cudaEventCreateWithFlags(&ctx->chunk_start, cudaEventDisableTiming));
+    // with the decision log on, the events keep time so that the log can show each chunk's way through the pipeline
+    const unsigned flags = ctx->trace ? cudaEventDefault : cudaEventDisableTiming;
+    CUDA_TRY(cudaEventCreateWithFlags(&ctx->chunk_start, flags));
     for (int i = 0; i < kMaxChunks; i++) {
-      CUDA_TRY(cudaEventCreateWithFlags(&ctx->chunk_in[i], cudaEventDisableTiming));
-      CUDA_TRY(cudaEventCreateWithFlags(&ctx->chunk_done[i], cudaEventDisableTiming));
+      CUDA_TRY(cudaEventCreateWithFlags(&ctx->chunk_in[i], flags));
+      CUDA_TRY(cudaEventCreateWithFlags(&ctx->chunk_done[i], flags));
+      if (ctx->trace) CUDA_TRY(cudaEventCreateWithFlags(&ctx->chunk_out[i], flags));
     }
   }
   const int width = L.m_side.width;
@@ -655,9 +690,22 @@ int run_chunks(ruyb200_ctx* ctx, const ruyb200_mul_desc& d, const TcI8Launch& L,
                                    cudaMemcpyDeviceToHost, ctx->copy_out));
       }
       ctx->counters[4] += dst_row_bytes * (size_t)w;
+      if (ctx->trace) CUDA_TRY(cudaEventRecord(ctx->chunk_out[c], ctx->copy_out));
     }
   }
   if (dst_host) CUDA_TRY(cudaStreamSynchronize(ctx->copy_out));
+  if (ctx->trace && m_host && dst_host) {
+    CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    fprintf(stderr, "ruy_b200: %d chunks of %d m indices; microseconds after the first copy could start (operand in, kernel done, destination out):", chunks, step);
+    for (int c = 0; c < chunks; c++) {
+      float a = 0, b = 0, o = 0;
+      cudaEventElapsedTime(&a, ctx->chunk_start, ctx->chunk_in[c]);
+      cudaEventElapsedTime(&b, ctx->chunk_start, ctx->chunk_done[c]);
+      cudaEventElapsedTime(&o, ctx->chunk_start, ctx->chunk_out[c]);
+      fprintf(stderr, " [%.0f %.0f %.0f]", a * 1e3, b * 1e3, o * 1e3);
+    }
+    fprintf(stderr, "\n");
+  }
   return RUYB200_OK;
 }
 
@@ -689,9 +737,13 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
     }
   }
   ctx->arena.reset(synchronous);
+  ctx->bounce_off = 0;
 
   const int depth = d.lhs.cols;
-  const bool is_float = d.params.accum_dtype == RUYB200_F32;
+  // double accumulation (ruy's mixed float/double cases) runs on the CUDA-core kernel only, straight from the
+  // operands as stored: no packing, no cache entry
+  const bool is_f64 = d.params.accum_dtype == RUYB200_F64;
+  const bool is_float = d.params.accum_dtype == RUYB200_F32 || is_f64;
   int kernel = choose_kernel(ctx, d);
   if (kernel == RUYB200_KERNEL_TC_I8 && (is_float || dtype_size(d.lhs.dtype) != 1 || dtype_size(d.rhs.dtype) != 1 ||
                                          depth == 0)) {
@@ -764,14 +816,14 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
   if (m_streamed && !m_is_rhs) {
     lhs_v = side_view(d.lhs, 0, m_dev);
   } else {
-    rc = prepare_side(ctx, d.lhs, 0, depth, should_cache(d.lhs, d.rhs.cols), need_lhs_sums && !(tc && !m_is_rhs), tc, &lhs_v,
+    rc = prepare_side(ctx, d.lhs, 0, depth, !is_f64 && should_cache(d.lhs, d.rhs.cols), need_lhs_sums && !(tc && !m_is_rhs), tc, &lhs_v,
                       &lhs_sums);
     if (rc) return rc;
   }
   if (m_streamed && m_is_rhs) {
     rhs_v = side_view(d.rhs, 1, m_dev);
   } else {
-    rc = prepare_side(ctx, d.rhs, 1, depth, should_cache(d.rhs, d.lhs.rows), need_rhs_sums && !(tc && m_is_rhs), tc, &rhs_v,
+    rc = prepare_side(ctx, d.rhs, 1, depth, !is_f64 && should_cache(d.rhs, d.lhs.rows), need_rhs_sums && !(tc && m_is_rhs), tc, &rhs_v,
                       &rhs_sums);
     if (rc) return rc;
   }
@@ -779,7 +831,7 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
   Epilogue ep;
   memset(&ep, 0, sizeof(ep));
   const void* p;
-  rc = stage_vector(ctx, d.params.bias, nch, &p);
+  rc = stage_vector(ctx, d.params.bias, nch, &p, is_f64 ? 8 : 4);
   if (rc) return rc;
   ep.bias = p;
   if (!is_float && d.dst.dtype != RUYB200_I32) {
@@ -907,6 +959,10 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
     ce = launch_gemv(r.m_side, r.n_side, r.dst, r.ep, ctx->stream);
     if (ctx->trace) fprintf(stderr, "ruy_b200: mul %dx%dx%d kernel=gemv (one pass over the wide operand, %s)\n", d.lhs.rows, d.lhs.cols, d.rhs.cols,
                             is_float ? "fp32 FFMA, compensated" : "dp4a, sums on the way");
+  } else if (is_f64) {
+    kernel = RUYB200_KERNEL_GENERIC;
+    ce = launch_generic_f64(r.m_side, r.n_side, r.dst, r.ep, d.params.clamp_min.d, d.params.clamp_max.d, ctx->stream);
+    if (ctx->trace) fprintf(stderr, "ruy_b200: mul %dx%dx%d kernel=generic (CUDA cores, double accumulation)\n", d.lhs.rows, d.lhs.cols, d.rhs.cols);
   } else if (is_float && kernel != RUYB200_KERNEL_GENERIC) {
     kernel = RUYB200_KERNEL_SGEMM;
     ce = launch_sgemm(r.m_side, r.n_side, r.dst, r.ep, ctx->stream);
@@ -1078,6 +1134,7 @@ int ruyb200_ctx_destroy(ruyb200_ctx* ctx) {
   }
   ctx->cache_slabs.clear();
   ctx->arena.release();
+  if (ctx->bounce) cudaFreeHost(ctx->bounce);
   if (ctx->d_status) cudaFree(ctx->d_status);
   if (ctx->h_status) cudaFreeHost(ctx->h_status);
   if (ctx->copy_in) cudaStreamDestroy(ctx->copy_in);
@@ -1085,6 +1142,7 @@ int ruyb200_ctx_destroy(ruyb200_ctx* ctx) {
   for (int i = 0; i < kMaxChunks; i++) {
     if (ctx->chunk_in[i]) cudaEventDestroy(ctx->chunk_in[i]);
     if (ctx->chunk_done[i]) cudaEventDestroy(ctx->chunk_done[i]);
+    if (ctx->chunk_out[i]) cudaEventDestroy(ctx->chunk_out[i]);
   }
   if (ctx->chunk_start) cudaEventDestroy(ctx->chunk_start);
   if (ctx->own_stream && ctx->stream) cudaStreamDestroy(ctx->stream);

@@ -118,6 +118,11 @@ __device__ __forceinline__ void store_int(const DstView& d, uint8_t dtype, int m
 cudaError_t launch_generic(const SideView& m_side, const SideView& n_side, const DstView& dst,
                            const Epilogue& ep, cudaStream_t stream);
 
+// The same for ruy's mixed floating-point cases: float or double operands and destination (the dtype fields say
+// which), double accumulation, double bias and clamp bounds.
+cudaError_t launch_generic_f64(const SideView& m_side, const SideView& n_side, const DstView& dst, const Epilogue& ep,
+                               double clamp_min, double clamp_max, cudaStream_t stream);
+
 // Sum over depth of every width-row of a side (int32, wrap-around).
 cudaError_t launch_sums(const SideView& side, int depth, int32_t* sums, cudaStream_t stream);
 

@@ -95,6 +95,57 @@ __global__ void __launch_bounds__(256) generic_mul_kernel(SideView ms, SideView 
   }
 }
 
+// Double accumulation over float or double operands (ruy's type mixes (f64, f32, f64, f32) and (f32, f64, f64, f64),
+// ruy/BUILD:1195-1207, served in ruy by the standard C++ kernel, ruy/kernel.h:176-241).  Same tiling as above; the
+// products and the sum are double, in depth order, which is the order ruy's kernel adds in.
+template <typename TM, typename TN, typename TD>
+__global__ void __launch_bounds__(256) generic_f64_kernel(SideView ms, SideView ns, DstView dst, Epilogue ep, double clamp_min,
+                                                          double clamp_max) {
+  __shared__ double sm[kTile][kChunk + 1];
+  __shared__ double sn[kTile][kChunk + 1];
+  const int m0 = blockIdx.y * kTile;
+  const int n0 = blockIdx.x * kTile;
+  const int tx = threadIdx.x % 32;
+  const int ty = threadIdx.x / 32;
+  double acc[4] = {0.0, 0.0, 0.0, 0.0};
+  for (int k0 = 0; k0 < ep.depth; k0 += kChunk) {
+    for (int e = threadIdx.x; e < kTile * kChunk; e += 256) {
+      int wm, km, wn, kn;
+      if (ms.stride_k == 1) { km = e % kChunk; wm = e / kChunk; } else { wm = e % kTile; km = e / kTile; }
+      if (ns.stride_k == 1) { kn = e % kChunk; wn = e / kChunk; } else { wn = e % kTile; kn = e / kTile; }
+      double vm = 0.0, vn = 0.0;
+      if (m0 + wm < ms.width && k0 + km < ep.depth) {
+        vm = (double)((const TM*)ms.data)[(int64_t)(m0 + wm) * ms.stride_w + (int64_t)(k0 + km) * ms.stride_k];
+      }
+      if (n0 + wn < ns.width && k0 + kn < ep.depth) {
+        vn = (double)((const TN*)ns.data)[(int64_t)(n0 + wn) * ns.stride_w + (int64_t)(k0 + kn) * ns.stride_k];
+      }
+      sm[wm][km] = vm;
+      sn[wn][kn] = vn;
+    }
+    __syncthreads();
+#pragma unroll 4
+    for (int k = 0; k < kChunk; k++) {
+      const double bn = sn[tx][k];
+#pragma unroll
+      for (int r = 0; r < 4; r++) acc[r] = fma(sm[ty * 4 + r][k], bn, acc[r]);
+    }
+    __syncthreads();
+  }
+  const int n = n0 + tx;
+#pragma unroll
+  for (int r = 0; r < 4; r++) {
+    const int m = m0 + ty * 4 + r;
+    if (m < dst.size_m && n < dst.size_n) {
+      double v = acc[r];
+      if (ep.bias) v += ((const double*)ep.bias)[ep.channel_on_n ? n : m];
+      v = fmin(v, clamp_max);
+      v = fmax(v, clamp_min);
+      ((TD*)dst.data)[(int64_t)m * dst.stride_m + n] = (TD)v;
+    }
+  }
+}
+
 // One warp per width-row; lanes stride over depth.
 __global__ void sums_kernel(SideView s, int depth, int32_t* sums) {
   const int w = blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
@@ -188,6 +239,28 @@ cudaError_t launch_generic(const SideView& m_side, const SideView& n_side, const
   } else {
     generic_mul_kernel<false><<<grid, 256, 0, stream>>>(m_side, n_side, dst, ep);
   }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_generic_f64(const SideView& m_side, const SideView& n_side, const DstView& dst, const Epilogue& ep,
+                               double clamp_min, double clamp_max, cudaStream_t stream) {
+  if (dst.size_m <= 0 || dst.size_n <= 0) return cudaSuccess;
+  dim3 grid((dst.size_n + kTile - 1) / kTile, (dst.size_m + kTile - 1) / kTile);
+  if (grid.y > 65535) return cudaErrorInvalidConfiguration;
+  const int code = (m_side.dtype == RUYB200_F64 ? 4 : 0) | (n_side.dtype == RUYB200_F64 ? 2 : 0) | (ep.dst_dtype == RUYB200_F64 ? 1 : 0);
+#define RUYB200_F64_CASE(c, TM, TN, TD) \
+  case c: generic_f64_kernel<TM, TN, TD><<<grid, 256, 0, stream>>>(m_side, n_side, dst, ep, clamp_min, clamp_max); break;
+  switch (code) {
+    RUYB200_F64_CASE(0, float, float, float)
+    RUYB200_F64_CASE(1, float, float, double)
+    RUYB200_F64_CASE(2, float, double, float)
+    RUYB200_F64_CASE(3, float, double, double)
+    RUYB200_F64_CASE(4, double, float, float)
+    RUYB200_F64_CASE(5, double, float, double)
+    RUYB200_F64_CASE(6, double, double, float)
+    RUYB200_F64_CASE(7, double, double, double)
+  }
+#undef RUYB200_F64_CASE
   return cudaGetLastError();
 }
 

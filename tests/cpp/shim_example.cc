@@ -1,5 +1,5 @@
 // The usage patterns of the reference's example program (example/example.cc:21-182), written against the
-// drop-in headers: float, float with bias and clamp, asymmetric uint8, per-channel int8, raw int32
+// drop-in headers: float, float with bias and clamp, double x float, asymmetric uint8, per-channel int8, raw int32
 // accumulators, int8 x int16.  Prints each destination as one line of integers/floats so that the Python
 // test can compare them with the oracle.  Also exercises the Context methods.
 #include <cstdint>
@@ -35,6 +35,26 @@ int main() {
     mul_params.set_clamp_max(15);
     ruy::Mul(lhs, rhs, mul_params, &context, &dst);
     Print("float_bias_clamp", dst_data, 4);
+  }
+  {
+    // one of ruy's mixed floating-point cases: double LHS, float RHS, double accumulator and bias, float destination
+    const double lhs_data[] = {1.5, 2, 3, 4};
+    const float rhs_data[] = {1, 2, 3, 4.25f};
+    const double bias_data[] = {0.5, -1};
+    float dst_data[4];
+    ruy::Matrix<double> lhs;
+    ruy::Matrix<float> rhs, dst;
+    ruy::MakeSimpleLayout(2, 2, ruy::Order::kRowMajor, lhs.mutable_layout());
+    lhs.set_data(lhs_data);
+    ruy::MakeSimpleLayout(2, 2, ruy::Order::kColMajor, rhs.mutable_layout());
+    rhs.set_data(rhs_data);
+    ruy::MakeSimpleLayout(2, 2, ruy::Order::kColMajor, dst.mutable_layout());
+    dst.set_data(dst_data);
+    ruy::MulParams<double, float> mul_params;
+    mul_params.set_bias(bias_data);
+    mul_params.set_clamp_max(20);
+    ruy::Mul(lhs, rhs, mul_params, &context, &dst);
+    Print("double_lhs_float_rhs", dst_data, 4);
   }
   {
     const std::uint8_t lhs_data[] = {124, 125, 126, 127}, rhs_data[] = {129, 130, 131, 132};

@@ -37,6 +37,10 @@ def golden_cases():
     out.append(cases.random_case(64, 3, 65, "int8", "int8", "int8", seed=9))           # shallow
     out.append(cases.random_case(37, 43, 1, "uint8", "uint8", "uint8", seed=10))       # matrix * vector
     out.append(cases.random_case(40, 40, 40, "float32", "float32", "float32", orders="CRR", extra_stride=1, seed=11))
+    # ruy's two mixed floating-point cases, double accumulator (ruy/BUILD:1195-1207)
+    out.append(cases.random_case(33, 70, 17, "float64", "float32", "float32", orders="RCC", extra_stride=1, seed=12))
+    out.append(cases.random_case(29, 65, 40, "float32", "float64", "float64", orders="CRR", seed=13,
+                                 channel=ChannelDimension.kCol))
     names = [c.name for c in out]
     assert len(set(names)) == len(names), "golden case names must be unique"
     return out

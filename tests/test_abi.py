@@ -62,7 +62,7 @@ def _mk(rows=4, depth=5, cols=3, lhs="int8", rhs="int8", dst="int8"):
 
 
 def test_validate_accepts_ruys_type_matrix():
-    combos = [("float32",) * 3, ("uint8", "uint8", "uint8"), ("int8", "int8", "int8"), ("int8", "int8", "uint8"),
+    combos = [("float32",) * 3, ("float64", "float32", "float32"), ("float32", "float64", "float64"), ("uint8", "uint8", "uint8"), ("int8", "int8", "int8"), ("int8", "int8", "uint8"),
               ("int8", "uint8", "int8"), ("uint8", "uint8", "int16"), ("int8", "int8", "int32"), ("int8", "uint8", "int32"),
               ("int8", "int16", "int16"), ("int16", "int8", "int16")]
     for l, r, d in combos:
@@ -75,6 +75,13 @@ def test_validate_zero_point_rules():
     lhs, rhs, p, dst, keep = _mk(lhs="float32", rhs="float32", dst="float32")
     lhs.zero_point = 1
     assert ruy_b200.validate(lhs, rhs, p, dst) == _abi.ERR_INVALID
+    lhs, rhs, p, dst, keep = _mk(lhs="float64", rhs="float32", dst="float32")
+    assert p.accum == "float64"
+    rhs.zero_point = 1
+    assert ruy_b200.validate(lhs, rhs, p, dst) == _abi.ERR_INVALID
+    lhs, rhs, p, dst, keep = _mk(lhs="float64", rhs="float32", dst="float32")
+    p.accum = "int32"       # a double operand with an integer accumulator is outside ruy's type space
+    assert ruy_b200.validate(lhs, rhs, p, dst) == _abi.ERR_UNSUPPORTED
     # ruy/validate.h:47-57: 16-bit inputs need every zero point to be 0
     lhs, rhs, p, dst, keep = _mk(lhs="int8", rhs="int16", dst="int16")
     dst.zero_point = 3

@@ -42,6 +42,8 @@ def _expected():
         "float": cases.MulCase("f", f, rm, 0, f.copy(), cm, 0, "float32", cm),
         "float_bias_clamp": cases.MulCase("fb", f, rm, 0, f.copy(), cm, 0, "float32", cm, 0, np.array([1, 0], np.float32),
                                           clamp=(0.0, 15.0)),
+        "double_lhs_float_rhs": cases.MulCase("d", np.array([1.5, 2, 3, 4], np.float64), rm, 0, np.array([1, 2, 3, 4.25], np.float32),
+                                              cm, 0, "float32", cm, 0, np.array([0.5, -1], np.float64), clamp=(-np.inf, 20.0)),
         "uint8_asymmetric": cases.MulCase("u8", np.array([124, 125, 126, 127], np.uint8), rm, 125,
                                           np.array([129, 130, 131, 132], np.uint8), cm, 132, "uint8", cm, 129, None, 1 << 30, 0),
         "int8_perchannel": cases.MulCase("pc", i8, rm, 0, i8.copy(), cm, 0, "int8", cm, 0, None, mfp, mexp),

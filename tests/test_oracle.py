@@ -11,7 +11,7 @@ import oracle
 import util
 from golden_cases import golden_cases, requant_extreme_cases
 from ruy_b200 import cases
-from ruy_b200.api import ChannelDimension, Rounding
+from ruy_b200.api import ChannelDimension, Order, Rounding
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 GOLDEN = os.path.join(HERE, "golden")
@@ -94,7 +94,13 @@ def test_oracle_matches_golden_reference_outputs(case):
     avx = g[case.name + "/avx512"]
     std = want if std.size == 0 else std
     avx = want if avx.size == 0 else avx
-    if case.accum == "float32":
+    if case.accum == "float64":
+        # double sums in depth order on both sides; only the contraction of a*b+c may differ between compilers
+        tol = 1e-6 if case.dst_dtype == "float32" else 1e-13
+        got = util.run_oracle(case).astype(np.float64)
+        for other in (want, std, avx):
+            assert np.all(np.abs(got - other) <= tol * np.maximum(np.abs(other), 1.0))
+    elif case.accum == "float32":
         wide = util.run_oracle(case, wide_float=True).astype(np.float64)
         got = util.run_oracle(case)
         assert np.array_equal(got, want)  # same summation order as ReferenceMul<float>
@@ -166,3 +172,40 @@ def test_sums_oracle():
             mat = logical.reshape(lay.rows, lay.stride)[:, :lay.cols]
         want = mat.astype(np.int64).sum(axis=1 if side == 0 else 0)
         assert np.array_equal(sums, want)
+
+
+def _f64_mix_cases():
+    # the two mixed floating-point cases ruy's own tests instantiate (ruy/BUILD:1195-1207)
+    out = []
+    for s, (r, d, c) in enumerate([(1, 1, 1), (7, 9, 5), (31, 32, 33), (64, 100, 48), (9, 300, 11)]):
+        for o, ords in enumerate(["RCC", "CRR", "CCC", "RRR"]):
+            for l, rr, dd in (("float64", "float32", "float32"), ("float32", "float64", "float64")):
+                out.append(cases.random_case(r, d, c, l, rr, dd, orders=ords, extra_stride=o % 2,
+                                             channel=ChannelDimension.kCol if o >= 2 else ChannelDimension.kRow,
+                                             seed=3000 + s * 4 + o))
+    return out
+
+
+@pytest.mark.parametrize("case", _f64_mix_cases(), ids=lambda c: c.name)
+def test_oracle_matches_compiled_reference_on_double_accumulation(case):
+    """(f64, f32, f64, f32) and (f32, f64, f64, f64): the restatement against ReferenceMul and kStandardCpp.  The sums are
+    double in depth order on both sides; the compiler may or may not contract a*b+c, hence a bound of a few ulps of the
+    destination type instead of equality."""
+    if oracle.reference() is None:
+        pytest.skip("compiled reference not built on this machine")
+    assert case.accum == "float64"
+    ref = util.run_reference(case, reference_mul=True).astype(np.float64)
+    got = util.run_oracle(case).astype(np.float64)
+    tol = 1e-6 if case.dst_dtype == "float32" else 1e-13
+    assert np.all(np.abs(got - ref) <= tol * np.maximum(np.abs(ref), 1.0))
+    std = util.run_reference(case, path=0x1).astype(np.float64)
+    assert np.all(np.abs(std - ref) <= tol * np.maximum(np.abs(ref), 1.0))
+    # and against numpy's own double product, bias and clamp
+    def logical(storage, lay):
+        if lay.order == Order.kColMajor:
+            return storage.reshape(lay.cols, lay.stride)[:, :lay.rows].T
+        return storage.reshape(lay.rows, lay.stride)[:, :lay.cols]
+    want = logical(case.lhs, case.lhs_layout).astype(np.float64) @ logical(case.rhs, case.rhs_layout).astype(np.float64)
+    want = want + (case.bias[:, None] if case.channel == ChannelDimension.kRow else case.bias[None, :])
+    want = np.clip(want, *case.clamp)
+    assert np.all(np.abs(want - ref) <= tol * np.maximum(np.abs(want), 1.0))
