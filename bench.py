@@ -240,8 +240,8 @@ def run_reference_arm(args):
 # GPU, from ncu captures of this benchmark; a capture cannot run inside a timed benchmark, so the figure is carried
 # here with the commit it was taken at.
 NCU_TRAFFIC = {
-    "c3_i8": {"bytes": 53.3e6, "source": "ncu launch list of `bench.py --steps 2 --warmup 1`, captured at commit e7487d4"},
-    "c2": {"bytes": 192.4e6, "source": "ncu capture of `bench.py --workload c2 --steps 2 --warmup 1`, captured at commit 68ef5d2"},
+    "c3_i8": {"bytes": 51.7e6, "source": "ncu launch list of `bench.py --steps 3 --warmup 3 --no-sustained --no-cpu-baseline`, captured at commit d076546"},
+    "c2": {"bytes": 193.3e6, "source": "ncu capture of `bench.py --workload c2 --steps 3 --warmup 3 --no-cpu-baseline`, captured at commit d076546"},
 }
 NOMINAL_INT8_TOPS = 4500.0   # B200 dense int8, vendor figure
 

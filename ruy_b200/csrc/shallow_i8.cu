@@ -34,8 +34,7 @@ constexpr int kStageBytes = kLines * 128;      // 16 KiB
 constexpr int kStages = 8;
 constexpr int kWeightBytes = 128 * 64;         // at most 128 weight rows x 64 bytes
 constexpr int kSmemBytes = kStages * kStageBytes + kWeightBytes + 1024;
-constexpr int kWarpsPerQuarter = 1;            // epilogue warps per lane quarter within a group (measured: 2 was slower, 67 vs 44 us on 64 x 32 x 802816)
-constexpr int kGroupWarps = 4 * kWarpsPerQuarter;
+constexpr int kGroupWarps = 4;                 // one epilogue warp per lane quarter within a group (measured: two were slower, 67 vs 44 us on 64 x 32 x 802816)
 constexpr int kEpilogueWarps = 2 * kGroupWarps;
 constexpr int kThreads = 64 + 32 * kEpilogueWarps;
 constexpr int kTmemCols = 512;                 // two buffers of 256 columns: F accumulators of N columns each
@@ -54,7 +53,6 @@ struct ShallowArgs {
   uint32_t idesc;
   uint32_t desc_hi_b;   // high word of the weights' shared-memory descriptor (32- or 64-byte swizzle)
   int m_signed;      // activations are int8 (else uint8)
-  int pack_clamps;
   uint32_t clamp_lo2, clamp_hi2;
   int* status;
 };
@@ -79,6 +77,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "r"(smem_u32(bar)), "r"(parity)
       : "memory");
   return ok != 0;
+}
+// The same probe with a suspend-time hint: the warp may stay parked for up to `ns` nanoseconds or until the phase
+// completes.  For the roles whose hand-offs are not on the critical path (copy and MMA issue run several tiles ahead
+// of the epilogue): a parked warp leaves the issue slots of its scheduler to the epilogue warps that share it.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_parked(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < kSpinLimit / 16; i++) {
+    if (mbar_try_wait_parked(bar, parity, 2000)) return true;
+    if (*abort_flag) return false;
+  }
+  return false;
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   for (uint32_t i = 0; i < kSpinLimit; i++) {
@@ -138,6 +157,17 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// The same wait, with the 32 registers of an earlier load as in/out operands: code that reads them cannot be moved
+// above the wait, which matters once a load stays in flight while other values are processed.
+__device__ __forceinline__ void tmem_ld_wait_for(uint32_t* r) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]),
+                 "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]),
+                 "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]),
+                 "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 // AND-reduction of `ok` over the threads of one epilogue group (named barrier 1 + group).
@@ -155,13 +185,13 @@ __device__ __forceinline__ bool group_all(bool ok, int group) {
 }
 
 // Narrows 32 int32 values to bytes (8 words); with `clamp`, two values at a time are saturated to 16 bits and clamped.
-__device__ __forceinline__ void narrow_u8x32(const int32_t* v, bool clamp, uint32_t lo2, uint32_t hi2, uint32_t* w) {
+__device__ __forceinline__ void narrow_u8x32(const uint32_t* v, bool clamp, uint32_t lo2, uint32_t hi2, uint32_t* w) {
   if (clamp) {
 #pragma unroll
     for (int q = 0; q < 8; q++) {
       uint32_t a, b;
-      asm("cvt.pack.sat.s16.s32 %0, %1, %2;" : "=r"(a) : "r"(v[4 * q + 1]), "r"(v[4 * q]));
-      asm("cvt.pack.sat.s16.s32 %0, %1, %2;" : "=r"(b) : "r"(v[4 * q + 3]), "r"(v[4 * q + 2]));
+      asm("cvt.pack.sat.s16.s32 %0, %1, %2;" : "=r"(a) : "r"((int32_t)v[4 * q + 1]), "r"((int32_t)v[4 * q]));
+      asm("cvt.pack.sat.s16.s32 %0, %1, %2;" : "=r"(b) : "r"((int32_t)v[4 * q + 3]), "r"((int32_t)v[4 * q + 2]));
       a = __vmaxs2(__vmins2(a, hi2), lo2);
       b = __vmaxs2(__vmins2(b, hi2), lo2);
       w[q] = __byte_perm(a, b, 0x6420);
@@ -169,13 +199,14 @@ __device__ __forceinline__ void narrow_u8x32(const int32_t* v, bool clamp, uint3
   } else {
 #pragma unroll
     for (int q = 0; q < 8; q++) {
-      w[q] = (uint32_t)(v[4 * q] & 0xff) | ((uint32_t)(v[4 * q + 1] & 0xff) << 8) | ((uint32_t)(v[4 * q + 2] & 0xff) << 16) |
-             ((uint32_t)(v[4 * q + 3] & 0xff) << 24);
+      w[q] = (v[4 * q] & 0xff) | ((v[4 * q + 1] & 0xff) << 8) | ((v[4 * q + 2] & 0xff) << 16) | ((v[4 * q + 3] & 0xff) << 24);
     }
   }
 }
 
-template <bool kX86>
+// kMulPerN: the multipliers vary along the accumulator columns (per-channel multipliers with the channels on n); a
+// variant of its own because its column terms need many more registers.
+template <bool kX86, bool kMulPerN>
 __global__ void __launch_bounds__(kThreads, 1)
 shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_constant__ CUtensorMap map_w, const ShallowArgs args) {
   extern __shared__ uint8_t smem_raw[];
@@ -253,7 +284,7 @@ shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_co
       uint32_t s = 0, ph = 0, issued = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        if (!mbar_wait(&empty_bar[s], ph ^ 1, abortp)) {
+        if (!mbar_wait_parked(&empty_bar[s], ph ^ 1, abortp)) {
           if (!*abortp) atomicCAS(args.status, 0, 1);
           *abortp = 1;
           ok = false;
@@ -285,7 +316,7 @@ shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_co
     const int ksteps = pitch / 32;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, tcount++) {
       const uint32_t buf = tcount & 1, aph = (tcount >> 1) & 1;
-      if (!mbar_wait(&acc_empty_bar[buf], aph ^ 1, abortp) || !mbar_wait(&full_bar[s], ph, abortp)) {
+      if (!mbar_wait_parked(&acc_empty_bar[buf], aph ^ 1, abortp) || !mbar_wait_parked(&full_bar[s], ph, abortp)) {
         if (!*abortp) atomicCAS(args.status, 0, 2);
         *abortp = 1;
         break;
@@ -307,16 +338,15 @@ shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_co
     }
   } else {
     // ---------------- epilogue: two groups take tiles in turn ----------------
-    // Within a group, kWarpsPerQuarter warps share each lane quarter and take the (row-of-line, 32-column chunk)
-    // pieces of the tile in turn.
     const int ew = warp - 2;
     const int group = ew / kGroupWarps;
     const int quarter = warp % 4;             // TMEM lane quarter this warp may read
-    const int half = (ew % kGroupWarps) / 4;  // which of the warps of this quarter in the group
     const int line_in_tile = quarter * 32 + lane;
     const int32_t cmin = ep.clamp_min, cmax = ep.clamp_max;
-    const bool late_clamp = args.pack_clamps != 0;
-    const bool mul_per_n = ch_n && (ep.mfp_pc != nullptr || ep.mexp_pc != nullptr);
+    // 8-bit destinations: the clamp bounds fit 16 bits, so the bounds are applied to two values at a time while narrowing
+    // (min with the upper bound first, then max with the lower one: the order of ruy/kernel.h:232-233)
+    constexpr bool late_clamp = true;
+    constexpr bool mul_per_n = kMulPerN;
     const bool zp_small = ep.dst_zp > -32768 && ep.dst_zp < 32768;
     const int chunks = (args.size_n + 31) / 32;
     uint32_t tcount = 0;
@@ -337,6 +367,18 @@ shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_co
       tc_fence_after();
       // the stage's bytes were written by the copy engine: observing its barrier orders them before these reads
       mbar_try_wait(&full_bar[s], sph);
+      // Two tensor-memory loads deep: the first one is in flight while the per-row terms are prepared, the load of the
+      // next piece while the current one is requantised and stored.
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256u;
+      const int n_pieces = fold * chunks;
+      uint32_t ra[32], rb[32];
+      int q_ld = 0, c_ld = 0;      // the piece the next load fetches
+      auto issue_load = [&](uint32_t* r) {
+        tmem_ld_32(taddr + (uint32_t)(q_ld * n_cols + c_ld), r);
+        c_ld += 32;
+        if (c_ld >= chunks * 32) { c_ld = 0; q_ld++; }
+      };
+      issue_load(ra);
       const long long line = (long long)tile * kLines + line_in_tile;
       const int m0 = (int)(line * fold);
       // Per-row terms of this thread's rows: the zero-point sum comes from the thread's own line in shared memory
@@ -387,10 +429,10 @@ shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_co
       const bool fast_m = __all_sync(0xffffffffu, fast_lane) != 0;
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty_bar[s]);       // the stage may be refilled
-      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256u;
-      for (int piece = half; piece < fold * chunks; piece += kWarpsPerQuarter) {
-        const int q = piece / chunks;
-        const int c = (piece - q * chunks) * 32;
+      // The pieces of the tile in order (row q of the line, 32 columns from c), results replacing the accumulators
+      // in the registers that held them.
+      int q = 0, c = 0;
+      auto process = [&](uint32_t* r) {
         const int m = m0 + q;
         const bool m_ok = m < args.size_m;
         int32_t addm = add_q[0], mulm = mul_q[0], expm = exp_q[0], rndm = rnd_q[0];
@@ -398,11 +440,7 @@ shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_co
         for (int t = 1; t < 4; t++) {
           if (q == t) { addm = add_q[t]; mulm = mul_q[t]; expm = exp_q[t]; rndm = rnd_q[t]; }
         }
-        uint32_t r[32];
-        tmem_ld_32(taddr + (uint32_t)(q * n_cols + c), r);
-        tmem_ld_wait();
         if (m_ok) {
-          int32_t v[32];
           if (!kX86 && (mul_per_n ? all_n_fast != 0 : fast_m)) {
             const int sh_hi = (31 - expm - 32) & 31;
 #pragma unroll
@@ -413,7 +451,7 @@ shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_co
                   const int4 nt = nt4[c + 4 * j4 + t];
                   const int32_t x = (int32_t)(r[4 * j4 + t] + (uint32_t)nt.x + (uint32_t)addm);
                   const int32_t y = (__mulhi(x, nt.y) + nt.z) >> nt.w;
-                  v[4 * j4 + t] = late_clamp ? y : max(min(y, cmax), cmin);
+                  r[4 * j4 + t] = (uint32_t)(late_clamp ? y : max(min(y, cmax), cmin));
                 }
               } else {
                 const int4 ad = *reinterpret_cast<const int4*>(&nt_add[c + 4 * j4]);
@@ -422,7 +460,7 @@ shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_co
                 for (int t = 0; t < 4; t++) {
                   const int32_t x = (int32_t)(r[4 * j4 + t] + (uint32_t)adds[t] + (uint32_t)addm);
                   const int32_t y = (__mulhi(x, mulm) + rndm) >> sh_hi;
-                  v[4 * j4 + t] = late_clamp ? y : max(min(y, cmax), cmin);
+                  r[4 * j4 + t] = (uint32_t)(late_clamp ? y : max(min(y, cmax), cmin));
                 }
               }
             }
@@ -435,23 +473,34 @@ shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_co
               const int e = mul_per_n ? -1 - nt.w : expm;     // nt.w holds 31 - e - 32
               x = kX86 ? requant_x86(x, mul, e) : requant_reference(x, mul, e);
               x = (int32_t)((uint32_t)x + (uint32_t)ep.dst_zp);
-              v[j] = late_clamp ? x : max(min(x, cmax), cmin);
+              r[j] = (uint32_t)(late_clamp ? x : max(min(x, cmax), cmin));
             }
           }
           uint8_t* out = (uint8_t*)args.dst.data + (int64_t)m * args.dst.stride_m + c;
           if (c + 32 <= args.size_n && (((uintptr_t)out) & 15) == 0) {
             uint32_t w[8];
-            narrow_u8x32(v, late_clamp, args.clamp_lo2, args.clamp_hi2, w);
+            narrow_u8x32(r, late_clamp, args.clamp_lo2, args.clamp_hi2, w);
             __stcs(reinterpret_cast<uint4*>(out), make_uint4(w[0], w[1], w[2], w[3]));
             __stcs(reinterpret_cast<uint4*>(out) + 1, make_uint4(w[4], w[5], w[6], w[7]));
           } else {
 #pragma unroll
             for (int j = 0; j < 32; j++) {
-              if (c + j < args.size_n) out[j] = (uint8_t)(late_clamp ? max(min(v[j], cmax), cmin) : v[j]);
+              if (c + j < args.size_n) out[j] = (uint8_t)(late_clamp ? max(min((int32_t)r[j], cmax), cmin) : (int32_t)r[j]);
             }
           }
         }
-        __syncwarp();   // the next tensor-memory load is a warp-wide instruction
+        c += 32;
+        if (c >= chunks * 32) { c = 0; q++; }
+        __syncwarp();   // the next tensor-memory instruction is warp-wide
+      };
+      for (int piece = 0; piece < n_pieces; piece += 2) {
+        tmem_ld_wait_for(ra);
+        if (piece + 1 < n_pieces) issue_load(rb);
+        process(ra);
+        if (piece + 1 >= n_pieces) break;
+        tmem_ld_wait_for(rb);
+        if (piece + 2 < n_pieces) issue_load(ra);
+        process(rb);
       }
       tc_fence_before();
       __syncwarp();
@@ -539,7 +588,6 @@ cudaError_t launch_shallow_i8(const TcI8Launch& L, cudaStream_t stream) {
   a.idesc = (2u << 4) | (fmt_m << 7) | (fmt_n << 10) | ((uint32_t)(a.n_cols >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
   // weights: rows of `pitch` bytes with the matching swizzle (mode 4: 64 bytes, 6: 32 bytes), 8-row groups 8 * pitch apart
   a.desc_hi_b = ((uint32_t)(8 * a.pitch) >> 4) | (1u << 14) | ((a.pitch == 64 ? 4u : 6u) << 29);
-  a.pack_clamps = L.ep.clamp_min >= -32768 && L.ep.clamp_max <= 32767 && L.ep.clamp_min <= L.ep.clamp_max;
   a.clamp_lo2 = ((uint32_t)L.ep.clamp_min & 0xffffu) * 0x10001u;
   a.clamp_hi2 = ((uint32_t)L.ep.clamp_max & 0xffffu) * 0x10001u;
   a.status = L.status;
@@ -550,17 +598,21 @@ cudaError_t launch_shallow_i8(const TcI8Launch& L, cudaStream_t stream) {
     return cudaErrorInvalidValue;
   }
   const bool x86 = L.ep.rounding_x86 != 0;
+  const bool mul_per_n = L.ep.channel_on_n != 0 && (L.ep.mfp_pc != nullptr || L.ep.mexp_pc != nullptr);
+  typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const ShallowArgs);
+  static const KernelFn kernels[2][2] = {{shallow_i8_kernel<false, false>, shallow_i8_kernel<false, true>},
+                                         {shallow_i8_kernel<true, false>, shallow_i8_kernel<true, true>}};
+  const KernelFn kernel = kernels[x86][mul_per_n];
   {
     static std::mutex mu;
-    static bool attr_set[kMaxDevices][2] = {};
+    static bool attr_set[kMaxDevices][2][2] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     std::lock_guard<std::mutex> lock(mu);
-    if (dev < 0 || dev >= kMaxDevices || !attr_set[dev][x86]) {
-      cudaError_t e = x86 ? cudaFuncSetAttribute(shallow_i8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes)
-                          : cudaFuncSetAttribute(shallow_i8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (dev < 0 || dev >= kMaxDevices || !attr_set[dev][x86][mul_per_n]) {
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
       if (e != cudaSuccess) return e;
-      if (dev >= 0 && dev < kMaxDevices) attr_set[dev][x86] = true;
+      if (dev >= 0 && dev < kMaxDevices) attr_set[dev][x86][mul_per_n] = true;
     }
   }
   const int grid = a.num_tiles < L.sm_count ? a.num_tiles : L.sm_count;
@@ -574,11 +626,7 @@ cudaError_t launch_shallow_i8(const TcI8Launch& L, cudaStream_t stream) {
     L.info->est_cycles = 0.0;
     L.info->shallow = a.fold;
   }
-  if (x86) {
-    shallow_i8_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(map_lines, map_w, a);
-  } else {
-    shallow_i8_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(map_lines, map_w, a);
-  }
+  kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_lines, map_w, a);
   return cudaGetLastError();
 }
 
