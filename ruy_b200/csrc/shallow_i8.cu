@@ -13,11 +13,14 @@
 //
 //   warp 0     : TMA producer: the weights once, then one 16 KB stage of activation lines per tile
 //   warp 1     : F x (depth / 32) tcgen05.mma kind::i8 per tile into F accumulators (M = 128 lines, N = weight rows)
-//   warps 2-9  : two epilogue groups of four warps that take tiles in turn.  The zero-point sums of the activation
-//                rows (ruy/pack.h:117-129) are taken from the stage in shared memory (each thread sums its own
-//                line), which is why the epilogue, not the MMA, releases the stage.
+//   warps 2-   : two epilogue groups of four or eight warps that take tiles in turn (one or two warps per tensor-memory
+//                lane quarter; two split the rows of a line).  The zero-point sums of the activation rows
+//                (ruy/pack.h:117-129) are taken from the stage in shared memory (each thread sums its own line),
+//                which is why the epilogue, not the MMA, releases the stage.
 //
-// No cluster multicast; all mbarrier waits are bounded as in the general kernel.
+// The kernel is bound by the epilogue's integer work, so the copy and MMA warps park in their waits (a suspend-time
+// hint) instead of probing: probing warps took a quarter of the issued instructions from the epilogue warps that share
+// their schedulers.  No cluster multicast; all mbarrier waits are bounded as in the general kernel.
 #include <cuda.h>
 
 #include <cstring>
@@ -34,9 +37,8 @@ constexpr int kStageBytes = kLines * 128;      // 16 KiB
 constexpr int kStages = 8;
 constexpr int kWeightBytes = 128 * 64;         // at most 128 weight rows x 64 bytes
 constexpr int kSmemBytes = kStages * kStageBytes + kWeightBytes + 1024;
-constexpr int kGroupWarps = 4;                 // one epilogue warp per lane quarter within a group (measured: two were slower, 67 vs 44 us on 64 x 32 x 802816)
-constexpr int kEpilogueWarps = 2 * kGroupWarps;
-constexpr int kThreads = 64 + 32 * kEpilogueWarps;
+// Threads of a CTA with kWpq epilogue warps per lane quarter in each of the two epilogue groups.
+constexpr int threads_for(int wpq) { return 64 + 2 * 4 * wpq * 32; }
 constexpr int kTmemCols = 512;                 // two buffers of 256 columns: F accumulators of N columns each
 constexpr int kMaxN = 128;
 constexpr uint32_t kSpinLimit = 4u << 20;
@@ -170,20 +172,6 @@ __device__ __forceinline__ void tmem_ld_wait_for(uint32_t* r) {
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-// AND-reduction of `ok` over the threads of one epilogue group (named barrier 1 + group).
-__device__ __forceinline__ bool group_all(bool ok, int group) {
-  uint32_t res;
-  asm volatile(
-      "{\n\t.reg .pred p, q;\n\t"
-      "setp.ne.u32 q, %1, 0;\n\t"
-      "bar.red.and.pred p, %2, %3, q;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(res)
-      : "r"((uint32_t)ok), "r"(1 + group), "r"(32 * kGroupWarps)
-      : "memory");
-  return res != 0;
-}
-
 // Narrows 32 int32 values to bytes (8 words); with `clamp`, two values at a time are saturated to 16 bits and clamped.
 __device__ __forceinline__ void narrow_u8x32(const uint32_t* v, bool clamp, uint32_t lo2, uint32_t hi2, uint32_t* w) {
   if (clamp) {
@@ -206,8 +194,27 @@ __device__ __forceinline__ void narrow_u8x32(const uint32_t* v, bool clamp, uint
 
 // kMulPerN: the multipliers vary along the accumulator columns (per-channel multipliers with the channels on n); a
 // variant of its own because its column terms need many more registers.
-template <bool kX86, bool kMulPerN>
-__global__ void __launch_bounds__(kThreads, 1)
+// Narrows 32 int32 values to bytes with saturation to the destination type's range (two instructions per word).
+__device__ __forceinline__ void narrow_sat_x32(const uint32_t* v, bool to_unsigned, uint32_t* w) {
+#pragma unroll
+  for (int q = 0; q < 8; q++) {
+    uint32_t hi, d;
+    if (to_unsigned) {
+      asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"((int32_t)v[4 * q + 3]), "r"((int32_t)v[4 * q + 2]), "r"(0u));
+      asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"((int32_t)v[4 * q + 1]), "r"((int32_t)v[4 * q]), "r"(hi));
+    } else {
+      asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"((int32_t)v[4 * q + 3]), "r"((int32_t)v[4 * q + 2]), "r"(0u));
+      asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"((int32_t)v[4 * q + 1]), "r"((int32_t)v[4 * q]), "r"(hi));
+    }
+    w[q] = d;
+  }
+}
+
+// kWpq: epilogue warps per lane quarter within a group (1 or 2); two split the rows of a line between them.  Measured
+// on 64 x 32 x 802816 (four rows per line): 33.9 us with two, 37.1 us with one; on 128 x 64 x 200704 (two rows per
+// line, five tiles per CTA): 21.4 against 20.7 us.  The launcher takes two when a line holds four rows.
+template <bool kX86, bool kMulPerN, int kWpq>
+__global__ void __launch_bounds__(threads_for(kWpq), 1)
 shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_constant__ CUtensorMap map_w, const ShallowArgs args) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kStages];
@@ -223,6 +230,8 @@ shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_co
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
+  constexpr int kWarpsPerQuarter = kWpq;
+  constexpr int kGroupWarps = 4 * kWpq;
   const int warp = threadIdx.x / 32;
   const int lane = threadIdx.x % 32;
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -252,7 +261,7 @@ shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_co
   // the per-n terms are the same for every tile (there is one n tile): stage them once
   if (threadIdx.x == 0) all_n_fast = 1;
   __syncthreads();
-  for (int n = threadIdx.x; n < kMaxN; n += kThreads) {
+  for (int n = threadIdx.x; n < kMaxN; n += threads_for(kWpq)) {
     int32_t add = ep.zp_m * ep.zp_n * ep.depth, mul = ep.mfp, e = ep.mexp;
     if (n < args.size_n) {
       if (ep.zp_m) add -= ep.zp_m * ep.sums_n[n];
@@ -341,6 +350,7 @@ shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_co
     const int ew = warp - 2;
     const int group = ew / kGroupWarps;
     const int quarter = warp % 4;             // TMEM lane quarter this warp may read
+    const int half = (ew % kGroupWarps) / 4;  // which of the warps of this quarter in the group: it takes rows half, half + kWarpsPerQuarter, ...
     const int line_in_tile = quarter * 32 + lane;
     const int32_t cmin = ep.clamp_min, cmax = ep.clamp_max;
     // 8-bit destinations: the clamp bounds fit 16 bits, so the bounds are applied to two values at a time while narrowing
@@ -348,6 +358,9 @@ shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_co
     constexpr bool late_clamp = true;
     constexpr bool mul_per_n = kMulPerN;
     const bool zp_small = ep.dst_zp > -32768 && ep.dst_zp < 32768;
+    // clamp bounds equal to the destination type's range: the saturating narrowing alone applies them
+    const bool full_range = ep.dst_dtype == RUYB200_U8 ? (cmin == 0 && cmax == 255) : (cmin == -128 && cmax == 127);
+    const bool dst_unsigned = ep.dst_dtype == RUYB200_U8;
     const int chunks = (args.size_n + 31) / 32;
     uint32_t tcount = 0;
     bool ok = true;
@@ -362,23 +375,22 @@ shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_co
         }
         ok = false;
       }
-      ok = group_all(ok, group);     // collective continue/abort decision
       if (!ok) break;
       tc_fence_after();
       // the stage's bytes were written by the copy engine: observing its barrier orders them before these reads
       mbar_try_wait(&full_bar[s], sph);
-      // Two tensor-memory loads deep: the first one is in flight while the per-row terms are prepared, the load of the
-      // next piece while the current one is requantised and stored.
+      // (Keeping a second tensor-memory load in flight while a piece is processed was measured and dropped: 38.8 us
+      // against 37.1 us on 64 x 32 x 802816; the registers it takes are worth more as a second warp per quarter.)
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256u;
-      const int n_pieces = fold * chunks;
-      uint32_t ra[32], rb[32];
-      int q_ld = 0, c_ld = 0;      // the piece the next load fetches
+      const int n_pieces = ((fold - half + kWarpsPerQuarter - 1) / kWarpsPerQuarter) * chunks;   // this warp's rows of the line
+      uint32_t ra[32];
+      int q_ld = half, c_ld = 0;      // the piece the next load fetches
       auto issue_load = [&](uint32_t* r) {
         tmem_ld_32(taddr + (uint32_t)(q_ld * n_cols + c_ld), r);
         c_ld += 32;
-        if (c_ld >= chunks * 32) { c_ld = 0; q_ld++; }
+        if (c_ld >= chunks * 32) { c_ld = 0; q_ld += kWarpsPerQuarter; }
       };
-      issue_load(ra);
+
       const long long line = (long long)tile * kLines + line_in_tile;
       const int m0 = (int)(line * fold);
       // Per-row terms of this thread's rows: the zero-point sum comes from the thread's own line in shared memory
@@ -395,7 +407,7 @@ shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_co
           add_q[q] = 0;
           mul_q[q] = ep.mfp;
           exp_q[q] = ep.mexp;
-          if (q < fold) {
+          if (q < fold && (q % kWarpsPerQuarter) == half) {
             const int m = m0 + q;
             if (ep.zp_n) {
               int32_t sum = 0;
@@ -431,7 +443,7 @@ shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_co
       if (lane == 0) mbar_arrive(&empty_bar[s]);       // the stage may be refilled
       // The pieces of the tile in order (row q of the line, 32 columns from c), results replacing the accumulators
       // in the registers that held them.
-      int q = 0, c = 0;
+      int q = half, c = 0;
       auto process = [&](uint32_t* r) {
         const int m = m0 + q;
         const bool m_ok = m < args.size_m;
@@ -479,7 +491,8 @@ shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_co
           uint8_t* out = (uint8_t*)args.dst.data + (int64_t)m * args.dst.stride_m + c;
           if (c + 32 <= args.size_n && (((uintptr_t)out) & 15) == 0) {
             uint32_t w[8];
-            narrow_u8x32(r, late_clamp, args.clamp_lo2, args.clamp_hi2, w);
+            if (full_range) narrow_sat_x32(r, dst_unsigned, w);
+            else narrow_u8x32(r, late_clamp, args.clamp_lo2, args.clamp_hi2, w);
             __stcs(reinterpret_cast<uint4*>(out), make_uint4(w[0], w[1], w[2], w[3]));
             __stcs(reinterpret_cast<uint4*>(out) + 1, make_uint4(w[4], w[5], w[6], w[7]));
           } else {
@@ -490,17 +503,13 @@ shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_co
           }
         }
         c += 32;
-        if (c >= chunks * 32) { c = 0; q++; }
+        if (c >= chunks * 32) { c = 0; q += kWarpsPerQuarter; }
         __syncwarp();   // the next tensor-memory instruction is warp-wide
       };
-      for (int piece = 0; piece < n_pieces; piece += 2) {
+      for (int piece = 0; piece < n_pieces; piece++) {
+        issue_load(ra);
         tmem_ld_wait_for(ra);
-        if (piece + 1 < n_pieces) issue_load(rb);
         process(ra);
-        if (piece + 1 >= n_pieces) break;
-        tmem_ld_wait_for(rb);
-        if (piece + 2 < n_pieces) issue_load(ra);
-        process(rb);
       }
       tc_fence_before();
       __syncwarp();
@@ -599,20 +608,25 @@ cudaError_t launch_shallow_i8(const TcI8Launch& L, cudaStream_t stream) {
   }
   const bool x86 = L.ep.rounding_x86 != 0;
   const bool mul_per_n = L.ep.channel_on_n != 0 && (L.ep.mfp_pc != nullptr || L.ep.mexp_pc != nullptr);
+  // two warps per lane quarter when a line holds four rows; the per-column-multiplier variant would spill at the 96
+  // registers that 18 warps leave per thread and stays with one
+  const int wpq = (a.fold >= 4 && !mul_per_n) ? 2 : 1;
   typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const ShallowArgs);
-  static const KernelFn kernels[2][2] = {{shallow_i8_kernel<false, false>, shallow_i8_kernel<false, true>},
-                                         {shallow_i8_kernel<true, false>, shallow_i8_kernel<true, true>}};
-  const KernelFn kernel = kernels[x86][mul_per_n];
+  static const KernelFn kernels[2][3] = {
+      {shallow_i8_kernel<false, false, 1>, shallow_i8_kernel<false, false, 2>, shallow_i8_kernel<false, true, 1>},
+      {shallow_i8_kernel<true, false, 1>, shallow_i8_kernel<true, false, 2>, shallow_i8_kernel<true, true, 1>}};
+  const int variant = mul_per_n ? 2 : wpq - 1;
+  const KernelFn kernel = kernels[x86][variant];
   {
     static std::mutex mu;
-    static bool attr_set[kMaxDevices][2][2] = {};
+    static bool attr_set[kMaxDevices][2][3] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     std::lock_guard<std::mutex> lock(mu);
-    if (dev < 0 || dev >= kMaxDevices || !attr_set[dev][x86][mul_per_n]) {
+    if (dev < 0 || dev >= kMaxDevices || !attr_set[dev][x86][variant]) {
       cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
       if (e != cudaSuccess) return e;
-      if (dev >= 0 && dev < kMaxDevices) attr_set[dev][x86][mul_per_n] = true;
+      if (dev >= 0 && dev < kMaxDevices) attr_set[dev][x86][variant] = true;
     }
   }
   const int grid = a.num_tiles < L.sm_count ? a.num_tiles : L.sm_count;
@@ -626,7 +640,7 @@ cudaError_t launch_shallow_i8(const TcI8Launch& L, cudaStream_t stream) {
     L.info->est_cycles = 0.0;
     L.info->shallow = a.fold;
   }
-  kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_lines, map_w, a);
+  kernel<<<grid, threads_for(wpq), kSmemBytes, stream>>>(map_lines, map_w, a);
   return cudaGetLastError();
 }
 
