@@ -462,42 +462,70 @@ def run_gpu_arm(args):
     stream = torch.cuda.Stream(device=dev)
     ctx = ruy_b200.Context(local, stream=stream.cuda_stream)
     mirrored = use_dist and args.gather == "mirror"
-    peer_bufs, flags = [], None
+    flags = None
+    gather_sets = {}     # how the shards reach every rank -> two gathered destination buffers, used by step parity
     if use_dist:
         from ruy_b200 import peer
     if mirrored:
-        # two gathered destinations, used by step parity: a rank that has left its exchange may start the next step
-        # while a slower peer still reads the previous one (see ruyb200_mul_async_mirrored_exchange)
-        peer_bufs = [peer.PeerBuffer(cols_total * case.rows * esz, dev) for _ in range(2)]
+        # Two gathered destinations per mode: a rank that has left its exchange may start the next step while a slower
+        # peer still reads the previous one (see ruyb200_mul_async_mirrored_exchange).  "multicast": an NVLink multicast
+        # mapping over every rank's buffer, a rank stores its shard once and the switch delivers it everywhere (not on
+        # platforms without such mappings, nor with RUYB200_BENCH_MULTICAST=0); "peer_stores": the epilogue stores to
+        # each peer's buffer.  Which of the two is faster depends on the number of ranks; a short trial below decides.
+        nbytes = cols_total * case.rows * esz
+        if esz == 1 and os.environ.get("RUYB200_BENCH_MULTICAST", "1") != "0":
+            bufs = None
+            try:
+                bufs = [peer.MulticastBuffer(nbytes, dev) for _ in range(2)]
+            except Exception as e:
+                if rank == 0:
+                    print(f"bench.py: no multicast mapping ({type(e).__name__}: {str(e)[:120]})", file=sys.stderr)
+            ok = torch.tensor([1 if bufs else 0], dtype=torch.int32, device=dev)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if int(ok[0]) == 1:
+                gather_sets["multicast"] = bufs
+            elif bufs:
+                for b in bufs:
+                    b.close()
+        if os.environ.get("RUYB200_BENCH_MULTICAST", "1") != "only" or not gather_sets:
+            gather_sets["peer_stores"] = [peer.PeerBuffer(nbytes, dev) for _ in range(2)]
         flags = peer.StepFlags(dev)
     shard_elems = shard * case.rows
     shard_bytes = shard_elems * esz
     # even / odd steps are told apart by the destination zero point (5 / 6): every unsaturated output differs by one
     tag = (lambda par: par) if dst_name == "int8" else (lambda par: 0)
     with torch.cuda.stream(stream):
-        fulls = ([b.tensor.view(tdtype) for b in peer_bufs] if mirrored
-                 else [torch.zeros(cols_total * case.rows, dtype=tdtype, device=dev)])
-        mines = [f[rank * shard_elems:(rank + 1) * shard_elems] for f in fulls]
-        lhs, rhs, p, d0, keep = case.bind(mines[0], device=dev, rounding=Rounding.kReference)
-        dsts = []
-        for par, m in enumerate(mines):
-            dd = ruy_b200.Matrix(m, case.dst_layout, case.dst_zp + tag(par))
-            dsts.append(dd)
+        G = {}     # the gather mode in use: its buffers and the views and addresses derived from them
+
+        def use_gather(name):
+            bufs = gather_sets.get(name, [])
+            G["name"], G["bufs"] = name, bufs
+            G["fulls"] = ([b.tensor.view(tdtype) for b in bufs] if mirrored
+                          else [torch.zeros(cols_total * case.rows, dtype=tdtype, device=dev)])
+            G["mines"] = [f[rank * shard_elems:(rank + 1) * shard_elems] for f in G["fulls"]]
+            G["dsts"] = [ruy_b200.Matrix(m, case.dst_layout, case.dst_zp + tag(par)) for par, m in enumerate(G["mines"])]
+            G["mirror_ptrs"] = [[q + rank * shard_bytes for r_, q in enumerate(b.ptrs) if r_ != rank] for b in bufs]
+
+        use_gather(next(iter(gather_sets)) if gather_sets else None)
+        lhs, rhs, p, d0, keep = case.bind(G["mines"][0], device=dev, rounding=Rounding.kReference)
         flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
-        ruy_b200.mul(lhs, rhs, p, ctx, dsts[0])  # packs the weights into the context's device cache
-        mirror_ptrs = [[q + rank * shard_bytes for r_, q in enumerate(b.ptrs) if r_ != rank] for b in peer_bufs]
+        ruy_b200.mul(lhs, rhs, p, ctx, G["dsts"][0])  # packs the weights into the context's device cache
         step_no = [0]
 
         def plain_step(gather):
-            ruy_b200.mul_async(lhs, rhs, p, ctx, dsts[0])
+            ruy_b200.mul_async(lhs, rhs, p, ctx, G["dsts"][0])
             if gather:
-                dist.all_gather_into_tensor(fulls[0], mines[0])
+                dist.all_gather_into_tensor(G["fulls"][0], G["mines"][0])
 
         def fused_step():
             step_no[0] += 1
             par = step_no[0] & 1
             # the epilogue stores each tile here and in every peer's buffer, and the launch ends with the flag exchange
-            peer.mul_async_mirrored(lhs, rhs, p, ctx, dsts[par], mirror_ptrs[par], flags=flags, value=step_no[0])
+            if G["name"] == "multicast":
+                peer.mul_async_multicast(lhs, rhs, p, ctx, G["dsts"][par], G["bufs"][par].multicast_ptr + rank * shard_bytes, flags,
+                                         step_no[0])
+            else:
+                peer.mul_async_mirrored(lhs, rhs, p, ctx, G["dsts"][par], G["mirror_ptrs"][par], flags=flags, value=step_no[0])
 
         def timed(fn, steps):
             """`steps` calls of fn, each between its own event pair after an untimed L2 flush; max over ranks of the mean ms."""
@@ -527,6 +555,13 @@ def run_gpu_arm(args):
             return ms
 
         main_step = fused_step if mirrored else (lambda: plain_step(use_dist))
+        gather_trial = {}
+        if len(gather_sets) > 1:
+            # five steps of each mode (the time is the max over ranks, so every rank takes the same decision)
+            for name in gather_sets:
+                use_gather(name)
+                gather_trial[name] = timed(fused_step, 5)
+            use_gather(min(gather_trial, key=gather_trial.get))
         sampler = ClockSampler(local)
         sampler.start()
         for _ in range(max(args.warmup, 3)):
@@ -552,7 +587,7 @@ def run_gpu_arm(args):
         def check_buffers(when):
             """Sampled sub-blocks of this rank's shard and of the next rank's shard as gathered here, in every
             destination buffer, against 64-bit numpy arithmetic."""
-            for par, f in enumerate(fulls):
+            for par, f in enumerate(G["fulls"]):
                 out = case.dst_view(f[rank * shard_elems:(rank + 1) * shard_elems].cpu().numpy())
                 if not np.array_equal(out[np.ix_(rs, cs)].astype(np.int64), expected(case, par)):
                     raise SystemExit(f"bench.py: GPU result does not match the reference arithmetic ({when}); refusing to report")
@@ -588,6 +623,10 @@ def run_gpu_arm(args):
             variants["gather_nccl_tops"] = total_ops / (nccl_ms * 1e-3) / 1e12
             variants["gather_fused_tops"] = value if mirrored else None
             variants["value_is"] = "gather_fused_tops" if mirrored else "gather_nccl_tops"
+            if mirrored:
+                variants["gather_mode"] = G["name"]
+                if gather_trial:
+                    variants["gather_trial_ms"] = gather_trial
             variants["note"] = ("strong scaling of one 4096x4096x8192 mul: every rank must receive (N-1)/N of the 33.6 MB "
                                 "destination, so the gather-inclusive step is bounded by NVLink ingress, not by the math")
 
@@ -684,8 +723,10 @@ def run_gpu_arm(args):
                    "dst": dst_name,
                    "sharding": f"{world} column shard(s) of {shard}" + (
                        (", dst gathered on every rank inside the step by " +
-                        ("epilogue stores into peers' memory over NVLink, flag exchange inside the same launch, two destination "
-                         "buffers used by step parity" if mirrored else "an NCCL all-gather"))
+                        (("one multimem store per piece into an NVLink multicast mapping of every rank's buffer" if G["name"] == "multicast"
+                          else "epilogue stores into each peer's memory over NVLink") +
+                         ", flag exchange inside the same launch, two destination buffers used by step parity"
+                         if mirrored else "an NCCL all-gather"))
                        if use_dist else ""),
                    "l2": f"flushed between steps ({L2_FLUSH_BYTES >> 20} MiB fill, untimed)"},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
@@ -704,10 +745,12 @@ def run_gpu_arm(args):
     ctx.sync()
     if mirrored:
         flags.close()
-        for b in peer_bufs:
-            b.close()
+        for bufs in gather_sets.values():
+            for b in bufs:
+                b.close()
     ctx.close()
-    del fulls, mines, flush
+    G.clear()
+    del flush
     torch.cuda.empty_cache()
     # the small-mul half of the metric, in the same process: 16384 small muls as one plan, sharded by mul index
     if not args.no_c2:

@@ -279,6 +279,17 @@ RUYB200_API int ruyb200_mul_async_mirrored(ruyb200_ctx* ctx, const ruyb200_mul_d
 RUYB200_API int ruyb200_mul_async_mirrored_exchange(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, void* const* mirror_dst,
                                                     int n_mirrors, uint32_t* const* remote_flags_device_array,
                                                     const uint32_t* local_flags, int n_flags, uint32_t value);
+/* The same step with the gather done by NVSwitch: `multicast_dst` is the address that corresponds to desc->dst.data in
+ * an NVLink multicast mapping bound to every rank's copy of the destination (this rank's included; created by the
+ * caller, e.g. with cuMulticastCreate / cuMulticastBindMem or a library that wraps them).  Every 16-byte piece of the
+ * destination is stored there once (multimem.st) and the switch writes it into all copies, so a rank sends its shard
+ * over NVLink once instead of once per peer.  8-bit destinations only; base addresses and stride multiples of 16 bytes,
+ * contiguous dimension a multiple of 16 elements (RUYB200_ERR_UNSUPPORTED otherwise).  The flag arguments and the
+ * two-buffer reuse rule are those of ruyb200_mul_async_mirrored_exchange.  Unbind and free the multicast mapping only
+ * after every rank has passed a barrier that follows its last use. */
+RUYB200_API int ruyb200_mul_async_multicast_exchange(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, void* multicast_dst,
+                                                     uint32_t* const* remote_flags_device_array, const uint32_t* local_flags,
+                                                     int n_flags, uint32_t value);
 RUYB200_API int ruyb200_peer_alloc(size_t bytes, void** out);
 RUYB200_API int ruyb200_peer_free(void* ptr);
 RUYB200_API int ruyb200_peer_export(void* ptr, unsigned char handle[64]);

@@ -128,6 +128,8 @@ PROTOTYPES = {
     "ruyb200_mul_async_mirrored": (C.c_int, [C.c_void_p, _P(MulDesc), _P(C.c_void_p), C.c_int]),
     "ruyb200_mul_async_mirrored_exchange": (C.c_int, [C.c_void_p, _P(MulDesc), _P(C.c_void_p), C.c_int, C.c_void_p, C.c_void_p,
                                                       C.c_int, C.c_uint32]),
+    "ruyb200_mul_async_multicast_exchange": (C.c_int, [C.c_void_p, _P(MulDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
+                                                       C.c_uint32]),
     "ruyb200_peer_alloc": (C.c_int, [C.c_size_t, _P(C.c_void_p)]),
     "ruyb200_peer_free": (C.c_int, [C.c_void_p]),
     "ruyb200_peer_export": (C.c_int, [C.c_void_p, C.c_char_p]),

@@ -715,6 +715,7 @@ struct Exchange {
   const uint32_t* local = nullptr;
   int n = 0;
   uint32_t value = 0;
+  void* multicast = nullptr;   // the destination's address in a multicast mapping over all ranks' copies, or null
 };
 
 int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, void* const* mirrors = nullptr,
@@ -753,7 +754,7 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
   // Narrow muls (at most kGemvMaxNarrow destination rows or columns) are a single pass over the wide operand
   // (ruy's single-column kernels, ruy/kernel_avx512.cc:628-870,1238-1320).  Both operands must be
   // depth-contiguous where the kernel will read them: as stored, or in their packed form when they are cached.
-  if ((kernel == RUYB200_KERNEL_TC_I8 || kernel == RUYB200_KERNEL_SGEMM) && !ctx->force_kernel && n_mirrors == 0 && depth > 0 &&
+  if ((kernel == RUYB200_KERNEL_TC_I8 || kernel == RUYB200_KERNEL_SGEMM) && !ctx->force_kernel && n_mirrors == 0 && !xchg && depth > 0 &&
       std::min(d.dst.rows, d.dst.cols) <= kGemvMaxNarrow) {
     const bool lhs_ok = side_view(d.lhs, 0, d.lhs.data).stride_k == 1 || should_cache(d.lhs, d.rhs.cols);
     const bool rhs_ok = side_view(d.rhs, 1, d.rhs.data).stride_k == 1 || should_cache(d.rhs, d.lhs.rows);
@@ -913,6 +914,7 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
     L.force_block_n = ctx->force_block_n;
     L.fuse_sums_m = true;
     L.n_mirrors = n_mirrors;
+    L.multicast = xchg ? xchg->multicast : nullptr;
     for (int i = 0; i < 7; i++) L.mirrors[i] = i < n_mirrors ? mirrors[i] : nullptr;
     if (xchg && xchg->n > 0) {
       L.xchg_remote = xchg->remote;
@@ -1262,6 +1264,28 @@ int ruyb200_mul_async_mirrored_exchange(ruyb200_ctx* ctx, const ruyb200_mul_desc
   x.n = n_flags;
   x.value = value;
   return run_mul(ctx, desc, false, mirror_dst, n_mirrors, &x);
+}
+
+int ruyb200_mul_async_multicast_exchange(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, void* multicast_dst,
+                                         uint32_t* const* remote_flags_device_array, const uint32_t* local_flags, int n_flags,
+                                         uint32_t value) {
+  if (!ctx) return fail(RUYB200_ERR_INVALID, "null context");
+  if (!multicast_dst) return fail(RUYB200_ERR_INVALID, "null multicast address");
+  if (!remote_flags_device_array || !local_flags || n_flags < 1 || n_flags > 32) return fail(RUYB200_ERR_INVALID, "bad flag arguments");
+  if (desc && desc->dst.dtype != RUYB200_I8 && desc->dst.dtype != RUYB200_U8)
+    return fail(RUYB200_ERR_UNSUPPORTED, "a multicast destination must be 8-bit");
+  if (desc) {
+    const int inner = desc->dst.order == RUYB200_COL_MAJOR ? desc->dst.rows : desc->dst.cols;
+    if ((((uintptr_t)desc->dst.data | (uintptr_t)multicast_dst) & 15) != 0 || (desc->dst.stride & 15) != 0 || (inner & 15) != 0)
+      return fail(RUYB200_ERR_UNSUPPORTED, "a multicast destination needs a 16-byte aligned base and stride and a contiguous dimension that is a multiple of 16");
+  }
+  Exchange x;
+  x.remote = remote_flags_device_array;
+  x.local = local_flags;
+  x.n = n_flags;
+  x.value = value;
+  x.multicast = multicast_dst;
+  return run_mul(ctx, desc, false, nullptr, 0, &x);
 }
 
 int ruyb200_pack(ruyb200_ctx* ctx, const ruyb200_matrix* src, int side, void* packed, size_t packed_capacity,

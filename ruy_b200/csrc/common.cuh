@@ -151,6 +151,11 @@ struct TcI8Launch {
   bool allow_pair;   // permit the two-CTA (cta_group::2) variant
   void* mirrors[7];  // addresses in peers' buffers that correspond to dst.data; every destination store is repeated there
   int n_mirrors;
+  // Address that corresponds to dst.data in an NVLink multicast mapping bound to every rank's copy of the destination
+  // (this rank's included): when set, each piece of the destination is stored there once (multimem.st; the switch
+  // delivers it to all copies) instead of to dst.data and the mirrors.  8-bit destinations with a 16-byte aligned base
+  // and stride and a contiguous dimension that is a multiple of 16 only.
+  void* multicast = nullptr;
   TcI8Info* info = nullptr;   // filled in when not null
   bool fuse_sums_m;  // if ep.zp_n != 0 and ep.sums_m == nullptr, let the kernel produce the m-side sums itself
   // Overrides of the tile-shape choice (tests and measurements): force_pair -1 = free, 0 = one-CTA tiles only,

@@ -561,7 +561,7 @@ bool is_8bit(uint8_t dtype) { return dtype == RUYB200_I8 || dtype == RUYB200_U8;
 bool shallow_i8_eligible(const TcI8Launch& L) {
   const int depth = L.depth;
   if (depth != 32 && depth != 64) return false;
-  if (L.n_mirrors > 0 || L.n_xchg > 0) return false;
+  if (L.n_mirrors > 0 || L.n_xchg > 0 || L.multicast != nullptr) return false;
   if (!is_8bit(L.m_side.dtype) || !is_8bit(L.n_side.dtype)) return false;
   if (L.ep.dst_dtype != RUYB200_I8 && L.ep.dst_dtype != RUYB200_U8) return false;
   // activation rows back to back, so that 128 bytes hold 128 / depth whole rows

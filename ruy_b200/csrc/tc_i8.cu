@@ -77,6 +77,7 @@ struct KernelArgs {
   int* status;
   void* mirror[7]; // peers' copies of the destination: same layout, every store is repeated there
   int n_mirror;
+  void* multicast; // not null: the destination's address in a multicast mapping over every rank's copy; stores go there only
   int row_pitch;   // bytes per tile row in shared memory = width of the swizzle pattern: 128, or 64 / 32 for depth <= 64 / 32
   uint32_t desc_hi; // high word of the shared-memory matrix descriptors for that pattern
   int pack_clamps; // 8-bit destination with a clamp range inside int16: values are clamped two at a time while being narrowed
@@ -97,6 +98,12 @@ struct KernelArgs {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
+}
+// A 16-byte store to a multicast address: NVSwitch writes it into the memory of every GPU bound to the mapping.
+__device__ __forceinline__ void multimem_st_16(void* p, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+               ::"l"(p), "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+               : "memory");
 }
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -830,7 +837,7 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
           }
         }
       };
-      if (kDstBytes == 1 && args.n_mirror > 0 && groups == 1) {
+      if (kDstBytes == 1 && (args.n_mirror > 0 || args.multicast != nullptr) && groups == 1) {
         // Mirrored 8-bit destination.  A thread owns 32 bytes of one destination column; written directly, a warp's
         // store would be 32 separate 32-byte pieces, which NVLink moves poorly.  So the tile is staged through
         // shared memory 128 columns at a time and written out with every warp instruction covering 128 contiguous
@@ -870,8 +877,12 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
               for (int it = 0; it < kBlockM / (4 * kEpilogueWarps); it++) {
                 if (mm < args.size_m) {
                   const uint4 val = *reinterpret_cast<const uint4*>(sp);
-                  *reinterpret_cast<uint4*>((uint8_t*)args.dst.data + off) = val;
-                  for (int t = 0; t < args.n_mirror; t++) *reinterpret_cast<uint4*>((uint8_t*)args.mirror[t] + off) = val;
+                  if (args.multicast) {
+                    multimem_st_16((uint8_t*)args.multicast + off, val);   // one store, delivered to every rank's copy
+                  } else {
+                    *reinterpret_cast<uint4*>((uint8_t*)args.dst.data + off) = val;
+                    for (int t = 0; t < args.n_mirror; t++) *reinterpret_cast<uint4*>((uint8_t*)args.mirror[t] + off) = val;
+                  }
                 }
                 mm += 4 * kEpilogueWarps;
                 off += (int64_t)(4 * kEpilogueWarps) * args.dst.stride_m;
@@ -1214,6 +1225,12 @@ bool tc_i8_eligible(const SideView& m_side, const SideView& n_side) {
 }
 
 cudaError_t launch_tc_i8(const TcI8Launch& L, cudaStream_t stream) {
+  if (L.multicast) {
+    const bool ok = (L.ep.dst_dtype == RUYB200_I8 || L.ep.dst_dtype == RUYB200_U8) && L.n_mirrors <= 0 &&
+                    ((((uintptr_t)L.dst.data | (uintptr_t)L.multicast | (uintptr_t)L.dst.stride_m) & 15) == 0) &&
+                    (L.dst.size_n & 15) == 0;
+    if (!ok) return cudaErrorInvalidValue;
+  }
   if (shallow_i8_eligible(L)) return launch_shallow_i8(L, stream);
   KernelArgs a;
   a.dst = L.dst;
@@ -1224,6 +1241,7 @@ cudaError_t launch_tc_i8(const TcI8Launch& L, cudaStream_t stream) {
   a.status = L.status;
   a.n_mirror = L.n_mirrors < 0 ? 0 : (L.n_mirrors > 7 ? 7 : L.n_mirrors);
   for (int i = 0; i < 7; i++) a.mirror[i] = i < a.n_mirror ? L.mirrors[i] : nullptr;
+  a.multicast = L.multicast;
   a.mirror_wide = (((uintptr_t)L.dst.data | (uintptr_t)L.dst.stride_m) & 15) == 0;
   for (int i = 0; i < a.n_mirror; i++) a.mirror_wide = a.mirror_wide && ((uintptr_t)L.mirrors[i] & 15) == 0;
   a.debug = 0;
@@ -1243,7 +1261,7 @@ cudaError_t launch_tc_i8(const TcI8Launch& L, cudaStream_t stream) {
   const bool fuse = L.fuse_sums_m && L.ep.zp_n != 0 && L.ep.sums_m == nullptr;
   const bool pair_possible = !fuse && L.allow_pair && a.size_m >= 256 && a.size_n >= 256 && L.sm_count >= 2;
   const int pairs_resident = pair_possible ? max_resident_pairs(L.sm_count) : 0;
-  a.epi_groups = (L.depth <= 512 && L.n_mirrors <= 0) ? 2 : 1;
+  a.epi_groups = (L.depth <= 512 && L.n_mirrors <= 0 && !L.multicast) ? 2 : 1;
   const TileShape shape = choose_tile_shape(a.size_m, a.size_n, L.depth, fuse, pair_possible, L.sm_count, pairs_resident,
                                             L.force_pair, L.force_block_n, a.epi_groups == 2);
   const bool pair = shape.pair;

@@ -52,6 +52,33 @@ class PeerBuffer:
             self.local_ptr = None
 
 
+class MulticastBuffer:
+    """The same-sized buffer on every rank plus an NVLink multicast mapping bound to all of them: one store to
+    `multicast_ptr + offset` lands at `offset` in every rank's buffer.  Allocation, handle exchange and binding are
+    torch's symmetric memory (plumbing); raises RuntimeError where the platform offers no multicast mapping, and the
+    caller falls back to PeerBuffer."""
+
+    def __init__(self, nbytes, device):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.rank, self.world = dist.get_rank(), dist.get_world_size()
+        self.nbytes = nbytes
+        self.tensor = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+        self.handle = symm_mem.rendezvous(self.tensor, dist.group.WORLD.group_name)
+        self.multicast_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+        if not self.multicast_ptr:
+            raise RuntimeError("no multicast mapping on this platform")
+        self.local_ptr = self.tensor.data_ptr()
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+
+    def close(self):
+        # the mapping must stay bound until every rank is done with it
+        torch.cuda.synchronize()
+        dist.barrier()
+        self.handle = None
+        self.tensor = None
+        dist.barrier()
+
+
 class StepFlags:
     """flags[r] on every rank is raised by rank r at the end of its step; a rank's step is over when all are up."""
 
@@ -81,3 +108,12 @@ def mul_async_mirrored(lhs, rhs, mul_params, context, dst, mirror_ptrs, flags=No
         _check(lib().ruyb200_mul_async_mirrored_exchange(context._h, C.byref(d), arr, len(mirror_ptrs),
                                                          C.c_void_p(flags.targets.data_ptr()), C.c_void_p(flags.buf.local_ptr),
                                                          flags.world, value), "ruyb200_mul_async_mirrored_exchange")
+
+
+def mul_async_multicast(lhs, rhs, mul_params, context, dst, multicast_ptr, flags, value):
+    """The mul whose epilogue stores every piece of the destination once, to `multicast_ptr` (the address of dst in a
+    MulticastBuffer's mapping), and whose launch ends with the step's flag exchange."""
+    d = make_desc(lhs, rhs, mul_params, dst)
+    _check(lib().ruyb200_mul_async_multicast_exchange(context._h, C.byref(d), C.c_void_p(multicast_ptr),
+                                                      C.c_void_p(flags.targets.data_ptr()), C.c_void_p(flags.buf.local_ptr),
+                                                      flags.world, value), "ruyb200_mul_async_multicast_exchange")
