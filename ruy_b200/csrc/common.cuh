@@ -162,7 +162,7 @@ struct TcI8Launch {
   // 1 = two-CTA tiles when possible; force_block_n 0 = free, else the widest n tile of at most that many columns.
   int force_pair = -1;
   int force_block_n = 0;
-  bool allow_shallow = true;   // permit the shallow-depth kernel (depth 32 or 64, contiguous activation rows)
+  bool allow_shallow = true;   // permit the shallow-depth kernel (depth 32, 64 or 128, contiguous activation rows)
   // Optional step-end flag exchange done by the launch itself (see ruyb200_mul_async_mirrored_exchange).
   uint32_t* const* xchg_remote = nullptr;
   const uint32_t* xchg_local = nullptr;

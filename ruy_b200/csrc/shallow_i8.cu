@@ -1,4 +1,4 @@
-// 8-bit muls with a very shallow depth (32 or 64) and a long activation side: the first pointwise-convolution
+// 8-bit muls with a very shallow depth (32, 64 or 128) and a long activation side: the first pointwise-convolution
 // layers of a mobile network, e.g. 64 x 32 x 802816.  Same arithmetic as the general tensor-core kernel
 // (ruy/kernel_avx512.cc:55-626, ruy/kernel.h:213-237); what differs is how the activations travel.
 //
@@ -23,6 +23,7 @@
 // their schedulers.  No cluster multicast; all mbarrier waits are bounded as in the general kernel.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -35,12 +36,12 @@ namespace {
 constexpr int kLines = 128;                    // 128-byte lines per tile = TMEM lanes
 constexpr int kStageBytes = kLines * 128;      // 16 KiB
 constexpr int kStages = 8;
-constexpr int kWeightBytes = 128 * 64;         // at most 128 weight rows x 64 bytes
+constexpr int kWeightBytes = 256 * 128;        // at most 256 weight rows x 128 bytes
 constexpr int kSmemBytes = kStages * kStageBytes + kWeightBytes + 1024;
 // Threads of a CTA with kWpq epilogue warps per lane quarter in each of the two epilogue groups.
 constexpr int threads_for(int wpq) { return 64 + 2 * 4 * wpq * 32; }
 constexpr int kTmemCols = 512;                 // two buffers of 256 columns: F accumulators of N columns each
-constexpr int kMaxN = 128;
+constexpr int kMaxN = 256;
 constexpr uint32_t kSpinLimit = 4u << 20;
 constexpr int kMaxDevices = 64;
 
@@ -48,12 +49,13 @@ struct ShallowArgs {
   DstView dst;
   Epilogue ep;
   int size_m, size_n;
-  int pitch;         // bytes per activation row = depth: 32 or 64
+  int pitch;         // bytes per activation row = depth: 32, 64 or 128
   int fold;          // rows per 128-byte line: 128 / pitch
   int n_cols;        // accumulator columns per sub-accumulator: size_n rounded up to 16
   int num_tiles;
   uint32_t idesc;
-  uint32_t desc_hi_b;   // high word of the weights' shared-memory descriptor (32- or 64-byte swizzle)
+  uint32_t desc_hi_b;   // high word of the weights' shared-memory descriptor (32-, 64- or 128-byte swizzle)
+  int split_cols;       // two warps per lane quarter: 1 = they take alternate 32-column chunks, 0 = alternate rows of the line
   int m_signed;      // activations are int8 (else uint8)
   uint32_t clamp_lo2, clamp_hi2;
   int* status;
@@ -362,6 +364,7 @@ shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_co
     const bool full_range = ep.dst_dtype == RUYB200_U8 ? (cmin == 0 && cmax == 255) : (cmin == -128 && cmax == 127);
     const bool dst_unsigned = ep.dst_dtype == RUYB200_U8;
     const int chunks = (args.size_n + 31) / 32;
+    const bool split_cols = kWpq > 1 && args.split_cols != 0;
     uint32_t tcount = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, tcount++) {
@@ -382,13 +385,16 @@ shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_co
       // (Keeping a second tensor-memory load in flight while a piece is processed was measured and dropped: 38.8 us
       // against 37.1 us on 64 x 32 x 802816; the registers it takes are worth more as a second warp per quarter.)
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256u;
-      const int n_pieces = ((fold - half + kWarpsPerQuarter - 1) / kWarpsPerQuarter) * chunks;   // this warp's rows of the line
+      // this warp's pieces: with two warps per quarter either alternate rows of the line or alternate column chunks
+      const int q_first = split_cols ? 0 : half, q_step = split_cols ? 1 : kWarpsPerQuarter;
+      const int c_first = split_cols ? 32 * half : 0, c_step = split_cols ? 32 * kWarpsPerQuarter : 32;
+      const int n_pieces = ((fold - q_first + q_step - 1) / q_step) * ((chunks * 32 - c_first + c_step - 1) / c_step);
       uint32_t ra[32];
-      int q_ld = half, c_ld = 0;      // the piece the next load fetches
+      int q_ld = q_first, c_ld = c_first;      // the piece the next load fetches
       auto issue_load = [&](uint32_t* r) {
         tmem_ld_32(taddr + (uint32_t)(q_ld * n_cols + c_ld), r);
-        c_ld += 32;
-        if (c_ld >= chunks * 32) { c_ld = 0; q_ld += kWarpsPerQuarter; }
+        c_ld += c_step;
+        if (c_ld >= chunks * 32) { c_ld = c_first; q_ld += q_step; }
       };
 
       const long long line = (long long)tile * kLines + line_in_tile;
@@ -407,7 +413,7 @@ shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_co
           add_q[q] = 0;
           mul_q[q] = ep.mfp;
           exp_q[q] = ep.mexp;
-          if (q < fold && (q % kWarpsPerQuarter) == half) {
+          if (q < fold && (split_cols || (q % kWarpsPerQuarter) == half)) {
             const int m = m0 + q;
             if (ep.zp_n) {
               int32_t sum = 0;
@@ -443,7 +449,7 @@ shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_co
       if (lane == 0) mbar_arrive(&empty_bar[s]);       // the stage may be refilled
       // The pieces of the tile in order (row q of the line, 32 columns from c), results replacing the accumulators
       // in the registers that held them.
-      int q = half, c = 0;
+      int q = q_first, c = c_first;
       auto process = [&](uint32_t* r) {
         const int m = m0 + q;
         const bool m_ok = m < args.size_m;
@@ -502,8 +508,8 @@ shallow_i8_kernel(const __grid_constant__ CUtensorMap map_lines, const __grid_co
             }
           }
         }
-        c += 32;
-        if (c >= chunks * 32) { c = 0; q += kWarpsPerQuarter; }
+        c += c_step;
+        if (c >= chunks * 32) { c = c_first; q += q_step; }
         __syncwarp();   // the next tensor-memory instruction is warp-wide
       };
       for (int piece = 0; piece < n_pieces; piece++) {
@@ -560,7 +566,7 @@ bool is_8bit(uint8_t dtype) { return dtype == RUYB200_I8 || dtype == RUYB200_U8;
 
 bool shallow_i8_eligible(const TcI8Launch& L) {
   const int depth = L.depth;
-  if (depth != 32 && depth != 64) return false;
+  if (depth != 32 && depth != 64 && depth != 128) return false;
   if (L.n_mirrors > 0 || L.n_xchg > 0 || L.multicast != nullptr) return false;
   if (!is_8bit(L.m_side.dtype) || !is_8bit(L.n_side.dtype)) return false;
   if (L.ep.dst_dtype != RUYB200_I8 && L.ep.dst_dtype != RUYB200_U8) return false;
@@ -596,21 +602,31 @@ cudaError_t launch_shallow_i8(const TcI8Launch& L, cudaStream_t stream) {
   // int32 accumulate, operand signedness, both operands depth-major, N / 8 at bit 17, M / 16 at bit 24
   a.idesc = (2u << 4) | (fmt_m << 7) | (fmt_n << 10) | ((uint32_t)(a.n_cols >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
   // weights: rows of `pitch` bytes with the matching swizzle (mode 4: 64 bytes, 6: 32 bytes), 8-row groups 8 * pitch apart
-  a.desc_hi_b = ((uint32_t)(8 * a.pitch) >> 4) | (1u << 14) | ((a.pitch == 64 ? 4u : 6u) << 29);
+  a.desc_hi_b = ((uint32_t)(8 * a.pitch) >> 4) | (1u << 14) | ((a.pitch == 128 ? 2u : (a.pitch == 64 ? 4u : 6u)) << 29);
   a.clamp_lo2 = ((uint32_t)L.ep.clamp_min & 0xffffu) * 0x10001u;
   a.clamp_hi2 = ((uint32_t)L.ep.clamp_max & 0xffffu) * 0x10001u;
   a.status = L.status;
   CUtensorMap map_lines, map_w;
   if (!make_map(&map_lines, L.m_side.data, 128, (uint64_t)lines, 128, 128, kLines, CU_TENSOR_MAP_SWIZZLE_128B) ||
       !make_map(&map_w, L.n_side.data, (uint64_t)L.depth, (uint64_t)a.size_n, (uint64_t)L.n_side.stride_w, (uint32_t)a.pitch,
-                (uint32_t)a.n_cols, a.pitch == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B)) {
+                (uint32_t)a.n_cols,
+                a.pitch == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (a.pitch == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B))) {
     return cudaErrorInvalidValue;
   }
   const bool x86 = L.ep.rounding_x86 != 0;
   const bool mul_per_n = L.ep.channel_on_n != 0 && (L.ep.mfp_pc != nullptr || L.ep.mexp_pc != nullptr);
   // two warps per lane quarter when a line holds four rows; the per-column-multiplier variant would spill at the 96
   // registers that 18 warps leave per thread and stays with one
-  const int wpq = (a.fold >= 4 && !mul_per_n) ? 2 : 1;
+  const int chunks = (a.size_n + 31) / 32;
+  int wpq = (a.fold >= 4 && !mul_per_n) ? 2 : 1;
+  a.split_cols = 0;
+  if (a.fold == 1 && !mul_per_n && chunks >= 4 && chunks % 2 == 0) {   // one row per line: the two warps share its columns
+    wpq = 2;
+    a.split_cols = 1;
+  }
+  if (const char* env = getenv("RUYB200_SHALLOW_WPQ")) {               // measurement knob: 1 = one warp per quarter always
+    if (atoi(env) == 1) { wpq = 1; a.split_cols = 0; }
+  }
   typedef void (*KernelFn)(const CUtensorMap, const CUtensorMap, const ShallowArgs);
   static const KernelFn kernels[2][3] = {
       {shallow_i8_kernel<false, false, 1>, shallow_i8_kernel<false, false, 2>, shallow_i8_kernel<false, true, 1>},

@@ -163,12 +163,15 @@ SHALLOW = [  # (rows, depth, cols, lhs, rhs, dst, per-channel, channel dimension
     (40, 32, 160000, "int8", "uint8", "int8", True, "row"),                 # n not a multiple of 16, per-row multipliers
     (128, 64, 75776 + 2 * 51, "int8", "uint8", "int8", True, "col"),        # depth 64, per-column (activation side) channels
     (100, 64, 80000, "int8", "int8", "int8", False, "row"),
+    (256, 128, 37888 + 77, "uint8", "uint8", "uint8", False, "row"),        # depth 128: one row per line, 256 columns shared by two warps per quarter
+    (200, 128, 40000, "int8", "uint8", "int8", True, "row"),                # an odd number of 32-column chunks, per-row multipliers
+    (96, 128, 38000, "int8", "int8", "int8", True, "col"),
 ]
 
 
 @pytest.mark.parametrize("spec", SHALLOW, ids=lambda s: "x".join(map(str, s[:3])) + "_" + s[7])
 def test_shallow_depth_kernel(spec, capfd):
-    """Depth 32 / 64 with contiguous activation rows takes the kernel that fetches 128-byte lines of several rows;
+    """Depth 32 / 64 / 128 with contiguous activation rows takes the kernel that fetches 128-byte lines of whole rows;
     the same cases on the general kernel (RUYB200_NO_SHALLOW=1) must give the same bits."""
     from ruy_b200.api import ChannelDimension
     rows, depth, cols, lt, rt, dt, pc, ch = spec
