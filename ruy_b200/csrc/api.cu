@@ -189,6 +189,11 @@ struct ruyb200_ctx {
   int advisory = RUYB200_ADVISORY_NONE;
   Arena arena;
   std::map<CacheKey, CacheEntry> cache;
+  // Tensor maps for the copy-engine stores of mirrored destinations, in device memory, by (destination and mirror
+  // addresses, shape, stride): a step loop passes the same few buffers again and again.  RUYB200_NO_STORE_MAPS=1
+  // keeps the mirrored epilogue on store instructions.
+  std::map<std::vector<uint64_t>, void*> store_maps;
+  bool no_store_maps = false;
   std::vector<CacheSlab> cache_slabs;
   int cache_open_slab = -1;   // the block new small entries are carved from
   size_t cache_bytes = 0;
@@ -709,6 +714,42 @@ int run_chunks(ruyb200_ctx* ctx, const ruyb200_mul_desc& d, const TcI8Launch& L,
   return RUYB200_OK;
 }
 
+// The device array of tensor maps (destination first, then the mirrors) that lets the copy engine write a mirrored
+// 8-bit destination; made on first use of a set of buffers (one synchronous 1 KB copy), null when a base or the stride
+// is not 16-byte aligned.
+const void* mirrored_store_maps(ruyb200_ctx* ctx, const DstView& dst, void* const* mirrors, int n_mirrors) {
+  std::vector<uint64_t> key;
+  key.push_back((uint64_t)(uintptr_t)dst.data);
+  for (int i = 0; i < n_mirrors; i++) key.push_back((uint64_t)(uintptr_t)mirrors[i]);
+  key.push_back((uint64_t)dst.size_m);
+  key.push_back((uint64_t)dst.size_n);
+  key.push_back((uint64_t)dst.stride_m);
+  auto it = ctx->store_maps.find(key);
+  if (it != ctx->store_maps.end()) return it->second;
+  alignas(64) unsigned char host[8 * kStoreMapBytes];
+  for (int i = 0; i <= n_mirrors; i++) {
+    void* base = i == 0 ? dst.data : mirrors[i - 1];
+    if (!make_i8_store_map(host + i * kStoreMapBytes, base, dst.size_n, dst.size_m, dst.stride_m)) return nullptr;
+  }
+  if (ctx->store_maps.size() >= 64) {   // a caller that keeps changing buffers: start over rather than grow
+    cudaStreamSynchronize(ctx->stream);
+    for (auto& kv : ctx->store_maps) cudaFree(kv.second);
+    ctx->store_maps.clear();
+  }
+  void* dev = nullptr;
+  if (cudaMalloc(&dev, 8 * kStoreMapBytes) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  if (cudaMemcpy(dev, host, (size_t)(n_mirrors + 1) * kStoreMapBytes, cudaMemcpyHostToDevice) != cudaSuccess) {
+    cudaGetLastError();
+    cudaFree(dev);
+    return nullptr;
+  }
+  ctx->store_maps.emplace(std::move(key), dev);
+  return dev;
+}
+
 // The flag exchange a mirrored mul can carry out at its end.
 struct Exchange {
   uint32_t* const* remote = nullptr;
@@ -916,6 +957,9 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
     L.n_mirrors = n_mirrors;
     L.multicast = xchg ? xchg->multicast : nullptr;
     for (int i = 0; i < 7; i++) L.mirrors[i] = i < n_mirrors ? mirrors[i] : nullptr;
+    if (n_mirrors > 0 && !L.multicast && !ctx->no_store_maps && dtype_size(d.dst.dtype) == 1) {
+      L.store_maps = mirrored_store_maps(ctx, r.dst, mirrors, n_mirrors);   // null: the epilogue uses store instructions
+    }
     if (xchg && xchg->n > 0) {
       L.xchg_remote = xchg->remote;
       L.xchg_local = xchg->local;
@@ -1116,6 +1160,8 @@ int ruyb200_ctx_create_on_stream(int device, void* cuda_stream, ruyb200_ctx** ou
   ctx->no_shallow = ns && *ns && *ns != '0';
   const char* nc = getenv("RUYB200_NO_CHUNKS");
   ctx->no_chunks = nc && *nc && *nc != '0';
+  const char* nsm = getenv("RUYB200_NO_STORE_MAPS");
+  ctx->no_store_maps = nsm && *nsm && *nsm != '0';
   const char* ck = getenv("RUYB200_CHUNKS");
   if (ck && atoi(ck) >= 2 && atoi(ck) <= kMaxChunks) ctx->chunk_target = atoi(ck);
   const char* tr = getenv("RUYB200_TRACE");
@@ -1137,6 +1183,7 @@ int ruyb200_ctx_destroy(ruyb200_ctx* ctx) {
   ctx->cache_slabs.clear();
   ctx->arena.release();
   if (ctx->bounce) cudaFreeHost(ctx->bounce);
+  for (auto& kv : ctx->store_maps) cudaFree(kv.second);
   if (ctx->d_status) cudaFree(ctx->d_status);
   if (ctx->h_status) cudaFreeHost(ctx->h_status);
   if (ctx->copy_in) cudaStreamDestroy(ctx->copy_in);

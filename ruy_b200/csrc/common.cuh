@@ -156,6 +156,9 @@ struct TcI8Launch {
   // delivers it to all copies) instead of to dst.data and the mirrors.  8-bit destinations with a 16-byte aligned base
   // and stride and a contiguous dimension that is a multiple of 16 only.
   void* multicast = nullptr;
+  // Device array of 1 + n_mirrors tensor maps made by make_i8_store_map over dst.data and the mirrors, or null: with
+  // them the copy engine writes each staged half tile to every copy (no store instruction crosses NVLink).
+  const void* store_maps = nullptr;
   TcI8Info* info = nullptr;   // filled in when not null
   bool fuse_sums_m;  // if ep.zp_n != 0 and ep.sums_m == nullptr, let the kernel produce the m-side sums itself
   // Overrides of the tile-shape choice (tests and measurements): force_pair -1 = free, 0 = one-CTA tiles only,
@@ -172,6 +175,11 @@ struct TcI8Launch {
   unsigned long long xchg_limit_ns = 0;
 };
 cudaError_t launch_tc_i8(const TcI8Launch& args, cudaStream_t stream);
+// Encodes (on the host, 128 bytes at map_out) the tensor map the mirrored epilogue's copy-engine stores use for an
+// 8-bit destination whose element (m, n) lives at base + m * stride_m + n.  False when base or stride_m is not a
+// multiple of 16 bytes.
+constexpr size_t kStoreMapBytes = 128;
+bool make_i8_store_map(void* map_out, void* base, int size_n, int size_m, int64_t stride_m);
 // True when the operands satisfy launch_tc_i8's requirements.
 bool tc_i8_eligible(const SideView& m_side, const SideView& n_side);
 // The shallow-depth variant (shallow_i8.cu); launch_tc_i8 hands eligible launches over to it.

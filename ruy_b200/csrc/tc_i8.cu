@@ -43,6 +43,8 @@ constexpr int kBBytes = kMaxBlockN * kBlockKBytes;     // 32 KiB
 constexpr int kStageBytes = kABytes + kBBytes;         // 48 KiB
 // staging area used when the destination is mirrored into peers' memory: 128 rows x 128 bytes, pitch 144
 constexpr int kMirrorPitch = 144;
+// ... or, when the copy engine writes the tile out (tensor-map stores), 128 rows x 128 bytes in the 128-byte swizzle
+// pattern (the same area: the kernel's static shared memory leaves no room for a second buffer)
 constexpr int kMirrorStagingBytes = 128 * kMirrorPitch;
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 + kMirrorStagingBytes;  // + alignment slack
 // two-CTA variant: each CTA stages 128 rows of each operand per stage
@@ -78,6 +80,9 @@ struct KernelArgs {
   void* mirror[7]; // peers' copies of the destination: same layout, every store is repeated there
   int n_mirror;
   void* multicast; // not null: the destination's address in a multicast mapping over every rank's copy; stores go there only
+  // not null: 1 + n_mirror tensor maps in device memory over the destination and its mirrors (uint8, 128 x 128 boxes,
+  // 128-byte swizzle): staged half tiles are written out by the copy engine instead of by store instructions
+  const CUtensorMap* store_maps;
   int row_pitch;   // bytes per tile row in shared memory = width of the swizzle pattern: 128, or 64 / 32 for depth <= 64 / 32
   uint32_t desc_hi; // high word of the shared-memory matrix descriptors for that pattern
   int pack_clamps; // 8-bit destination with a clamp range inside int16: values are clamped two at a time while being narrowed
@@ -99,6 +104,20 @@ struct KernelArgs {
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
 }
+// Tensor-map store of one staged 128 x 128-byte tile: shared memory -> global (this GPU's or a peer's), part of the
+// calling thread's current bulk group.  Rows and columns outside the tensor are not written.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+               ::"l"(map), "r"(x), "r"(y), "r"(smem_u32(smem_src))
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// until none of this thread's bulk groups is still reading its shared-memory source
+__device__ __forceinline__ void bulk_wait_read_0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// until all of this thread's bulk groups have completed their writes
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
 // A 16-byte store to a multicast address: NVSwitch writes it into the memory of every GPU bound to the mapping.
 __device__ __forceinline__ void multimem_st_16(void* p, uint4 v) {
   asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
@@ -842,12 +861,61 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
         // store would be 32 separate 32-byte pieces, which NVLink moves poorly.  So the tile is staged through
         // shared memory 128 columns at a time and written out with every warp instruction covering 128 contiguous
         // bytes, locally and to every peer.
-        uint8_t* stg = smem + kNumStages * kStageSize;
+        uint8_t* const stg0 = smem + kNumStages * kStageSize;
         const int ml = lane_group * 32 + lane;
         const int halves = (args.block_n + 127) / 128;
+        const bool issuer = ew == 0 && lane == 0;            // the thread that owns this CTA's bulk groups
         for (int h = 0; h < halves; h++) {
           const int nh0 = tn * args.block_n + h * 128;       // first destination index of this half
           if (nh0 >= n_end) break;                           // uniform over the CTA
+          // The copy engine writes the half out when it is a whole 128-byte box, or ends where the tensor ends on a
+          // 16-byte boundary (rows and 16-byte pieces outside the tensor are not written; a tensor that ends inside a
+          // piece gets the whole piece, measured, so such an edge is left to the store instructions below, like
+          // any other width).
+          const bool by_tma = args.store_maps != nullptr &&
+                              (n_end - nh0 >= 128 || (n_end == args.size_n && (args.size_n & 15) == 0));
+          if (by_tma) {
+            // values first, so that this half's arithmetic overlaps the copy engine's reads of the previous one
+            uint32_t w[2][8];
+            bool have[2];
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+              const int c = h * 128 + j * 64 + c_first;
+              have[j] = !(c >= args.block_n || tn * args.block_n + c >= args.size_n);   // uniform across the warp
+              if (!have[j]) continue;
+              if (c != c_first) {
+                tmem_ld_32(taddr + c, r);
+                tmem_ld_wait();
+              }
+              int32_t v[32];
+              finish_chunk(c, v);
+              narrow_u8x32(v, late_clamp, args.clamp_lo2, args.clamp_hi2, w[j]);
+            }
+            if (issuer) bulk_wait_read_0();                  // the stores that last read the staging area are done with it
+            epilogue_all(true, group, group_threads);
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+              if (!have[j]) continue;
+              // row ml of the box; its 16-byte piece p sits at p ^ (ml & 7)
+              const int p0 = (j * 64 + c_first) >> 4;
+              uint8_t* row = stg0 + ml * 128;
+              *reinterpret_cast<uint4*>(row + (((p0) ^ (ml & 7)) << 4)) = make_uint4(w[j][0], w[j][1], w[j][2], w[j][3]);
+              *reinterpret_cast<uint4*>(row + (((p0 + 1) ^ (ml & 7)) << 4)) = make_uint4(w[j][4], w[j][5], w[j][6], w[j][7]);
+            }
+            fence_proxy_async();                             // these writes, before the copy engine reads them
+            epilogue_all(true, group, group_threads);        // the half tile is staged
+            if (issuer) {
+              const int y = tm * kUnitM + (int)rank * kBlockM;
+              for (int t = 0; t <= args.n_mirror; t++) tma_store_2d(args.store_maps + t, stg0, nh0, y);
+              bulk_commit();
+            }
+            continue;
+          }
+          uint8_t* const stg = stg0;
+          if (args.store_maps != nullptr) {
+            if (issuer) bulk_wait_read_0();
+            epilogue_all(true, group, group_threads);
+          }
           for (int j = 0; j < 2; j++) {
             const int c = h * 128 + j * 64 + c_first;
             if (c >= args.block_n || tn * args.block_n + c >= args.size_n) continue;   // uniform across the warp
@@ -942,6 +1010,10 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
       printf("epilogue warp: staging %lld, waiting for a tile %lld, working %lld cycles over %u tiles\n", dbg_stage,
              dbg_wait, dbg_busy, tcount);
 #endif
+    if (args.store_maps != nullptr && ew == 0 && lane == 0) {
+      bulk_wait_all();          // the copy engine has written every tile of this CTA, here and in the peers' memory
+      fence_proxy_async();
+    }
     // this thread's stores into peers' memory are visible system-wide before the CTA counts itself as finished
     if (args.n_xchg > 0) __threadfence_system();
   }
@@ -1031,6 +1103,17 @@ bool make_map(CUtensorMap* map, const SideView& s, int depth, int box_rows, int 
 }
 
 }  // namespace
+
+bool make_i8_store_map(void* map_out, void* base, int size_n, int size_m, int64_t stride_m) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn || ((uintptr_t)base & 15) != 0 || (stride_m & 15) != 0 || size_n <= 0 || size_m <= 0) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)size_n, (cuuint64_t)size_m};
+  cuuint64_t strides[1] = {(cuuint64_t)stride_m};
+  cuuint32_t box[2] = {128, 128};
+  cuuint32_t estr[2] = {1, 1};
+  return fn((CUtensorMap*)map_out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
 
 bool make_i8_tile_map(CUtensorMap* map, const void* base, int depth, int width, int64_t stride_w, int box_rows) {
   SideView s;
@@ -1242,6 +1325,9 @@ cudaError_t launch_tc_i8(const TcI8Launch& L, cudaStream_t stream) {
   a.n_mirror = L.n_mirrors < 0 ? 0 : (L.n_mirrors > 7 ? 7 : L.n_mirrors);
   for (int i = 0; i < 7; i++) a.mirror[i] = i < a.n_mirror ? L.mirrors[i] : nullptr;
   a.multicast = L.multicast;
+  a.store_maps = (L.store_maps != nullptr && a.n_mirror > 0 && L.multicast == nullptr && (L.ep.dst_dtype == RUYB200_I8 || L.ep.dst_dtype == RUYB200_U8))
+                     ? (const CUtensorMap*)L.store_maps
+                     : nullptr;
   a.mirror_wide = (((uintptr_t)L.dst.data | (uintptr_t)L.dst.stride_m) & 15) == 0;
   for (int i = 0; i < a.n_mirror; i++) a.mirror_wide = a.mirror_wide && ((uintptr_t)L.mirrors[i] & 15) == 0;
   a.debug = 0;

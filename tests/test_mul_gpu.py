@@ -528,7 +528,8 @@ def test_mirrored_destination_and_step_flags(gpu_ctx):
     from ruy_b200._lib import lib
     dev = torch.device("cuda", 0)
     # destination strides that are / are not multiples of 16 bytes, ragged ends in both dimensions
-    for shape, extra in (((300, 208, 700), 0), ((64, 96, 40), 0), ((512, 128, 520), 0), ((300, 60, 270), 4)):
+    for shape, extra in (((300, 208, 700), 0), ((64, 96, 40), 0), ((512, 128, 520), 0), ((300, 60, 270), 4), ((1024, 256, 600), 0),
+                         ((384, 4096, 512), 16)):
         c = cases.random_case(*shape, "uint8", "int8", "uint8", orders="RCC", perchannel=True, symmetric=False, seed=77,
                               extra_stride=extra)
         want = util.run_oracle(c, Rounding.kReference)
@@ -539,6 +540,24 @@ def test_mirrored_destination_and_step_flags(gpu_ctx):
         gpu_ctx.sync()
         for b in bufs:
             assert np.array_equal(c.dst_view(b.cpu().numpy()), want)
+            assert util.padding_untouched(c, b.cpu().numpy(), 9)
+        # the same with the mirrored epilogue kept on store instructions (no copy-engine stores)
+        os.environ["RUYB200_NO_STORE_MAPS"] = "1"
+        try:
+            plain = ruy_b200.Context(0)
+        finally:
+            del os.environ["RUYB200_NO_STORE_MAPS"]
+        try:
+            for b in bufs:
+                b.fill_(9)
+            torch.cuda.synchronize()
+            peer.mul_async_mirrored(lhs, rhs, p, plain, d, [bufs[1].data_ptr(), bufs[2].data_ptr()])
+            plain.sync()
+            for b in bufs:
+                assert np.array_equal(c.dst_view(b.cpu().numpy()), want)
+                assert util.padding_untouched(c, b.cpu().numpy(), 9)
+        finally:
+            plain.close()
     flag_words = torch.zeros(8, dtype=torch.int32, device=dev)
     targets = torch.tensor([flag_words.data_ptr(), flag_words.data_ptr() + 4], dtype=torch.int64, device=dev)
     torch.cuda.synchronize()
