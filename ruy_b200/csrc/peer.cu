@@ -20,8 +20,8 @@ namespace {
 __global__ void signal_kernel(uint32_t* const* remote_flags, int n, uint32_t value) {
   const int i = threadIdx.x;
   if (i < n && remote_flags[i]) {
-    __threadfence_system();
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote_flags[i]), "r"(value) : "memory");
+    __threadfence_system();   // one system-scope fence, then a relaxed store: a release store would fence again
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(remote_flags[i]), "r"(value) : "memory");
   }
 }
 
@@ -33,8 +33,11 @@ __global__ void wait_kernel(const uint32_t* local_flags, int n, uint32_t value, 
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
   for (;;) {
     uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(local_flags + i) : "memory");
-    if ((int32_t)(v - value) >= 0) return;
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(local_flags + i) : "memory");
+    if ((int32_t)(v - value) >= 0) {
+      __threadfence_system();   // acquire side, once: relaxed polls are cheap, acquire loads are not
+      return;
+    }
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     if (t - t0 > limit_ns) {
@@ -53,14 +56,17 @@ __global__ void exchange_kernel(uint32_t* const* remote_flags, const uint32_t* l
   if (i >= n) return;
   if (remote_flags[i]) {
     __threadfence_system();
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote_flags[i]), "r"(value) : "memory");
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(remote_flags[i]), "r"(value) : "memory");
   }
   unsigned long long t0;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
   for (unsigned it = 0;; it++) {
     uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(local_flags + i) : "memory");
-    if ((int32_t)(v - value) >= 0) return;
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(local_flags + i) : "memory");
+    if ((int32_t)(v - value) >= 0) {
+      __threadfence_system();
+      return;
+    }
     if ((it & 15) == 15) {
       unsigned long long t;
       asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
