@@ -199,3 +199,27 @@ def test_shallow_depth_kernel(spec, capfd):
     finally:
         plain.close()
     assert np.array_equal(got, want)
+
+
+def test_shallow_depth_kernel_clamp_forms(gpu_ctx):
+    """The shallow-depth kernel applies the clamp while narrowing: a clamp that is the whole range of the destination
+    type (saturating narrowing only), an ordinary one, and a degenerate one whose lower bound exceeds the upper
+    (ruy takes the minimum with the upper bound first, then the maximum with the lower: every output is the lower)."""
+    for dt, clamp in (("uint8", (0, 255)), ("int8", (-128, 127)), ("uint8", (17, 201)), ("int8", (50, 10))):
+        c = cases.random_case(48, 64, 75776, "int8" if dt == "int8" else "uint8", "uint8", dt, orders="RCC", symmetric=False, seed=9,
+                              lhs_cache=CachePolicy.kAlwaysCache)
+        c.clamp = clamp
+        check_against_reference(c, gpu_ctx, sample_seed=3)
+        got, _ = util.run_gpu(c, gpu_ctx, rounding=Rounding.kReference)
+        if clamp[0] > clamp[1]:
+            assert np.all(got == clamp[0])
+        else:
+            assert got.min() >= clamp[0] and got.max() <= clamp[1]
+
+
+def test_general_kernel_clamp_forms(gpu_ctx):
+    """The same three clamp forms on the general tensor-core kernel (depth 512 keeps it off the shallow-depth one)."""
+    for dt, clamp in (("uint8", (0, 255)), ("int8", (-128, 127)), ("uint8", (17, 201)), ("int8", (50, 10))):
+        c = cases.random_case(200, 512, 1000, "int8" if dt == "int8" else "uint8", "uint8", dt, orders="RCC", symmetric=False, seed=10)
+        c.clamp = clamp
+        check_against_reference(c, gpu_ctx, sample_seed=4)
