@@ -832,6 +832,10 @@ def run_small_arm(args):
     if args.workload in ("c4", "small"):
         for batch in (1, 64):
             todo.extend(cases.config4(layer, batch=batch) for layer in range(len(cases.CONFIG4_LAYERS)))
+    if args.only:
+        todo = [c for c in todo if args.only in c.name]
+        if not todo:
+            raise SystemExit(f"bench.py: --only {args.only!r} matches no case of workload {args.workload}")
     ref = oracle.reference()
     host = host_cpu()
     cores = host["logical_cpus"]
@@ -932,6 +936,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-c2", action="store_true", help="leave the small-mul sub-record out of the default line")
     ap.add_argument("--no-sustained", action="store_true", help="skip the one-second back-to-back measurement")
+    ap.add_argument("--only", default="", help="workloads c0/c1/c4/small: run only the cases whose name contains this text")
     ap.add_argument("--gather", default="mirror", choices=["mirror", "nccl"],
                     help="N>1: how the column-sharded destination is gathered (epilogue peer stores, or an NCCL all-gather)")
     ap.add_argument("--cols", type=int, default=8192,
