@@ -739,6 +739,9 @@ def run_gpu_arm(args):
         "roofline": roofline,
         "wall_s": wall,
     }
+    if use_dist:
+        line["e2e"]["note"] = (f"each of the {world} ranks moves its own column shard over its own PCIe link (bytes per step are "
+                               "one rank's); the destination stays in host memory as one slice per rank, it is not gathered")
     line.update(variants)
     if sustained:
         line["sustained"] = sustained
