@@ -510,6 +510,18 @@ def run_gpu_arm(args):
         lhs, rhs, p, d0, keep = case.bind(G["mines"][0], device=dev, rounding=Rounding.kReference)
         flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev)
         ruy_b200.mul(lhs, rhs, p, ctx, G["dsts"][0])  # packs the weights into the context's device cache
+        # With four or more ranks a shard is one or two rounds of 256 x 256 tiles, and a tile's stores can only start when
+        # its whole depth is done: a second context with 256 x 128 tiles (more rounds, stores start earlier, slower
+        # kernel) takes part in the trial below.
+        tile_ctxs = {"": ctx}
+        if mirrored and world >= 4 and not os.environ.get("RUYB200_TILE"):
+            os.environ["RUYB200_TILE"] = "pair:128"
+            try:
+                tile_ctxs["pair:128"] = ruy_b200.Context(local, stream=stream.cuda_stream)
+            finally:
+                del os.environ["RUYB200_TILE"]
+            ruy_b200.mul(lhs, rhs, p, tile_ctxs["pair:128"], G["dsts"][0])
+        G["ctx"], G["tile"] = ctx, ""
         step_no = [0]
 
         def plain_step(gather):
@@ -522,10 +534,10 @@ def run_gpu_arm(args):
             par = step_no[0] & 1
             # the epilogue stores each tile here and in every peer's buffer, and the launch ends with the flag exchange
             if G["name"] == "multicast":
-                peer.mul_async_multicast(lhs, rhs, p, ctx, G["dsts"][par], G["bufs"][par].multicast_ptr + rank * shard_bytes, flags,
-                                         step_no[0])
+                peer.mul_async_multicast(lhs, rhs, p, G["ctx"], G["dsts"][par], G["bufs"][par].multicast_ptr + rank * shard_bytes,
+                                         flags, step_no[0])
             else:
-                peer.mul_async_mirrored(lhs, rhs, p, ctx, G["dsts"][par], G["mirror_ptrs"][par], flags=flags, value=step_no[0])
+                peer.mul_async_mirrored(lhs, rhs, p, G["ctx"], G["dsts"][par], G["mirror_ptrs"][par], flags=flags, value=step_no[0])
 
         def timed(fn, steps):
             """`steps` calls of fn, each between its own event pair after an untimed L2 flush; max over ranks of the mean ms."""
@@ -556,12 +568,16 @@ def run_gpu_arm(args):
 
         main_step = fused_step if mirrored else (lambda: plain_step(use_dist))
         gather_trial = {}
-        if len(gather_sets) > 1:
-            # five steps of each mode (the time is the max over ranks, so every rank takes the same decision)
-            for name in gather_sets:
+        if len(gather_sets) * len(tile_ctxs) > 1:
+            # five steps of each mode and tile shape (the time is the max over ranks, so every rank takes the same decision)
+            combos = [(name, tile) for name in gather_sets for tile in tile_ctxs]
+            for name, tile in combos:
                 use_gather(name)
-                gather_trial[name] = timed(fused_step, 5)
-            use_gather(min(gather_trial, key=gather_trial.get))
+                G["ctx"], G["tile"] = tile_ctxs[tile], tile
+                gather_trial[name + (" " + tile if tile else "")] = timed(fused_step, 5)
+            best = min(range(len(combos)), key=lambda i: list(gather_trial.values())[i])
+            use_gather(combos[best][0])
+            G["ctx"], G["tile"] = tile_ctxs[combos[best][1]], combos[best][1]
         sampler = ClockSampler(local)
         sampler.start()
         for _ in range(max(args.warmup, 3)):
@@ -601,7 +617,7 @@ def run_gpu_arm(args):
             stream.synchronize()
         check_buffers("after warm-up")
 
-        launches0 = ctx.counters()["launches"]
+        launches0 = G["ctx"].counters()["launches"]
         if use_dist:
             dist.barrier()
         torch.cuda.synchronize()
@@ -611,7 +627,7 @@ def run_gpu_arm(args):
         wall = time.perf_counter() - wall0
         sampler.mark_end()
         clocks = sampler.stop()
-        launches = ctx.counters()["launches"] - launches0 - 3     # `timed` runs three untimed calls first
+        launches = G["ctx"].counters()["launches"] - launches0 - 3     # `timed` runs three untimed calls first
         check_buffers("after the timed steps")
         total_ops = 2.0 * case.rows * case.depth * cols_total
         value = total_ops / (ms_per_step * 1e-3) / 1e12
@@ -624,7 +640,7 @@ def run_gpu_arm(args):
             variants["gather_fused_tops"] = value if mirrored else None
             variants["value_is"] = "gather_fused_tops" if mirrored else "gather_nccl_tops"
             if mirrored:
-                variants["gather_mode"] = G["name"]
+                variants["gather_mode"] = G["name"] + (", tiles " + G["tile"] if G["tile"] else "")
                 if gather_trial:
                     variants["gather_trial_ms"] = gather_trial
             variants["note"] = ("strong scaling of one 4096x4096x8192 mul: every rank must receive (N-1)/N of the 33.6 MB "
@@ -751,6 +767,10 @@ def run_gpu_arm(args):
         for bufs in gather_sets.values():
             for b in bufs:
                 b.close()
+    for t, c in tile_ctxs.items():
+        if t:
+            c.sync()
+            c.close()
     ctx.close()
     G.clear()
     del flush
