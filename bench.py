@@ -589,8 +589,10 @@ def run_gpu_arm(args):
         cs = np.arange(0, shard, 211)
         Lrows = case.lhs.reshape(case.rows, case.depth).astype(np.int64)[rs]
 
-        def expected(c, par):
-            acc = Lrows @ c.rhs.reshape(shard, case.depth).astype(np.int64)[cs].T
+        def expected(c, par, ncols=None, cols_sel=None):
+            ncols = shard if ncols is None else ncols
+            cols_sel = cs if cols_sel is None else cols_sel
+            acc = Lrows @ c.rhs.reshape(ncols, case.depth).astype(np.int64)[cols_sel].T
             if dst_name == "int8":
                 acc = acc + case.bias.astype(np.int64)[rs][:, None]
                 m, e = case.mfp.astype(np.int64)[rs][:, None], case.mexp.astype(np.int64)[rs][:, None]
@@ -645,6 +647,22 @@ def run_gpu_arm(args):
                     variants["gather_trial_ms"] = gather_trial
             variants["note"] = ("strong scaling of one 4096x4096x8192 mul: every rank must receive (N-1)/N of the 33.6 MB "
                                 "destination, so the gather-inclusive step is bounded by NVLink ingress, not by the math")
+            # Weak scaling beside it: the benchmark's whole mul on every rank (its own 8192 activation columns of an
+            # 8192 x N column problem, same weights), destination left sharded, no exchange: the data-parallel reading.
+            wcase = cases.config3(dst=dst_name, col_begin=rank * cols_total, col_count=cols_total)
+            wdst = torch.zeros(wcase.dst_storage_elems(), dtype=tdtype, device=dev)
+            wl, wr, wp, wd, wkeep = wcase.bind(wdst, device=dev, rounding=Rounding.kReference)
+            ruy_b200.mul(wl, wr, wp, ctx, wd)
+            weak_ms = timed(lambda: ruy_b200.mul_async(wl, wr, wp, ctx, wd), args.steps)
+            wcs = np.arange(0, cols_total, 997)
+            wout = wcase.dst_view(wdst.cpu().numpy())[np.ix_(rs, wcs)].astype(np.int64)
+            if not np.array_equal(wout, expected(wcase, 0, cols_total, wcs)):
+                raise SystemExit("bench.py: weak-scaling result does not match the reference arithmetic; refusing to report")
+            variants["weak"] = {"cols_per_rank": cols_total, "ms_per_step": weak_ms,
+                                "tops": world * 2.0 * case.rows * case.depth * cols_total / (weak_ms * 1e-3) / 1e12,
+                                "note": "every rank multiplies the same weights by its own 8192 activation columns; "
+                                        "destination left sharded, no exchange"}
+            del wdst, wkeep
 
         # sustained: at least a second of back-to-back muls over four rotating activation / destination sets (268 MB, more
         # than L2), compared with the sustained (power-capped) peak
