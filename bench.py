@@ -602,17 +602,39 @@ def run_gpu_arm(args):
         nb = (rank + 1) % world
         nb_case = cases.config3(dst=dst_name, col_begin=nb * shard, col_count=shard) if use_dist else None
 
+        def leave_together(problem):
+            """A failed check ends the run on every rank at the same point and in order (buffers unbound after a barrier,
+            nobody left waiting in a collective): a rank must not disappear while its memory is part of a mapping that
+            its peers still store into."""
+            if use_dist:
+                t = torch.tensor([1 if problem else 0], dtype=torch.int32, device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                if int(t[0]) == 0:
+                    return
+                stream.synchronize()
+                if mirrored:
+                    flags.close()
+                    for bufs in gather_sets.values():
+                        for b in bufs:
+                            b.close()
+                dist.barrier()
+                raise SystemExit(problem or "bench.py: another rank found a wrong result; refusing to report")
+            if problem:
+                raise SystemExit(problem)
+
         def check_buffers(when):
             """Sampled sub-blocks of this rank's shard and of the next rank's shard as gathered here, in every
             destination buffer, against 64-bit numpy arithmetic."""
+            problem = None
             for par, f in enumerate(G["fulls"]):
                 out = case.dst_view(f[rank * shard_elems:(rank + 1) * shard_elems].cpu().numpy())
                 if not np.array_equal(out[np.ix_(rs, cs)].astype(np.int64), expected(case, par)):
-                    raise SystemExit(f"bench.py: GPU result does not match the reference arithmetic ({when}); refusing to report")
+                    problem = f"bench.py: GPU result does not match the reference arithmetic ({when}); refusing to report"
                 if use_dist:
                     nb_out = nb_case.dst_view(f[nb * shard_elems:(nb + 1) * shard_elems].cpu().numpy())
                     if not np.array_equal(nb_out[np.ix_(rs, cs)].astype(np.int64), expected(nb_case, par)):
-                        raise SystemExit(f"bench.py: the gathered destination is wrong ({when}); refusing to report")
+                        problem = f"bench.py: the gathered destination is wrong ({when}); refusing to report"
+            leave_together(problem)
 
         if mirrored and (step_no[0] & 1) == 0:
             fused_step()      # so that both buffers have been written
@@ -656,8 +678,8 @@ def run_gpu_arm(args):
             weak_ms = timed(lambda: ruy_b200.mul_async(wl, wr, wp, ctx, wd), args.steps)
             wcs = np.arange(0, cols_total, 997)
             wout = wcase.dst_view(wdst.cpu().numpy())[np.ix_(rs, wcs)].astype(np.int64)
-            if not np.array_equal(wout, expected(wcase, 0, cols_total, wcs)):
-                raise SystemExit("bench.py: weak-scaling result does not match the reference arithmetic; refusing to report")
+            leave_together(None if np.array_equal(wout, expected(wcase, 0, cols_total, wcs)) else
+                           "bench.py: weak-scaling result does not match the reference arithmetic; refusing to report")
             variants["weak"] = {"cols_per_rank": cols_total, "ms_per_step": weak_ms,
                                 "tops": world * 2.0 * case.rows * case.depth * cols_total / (weak_ms * 1e-3) / 1e12,
                                 "note": "every rank multiplies the same weights by its own 8192 activation columns; "
@@ -733,7 +755,9 @@ def run_gpu_arm(args):
         h2d = (c1["h2d_bytes"] - c0["h2d_bytes"]) // e2e_steps
         d2h = (c1["d2h_bytes"] - c0["d2h_bytes"]) // e2e_steps
         if not np.array_equal(case.dst_view(pinned_dst.numpy())[np.ix_(rs, cs)].astype(np.int64), expected(case, 0)):
-            raise SystemExit("bench.py: end-to-end result mismatch")
+            leave_together("bench.py: end-to-end result mismatch")
+        elif use_dist:
+            leave_together(None)
         copy_peak = pinned_copy_peak(dev, torch)
         e2e_gbs = max(h2d, d2h) / e2e_s / 1e9
 
