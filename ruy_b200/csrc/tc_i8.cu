@@ -1053,8 +1053,8 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
       if (args.xchg_remote[i]) {
         asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(args.xchg_remote[i]), "r"(args.xchg_value) : "memory");
       }
-      // The peers' flags are polled with relaxed loads: what reads the gathered tiles is a later kernel of the
-      // stream, and a kernel boundary orders it after this one.
+      // The peers' flags are polled with relaxed loads (an acquire load costs as much as a fence, every time); one
+      // fence follows the loop.
       unsigned long long t0;
       asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
       for (unsigned it = 0;; it++) {
@@ -1070,6 +1070,7 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
           }
         }
       }
+      __threadfence_system();   // the acquire side of the flags, once: what follows this launch reads the peers' tiles
     }
   }
 }
