@@ -85,7 +85,7 @@ struct KernelArgs {
   const CUtensorMap* store_maps;
   int row_pitch;   // bytes per tile row in shared memory = width of the swizzle pattern: 128, or 64 / 32 for depth <= 64 / 32
   uint32_t desc_hi; // high word of the shared-memory matrix descriptors for that pattern
-  int pack_clamps; // 8-bit destination with a clamp range inside int16: values are clamped two at a time while being narrowed
+  int pack_clamps; // 8-bit destination: 1 = clamp range inside int16, values are clamped two at a time while being narrowed; 2 / 3 = the clamp is all of uint8 / int8 and the saturating narrowing applies it; 0 = each value is clamped first
   uint32_t clamp_lo2, clamp_hi2;   // the clamp bounds replicated in both 16-bit halves
   int tight_wait;  // shallow main loops: the epilogue probes its barrier without backing off
   int mirror_wide; // every destination base and the destination stride are multiples of 16 bytes
@@ -353,8 +353,23 @@ struct NTerms {
 // Narrows 32 int32 values to bytes (8 words).  With `clamp`, the values are first saturated to 16 bits two at a
 // time, clamped to [lo2, hi2] per 16-bit half (bounds replicated in both halves) and then reduced to their low bytes:
 // 7 instructions per 4 values instead of 14 for clamping and masking them one by one.
-__device__ __forceinline__ void narrow_u8x32(const int32_t* v, bool clamp, uint32_t lo2, uint32_t hi2, uint32_t* w) {
-  if (clamp) {
+// `mode` (KernelArgs::pack_clamps): 0 = the values are already clamped, 1 = clamp two at a time in 16-bit halves,
+// 2 / 3 = the clamp is the whole range of uint8 / int8, which the saturating narrowing applies by itself.
+__device__ __forceinline__ void narrow_u8x32(const int32_t* v, int mode, uint32_t lo2, uint32_t hi2, uint32_t* w) {
+  if (mode >= 2) {
+#pragma unroll
+    for (int q = 0; q < 8; q++) {
+      uint32_t hi, d;
+      if (mode == 2) {
+        asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(v[4 * q + 3]), "r"(v[4 * q + 2]), "r"(0u));
+        asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(v[4 * q + 1]), "r"(v[4 * q]), "r"(hi));
+      } else {
+        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(v[4 * q + 3]), "r"(v[4 * q + 2]), "r"(0u));
+        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(v[4 * q + 1]), "r"(v[4 * q]), "r"(hi));
+      }
+      w[q] = d;
+    }
+  } else if (mode == 1) {
 #pragma unroll
     for (int q = 0; q < 8; q++) {
       uint32_t a, b;
@@ -383,7 +398,7 @@ __device__ __forceinline__ void store_run32_at(char* dst_base, const KernelArgs&
     uint4* out = (uint4*)base;
     if (kDstBytes == 1) {
       uint32_t w[8];
-      narrow_u8x32(v, a.pack_clamps != 0, a.clamp_lo2, a.clamp_hi2, w);
+      narrow_u8x32(v, a.pack_clamps, a.clamp_lo2, a.clamp_hi2, w);
       __stcs(&out[0], make_uint4(w[0], w[1], w[2], w[3]));
       __stcs(&out[1], make_uint4(w[4], w[5], w[6], w[7]));
     } else if (kDstBytes == 2) {
@@ -892,7 +907,7 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
               }
               int32_t v[32];
               finish_chunk(c, v);
-              narrow_u8x32(v, late_clamp, args.clamp_lo2, args.clamp_hi2, w[j]);
+              narrow_u8x32(v, args.pack_clamps, args.clamp_lo2, args.clamp_hi2, w[j]);
             }
             if (issuer) bulk_wait_read_0();                  // the stores that last read the staging area are done with it
             epilogue_all(true, group, group_threads);
@@ -929,7 +944,7 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
             int32_t v[32];
             finish_chunk(c, v);
             uint32_t w[8];
-            narrow_u8x32(v, late_clamp, args.clamp_lo2, args.clamp_hi2, w);
+            narrow_u8x32(v, args.pack_clamps, args.clamp_lo2, args.clamp_hi2, w);
             uint4* sp = reinterpret_cast<uint4*>(stg + ml * kMirrorPitch + (c - h * 128));
             sp[0] = make_uint4(w[0], w[1], w[2], w[3]);
             sp[1] = make_uint4(w[4], w[5], w[6], w[7]);
@@ -1382,6 +1397,8 @@ cudaError_t launch_tc_i8(const TcI8Launch& L, cudaStream_t stream) {
   a.acc_bufs = 1 << a.acc_shift;
   const bool dst8 = L.ep.dst_dtype == RUYB200_I8 || L.ep.dst_dtype == RUYB200_U8;
   a.pack_clamps = dst8 && L.ep.clamp_min >= -32768 && L.ep.clamp_max <= 32767 && L.ep.clamp_min <= L.ep.clamp_max;
+  if (a.pack_clamps && L.ep.dst_dtype == RUYB200_U8 && L.ep.clamp_min == 0 && L.ep.clamp_max == 255) a.pack_clamps = 2;
+  if (a.pack_clamps && L.ep.dst_dtype == RUYB200_I8 && L.ep.clamp_min == -128 && L.ep.clamp_max == 127) a.pack_clamps = 3;
   a.clamp_lo2 = ((uint32_t)L.ep.clamp_min & 0xffffu) * 0x10001u;
   a.clamp_hi2 = ((uint32_t)L.ep.clamp_max & 0xffffu) * 0x10001u;
   a.tight_wait = L.depth <= 512 ? 1 : 0;
