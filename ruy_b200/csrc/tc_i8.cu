@@ -893,32 +893,34 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
           const bool by_tma = args.store_maps != nullptr &&
                               (n_end - nh0 >= 128 || (n_end == args.size_n && (args.size_n & 15) == 0));
           if (by_tma) {
-            // values first, so that this half's arithmetic overlaps the copy engine's reads of the previous one
-            uint32_t w[2][8];
-            bool have[2];
+            // The first 32-column chunk is worked out before the wait, so that arithmetic overlaps the copy engine's reads
+            // of the previous half; the second follows once the staging area is free (one chunk of results live across
+            // the barrier, not two: the registers are short in this variant).
 #pragma unroll
             for (int j = 0; j < 2; j++) {
               const int c = h * 128 + j * 64 + c_first;
-              have[j] = !(c >= args.block_n || tn * args.block_n + c >= args.size_n);   // uniform across the warp
-              if (!have[j]) continue;
-              if (c != c_first) {
-                tmem_ld_32(taddr + c, r);
-                tmem_ld_wait();
+              const bool have = !(c >= args.block_n || tn * args.block_n + c >= args.size_n);   // uniform across the warp
+              uint32_t w[8];
+              if (have) {
+                if (c != c_first) {
+                  tmem_ld_32(taddr + c, r);
+                  tmem_ld_wait();
+                }
+                int32_t v[32];
+                finish_chunk(c, v);
+                narrow_u8x32(v, late_clamp ? 1 : 0, args.clamp_lo2, args.clamp_hi2, w);
               }
-              int32_t v[32];
-              finish_chunk(c, v);
-              narrow_u8x32(v, args.pack_clamps, args.clamp_lo2, args.clamp_hi2, w[j]);
-            }
-            if (issuer) bulk_wait_read_0();                  // the stores that last read the staging area are done with it
-            epilogue_all(true, group, group_threads);
-#pragma unroll
-            for (int j = 0; j < 2; j++) {
-              if (!have[j]) continue;
-              // row ml of the box; its 16-byte piece p sits at p ^ (ml & 7)
-              const int p0 = (j * 64 + c_first) >> 4;
-              uint8_t* row = stg0 + ml * 128;
-              *reinterpret_cast<uint4*>(row + (((p0) ^ (ml & 7)) << 4)) = make_uint4(w[j][0], w[j][1], w[j][2], w[j][3]);
-              *reinterpret_cast<uint4*>(row + (((p0 + 1) ^ (ml & 7)) << 4)) = make_uint4(w[j][4], w[j][5], w[j][6], w[j][7]);
+              if (j == 0) {
+                if (issuer) bulk_wait_read_0();                // the stores that last read the staging area are done with it
+                epilogue_all(true, group, group_threads);
+              }
+              if (have) {
+                // row ml of the box; its 16-byte piece p sits at p ^ (ml & 7)
+                const int p0 = (j * 64 + c_first) >> 4;
+                uint8_t* row = stg0 + ml * 128;
+                *reinterpret_cast<uint4*>(row + (((p0) ^ (ml & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+                *reinterpret_cast<uint4*>(row + (((p0 + 1) ^ (ml & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+              }
             }
             fence_proxy_async();                             // these writes, before the copy engine reads them
             epilogue_all(true, group, group_threads);        // the half tile is staged
@@ -944,7 +946,7 @@ tc_i8_kernel(const __grid_constant__ CUtensorMap map_m, const __grid_constant__ 
             int32_t v[32];
             finish_chunk(c, v);
             uint32_t w[8];
-            narrow_u8x32(v, args.pack_clamps, args.clamp_lo2, args.clamp_hi2, w);
+            narrow_u8x32(v, late_clamp ? 1 : 0, args.clamp_lo2, args.clamp_hi2, w);
             uint4* sp = reinterpret_cast<uint4*>(stg + ml * kMirrorPitch + (c - h * 128));
             sp[0] = make_uint4(w[0], w[1], w[2], w[3]);
             sp[1] = make_uint4(w[4], w[5], w[6], w[7]);
