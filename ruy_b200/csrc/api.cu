@@ -799,7 +799,12 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
       std::min(d.dst.rows, d.dst.cols) <= kGemvMaxNarrow) {
     const bool lhs_ok = side_view(d.lhs, 0, d.lhs.data).stride_k == 1 || should_cache(d.lhs, d.rhs.cols);
     const bool rhs_ok = side_view(d.rhs, 1, d.rhs.data).stride_k == 1 || should_cache(d.rhs, d.lhs.rows);
-    if (lhs_ok && rhs_ok) kernel = RUYB200_KERNEL_GEMV;
+    // one warp per wide row: a wide side of fewer than 128 rows leaves most SMs idle, and with a very deep 8-bit depth
+    // and more than one narrow row the tensor-core kernel is faster (64 x 16384 x 4: 47 us against 68 us)
+    const int wide_rows = std::max(d.dst.rows, d.dst.cols);
+    const bool few_deep_rows = !is_float && wide_rows >= 32 && wide_rows < 128 && depth >= 8192 &&
+                               std::min(d.dst.rows, d.dst.cols) > 1;
+    if (lhs_ok && rhs_ok && !few_deep_rows) kernel = RUYB200_KERNEL_GEMV;
   }
   // fp32 muls that fill tensor-core tiles go to the 3 x TF32 kernel; small ones stay on the FFMA kernel, whose single
   // launch costs less than the split pre-pass, and so do very deep ones: the tensor core truncates when it adds, each

@@ -16,6 +16,8 @@ namespace ruyb200 {
 namespace {
 
 constexpr int kWarpsPerBlock = 8;
+// From this many wide rows on, muls with two to eight narrow rows go to the MMA form (16 wide rows per CTA).
+constexpr int kMmaMinWide = 1024;
 
 template <bool kASigned, bool kBSigned>
 __device__ __forceinline__ int32_t dot4(uint32_t a, uint32_t b, int32_t c) {
@@ -157,6 +159,138 @@ __global__ void __launch_bounds__(32 * kWarpsPerBlock) gemv_i8_kernel(const Gemv
   }
 }
 
+// m16n8k32 integer MMA on the warp's registers (the legacy tensor-core path): d += a (16 x 32 bytes) * b (32 x 8).
+template <bool kASigned, bool kBSigned>
+__device__ __forceinline__ void mma_16x8x32(int32_t (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  if (kASigned && kBSigned) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  } else if (kASigned) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  } else if (kBSigned) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  } else {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  }
+}
+
+// Two to eight narrow rows against a wide operand of thousands of rows: dp4a runs at a quarter of the integer rate on
+// this part, and with four of them per narrow row and 16-byte piece the kernel above is bound by them, not by HBM
+// (16384 x 16384 x 8: 215 us against 41 us for the stream).  Here a CTA takes 16 wide rows; its warps take turns on
+// steps of 256 bytes of depth, each step feeding eight m16n8k32 MMAs: lane (g, t) (g = lane / 4, t = lane % 4) loads
+// the 16-byte pieces t, t + 4, t + 8, t + 12 of the step from wide rows g and g + 8 and from narrow row g; the MMA's k
+// index is a permutation of the byte index, the same for both operands, so the sums over k are unchanged.  The
+// zero-point sums still use dp4a, one per loaded word.  The warps' partial sums meet in shared memory and warp 0
+// finishes.  Needs 16-byte aligned rows and a depth that is a multiple of 16.
+template <bool kWideSigned, bool kNarrowSigned>
+__global__ void __launch_bounds__(32 * kWarpsPerBlock) gemv_i8_mma_kernel(const GemvArgs a) {
+  __shared__ int32_t part[kWarpsPerBlock - 1][7][32];
+  const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
+  const int g = lane >> 2, t = lane & 3;
+  const long long w0 = (long long)blockIdx.x * 16;
+  const int depth = a.ep.depth;
+  const long long last = a.wide.width - 1;
+  const long long r0 = w0 + g, r1 = w0 + g + 8;
+  const uint4* row0 = reinterpret_cast<const uint4*>((const uint8_t*)a.wide.data + (r0 < last ? r0 : last) * a.wide.stride_w);
+  const uint4* row1 = reinterpret_cast<const uint4*>((const uint8_t*)a.wide.data + (r1 < last ? r1 : last) * a.wide.stride_w);
+  const bool have_n = g < a.narrow.width;
+  const uint4* nrow = reinterpret_cast<const uint4*>((const uint8_t*)a.narrow.data + (have_n ? g : 0) * a.narrow.stride_w);
+  int32_t c[4] = {0, 0, 0, 0};
+  int32_t wsum0 = 0, wsum1 = 0, nsum = 0;
+  const int pieces = depth / 16;
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  for (int base = warp * 16; base < pieces; base += kWarpsPerBlock * 16) {
+    uint4 xa[4], xb[4], y[4];
+    if (base + 16 <= pieces) {
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        xa[i] = __ldcs(row0 + base + t + 4 * i);
+        xb[i] = __ldcs(row1 + base + t + 4 * i);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; i++) y[i] = have_n ? __ldg(nrow + base + t + 4 * i) : zero;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        const int p = base + t + 4 * i;
+        xa[i] = p < pieces ? __ldcs(row0 + p) : zero;
+        xb[i] = p < pieces ? __ldcs(row1 + p) : zero;
+        y[i] = (p < pieces && have_n) ? __ldg(nrow + p) : zero;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      mma_16x8x32<kWideSigned, kNarrowSigned>(c, xa[i].x, xb[i].x, xa[i].y, xb[i].y, y[i].x, y[i].y);
+      mma_16x8x32<kWideSigned, kNarrowSigned>(c, xa[i].z, xb[i].z, xa[i].w, xb[i].w, y[i].z, y[i].w);
+    }
+    if (a.need_wsum) {
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        wsum0 = sum4<kWideSigned>(xa[i].x, wsum0);
+        wsum0 = sum4<kWideSigned>(xa[i].y, wsum0);
+        wsum0 = sum4<kWideSigned>(xa[i].z, wsum0);
+        wsum0 = sum4<kWideSigned>(xa[i].w, wsum0);
+        wsum1 = sum4<kWideSigned>(xb[i].x, wsum1);
+        wsum1 = sum4<kWideSigned>(xb[i].y, wsum1);
+        wsum1 = sum4<kWideSigned>(xb[i].z, wsum1);
+        wsum1 = sum4<kWideSigned>(xb[i].w, wsum1);
+      }
+    }
+    if (a.need_nsum) {
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        nsum = sum4<kNarrowSigned>(y[i].x, nsum);
+        nsum = sum4<kNarrowSigned>(y[i].y, nsum);
+        nsum = sum4<kNarrowSigned>(y[i].z, nsum);
+        nsum = sum4<kNarrowSigned>(y[i].w, nsum);
+      }
+    }
+  }
+  if (warp > 0) {
+#pragma unroll
+    for (int i = 0; i < 4; i++) part[warp - 1][i][lane] = c[i];
+    part[warp - 1][4][lane] = wsum0;
+    part[warp - 1][5][lane] = wsum1;
+    part[warp - 1][6][lane] = nsum;
+  }
+  __syncthreads();
+  if (warp > 0) return;
+#pragma unroll
+  for (int w = 0; w < kWarpsPerBlock - 1; w++) {
+#pragma unroll
+    for (int i = 0; i < 4; i++) c[i] += part[w][i][lane];
+    wsum0 += part[w][4][lane];
+    wsum1 += part[w][5][lane];
+    nsum += part[w][6][lane];
+  }
+  // the four lanes of a quad hold the four quarters of each step
+#pragma unroll
+  for (int d = 1; d <= 2; d <<= 1) {
+    wsum0 += __shfl_xor_sync(0xffffffffu, wsum0, d);
+    wsum1 += __shfl_xor_sync(0xffffffffu, wsum1, d);
+    nsum += __shfl_xor_sync(0xffffffffu, nsum, d);
+  }
+  // this lane's outputs: wide rows r0 and r1, narrow rows 2 t and 2 t + 1, whose sums sit in quads 2 t and 2 t + 1
+  const int32_t nsum_a = __shfl_sync(0xffffffffu, nsum, (2 * t) * 4);
+  const int32_t nsum_b = __shfl_sync(0xffffffffu, nsum, (2 * t + 1) * 4);
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const long long w = i < 2 ? r0 : r1;
+    const int j = 2 * t + (i & 1);
+    if (w < a.wide.width && j < a.narrow.width) {
+      const int m = a.wide_is_m ? (int)w : j;
+      const int n = a.wide_is_m ? j : (int)w;
+      const int32_t ws = i < 2 ? wsum0 : wsum1, ns = (i & 1) ? nsum_b : nsum_a;
+      const int32_t sum_m = a.wide_is_m ? ws : ns;
+      const int32_t sum_n = a.wide_is_m ? ns : ws;
+      store_int(a.dst, a.ep.dst_dtype, m, n, finish_with_sums(c[i], sum_m, sum_n, m, n, a.ep));
+    }
+  }
+}
+
 // Compensated (Kahan) running sum: folds y into (sum, comp).
 __device__ __forceinline__ void kahan_add(float& sum, float& comp, float y) {
   const float yy = y - comp;
@@ -273,6 +407,15 @@ cudaError_t launch_gemv(const SideView& m_side, const SideView& n_side, const Ds
     if (narrow <= 1) gemv_f32_kernel<1><<<grid, 32 * kWarpsPerBlock, 0, stream>>>(a);
     else if (narrow <= 4) gemv_f32_kernel<4><<<grid, 32 * kWarpsPerBlock, 0, stream>>>(a);
     else gemv_f32_kernel<kGemvMaxNarrow><<<grid, 32 * kWarpsPerBlock, 0, stream>>>(a);
+    return cudaGetLastError();
+  }
+  if (narrow >= 2 && a.vec && (ep.depth & 15) == 0 && a.wide.width >= kMmaMinWide) {
+    const unsigned mgrid = (unsigned)(((long long)a.wide.width + 15) / 16);
+    const bool ws = a.wide.dtype == RUYB200_I8, ns = a.narrow.dtype == RUYB200_I8;
+    if (ws && ns) gemv_i8_mma_kernel<true, true><<<mgrid, 32 * kWarpsPerBlock, 0, stream>>>(a);
+    else if (ws) gemv_i8_mma_kernel<true, false><<<mgrid, 32 * kWarpsPerBlock, 0, stream>>>(a);
+    else if (ns) gemv_i8_mma_kernel<false, true><<<mgrid, 32 * kWarpsPerBlock, 0, stream>>>(a);
+    else gemv_i8_mma_kernel<false, false><<<mgrid, 32 * kWarpsPerBlock, 0, stream>>>(a);
     return cudaGetLastError();
   }
   if (narrow <= 1) return launch_i8<1>(a, grid, stream);

@@ -44,7 +44,9 @@ def exact(case, ctx, **kw):
 # ---- narrow muls ---------------------------------------------------------------------------------
 
 NARROW = [(256, 64, 1), (1, 64, 256), (4096, 512, 1), (300, 1000, 3), (5, 777, 130), (8, 4096, 8), (1000, 33, 8),
-          (7, 5, 2), (1, 32767, 1), (2, 45984, 3)]
+          (7, 5, 2), (1, 32767, 1), (2, 45984, 3),
+          # two and four wide rows per warp, with rows left over at the end
+          (2051, 100, 3), (9000, 96, 1), (4, 130, 8195), (16386, 64, 8)]
 
 
 @pytest.mark.parametrize("shape", NARROW, ids=lambda s: "x".join(map(str, s)))
@@ -72,6 +74,15 @@ def test_narrow_muls_other_layouts_and_host_operands(gpu_ctx):
     assert gpu_ctx.counters()["last_kernel"] == "gemv"
 
 
+def test_few_wide_rows_with_a_very_deep_depth_go_to_the_tensor_core(gpu_ctx):
+    c = cases.random_case(64, 16384, 4, "int8", "int8", "int8", orders="RCC", perchannel=True, seed=12)
+    exact(c, gpu_ctx)
+    assert gpu_ctx.counters()["last_kernel"] == "tc_i8"
+    c = cases.random_case(64, 16384, 1, "int8", "int8", "int8", orders="RCC", perchannel=True, seed=13)
+    exact(c, gpu_ctx)
+    assert gpu_ctx.counters()["last_kernel"] == "gemv"
+
+
 def test_narrow_muls_can_stay_on_the_tensor_core():
     ctx = ctx_with_env(RUYB200_FORCE_KERNEL="tc_i8")
     try:
@@ -83,7 +94,8 @@ def test_narrow_muls_can_stay_on_the_tensor_core():
         ctx.close()
 
 
-@pytest.mark.parametrize("shape", [(256, 64, 1), (1, 64, 256), (1000, 1000, 1), (3, 32767, 2), (500, 301, 8), (64, 7, 5)],
+@pytest.mark.parametrize("shape", [(256, 64, 1), (1, 64, 256), (1000, 1000, 1), (3, 32767, 2), (500, 301, 8), (64, 7, 5),
+                                   (2051, 100, 3), (8195, 68, 4), (7, 50, 8201)],
                          ids=lambda s: "x".join(map(str, s)))
 def test_narrow_float_muls(shape, gpu_ctx):
     for orders, extra in (("RCC", 0), ("RCR", 0), ("RCC", 1)):
