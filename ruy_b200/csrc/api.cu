@@ -795,8 +795,19 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
   // Narrow muls (at most kGemvMaxNarrow destination rows or columns) are a single pass over the wide operand
   // (ruy's single-column kernels, ruy/kernel_avx512.cc:628-870,1238-1320).  Both operands must be
   // depth-contiguous where the kernel will read them: as stored, or in their packed form when they are cached.
+  const int narrow_rows = std::min(d.dst.rows, d.dst.cols);
+  // 9 to kGemvMmaMaxNarrow narrow rows take that kernel only in its MMA form: 8-bit operands whose rows start on
+  // 16-byte boundaries (as stored, or packed, which always do)
+  const auto rows_aligned = [&](const ruyb200_matrix& m, int side, int other_width) {
+    if (should_cache(m, other_width)) return true;
+    const SideView v = side_view(m, side, m.data);
+    return v.stride_k == 1 && (((uintptr_t)m.data | (uintptr_t)v.stride_w) & 15) == 0;
+  };
+  const bool mma_form = !is_float && kernel == RUYB200_KERNEL_TC_I8 &&
+                        gemv_mma_shape(narrow_rows, std::max(d.dst.rows, d.dst.cols), depth) &&
+                        rows_aligned(d.lhs, 0, d.rhs.cols) && rows_aligned(d.rhs, 1, d.lhs.rows);
   if ((kernel == RUYB200_KERNEL_TC_I8 || kernel == RUYB200_KERNEL_SGEMM) && !ctx->force_kernel && n_mirrors == 0 && !xchg && depth > 0 &&
-      std::min(d.dst.rows, d.dst.cols) <= kGemvMaxNarrow) {
+      (narrow_rows <= kGemvMaxNarrow || mma_form)) {
     const bool lhs_ok = side_view(d.lhs, 0, d.lhs.data).stride_k == 1 || should_cache(d.lhs, d.rhs.cols);
     const bool rhs_ok = side_view(d.rhs, 1, d.rhs.data).stride_k == 1 || should_cache(d.rhs, d.lhs.rows);
     // one warp per wide row: a wide side of fewer than 128 rows leaves most SMs idle, and with a very deep 8-bit depth
@@ -1006,10 +1017,10 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
     ctx->counters[0] += 2;   // the two split launches
     if (ctx->trace) fprintf(stderr, "ruy_b200: mul %dx%dx%d kernel=tc_f32 (tcgen05 kind::tf32, hi/lo split, three products, 32-deep accumulation chains)\n",
                             d.lhs.rows, d.lhs.cols, d.rhs.cols);
-  } else if (kernel == RUYB200_KERNEL_GEMV && gemv_eligible(r.m_side, r.n_side, is_float)) {
+  } else if (kernel == RUYB200_KERNEL_GEMV && gemv_eligible(r.m_side, r.n_side, depth, is_float)) {
     ce = launch_gemv(r.m_side, r.n_side, r.dst, r.ep, ctx->stream);
     if (ctx->trace) fprintf(stderr, "ruy_b200: mul %dx%dx%d kernel=gemv (one pass over the wide operand, %s)\n", d.lhs.rows, d.lhs.cols, d.rhs.cols,
-                            is_float ? "fp32 FFMA, compensated" : "dp4a, sums on the way");
+                            is_float ? "fp32 FFMA, compensated" : "dp4a or register-level MMAs, sums on the way");
   } else if (is_f64) {
     kernel = RUYB200_KERNEL_GENERIC;
     ce = launch_generic_f64(r.m_side, r.n_side, r.dst, r.ep, d.params.clamp_min.d, d.params.clamp_max.d, ctx->stream);

@@ -189,7 +189,14 @@ cudaError_t launch_shallow_i8(const TcI8Launch& args, cudaStream_t stream);
 // Narrow muls (one side has at most kGemvMaxNarrow rows): one pass over the wide operand, no packing, no sums
 // needed from the caller.  Both sides must be depth-contiguous; 8-bit x 8-bit or fp32.
 constexpr int kGemvMaxNarrow = 8;
-bool gemv_eligible(const SideView& m_side, const SideView& n_side, bool is_float);
+bool gemv_eligible(const SideView& m_side, const SideView& n_side, int depth, bool is_float);
+// 8-bit muls with 2 to kGemvMmaMaxNarrow narrow rows on a wide operand of 1024 rows or more and a depth that is a
+// multiple of 16 run in the MMA form of the narrow kernel (16 wide rows per CTA, register-level m16n8k32 MMAs), which
+// also needs every row of both operands on a 16-byte boundary.
+constexpr int kGemvMmaMaxNarrow = 16;
+inline bool gemv_mma_shape(int narrow, long long wide, int depth) {
+  return narrow >= 2 && narrow <= kGemvMmaMaxNarrow && wide >= 1024 && depth >= 16 && (depth & 15) == 0;
+}
 cudaError_t launch_gemv(const SideView& m_side, const SideView& n_side, const DstView& dst, const Epilogue& ep,
                         cudaStream_t stream);
 

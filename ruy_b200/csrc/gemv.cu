@@ -11,13 +11,14 @@
 // of ruy/kernel.h:213-237.
 #include "common.cuh"
 
+#include <type_traits>
+
 namespace ruyb200 {
 
 namespace {
 
 constexpr int kWarpsPerBlock = 8;
-// From this many wide rows on, muls with two to eight narrow rows go to the MMA form (16 wide rows per CTA).
-constexpr int kMmaMinWide = 1024;
+
 
 template <bool kASigned, bool kBSigned>
 __device__ __forceinline__ int32_t dot4(uint32_t a, uint32_t b, int32_t c) {
@@ -181,13 +182,15 @@ __device__ __forceinline__ void mma_16x8x32(int32_t (&d)[4], uint32_t a0, uint32
 // this part, and with four of them per narrow row and 16-byte piece the kernel above is bound by them, not by HBM
 // (16384 x 16384 x 8: 215 us against 41 us for the stream).  Here a CTA takes 16 wide rows; its warps take turns on
 // steps of 256 bytes of depth, each step feeding eight m16n8k32 MMAs: lane (g, t) (g = lane / 4, t = lane % 4) loads
-// the 16-byte pieces t, t + 4, t + 8, t + 12 of the step from wide rows g and g + 8 and from narrow row g; the MMA's k
+// the 16-byte pieces t, t + 4, t + 8, t + 12 of the step from wide rows g and g + 8 and, for each tile of 8 narrow
+// rows (one or two tiles), from narrow row g of the tile; the MMA's k
 // index is a permutation of the byte index, the same for both operands, so the sums over k are unchanged.  The
 // zero-point sums still use dp4a, one per loaded word.  The warps' partial sums meet in shared memory and warp 0
 // finishes.  Needs 16-byte aligned rows and a depth that is a multiple of 16.
-template <bool kWideSigned, bool kNarrowSigned>
+template <bool kWideSigned, bool kNarrowSigned, int kTiles>
 __global__ void __launch_bounds__(32 * kWarpsPerBlock) gemv_i8_mma_kernel(const GemvArgs a) {
-  __shared__ int32_t part[kWarpsPerBlock - 1][7][32];
+  constexpr int kPart = 5 * kTiles + 2;  // per lane: 4 accumulators and a narrow sum per tile of 8 narrow rows, 2 wide sums
+  __shared__ int32_t part[kWarpsPerBlock - 1][kPart][32];
   const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
   const int g = lane >> 2, t = lane & 3;
   const long long w0 = (long long)blockIdx.x * 16;
@@ -196,35 +199,58 @@ __global__ void __launch_bounds__(32 * kWarpsPerBlock) gemv_i8_mma_kernel(const 
   const long long r0 = w0 + g, r1 = w0 + g + 8;
   const uint4* row0 = reinterpret_cast<const uint4*>((const uint8_t*)a.wide.data + (r0 < last ? r0 : last) * a.wide.stride_w);
   const uint4* row1 = reinterpret_cast<const uint4*>((const uint8_t*)a.wide.data + (r1 < last ? r1 : last) * a.wide.stride_w);
-  const bool have_n = g < a.narrow.width;
-  const uint4* nrow = reinterpret_cast<const uint4*>((const uint8_t*)a.narrow.data + (have_n ? g : 0) * a.narrow.stride_w);
-  int32_t c[4] = {0, 0, 0, 0};
-  int32_t wsum0 = 0, wsum1 = 0, nsum = 0;
+  const uint4* nrow[kTiles];
+  bool have_n[kTiles];
+#pragma unroll
+  for (int j = 0; j < kTiles; j++) {
+    have_n[j] = 8 * j + g < a.narrow.width;
+    nrow[j] = reinterpret_cast<const uint4*>((const uint8_t*)a.narrow.data + (have_n[j] ? 8 * j + g : 0) * a.narrow.stride_w);
+  }
+  int32_t c[kTiles][4];
+  int32_t nsum[kTiles];
+#pragma unroll
+  for (int j = 0; j < kTiles; j++) {
+    nsum[j] = 0;
+#pragma unroll
+    for (int i = 0; i < 4; i++) c[j][i] = 0;
+  }
+  int32_t wsum0 = 0, wsum1 = 0;
   const int pieces = depth / 16;
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-  for (int base = warp * 16; base < pieces; base += kWarpsPerBlock * 16) {
-    uint4 xa[4], xb[4], y[4];
-    if (base + 16 <= pieces) {
+  // one step: all of its loads first (8 of the wide rows, 4 per tile of narrow rows), then the MMAs and the sums
+  auto step = [&](const int base, auto whole_tag) {
+    constexpr bool kWhole = decltype(whole_tag)::value;
+    uint4 xa[4], xb[4], y[kTiles][4];
 #pragma unroll
-      for (int i = 0; i < 4; i++) {
-        xa[i] = __ldcs(row0 + base + t + 4 * i);
-        xb[i] = __ldcs(row1 + base + t + 4 * i);
-      }
+    for (int i = 0; i < 4; i++) {
+      const int p = base + t + 4 * i;
+      xa[i] = (kWhole || p < pieces) ? __ldcs(row0 + p) : zero;
+      xb[i] = (kWhole || p < pieces) ? __ldcs(row1 + p) : zero;
+    }
 #pragma unroll
-      for (int i = 0; i < 4; i++) y[i] = have_n ? __ldg(nrow + base + t + 4 * i) : zero;
-    } else {
+    for (int j = 0; j < kTiles; j++) {
 #pragma unroll
       for (int i = 0; i < 4; i++) {
         const int p = base + t + 4 * i;
-        xa[i] = p < pieces ? __ldcs(row0 + p) : zero;
-        xb[i] = p < pieces ? __ldcs(row1 + p) : zero;
-        y[i] = (p < pieces && have_n) ? __ldg(nrow + p) : zero;
+        y[j][i] = (have_n[j] && (kWhole || p < pieces)) ? __ldg(nrow[j] + p) : zero;
       }
     }
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
-      mma_16x8x32<kWideSigned, kNarrowSigned>(c, xa[i].x, xb[i].x, xa[i].y, xb[i].y, y[i].x, y[i].y);
-      mma_16x8x32<kWideSigned, kNarrowSigned>(c, xa[i].z, xb[i].z, xa[i].w, xb[i].w, y[i].z, y[i].w);
+    for (int j = 0; j < kTiles; j++) {
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        mma_16x8x32<kWideSigned, kNarrowSigned>(c[j], xa[i].x, xb[i].x, xa[i].y, xb[i].y, y[j][i].x, y[j][i].y);
+        mma_16x8x32<kWideSigned, kNarrowSigned>(c[j], xa[i].z, xb[i].z, xa[i].w, xb[i].w, y[j][i].z, y[j][i].w);
+      }
+      if (a.need_nsum) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+          nsum[j] = sum4<kNarrowSigned>(y[j][i].x, nsum[j]);
+          nsum[j] = sum4<kNarrowSigned>(y[j][i].y, nsum[j]);
+          nsum[j] = sum4<kNarrowSigned>(y[j][i].z, nsum[j]);
+          nsum[j] = sum4<kNarrowSigned>(y[j][i].w, nsum[j]);
+        }
+      }
     }
     if (a.need_wsum) {
 #pragma unroll
@@ -239,56 +265,72 @@ __global__ void __launch_bounds__(32 * kWarpsPerBlock) gemv_i8_mma_kernel(const 
         wsum1 = sum4<kWideSigned>(xb[i].w, wsum1);
       }
     }
-    if (a.need_nsum) {
-#pragma unroll
-      for (int i = 0; i < 4; i++) {
-        nsum = sum4<kNarrowSigned>(y[i].x, nsum);
-        nsum = sum4<kNarrowSigned>(y[i].y, nsum);
-        nsum = sum4<kNarrowSigned>(y[i].z, nsum);
-        nsum = sum4<kNarrowSigned>(y[i].w, nsum);
-      }
-    }
-  }
+  };
+  int base = warp * 16;
+  for (; base + 16 <= pieces; base += kWarpsPerBlock * 16) step(base, std::true_type{});
+  if (base < pieces) step(base, std::false_type{});
   if (warp > 0) {
 #pragma unroll
-    for (int i = 0; i < 4; i++) part[warp - 1][i][lane] = c[i];
-    part[warp - 1][4][lane] = wsum0;
-    part[warp - 1][5][lane] = wsum1;
-    part[warp - 1][6][lane] = nsum;
+    for (int j = 0; j < kTiles; j++) {
+#pragma unroll
+      for (int i = 0; i < 4; i++) part[warp - 1][5 * j + i][lane] = c[j][i];
+      part[warp - 1][5 * j + 4][lane] = nsum[j];
+    }
+    part[warp - 1][5 * kTiles][lane] = wsum0;
+    part[warp - 1][5 * kTiles + 1][lane] = wsum1;
   }
   __syncthreads();
   if (warp > 0) return;
 #pragma unroll
   for (int w = 0; w < kWarpsPerBlock - 1; w++) {
 #pragma unroll
-    for (int i = 0; i < 4; i++) c[i] += part[w][i][lane];
-    wsum0 += part[w][4][lane];
-    wsum1 += part[w][5][lane];
-    nsum += part[w][6][lane];
+    for (int j = 0; j < kTiles; j++) {
+#pragma unroll
+      for (int i = 0; i < 4; i++) c[j][i] += part[w][5 * j + i][lane];
+      nsum[j] += part[w][5 * j + 4][lane];
+    }
+    wsum0 += part[w][5 * kTiles][lane];
+    wsum1 += part[w][5 * kTiles + 1][lane];
   }
   // the four lanes of a quad hold the four quarters of each step
 #pragma unroll
   for (int d = 1; d <= 2; d <<= 1) {
     wsum0 += __shfl_xor_sync(0xffffffffu, wsum0, d);
     wsum1 += __shfl_xor_sync(0xffffffffu, wsum1, d);
-    nsum += __shfl_xor_sync(0xffffffffu, nsum, d);
-  }
-  // this lane's outputs: wide rows r0 and r1, narrow rows 2 t and 2 t + 1, whose sums sit in quads 2 t and 2 t + 1
-  const int32_t nsum_a = __shfl_sync(0xffffffffu, nsum, (2 * t) * 4);
-  const int32_t nsum_b = __shfl_sync(0xffffffffu, nsum, (2 * t + 1) * 4);
 #pragma unroll
-  for (int i = 0; i < 4; i++) {
-    const long long w = i < 2 ? r0 : r1;
-    const int j = 2 * t + (i & 1);
-    if (w < a.wide.width && j < a.narrow.width) {
-      const int m = a.wide_is_m ? (int)w : j;
-      const int n = a.wide_is_m ? j : (int)w;
-      const int32_t ws = i < 2 ? wsum0 : wsum1, ns = (i & 1) ? nsum_b : nsum_a;
-      const int32_t sum_m = a.wide_is_m ? ws : ns;
-      const int32_t sum_n = a.wide_is_m ? ns : ws;
-      store_int(a.dst, a.ep.dst_dtype, m, n, finish_with_sums(c[i], sum_m, sum_n, m, n, a.ep));
+    for (int j = 0; j < kTiles; j++) nsum[j] += __shfl_xor_sync(0xffffffffu, nsum[j], d);
+  }
+#pragma unroll
+  for (int j = 0; j < kTiles; j++) {
+    // this lane's outputs of the tile: wide rows r0 and r1, narrow rows 8 j + 2 t and 8 j + 2 t + 1, whose sums sit in
+    // quads 2 t and 2 t + 1
+    const int32_t nsum_a = __shfl_sync(0xffffffffu, nsum[j], (2 * t) * 4);
+    const int32_t nsum_b = __shfl_sync(0xffffffffu, nsum[j], (2 * t + 1) * 4);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const long long w = i < 2 ? r0 : r1;
+      const int col = 8 * j + 2 * t + (i & 1);
+      if (w < a.wide.width && col < a.narrow.width) {
+        const int m = a.wide_is_m ? (int)w : col;
+        const int n = a.wide_is_m ? col : (int)w;
+        const int32_t ws = i < 2 ? wsum0 : wsum1, ns = (i & 1) ? nsum_b : nsum_a;
+        const int32_t sum_m = a.wide_is_m ? ws : ns;
+        const int32_t sum_n = a.wide_is_m ? ns : ws;
+        store_int(a.dst, a.ep.dst_dtype, m, n, finish_with_sums(c[j][i], sum_m, sum_n, m, n, a.ep));
+      }
     }
   }
+}
+
+template <int kTiles>
+cudaError_t launch_i8_mma(const GemvArgs& a, cudaStream_t stream) {
+  const unsigned grid = (unsigned)(((long long)a.wide.width + 15) / 16);
+  const bool ws = a.wide.dtype == RUYB200_I8, ns = a.narrow.dtype == RUYB200_I8;
+  if (ws && ns) gemv_i8_mma_kernel<true, true, kTiles><<<grid, 32 * kWarpsPerBlock, 0, stream>>>(a);
+  else if (ws) gemv_i8_mma_kernel<true, false, kTiles><<<grid, 32 * kWarpsPerBlock, 0, stream>>>(a);
+  else if (ns) gemv_i8_mma_kernel<false, true, kTiles><<<grid, 32 * kWarpsPerBlock, 0, stream>>>(a);
+  else gemv_i8_mma_kernel<false, false, kTiles><<<grid, 32 * kWarpsPerBlock, 0, stream>>>(a);
+  return cudaGetLastError();
 }
 
 // Compensated (Kahan) running sum: folds y into (sum, comp).
@@ -375,16 +417,21 @@ cudaError_t launch_i8(const GemvArgs& a, unsigned grid, cudaStream_t stream) {
 
 }  // namespace
 
-bool gemv_eligible(const SideView& m_side, const SideView& n_side, bool is_float) {
+static bool rows_16_byte_aligned(const SideView& x, const SideView& y) {
+  return (((uintptr_t)x.data | (uintptr_t)y.data | (uintptr_t)x.stride_w | (uintptr_t)y.stride_w) & 15) == 0;
+}
+
+bool gemv_eligible(const SideView& m_side, const SideView& n_side, int depth, bool is_float) {
   const int narrow = m_side.width < n_side.width ? m_side.width : n_side.width;
-  if (narrow < 1 || narrow > kGemvMaxNarrow) return false;
+  if (narrow < 1 || narrow > kGemvMmaMaxNarrow) return false;
   if (m_side.stride_k != 1 || n_side.stride_k != 1) return false;
   const long long wide = m_side.width < n_side.width ? n_side.width : m_side.width;
   if ((wide + kWarpsPerBlock - 1) / kWarpsPerBlock > 0x7fffffffLL) return false;
-  if (is_float) return m_side.dtype == RUYB200_F32 && n_side.dtype == RUYB200_F32;
+  if (is_float) return narrow <= kGemvMaxNarrow && m_side.dtype == RUYB200_F32 && n_side.dtype == RUYB200_F32;
   const bool m8 = m_side.dtype == RUYB200_I8 || m_side.dtype == RUYB200_U8;
   const bool n8 = n_side.dtype == RUYB200_I8 || n_side.dtype == RUYB200_U8;
-  return m8 && n8;
+  if (!(m8 && n8)) return false;
+  return narrow <= kGemvMaxNarrow || (gemv_mma_shape(narrow, wide, depth) && rows_16_byte_aligned(m_side, n_side));
 }
 
 cudaError_t launch_gemv(const SideView& m_side, const SideView& n_side, const DstView& dst, const Epilogue& ep,
@@ -409,14 +456,9 @@ cudaError_t launch_gemv(const SideView& m_side, const SideView& n_side, const Ds
     else gemv_f32_kernel<kGemvMaxNarrow><<<grid, 32 * kWarpsPerBlock, 0, stream>>>(a);
     return cudaGetLastError();
   }
-  if (narrow >= 2 && a.vec && (ep.depth & 15) == 0 && a.wide.width >= kMmaMinWide) {
-    const unsigned mgrid = (unsigned)(((long long)a.wide.width + 15) / 16);
-    const bool ws = a.wide.dtype == RUYB200_I8, ns = a.narrow.dtype == RUYB200_I8;
-    if (ws && ns) gemv_i8_mma_kernel<true, true><<<mgrid, 32 * kWarpsPerBlock, 0, stream>>>(a);
-    else if (ws) gemv_i8_mma_kernel<true, false><<<mgrid, 32 * kWarpsPerBlock, 0, stream>>>(a);
-    else if (ns) gemv_i8_mma_kernel<false, true><<<mgrid, 32 * kWarpsPerBlock, 0, stream>>>(a);
-    else gemv_i8_mma_kernel<false, false><<<mgrid, 32 * kWarpsPerBlock, 0, stream>>>(a);
-    return cudaGetLastError();
+  if (a.vec && gemv_mma_shape(narrow, a.wide.width, ep.depth)) {
+    if (narrow <= 8) return launch_i8_mma<1>(a, stream);
+    return launch_i8_mma<2>(a, stream);
   }
   if (narrow <= 1) return launch_i8<1>(a, grid, stream);
   if (narrow <= 4) return launch_i8<4>(a, grid, stream);

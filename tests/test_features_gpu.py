@@ -59,6 +59,47 @@ def test_narrow_8bit_muls_take_the_gemv_kernel(shape, types, gpu_ctx):
         assert gpu_ctx.counters()["last_kernel"] == "gemv"
 
 
+# a wide side of 1024 rows or more, 2 to 16 narrow rows and a depth that is a multiple of 16: the form of the kernel
+# that feeds 16 wide rows per CTA to register-level MMAs.  Depths of one partial step (64), whole steps plus a tail
+# (4112 = 16 steps of 256 and 16 bytes), several rounds of the CTA's 8 warps; wide rows left over past the last 16;
+# one or two tiles of 8 narrow rows; the narrow side as either operand.
+NARROW_MMA = [(1030, 4112, 5), (3, 2064, 1100), (2048, 96, 9), (1024, 64, 16), (1500, 784, 13), (10, 272, 1024),
+              (1040, 16, 2), (4099, 2304, 15)]
+
+
+@pytest.mark.parametrize("shape", NARROW_MMA, ids=lambda s: "x".join(map(str, s)))
+@pytest.mark.parametrize("types", [("int8", "int8", "int8"), ("uint8", "uint8", "uint8"), ("int8", "uint8", "int16"),
+                                   ("uint8", "int8", "int32")], ids=lambda t: "-".join(t))
+def test_up_to_16_narrow_rows_on_a_wide_operand_take_the_gemv_kernel(shape, types, gpu_ctx):
+    narrow_is_rhs = shape[2] < shape[0]
+    for symmetric in (False, True):
+        # depth-contiguous operands: a row-major LHS and a column-major RHS
+        for dst_order, ch in (("C", ChannelDimension.kRow), ("R", ChannelDimension.kCol)):
+            c = cases.random_case(*shape, *types, orders="RC" + dst_order, perchannel=True, channel=ch, symmetric=symmetric,
+                                  seed=sum(shape) + int(symmetric))
+            exact(c, gpu_ctx)
+            assert gpu_ctx.counters()["last_kernel"] == "gemv", (shape, narrow_is_rhs)
+
+
+def test_more_than_8_narrow_rows_need_aligned_rows_for_the_gemv_kernel(gpu_ctx):
+    # a depth that is not a multiple of 16, or rows off the 16-byte grid: packing and the tensor core
+    c = cases.random_case(2048, 100, 12, "int8", "int8", "int8", orders="RCC", perchannel=True, seed=21)
+    exact(c, gpu_ctx)
+    assert gpu_ctx.counters()["last_kernel"] == "tc_i8"
+    c = cases.random_case(2048, 128 + 16, 12, "int8", "int8", "int8", orders="RCC", extra_stride=3, seed=22)
+    exact(c, gpu_ctx)
+    assert gpu_ctx.counters()["last_kernel"] == "tc_i8"
+    # a cached weight matrix is read in its packed form, whose rows are aligned
+    c = cases.random_case(2048, 640, 12, "int8", "int8", "int8", orders="RCC", perchannel=True, seed=23, lhs_cache=CachePolicy.kAlwaysCache)
+    exact(c, gpu_ctx, where="host")
+    assert gpu_ctx.counters()["last_kernel"] == "gemv"
+    # under 1024 wide rows, and from 17 narrow rows on, the tensor-core kernels keep the mul
+    for shape in ((1000, 256, 12), (2048, 256, 17)):
+        c = cases.random_case(*shape, "int8", "int8", "int8", orders="RCC", perchannel=True, seed=24)
+        exact(c, gpu_ctx)
+        assert gpu_ctx.counters()["last_kernel"] != "gemv"
+
+
 def test_narrow_muls_other_layouts_and_host_operands(gpu_ctx):
     # operands that are not depth-contiguous cannot be streamed: they go through packing and the tensor core
     c = cases.random_case(300, 200, 4, "int8", "int8", "int8", orders="CRC", perchannel=True, seed=3)
