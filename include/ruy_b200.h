@@ -317,7 +317,9 @@ RUYB200_API int ruyb200_ctx_set_peer_wait_ms(ruyb200_ctx* ctx, uint32_t ms);
  * `src` + `side` (0 = LHS, 1 = RHS) name the entry exactly as a later ruyb200_mul will look it up; import never
  * reads src->data, it only uses the pointer as the key.  After a successful import the next mul with that
  * operand is a cache hit and launches no packing kernel. */
-#define RUYB200_CACHE_FORMAT_ROWS16 1u   /* [width][depth rounded up to 16 bytes] depth-contiguous rows, int32 sums[width] */
+#define RUYB200_CACHE_FORMAT_ROWS16 1u   /* [width][packed_depth] depth-contiguous rows, int32 sums[width]; packed_depth is
+                                          * the depth rounded up to 16 bytes, or, for 8-bit rows of 256 bytes or more, to
+                                          * 128 bytes (what this library writes; both are accepted) */
 typedef struct ruyb200_cache_blob {
   uint32_t abi_version;
   uint32_t format;

@@ -460,6 +460,15 @@ int packed_depth_for(int depth, int dtype) {
   return std::max(per16, (depth + per16 - 1) / per16 * per16);
 }
 
+// Row length of the packed form this library makes for its own kernels (cache entries, per-call packing).  8-bit rows
+// of 256 bytes or more are padded to whole 128-byte lines: the tensor-core kernel's copy engine fetches 128-byte box
+// rows, and rows that start 16 bytes into a line make every one of them straddle two lines (measured 4096 x 4100 x
+// 4096, rows of 4112 bytes: 68 us against 53 us for depth 4096).
+int tc_packed_depth(int depth, int dtype) {
+  if (dtype_size(dtype) == 1 && depth >= 256) return (depth + 127) / 128 * 128;
+  return packed_depth_for(depth, dtype);
+}
+
 // A fully resolved mul: device pointers only, canonical (n = destination-contiguous) view.
 struct Resolved {
   SideView m_side, n_side;
@@ -474,8 +483,10 @@ struct Resolved {
 //   device   -> used in place
 // `need_sums`: the other side has a non-zero zero point (integer case).
 // `want_packed`: the tensor-core kernel will run and this operand is not in its layout.
+// `sums_if_packed`: sums the caller can do without (the tensor-core kernel can make its m-side sums itself, at the
+// price of one-CTA tiles) but takes when a packing pass runs anyway and yields them for free.
 int prepare_side(ruyb200_ctx* ctx, const ruyb200_matrix& m, int side, int depth, bool cache_it, bool need_sums,
-                 bool tc_path, SideView* out, const int32_t** sums_out) {
+                 bool tc_path, SideView* out, const int32_t** sums_out, bool sums_if_packed = false) {
   *sums_out = nullptr;
   const bool integer = m.dtype != RUYB200_F32 && m.dtype != RUYB200_F64;
   SideView src = side_view(m, side, m.data);
@@ -507,7 +518,7 @@ int prepare_side(ruyb200_ctx* ctx, const ruyb200_matrix& m, int side, int depth,
     auto it = ctx->cache.find(key);
     if (it == ctx->cache.end()) {
       ctx->counters[2]++;
-      const int pd = packed_depth_for(depth, m.dtype);
+      const int pd = tc_packed_depth(depth, m.dtype);
       const size_t data_bytes = ((size_t)src.width * pd * esz + 255) & ~size_t(255);
       const size_t sums_bytes = integer ? (((size_t)src.width * 4 + 255) & ~size_t(255)) : 0;
       const size_t total = data_bytes + sums_bytes;
@@ -560,10 +571,11 @@ int prepare_side(ruyb200_ctx* ctx, const ruyb200_matrix& m, int side, int depth,
   const bool layout_ok = v.stride_k == 1 && ((uintptr_t)v.data % 16 == 0) && ((v.stride_w * (int64_t)esz) % 16 == 0);
   if (tc_path && !layout_ok) {
     // PackImpl: re-tile into the depth-contiguous padded layout, sums on the way
-    const int pd = packed_depth_for(depth, m.dtype);
+    const int pd = tc_packed_depth(depth, m.dtype);
     void* packed = ctx->arena.alloc((size_t)v.width * pd * esz);
-    int32_t* sums = need_sums ? (int32_t*)ctx->arena.alloc(sizeof(int32_t) * v.width) : nullptr;
-    if (!packed || (need_sums && !sums)) return fail(RUYB200_ERR_OOM, "arena allocation failed");
+    const bool with_sums = (need_sums || sums_if_packed) && integer;
+    int32_t* sums = with_sums ? (int32_t*)ctx->arena.alloc(sizeof(int32_t) * v.width) : nullptr;
+    if (!packed || (with_sums && !sums)) return fail(RUYB200_ERR_OOM, "arena allocation failed");
     cudaError_t ce = launch_pack(v, depth, pd, packed, sums, ctx->stream);
     ctx->counters[0]++;
     if (ce != cudaSuccess) return fail(RUYB200_ERR_CUDA, "pack launch: %s", cudaGetErrorString(ce));
@@ -875,14 +887,14 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
     lhs_v = side_view(d.lhs, 0, m_dev);
   } else {
     rc = prepare_side(ctx, d.lhs, 0, depth, !is_f64 && should_cache(d.lhs, d.rhs.cols), need_lhs_sums && !(tc && !m_is_rhs), tc, &lhs_v,
-                      &lhs_sums);
+                      &lhs_sums, need_lhs_sums);
     if (rc) return rc;
   }
   if (m_streamed && m_is_rhs) {
     rhs_v = side_view(d.rhs, 1, m_dev);
   } else {
     rc = prepare_side(ctx, d.rhs, 1, depth, !is_f64 && should_cache(d.rhs, d.lhs.rows), need_rhs_sums && !(tc && m_is_rhs), tc, &rhs_v,
-                      &rhs_sums);
+                      &rhs_sums, need_rhs_sums);
     if (rc) return rc;
   }
 
@@ -1091,7 +1103,7 @@ int parse_blob(const void* blob, size_t n, BlobHeader* out) {
   if (h.format != RUYB200_CACHE_FORMAT_ROWS16) return fail(RUYB200_ERR_INVALID, "cache blob: unknown tile format %u", h.format);
   if (h.dtype > RUYB200_F32 || h.dtype == RUYB200_I32 || h.side > 1 || h.width <= 0 || h.depth <= 0)
     return fail(RUYB200_ERR_INVALID, "cache blob: bad field");
-  if (h.packed_depth != packed_depth_for(h.depth, h.dtype)) return fail(RUYB200_ERR_INVALID, "cache blob: packed depth does not match this library's layout");
+  if (h.packed_depth != packed_depth_for(h.depth, h.dtype) && h.packed_depth != tc_packed_depth(h.depth, h.dtype)) return fail(RUYB200_ERR_INVALID, "cache blob: packed depth does not match this library's layout");
   const uint64_t want_data = (uint64_t)h.width * h.packed_depth * dtype_size(h.dtype);
   const uint64_t want_sums = h.has_sums ? (uint64_t)h.width * 4 : 0;
   if ((h.has_sums != 0) != (h.dtype != RUYB200_F32) || h.data_bytes != want_data || h.sums_bytes != want_sums ||

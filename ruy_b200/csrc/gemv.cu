@@ -94,7 +94,44 @@ __global__ void __launch_bounds__(32 * kWarpsPerBlock) gemv_i8_kernel(const Gemv
   int k = 0;
   if (a.vec) {
     const int pieces = depth / 16;
-    for (int c = lane; c < pieces; c += 32) {
+    int c = lane;
+    // four pieces per lane and trip, all loads of the wide row first: more bytes in flight per warp
+    for (; c + 96 < pieces; c += 128) {
+      uint4 x[4];
+#pragma unroll
+      for (int u = 0; u < 4; u++) x[u] = __ldcs(reinterpret_cast<const uint4*>(wrow) + c + 32 * u);
+      if (a.need_wsum) {
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+          wsum = sum4<kWideSigned>(x[u].x, wsum);
+          wsum = sum4<kWideSigned>(x[u].y, wsum);
+          wsum = sum4<kWideSigned>(x[u].z, wsum);
+          wsum = sum4<kWideSigned>(x[u].w, wsum);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < kNarrow; j++) {
+        if (j < a.narrow.width) {
+          uint4 y[4];
+#pragma unroll
+          for (int u = 0; u < 4; u++) y[u] = __ldg(reinterpret_cast<const uint4*>(nbase + j * nstride) + c + 32 * u);
+#pragma unroll
+          for (int u = 0; u < 4; u++) {
+            acc[j] = dot4<kWideSigned, kNarrowSigned>(x[u].x, y[u].x, acc[j]);
+            acc[j] = dot4<kWideSigned, kNarrowSigned>(x[u].y, y[u].y, acc[j]);
+            acc[j] = dot4<kWideSigned, kNarrowSigned>(x[u].z, y[u].z, acc[j]);
+            acc[j] = dot4<kWideSigned, kNarrowSigned>(x[u].w, y[u].w, acc[j]);
+            if (a.need_nsum) {
+              nsum[j] = sum4<kNarrowSigned>(y[u].x, nsum[j]);
+              nsum[j] = sum4<kNarrowSigned>(y[u].y, nsum[j]);
+              nsum[j] = sum4<kNarrowSigned>(y[u].z, nsum[j]);
+              nsum[j] = sum4<kNarrowSigned>(y[u].w, nsum[j]);
+            }
+          }
+        }
+      }
+    }
+    for (; c < pieces; c += 32) {
       const uint4 x = __ldcs(reinterpret_cast<const uint4*>(wrow) + c);   // streamed: read exactly once
       if (a.need_wsum) {
         wsum = sum4<kWideSigned>(x.x, wsum);
@@ -358,7 +395,31 @@ __global__ void __launch_bounds__(32 * kWarpsPerBlock) gemv_f32_kernel(const Gem
   int k = 0;
   if (a.vec) {
     const int pieces = depth / 4;
-    for (int c = lane; c < pieces; c += 32) {
+    int c = lane;
+    // one narrow row: four pieces per lane and trip, all loads of the wide row first, for more bytes in flight per warp
+    // (8192 x 8192 x 1: 67.6 -> 58.4 us; with four narrow rows the same loop was 5 % slower, so they keep single pieces)
+    for (; kNarrow == 1 && c + 96 < pieces; c += 128) {
+      float4 x[4];
+#pragma unroll
+      for (int u = 0; u < 4; u++) x[u] = __ldcs(reinterpret_cast<const float4*>(wrow) + c + 32 * u);
+#pragma unroll
+      for (int j = 0; j < kNarrow; j++) {
+        if (j < a.narrow.width) {
+          float4 y[4];
+#pragma unroll
+          for (int u = 0; u < 4; u++) y[u] = __ldg(reinterpret_cast<const float4*>(nbase + j * nstride) + c + 32 * u);
+#pragma unroll
+          for (int u = 0; u < 4; u++) {
+            float part = x[u].x * y[u].x;
+            part = fmaf(x[u].y, y[u].y, part);
+            part = fmaf(x[u].z, y[u].z, part);
+            part = fmaf(x[u].w, y[u].w, part);
+            kahan_add(sum[j], comp[j], part);
+          }
+        }
+      }
+    }
+    for (; c < pieces; c += 32) {
       const float4 x = __ldcs(reinterpret_cast<const float4*>(wrow) + c);
 #pragma unroll
       for (int j = 0; j < kNarrow; j++) {

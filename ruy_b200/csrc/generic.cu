@@ -146,43 +146,69 @@ __global__ void __launch_bounds__(256) generic_f64_kernel(SideView ms, SideView 
   }
 }
 
-// One warp per width-row; lanes stride over depth.
-__global__ void sums_kernel(SideView s, int depth, int32_t* sums) {
-  const int w = blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
-  if (w >= s.width) return;
-  const int lane = threadIdx.x % 32;
-  uint32_t acc = 0;
-  const bool vec = s.stride_k == 1 && (s.dtype == RUYB200_I8 || s.dtype == RUYB200_U8) &&
-                   (((uintptr_t)s.data + (uint64_t)w * s.stride_w) % 16 == 0);
-  int k = 0;
-  if (vec) {
-    const uint4* row = (const uint4*)((const char*)s.data + (int64_t)w * s.stride_w);
-    const int nvec = depth / 16;
-    for (int v = lane; v < nvec; v += 32) {
-      const uint4 q = row[v];
-      if (s.dtype == RUYB200_I8) {
-        int a = 0;
-        a = __dp4a((int)q.x, 0x01010101, a);
-        a = __dp4a((int)q.y, 0x01010101, a);
-        a = __dp4a((int)q.z, 0x01010101, a);
-        a = __dp4a((int)q.w, 0x01010101, a);
-        acc += (uint32_t)a;
-      } else {
-        unsigned a = 0;
-        a = __dp4a(q.x, 0x01010101u, a);
-        a = __dp4a(q.y, 0x01010101u, a);
-        a = __dp4a(q.z, 0x01010101u, a);
-        a = __dp4a(q.w, 0x01010101u, a);
-        acc += a;
-      }
-    }
-    k = nvec * 16;
+// Sum of the 16 bytes of q, each taken as signed or unsigned.
+__device__ __forceinline__ uint32_t sum16(const uint4 q, bool is_signed) {
+  if (is_signed) {
+    int a = 0;
+    a = __dp4a((int)q.x, 0x01010101, a);
+    a = __dp4a((int)q.y, 0x01010101, a);
+    a = __dp4a((int)q.z, 0x01010101, a);
+    a = __dp4a((int)q.w, 0x01010101, a);
+    return (uint32_t)a;
   }
-  for (int kk = k + lane; kk < depth; kk += 32) {
-    acc += (uint32_t)load_as_int(s.data, s.dtype, (int64_t)w * s.stride_w + (int64_t)kk * s.stride_k);
+  unsigned a = 0;
+  a = __dp4a(q.x, 0x01010101u, a);
+  a = __dp4a(q.y, 0x01010101u, a);
+  a = __dp4a(q.z, 0x01010101u, a);
+  a = __dp4a(q.w, 0x01010101u, a);
+  return a;
+}
+
+// kThreadsPerRow threads (a warp, or the whole CTA of 256) per width-row, striding over depth.  A CTA per row is for
+// operands of few rows: with one warp per row a 16-row operand of depth 16384 is a chain of 32 dependent-latency
+// trips on 16 warps (about 45 us); 256 threads with four loads in flight each finish it in a few microseconds.
+template <int kThreadsPerRow>
+__global__ void __launch_bounds__(256) sums_kernel(SideView s, int depth, int32_t* sums) {
+  __shared__ uint32_t warp_sums[8];
+  const int w = kThreadsPerRow == 256 ? blockIdx.x : blockIdx.x * 8 + threadIdx.x / 32;
+  const int lane = threadIdx.x % kThreadsPerRow;
+  uint32_t acc = 0;
+  if (w < s.width) {
+    const bool is_signed = s.dtype == RUYB200_I8;
+    const bool vec = s.stride_k == 1 && (s.dtype == RUYB200_I8 || s.dtype == RUYB200_U8) &&
+                     (((uintptr_t)s.data + (uint64_t)w * s.stride_w) % 16 == 0);
+    int k = 0;
+    if (vec) {
+      const uint4* row = (const uint4*)((const char*)s.data + (int64_t)w * s.stride_w);
+      const int nvec = depth / 16;
+      int v = lane;
+      for (; v + 3 * kThreadsPerRow < nvec; v += 4 * kThreadsPerRow) {
+        uint4 q[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) q[u] = row[v + u * kThreadsPerRow];
+#pragma unroll
+        for (int u = 0; u < 4; u++) acc += sum16(q[u], is_signed);
+      }
+      for (; v < nvec; v += kThreadsPerRow) acc += sum16(row[v], is_signed);
+      k = nvec * 16;
+    }
+    for (int kk = k + lane; kk < depth; kk += kThreadsPerRow) {
+      acc += (uint32_t)load_as_int(s.data, s.dtype, (int64_t)w * s.stride_w + (int64_t)kk * s.stride_k);
+    }
   }
   acc = __reduce_add_sync(0xffffffffu, acc);
-  if (lane == 0) sums[w] = (int32_t)acc;
+  if (kThreadsPerRow == 32) {
+    if (w < s.width && lane == 0) sums[w] = (int32_t)acc;
+    return;
+  }
+  if (threadIdx.x % 32 == 0) warp_sums[threadIdx.x / 32] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0 && w < s.width) {
+    uint32_t total = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) total += warp_sums[i];
+    sums[w] = (int32_t)total;
+  }
 }
 
 // Packing: out[w][k] (depth-contiguous, packed_depth elements per row, zero padded) and sums.
@@ -227,6 +253,124 @@ __global__ void __launch_bounds__(256) pack_kernel(SideView s, int depth, int pa
   }
 }
 
+// 16 bytes from any address, of which the first n_valid (1 or more) exist; the rest read as zero.  One or two aligned
+// 16-byte loads (only of 16-byte granules that hold at least one existing byte), then word selects and funnel shifts:
+// consecutive lanes reading consecutive pieces stay fully coalesced whatever the alignment.
+__device__ __forceinline__ uint4 load16_any(const uint8_t* p, int n_valid) {
+  const uintptr_t addr = (uintptr_t)p;
+  const int nv = n_valid < 16 ? n_valid : 16;
+  const int sh = (int)(addr & 15);
+  const uint4* base = reinterpret_cast<const uint4*>(addr - sh);
+  const uint4 a = base[0];
+  if (sh == 0 && nv == 16) return a;
+  uint4 b = make_uint4(0u, 0u, 0u, 0u);
+  if (sh + nv > 16) b = base[1];
+  const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+  const int wo = sh >> 2, bits = 8 * (sh & 3);
+  uint32_t x[5];
+#pragma unroll
+  for (int i = 0; i < 5; i++) x[i] = wo == 0 ? w[i] : (wo == 1 ? w[i + 1] : (wo == 2 ? w[i + 2] : w[i + 3 < 8 ? i + 3 : 7]));
+  uint32_t o[4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    o[i] = __funnelshift_r(x[i], x[i + 1], bits);
+    const int keep = nv - 4 * i;   // bytes of this word that exist
+    if (keep <= 0) o[i] = 0u;
+    else if (keep < 4) o[i] &= (1u << (8 * keep)) - 1u;
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// 8-bit operands stored depth-contiguous whose rows are not on 16-byte boundaries (or not as long as the packed
+// depth): a warp per row and slab of depth, every lane 16 packed bytes per trip, sums on the way.  With more than one
+// slab (gridDim.y) the sums are added atomically to a zeroed buffer.
+__global__ void __launch_bounds__(256) pack8_rows_kernel(SideView s, int depth, int packed_depth, uint8_t* out, int32_t* sums,
+                                                         int slab) {
+  const int lane = threadIdx.x % 32;
+  const long long w = (long long)blockIdx.x * 8 + threadIdx.x / 32;
+  if (w >= s.width) return;
+  const bool is_signed = s.dtype == RUYB200_I8;
+  const uint8_t* row = (const uint8_t*)s.data + w * s.stride_w;
+  uint8_t* orow = out + w * packed_depth;
+  const int k_begin = blockIdx.y * slab;
+  const int k_end = k_begin + slab < packed_depth ? k_begin + slab : packed_depth;
+  uint32_t acc = 0;
+  int k = k_begin + 16 * lane;
+  for (; k + 512 < k_end; k += 1024) {   // two pieces per trip: more loads in flight
+    const uint4 q0 = depth - k > 0 ? load16_any(row + k, depth - k) : make_uint4(0u, 0u, 0u, 0u);
+    const uint4 q1 = depth - k - 512 > 0 ? load16_any(row + k + 512, depth - k - 512) : make_uint4(0u, 0u, 0u, 0u);
+    *reinterpret_cast<uint4*>(orow + k) = q0;
+    *reinterpret_cast<uint4*>(orow + k + 512) = q1;
+    acc += sum16(q0, is_signed) + sum16(q1, is_signed);
+  }
+  for (; k < k_end; k += 512) {
+    const uint4 q = depth - k > 0 ? load16_any(row + k, depth - k) : make_uint4(0u, 0u, 0u, 0u);
+    *reinterpret_cast<uint4*>(orow + k) = q;
+    acc += sum16(q, is_signed);
+  }
+  if (sums) {
+    acc = __reduce_add_sync(0xffffffffu, acc);
+    if (lane == 0) {
+      if (gridDim.y == 1) sums[w] = (int32_t)acc;
+      else atomicAdd(&sums[w], (int32_t)acc);
+    }
+  }
+}
+
+// 8-bit operands stored width-contiguous (a column-major LHS, a row-major RHS): tiles of 64 widths x 64 of depth are
+// read as 16-byte runs along the width, turned in shared memory, and written as 16-byte runs along the depth.
+__global__ void __launch_bounds__(256) pack8_transpose_kernel(SideView s, int depth, int packed_depth, uint8_t* out,
+                                                              int32_t* sums, int slab) {
+  __shared__ uint32_t tile[64][17];   // [depth][width / 4], one word of padding per row
+  const bool is_signed = s.dtype == RUYB200_I8;
+  const int t = threadIdx.x;
+  const long long w0 = (long long)blockIdx.x * 64;
+  const int k_begin = blockIdx.y * slab;
+  const int k_end = k_begin + slab < packed_depth ? k_begin + slab : packed_depth;
+  const uint8_t* src = (const uint8_t*)s.data;
+  const uint8_t* tile_bytes = reinterpret_cast<const uint8_t*>(&tile[0][0]);
+  uint32_t acc = 0;
+  for (int k0 = k_begin; k0 < k_end; k0 += 64) {
+    {
+      const int k = k0 + t / 4, seg = t % 4;
+      const long long n_valid = s.width - (w0 + 16 * seg);
+      uint4 q = make_uint4(0u, 0u, 0u, 0u);
+      if (k < depth && n_valid > 0) q = load16_any(src + (int64_t)k * s.stride_k + w0 + 16 * seg, n_valid > 16 ? 16 : (int)n_valid);
+      tile[t / 4][4 * seg + 0] = q.x;
+      tile[t / 4][4 * seg + 1] = q.y;
+      tile[t / 4][4 * seg + 2] = q.z;
+      tile[t / 4][4 * seg + 3] = q.w;
+    }
+    __syncthreads();
+    {
+      const int w = t / 4, kseg = t % 4;
+      uint32_t o[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        uint32_t v = 0;
+#pragma unroll
+        for (int b = 0; b < 4; b++) v |= (uint32_t)tile_bytes[(16 * kseg + 4 * i + b) * 68 + w] << (8 * b);
+        o[i] = v;
+      }
+      const uint4 q = make_uint4(o[0], o[1], o[2], o[3]);
+      if (w0 + w < s.width && k0 + 16 * kseg < k_end) {
+        *reinterpret_cast<uint4*>(out + (w0 + w) * packed_depth + k0 + 16 * kseg) = q;
+        acc += sum16(q, is_signed);
+      }
+    }
+    __syncthreads();
+  }
+  if (sums) {
+    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+    const long long w = w0 + t / 4;
+    if (t % 4 == 0 && w < s.width) {
+      if (gridDim.y == 1) sums[w] = (int32_t)acc;
+      else atomicAdd(&sums[w], (int32_t)acc);
+    }
+  }
+}
+
 }  // namespace
 
 cudaError_t launch_generic(const SideView& m_side, const SideView& n_side, const DstView& dst,
@@ -266,15 +410,40 @@ cudaError_t launch_generic_f64(const SideView& m_side, const SideView& n_side, c
 
 cudaError_t launch_sums(const SideView& side, int depth, int32_t* sums, cudaStream_t stream) {
   if (side.width <= 0) return cudaSuccess;
-  const int warps_per_block = 8;
-  const int grid = (side.width + warps_per_block - 1) / warps_per_block;
-  sums_kernel<<<grid, warps_per_block * 32, 0, stream>>>(side, depth, sums);
+  // a CTA per row while that still leaves every SM several rows' worth of loads in flight
+  if (side.width <= 2048 && depth >= 2048) {
+    sums_kernel<256><<<side.width, 256, 0, stream>>>(side, depth, sums);
+  } else {
+    sums_kernel<32><<<(side.width + 7) / 8, 256, 0, stream>>>(side, depth, sums);
+  }
   return cudaGetLastError();
 }
 
 cudaError_t launch_pack(const SideView& side, int depth, int packed_depth, void* packed,
                         int32_t* sums, cudaStream_t stream) {
   if (side.width <= 0) return cudaSuccess;
+  const bool is8 = side.dtype == RUYB200_I8 || side.dtype == RUYB200_U8;
+  if (is8 && (side.stride_k == 1 || side.stride_w == 1) && ((uintptr_t)packed & 15) == 0 && packed_depth % 16 == 0) {
+    // the vector kernels; the depth is cut into slabs (gridDim.y) until the launch has a few thousand warps
+    const bool rows = side.stride_k == 1;
+    const int unit = rows ? 512 : 64;                     // depth bytes per trip
+    const long long blocks_x = rows ? ((long long)side.width + 7) / 8 : ((long long)side.width + 63) / 64;
+    const long long want = (1024 + blocks_x - 1) / blocks_x;
+    const int max_slabs = (packed_depth + unit - 1) / unit;
+    const int n_slabs = (int)(want < 1 ? 1 : (want > max_slabs ? max_slabs : want));
+    const int slab = ((packed_depth + n_slabs - 1) / n_slabs + unit - 1) / unit * unit;
+    const int blocks_y = (packed_depth + slab - 1) / slab;
+    if (blocks_x <= 0x7fffffffLL && blocks_y <= 65535) {
+      if (sums && blocks_y > 1) {
+        cudaError_t ce = cudaMemsetAsync(sums, 0, sizeof(int32_t) * (size_t)side.width, stream);
+        if (ce != cudaSuccess) return ce;
+      }
+      const dim3 grid((unsigned)blocks_x, (unsigned)blocks_y);
+      if (rows) pack8_rows_kernel<<<grid, 256, 0, stream>>>(side, depth, packed_depth, (uint8_t*)packed, sums, slab);
+      else pack8_transpose_kernel<<<grid, 256, 0, stream>>>(side, depth, packed_depth, (uint8_t*)packed, sums, slab);
+      return cudaGetLastError();
+    }
+  }
   const int grid = (side.width + 31) / 32;
   switch (side.dtype) {
     case RUYB200_I8:
