@@ -209,6 +209,7 @@ struct ruyb200_ctx {
   int force_pair = -1;
   int force_block_n = 0;
   bool no_shallow = false;   // RUYB200_NO_SHALLOW=1: keep shallow-depth muls on the general tensor-core kernel
+  int tc_f32_max_depth = 1 << 30;   // RUYB200_TC_F32_MAX_DEPTH: deepest fp32 mul that goes to the tensor-core kernel (measurements)
   // synchronous muls with large host operands are cut into chunks that move on these two streams while the
   // kernel of another chunk runs on `stream` (created on first use)
   cudaStream_t copy_in = nullptr;
@@ -830,11 +831,12 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
     if (lhs_ok && rhs_ok && !few_deep_rows) kernel = RUYB200_KERNEL_GEMV;
   }
   // fp32 muls that fill tensor-core tiles go to the 3 x TF32 kernel; small ones stay on the FFMA kernel, whose single
-  // launch costs less than the split pre-pass, and so do very deep ones: the tensor core truncates when it adds, each
-  // 32-deep chain leaves an error of a few 1e-7, and over more than 2048 of depth their sum (measured 1.5e-5 at depth
-  // 16384) would pass the 1e-5 this library promises, which the FFMA kernel's compensated sums keep at any depth
+  // launch costs less than the split pre-pass.  Depth does not decide: both kernels add 32-deep chains into a compensated
+  // total, their error grows alike with the square root of the depth, and measured against double precision the
+  // tensor-core kernel is the closer one at every depth (1024 x 4096 x 1024: 8.0e-6 against 1.02e-5 of max(|ref|, 1);
+  // depth 16384: 1.65e-5 against 1.84e-5) while being five to ten times faster.
   if (kernel == RUYB200_KERNEL_SGEMM && ctx->force_kernel != RUYB200_KERNEL_SGEMM && std::min(d.dst.rows, d.dst.cols) >= 64 &&
-      depth >= 32 && depth <= 2048 && (double)d.dst.rows * d.dst.cols * depth >= (double)(1 << 21)) {
+      depth >= 32 && depth <= ctx->tc_f32_max_depth && (double)d.dst.rows * d.dst.cols * depth >= (double)(1 << 21)) {
     kernel = RUYB200_KERNEL_TC_F32;
   }
   const bool tc = kernel == RUYB200_KERNEL_TC_I8;
@@ -1184,6 +1186,8 @@ int ruyb200_ctx_create_on_stream(int device, void* cuda_stream, ruyb200_ctx** ou
     const char* colon = strchr(tile, ':');
     if (colon && atoi(colon + 1) > 0) ctx->force_block_n = atoi(colon + 1);
   }
+  const char* fd = getenv("RUYB200_TC_F32_MAX_DEPTH");
+  if (fd && atoi(fd) >= 32) ctx->tc_f32_max_depth = atoi(fd);
   const char* ns = getenv("RUYB200_NO_SHALLOW");
   ctx->no_shallow = ns && *ns && *ns != '0';
   const char* nc = getenv("RUYB200_NO_CHUNKS");

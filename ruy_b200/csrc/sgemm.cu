@@ -3,7 +3,9 @@
 // FFMA in fp32 over chunks of 32 depth steps, and the chunk sums are folded into the running total
 // with a compensated (Kahan) addition.  A plain fp32 chain over depth 1024 drifts by a few 1e-5 from
 // a double-precision reference once the partial sums reach ~10; the two-level sum stays below 1e-5
-// (and a single-pass TF32 tensor-core product would be at 1e-3).
+// of max(|ref|, 1) up to a depth of about 4096 on uniform [-1, 1] data (measured 1.0e-5 there, 1.8e-5 at 16384: the
+// 32-deep chains' own rounding adds up with the square root of the depth), and a single-pass TF32 tensor-core product
+// would be at 1e-3.
 #include "common.cuh"
 
 namespace ruyb200 {
