@@ -872,7 +872,8 @@ def verify_case(case, got):
 def run_small_arm(args):
     """The remaining benchmark configurations, one JSON line each (single GPU, device-resident operands): config 0
     (256x512x128 int8), config 1 (the five fp32 shapes) and config 4 (the uint8 pointwise-conv layers at batch 1
-    and 64).  Timing follows ruy's cold protocol (ruy/test.h:2054-2080): the activations and the destination rotate
+    and 64); workload "narrow" adds config 3's weights against 1, 8 and 16 activation columns (one pass over the
+    weights per mul, HBM-bound).  Timing follows ruy's cold protocol (ruy/test.h:2054-2080): the activations and the destination rotate
     over enough copies to exceed L2 (at least 256 MB, at most 48 copies), one pass over the copies through the
     stream-ordered entry point is captured in a CUDA graph, and several replays run between ONE pair of events, so
     neither the event overhead nor a cache flush is inside the figure.  Every result is checked before its line is
@@ -897,6 +898,10 @@ def run_small_arm(args):
     if args.workload in ("c4", "small"):
         for batch in (1, 64):
             todo.extend(cases.config4(layer, batch=batch) for layer in range(len(cases.CONFIG4_LAYERS)))
+    if args.workload == "narrow":
+        # config 3's generator with a handful of columns: a weight matrix streamed once per mul (the narrow kernels)
+        for rows, cols in ((4096, 1), (4096, 8), (16384, 1), (16384, 8), (16384, 16)):
+            todo.append(cases.config3(rows=rows, depth=rows, cols=cols, dst="int8"))
     if args.only:
         todo = [c for c in todo if args.only in c.name]
         if not todo:
@@ -996,7 +1001,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c3_i8", choices=["c3_i8", "c3_i32", "c2", "c0", "c1", "c4", "small"])
+    ap.add_argument("--workload", default="c3_i8", choices=["c3_i8", "c3_i32", "c2", "c0", "c1", "c4", "small", "narrow"])
     ap.add_argument("--muls", type=int, default=16384, help="number of muls of workload c2")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-c2", action="store_true", help="leave the small-mul sub-record out of the default line")
@@ -1011,7 +1016,7 @@ def main():
         run_reference_arm(args)
     elif args.workload == "c2":
         run_c2_arm(args)
-    elif args.workload in ("c0", "c1", "c4", "small"):
+    elif args.workload in ("c0", "c1", "c4", "small", "narrow"):
         run_small_arm(args)
     else:
         run_gpu_arm(args)

@@ -224,10 +224,10 @@ __device__ __forceinline__ void mma_16x8x32(int32_t (&d)[4], uint32_t a0, uint32
 // index is a permutation of the byte index, the same for both operands, so the sums over k are unchanged.  The
 // zero-point sums still use dp4a, one per loaded word.  The warps' partial sums meet in shared memory and warp 0
 // finishes.  Needs 16-byte aligned rows and a depth that is a multiple of 16.
-template <bool kWideSigned, bool kNarrowSigned, int kTiles>
-__global__ void __launch_bounds__(32 * kWarpsPerBlock) gemv_i8_mma_kernel(const GemvArgs a) {
+template <bool kWideSigned, bool kNarrowSigned, int kTiles, int kWarps>
+__global__ void __launch_bounds__(32 * kWarps, kWarps == 2 ? 8 : (kTiles == 2 ? 16 : 24) / kWarps) gemv_i8_mma_kernel(const GemvArgs a) {
   constexpr int kPart = 5 * kTiles + 2;  // per lane: 4 accumulators and a narrow sum per tile of 8 narrow rows, 2 wide sums
-  __shared__ int32_t part[kWarpsPerBlock - 1][kPart][32];
+  __shared__ int32_t part[kWarps - 1][kPart][32];
   const int lane = threadIdx.x % 32, warp = threadIdx.x / 32;
   const int g = lane >> 2, t = lane & 3;
   const long long w0 = (long long)blockIdx.x * 16;
@@ -255,57 +255,79 @@ __global__ void __launch_bounds__(32 * kWarpsPerBlock) gemv_i8_mma_kernel(const 
   const int pieces = depth / 16;
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
   // one step: all of its loads first (8 of the wide rows, 4 per tile of narrow rows), then the MMAs and the sums
-  auto step = [&](const int base, auto whole_tag) {
-    constexpr bool kWhole = decltype(whole_tag)::value;
+  struct Frag {
     uint4 xa[4], xb[4], y[kTiles][4];
+  };
+  auto load = [&](Frag& f, const int base, auto whole_tag) {
+    constexpr bool kWhole = decltype(whole_tag)::value;
 #pragma unroll
     for (int i = 0; i < 4; i++) {
       const int p = base + t + 4 * i;
-      xa[i] = (kWhole || p < pieces) ? __ldcs(row0 + p) : zero;
-      xb[i] = (kWhole || p < pieces) ? __ldcs(row1 + p) : zero;
+      f.xa[i] = (kWhole || p < pieces) ? __ldcs(row0 + p) : zero;
+      f.xb[i] = (kWhole || p < pieces) ? __ldcs(row1 + p) : zero;
     }
 #pragma unroll
     for (int j = 0; j < kTiles; j++) {
 #pragma unroll
       for (int i = 0; i < 4; i++) {
         const int p = base + t + 4 * i;
-        y[j][i] = (have_n[j] && (kWhole || p < pieces)) ? __ldg(nrow[j] + p) : zero;
+        f.y[j][i] = (have_n[j] && (kWhole || p < pieces)) ? __ldg(nrow[j] + p) : zero;
       }
     }
+  };
+  auto compute = [&](const Frag& f) {
 #pragma unroll
     for (int j = 0; j < kTiles; j++) {
 #pragma unroll
       for (int i = 0; i < 4; i++) {
-        mma_16x8x32<kWideSigned, kNarrowSigned>(c[j], xa[i].x, xb[i].x, xa[i].y, xb[i].y, y[j][i].x, y[j][i].y);
-        mma_16x8x32<kWideSigned, kNarrowSigned>(c[j], xa[i].z, xb[i].z, xa[i].w, xb[i].w, y[j][i].z, y[j][i].w);
+        mma_16x8x32<kWideSigned, kNarrowSigned>(c[j], f.xa[i].x, f.xb[i].x, f.xa[i].y, f.xb[i].y, f.y[j][i].x, f.y[j][i].y);
+        mma_16x8x32<kWideSigned, kNarrowSigned>(c[j], f.xa[i].z, f.xb[i].z, f.xa[i].w, f.xb[i].w, f.y[j][i].z, f.y[j][i].w);
       }
       if (a.need_nsum) {
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-          nsum[j] = sum4<kNarrowSigned>(y[j][i].x, nsum[j]);
-          nsum[j] = sum4<kNarrowSigned>(y[j][i].y, nsum[j]);
-          nsum[j] = sum4<kNarrowSigned>(y[j][i].z, nsum[j]);
-          nsum[j] = sum4<kNarrowSigned>(y[j][i].w, nsum[j]);
+          nsum[j] = sum4<kNarrowSigned>(f.y[j][i].x, nsum[j]);
+          nsum[j] = sum4<kNarrowSigned>(f.y[j][i].y, nsum[j]);
+          nsum[j] = sum4<kNarrowSigned>(f.y[j][i].z, nsum[j]);
+          nsum[j] = sum4<kNarrowSigned>(f.y[j][i].w, nsum[j]);
         }
       }
     }
     if (a.need_wsum) {
 #pragma unroll
       for (int i = 0; i < 4; i++) {
-        wsum0 = sum4<kWideSigned>(xa[i].x, wsum0);
-        wsum0 = sum4<kWideSigned>(xa[i].y, wsum0);
-        wsum0 = sum4<kWideSigned>(xa[i].z, wsum0);
-        wsum0 = sum4<kWideSigned>(xa[i].w, wsum0);
-        wsum1 = sum4<kWideSigned>(xb[i].x, wsum1);
-        wsum1 = sum4<kWideSigned>(xb[i].y, wsum1);
-        wsum1 = sum4<kWideSigned>(xb[i].z, wsum1);
-        wsum1 = sum4<kWideSigned>(xb[i].w, wsum1);
+        wsum0 = sum4<kWideSigned>(f.xa[i].x, wsum0);
+        wsum0 = sum4<kWideSigned>(f.xa[i].y, wsum0);
+        wsum0 = sum4<kWideSigned>(f.xa[i].z, wsum0);
+        wsum0 = sum4<kWideSigned>(f.xa[i].w, wsum0);
+        wsum1 = sum4<kWideSigned>(f.xb[i].x, wsum1);
+        wsum1 = sum4<kWideSigned>(f.xb[i].y, wsum1);
+        wsum1 = sum4<kWideSigned>(f.xb[i].z, wsum1);
+        wsum1 = sum4<kWideSigned>(f.xb[i].w, wsum1);
       }
     }
   };
   int base = warp * 16;
-  for (; base + 16 <= pieces; base += kWarpsPerBlock * 16) step(base, std::true_type{});
-  if (base < pieces) step(base, std::false_type{});
+  if (kWarps <= 2 && kTiles == 1) {
+    // few warps per CTA (all CTAs resident at once, about 14 warps per SM): two steps' loads in flight per warp
+    for (; base + kWarps * 16 + 16 <= pieces; base += 2 * kWarps * 16) {
+      Frag f0, f1;
+      load(f0, base, std::true_type{});
+      load(f1, base + kWarps * 16, std::true_type{});
+      compute(f0);
+      compute(f1);
+    }
+  }
+  for (; base + 16 <= pieces; base += kWarps * 16) {
+    Frag f;
+    load(f, base, std::true_type{});
+    compute(f);
+  }
+  if (base < pieces) {
+    Frag f;
+    load(f, base, std::false_type{});
+    compute(f);
+  }
   if (warp > 0) {
 #pragma unroll
     for (int j = 0; j < kTiles; j++) {
@@ -319,7 +341,7 @@ __global__ void __launch_bounds__(32 * kWarpsPerBlock) gemv_i8_mma_kernel(const 
   __syncthreads();
   if (warp > 0) return;
 #pragma unroll
-  for (int w = 0; w < kWarpsPerBlock - 1; w++) {
+  for (int w = 0; w < kWarps - 1; w++) {
 #pragma unroll
     for (int j = 0; j < kTiles; j++) {
 #pragma unroll
@@ -359,15 +381,52 @@ __global__ void __launch_bounds__(32 * kWarpsPerBlock) gemv_i8_mma_kernel(const 
   }
 }
 
-template <int kTiles>
-cudaError_t launch_i8_mma(const GemvArgs& a, cudaStream_t stream) {
+template <int kTiles, int kWarps>
+cudaError_t launch_i8_mma_warps(const GemvArgs& a, cudaStream_t stream) {
   const unsigned grid = (unsigned)(((long long)a.wide.width + 15) / 16);
   const bool ws = a.wide.dtype == RUYB200_I8, ns = a.narrow.dtype == RUYB200_I8;
-  if (ws && ns) gemv_i8_mma_kernel<true, true, kTiles><<<grid, 32 * kWarpsPerBlock, 0, stream>>>(a);
-  else if (ws) gemv_i8_mma_kernel<true, false, kTiles><<<grid, 32 * kWarpsPerBlock, 0, stream>>>(a);
-  else if (ns) gemv_i8_mma_kernel<false, true, kTiles><<<grid, 32 * kWarpsPerBlock, 0, stream>>>(a);
-  else gemv_i8_mma_kernel<false, false, kTiles><<<grid, 32 * kWarpsPerBlock, 0, stream>>>(a);
+  if (ws && ns) gemv_i8_mma_kernel<true, true, kTiles, kWarps><<<grid, 32 * kWarps, 0, stream>>>(a);
+  else if (ws) gemv_i8_mma_kernel<true, false, kTiles, kWarps><<<grid, 32 * kWarps, 0, stream>>>(a);
+  else if (ns) gemv_i8_mma_kernel<false, true, kTiles, kWarps><<<grid, 32 * kWarps, 0, stream>>>(a);
+  else gemv_i8_mma_kernel<false, false, kTiles, kWarps><<<grid, 32 * kWarps, 0, stream>>>(a);
   return cudaGetLastError();
+}
+
+// Warps per CTA of the MMA form.  The grid is one CTA per 16 wide rows whatever their number, so what can be chosen is
+// how many CTAs an SM holds at once (24 warps' worth with one tile of narrow rows, 16 with two): with 8 warps per CTA,
+// 16384 rows are 1024 CTAs on 444 places, 2.3 rounds of which the last runs on a third of the machine (measured 50.9 us
+// where one narrow row, which has no such tail, takes 40.7 us); with 2 warps per CTA all 1024 are resident at once.
+// Taken: the largest CTA among those that waste the least of their last round.
+int mma_form_warps(long long ctas, int sm_count, int tiles) {
+  int best = 8;
+  double best_eff = 0.0;
+  for (int w = 8; w >= 2; w /= 2) {
+    const long long places = (long long)sm_count * (w == 2 ? 8 : (tiles == 2 ? 16 : 24) / w);   // the kernel's launch bounds
+    const long long rounds = (ctas + places - 1) / places;
+    const double eff = rounds <= 1 ? 1.0 : (double)ctas / (double)(rounds * places);
+    if (eff > best_eff + 0.02) {
+      best = w;
+      best_eff = eff;
+    }
+  }
+  return best;
+}
+
+template <int kTiles>
+cudaError_t launch_i8_mma(const GemvArgs& a, cudaStream_t stream) {
+  static int sm_counts[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int sms = dev >= 0 && dev < 64 ? sm_counts[dev] : 0;
+  if (sms == 0) {
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    if (dev >= 0 && dev < 64) sm_counts[dev] = sms;
+  }
+  switch (mma_form_warps(((long long)a.wide.width + 15) / 16, sms, kTiles)) {
+    case 2: return launch_i8_mma_warps<kTiles, 2>(a, stream);
+    case 4: return launch_i8_mma_warps<kTiles, 4>(a, stream);
+    default: return launch_i8_mma_warps<kTiles, 8>(a, stream);
+  }
 }
 
 // Compensated (Kahan) running sum: folds y into (sum, comp).
