@@ -952,12 +952,14 @@ def run_small_arm(args):
             # end to end with host operands through the synchronous call
             hdst = case.new_dst()
             hl, hr, hp, hd, hkeep = case.bind(hdst, rounding=Rounding.kReference)
-            ruy_b200.mul(hl, hr, hp, ctx, hd)
-            t0 = time.perf_counter()
-            reps = 5
-            for _ in range(reps):
+            for _ in range(3):    # the first call packs and caches the weights; the next ones settle the host side
                 ruy_b200.mul(hl, hr, hp, ctx, hd)
-            e2e_ms = (time.perf_counter() - t0) / reps * 1e3
+            per_call = []
+            for _ in range(9):
+                t0 = time.perf_counter()
+                ruy_b200.mul(hl, hr, hp, ctx, hd)
+                per_call.append(time.perf_counter() - t0)
+            e2e_ms = float(np.median(per_call)) * 1e3   # median: single calls right after a large upload ran 10-50x long
             gops = case.ops / (ms * 1e-3) / 1e9
             gbs = nbytes / (ms * 1e-3) / 1e9
             is_float = case.accum == "float32"

@@ -176,7 +176,7 @@ constexpr size_t kCacheSlabBytes = size_t(32) << 20;
 }  // namespace
 
 constexpr int kMaxChunks = 16;
-constexpr size_t kBounceBytes = size_t(256) << 10;   // pinned staging for per-channel vectors: 3 x 16384 channels and more
+constexpr size_t kBounceBytes = size_t(1) << 20;   // pinned staging for per-channel vectors (3 x 16384 channels and more), small host operands and destinations
 
 struct ruyb200_ctx {
   int device = 0;
@@ -216,7 +216,7 @@ struct ruyb200_ctx {
   cudaStream_t copy_out = nullptr;
   cudaEvent_t chunk_in[kMaxChunks] = {};
   cudaEvent_t chunk_done[kMaxChunks] = {};
-  char* bounce = nullptr;   // pinned staging for small host vectors (bias, multipliers), kBounceBytes
+  char* bounce = nullptr;   // pinned staging for small host vectors (bias, multipliers), operands and destinations, kBounceBytes
   size_t bounce_off = 0;
   cudaEvent_t chunk_out[kMaxChunks] = {};   // only with RUYB200_TRACE: when each chunk's destination rows have left
   cudaEvent_t chunk_start = nullptr;
@@ -478,6 +478,22 @@ struct Resolved {
   int depth;
 };
 
+// `bytes` of the context's pinned staging buffer, or null when it is full (or could not be had).  Copies between
+// pageable host memory and the device hold the calling thread (measured: 100 to 300 us per synchronous mul with a 4 KB
+// operand and a 4 KB destination); small operands and destinations go through this buffer instead, with a host memcpy on
+// the pageable side.  Host pointers only occur in synchronous muls, so the buffer is free again when the next call starts.
+char* bounce_take(ruyb200_ctx* ctx, size_t bytes) {
+  const size_t padded = (bytes + 63) & ~size_t(63);
+  if (!ctx->bounce && cudaHostAlloc(&ctx->bounce, kBounceBytes, cudaHostAllocDefault) != cudaSuccess) {
+    cudaGetLastError();
+    ctx->bounce = nullptr;
+  }
+  if (!ctx->bounce || ctx->bounce_off + padded > kBounceBytes) return nullptr;
+  char* p = ctx->bounce + ctx->bounce_off;
+  ctx->bounce_off += padded;
+  return p;
+}
+
 // One operand: finds or builds its device-resident form.
 //   cached   -> packed copy + sums from the prepacked cache (built on a miss)
 //   host     -> staged into the arena
@@ -508,7 +524,14 @@ int prepare_side(ruyb200_ctx* ctx, const ruyb200_matrix& m, int side, int depth,
     const size_t span = storage_span_bytes(m);
     void* dptr = ctx->arena.alloc(span);
     if (!dptr) return fail(RUYB200_ERR_OOM, "arena allocation of %zu bytes failed", span);
-    CUDA_TRY(cudaMemcpyAsync(dptr, m.data, span, cudaMemcpyHostToDevice, ctx->stream));
+    const void* from = m.data;
+    if (span <= kBounceBytes / 4) {
+      if (char* pinned = bounce_take(ctx, span)) {
+        memcpy(pinned, m.data, span);
+        from = pinned;
+      }
+    }
+    CUDA_TRY(cudaMemcpyAsync(dptr, from, span, cudaMemcpyHostToDevice, ctx->stream));
     ctx->counters[3] += span;
     v->data = dptr;
     return RUYB200_OK;
@@ -607,15 +630,9 @@ int stage_vector(ruyb200_ctx* ctx, const void* p, size_t count, const void** out
   void* d = ctx->arena.alloc(bytes);
   if (!d) return fail(RUYB200_ERR_OOM, "arena allocation failed");
   const void* src = p;
-  const size_t padded = (bytes + 63) & ~size_t(63);
-  if (!ctx->bounce && cudaHostAlloc(&ctx->bounce, kBounceBytes, cudaHostAllocDefault) != cudaSuccess) {
-    cudaGetLastError();
-    ctx->bounce = nullptr;
-  }
-  if (ctx->bounce && ctx->bounce_off + padded <= kBounceBytes) {
-    memcpy(ctx->bounce + ctx->bounce_off, p, bytes);
-    src = ctx->bounce + ctx->bounce_off;
-    ctx->bounce_off += padded;
+  if (char* pinned = bounce_take(ctx, bytes)) {
+    memcpy(pinned, p, bytes);
+    src = pinned;
   }
   CUDA_TRY(cudaMemcpyAsync(d, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
   ctx->counters[3] += bytes;
@@ -1053,9 +1070,18 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
   if (ce != cudaSuccess) return fail(RUYB200_ERR_CUDA, "kernel launch: %s", cudaGetErrorString(ce));
 
   if (!dst_on_device) {
-    CUDA_TRY(cudaMemcpy2DAsync(d.dst.data, (size_t)d.dst.stride * dst_esz, dst_dev, (size_t)d.dst.stride * dst_esz,
-                               (size_t)dst_inner * dst_esz, dst_outer, cudaMemcpyDeviceToHost, ctx->stream));
-    ctx->counters[4] += (size_t)dst_inner * dst_esz * dst_outer;
+    const size_t row_bytes = (size_t)dst_inner * dst_esz, pitch = (size_t)d.dst.stride * dst_esz;
+    ctx->counters[4] += row_bytes * dst_outer;
+    char* pinned = synchronous && row_bytes * dst_outer <= kBounceBytes / 2 ? bounce_take(ctx, row_bytes * dst_outer) : nullptr;
+    if (pinned) {
+      // a small destination: to the pinned buffer (rows packed tightly), then by memcpy to where the caller wants it
+      CUDA_TRY(cudaMemcpy2DAsync(pinned, row_bytes, dst_dev, pitch, row_bytes, dst_outer, cudaMemcpyDeviceToHost, ctx->stream));
+      const int rc_sync = ruyb200_ctx_sync(ctx);
+      if (rc_sync) return rc_sync;
+      for (int i = 0; i < dst_outer; i++) memcpy((char*)d.dst.data + (size_t)i * pitch, pinned + (size_t)i * row_bytes, row_bytes);
+      return RUYB200_OK;
+    }
+    CUDA_TRY(cudaMemcpy2DAsync(d.dst.data, pitch, dst_dev, pitch, row_bytes, dst_outer, cudaMemcpyDeviceToHost, ctx->stream));
   }
   if (synchronous) return ruyb200_ctx_sync(ctx);
   return RUYB200_OK;
