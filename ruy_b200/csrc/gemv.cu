@@ -394,16 +394,16 @@ cudaError_t launch_i8_mma_warps(const GemvArgs& a, cudaStream_t stream) {
 
 // Warps per CTA of the MMA form.  The grid is one CTA per 16 wide rows whatever their number, so what can be chosen is
 // how many CTAs an SM holds at once (24 warps' worth with one tile of narrow rows, 16 with two): with 8 warps per CTA,
-// 16384 rows are 1024 CTAs on 444 places, 2.3 rounds of which the last runs on a third of the machine (measured 50.9 us
+// 16384 rows are 1024 CTAs on 444 places, 2.3 waves of which the last runs on a third of the machine (measured 50.9 us
 // where one narrow row, which has no such tail, takes 40.7 us); with 2 warps per CTA all 1024 are resident at once.
-// Taken: the largest CTA among those that waste the least of their last round.
+// Taken: the largest CTA among those that waste the least of their last wave.
 int mma_form_warps(long long ctas, int sm_count, int tiles) {
   int best = 8;
   double best_eff = 0.0;
   for (int w = 8; w >= 2; w /= 2) {
     const long long places = (long long)sm_count * (w == 2 ? 8 : (tiles == 2 ? 16 : 24) / w);   // the kernel's launch bounds
-    const long long rounds = (ctas + places - 1) / places;
-    const double eff = rounds <= 1 ? 1.0 : (double)ctas / (double)(rounds * places);
+    const long long waves = (ctas + places - 1) / places;
+    const double eff = waves <= 1 ? 1.0 : (double)ctas / (double)(waves * places);
     if (eff > best_eff + 0.02) {
       best = w;
       best_eff = eff;
