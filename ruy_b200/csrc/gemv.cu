@@ -11,6 +11,7 @@
 // of ruy/kernel.h:213-237.
 #include "common.cuh"
 
+#include <atomic>
 #include <type_traits>
 
 namespace ruyb200 {
@@ -414,13 +415,14 @@ int mma_form_warps(long long ctas, int sm_count, int tiles) {
 
 template <int kTiles>
 cudaError_t launch_i8_mma(const GemvArgs& a, cudaStream_t stream) {
-  static int sm_counts[64] = {};
+  // per device, filled on first use; contexts on several threads may get here together, hence atomic
+  static std::atomic<int> sm_counts[64];
   int dev = 0;
   cudaGetDevice(&dev);
-  int sms = dev >= 0 && dev < 64 ? sm_counts[dev] : 0;
+  int sms = dev >= 0 && dev < 64 ? sm_counts[dev].load(std::memory_order_relaxed) : 0;
   if (sms == 0) {
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-    if (dev >= 0 && dev < 64) sm_counts[dev] = sms;
+    if (dev >= 0 && dev < 64) sm_counts[dev].store(sms, std::memory_order_relaxed);
   }
   switch (mma_form_warps(((long long)a.wide.width + 15) / 16, sms, kTiles)) {
     case 2: return launch_i8_mma_warps<kTiles, 2>(a, stream);
