@@ -41,6 +41,16 @@ def golden_cases():
     out.append(cases.random_case(33, 70, 17, "float64", "float32", "float32", orders="RCC", extra_stride=1, seed=12))
     out.append(cases.random_case(29, 65, 40, "float32", "float64", "float64", orders="CRR", seed=13,
                                  channel=ChannelDimension.kCol))
+    # a few columns against a wide operand (the register-level MMA form of the narrow kernel: whole steps of 256 bytes
+    # of depth plus a tail, wide rows left over past the last 16, one and two tiles of 8 narrow rows, the narrow side
+    # as either operand) and operands that must be packed first (rows off the 16-byte grid; width-contiguous storage)
+    out.append(cases.random_case(1030, 4112, 5, "int8", "uint8", "int8", orders="RCC", perchannel=True, symmetric=False, seed=14))
+    out.append(cases.random_case(1500, 784, 13, "uint8", "int8", "int8", orders="RCR", perchannel=True,
+                                 channel=ChannelDimension.kCol, symmetric=False, seed=15))
+    out.append(cases.random_case(3, 2064, 1100, "int8", "int8", "int16", orders="RCC", symmetric=False, seed=16))
+    out.append(cases.random_case(129, 4100, 96, "int8", "int8", "int8", orders="RCC", extra_stride=3, perchannel=True,
+                                 symmetric=False, seed=17))
+    out.append(cases.random_case(300, 260, 200, "uint8", "uint8", "uint8", orders="CRC", extra_stride=1, symmetric=False, seed=18))
     names = [c.name for c in out]
     assert len(set(names)) == len(names), "golden case names must be unique"
     return out
