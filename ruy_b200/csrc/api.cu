@@ -218,6 +218,9 @@ struct ruyb200_ctx {
   cudaEvent_t chunk_done[kMaxChunks] = {};
   char* bounce = nullptr;   // pinned staging for small host vectors (bias, multipliers), operands and destinations, kBounceBytes
   size_t bounce_off = 0;
+  char* d_bounce = nullptr;       // device mirror of `bounce`: what is staged for upload travels in one copy per launch
+  size_t bounce_h2d_end = 0;      // end of the staged uploads in `bounce`
+  size_t bounce_flushed = 0;      // what of them has been sent
   cudaEvent_t chunk_out[kMaxChunks] = {};   // only with RUYB200_TRACE: when each chunk's destination rows have left
   cudaEvent_t chunk_start = nullptr;
   bool no_chunks = false;   // RUYB200_NO_CHUNKS=1: one copy in, one kernel, one copy out
@@ -494,6 +497,33 @@ char* bounce_take(ruyb200_ctx* ctx, size_t bytes) {
   return p;
 }
 
+// Stages `bytes` of host data for upload: copies them into the pinned buffer and returns where they will be on the
+// device once bounce_flush has run (null: no room, the caller copies by itself).  All that is staged between two
+// flushes travels in ONE copy: a small synchronous mul with a host operand and three per-channel vectors issues one
+// upload instead of four.
+void* bounce_stage(ruyb200_ctx* ctx, const void* src, size_t bytes) {
+  if (!ctx->d_bounce) {
+    if (cudaMalloc(&ctx->d_bounce, kBounceBytes) != cudaSuccess) {
+      cudaGetLastError();
+      ctx->d_bounce = nullptr;
+      return nullptr;
+    }
+  }
+  char* pinned = bounce_take(ctx, bytes);
+  if (!pinned) return nullptr;
+  memcpy(pinned, src, bytes);
+  ctx->bounce_h2d_end = ctx->bounce_off;
+  return ctx->d_bounce + (pinned - ctx->bounce);
+}
+
+// Sends what has been staged since the last flush; called before every launch that may read staged data.
+cudaError_t bounce_flush(ruyb200_ctx* ctx) {
+  if (ctx->bounce_h2d_end <= ctx->bounce_flushed) return cudaSuccess;
+  const size_t from = ctx->bounce_flushed;
+  ctx->bounce_flushed = ctx->bounce_h2d_end;
+  return cudaMemcpyAsync(ctx->d_bounce + from, ctx->bounce + from, ctx->bounce_h2d_end - from, cudaMemcpyHostToDevice, ctx->stream);
+}
+
 // One operand: finds or builds its device-resident form.
 //   cached   -> packed copy + sums from the prepacked cache (built on a miss)
 //   host     -> staged into the arena
@@ -522,17 +552,16 @@ int prepare_side(ruyb200_ctx* ctx, const ruyb200_matrix& m, int side, int depth,
 
   auto stage_to_device = [&](SideView* v) -> int {
     const size_t span = storage_span_bytes(m);
-    void* dptr = ctx->arena.alloc(span);
-    if (!dptr) return fail(RUYB200_ERR_OOM, "arena allocation of %zu bytes failed", span);
-    const void* from = m.data;
+    ctx->counters[3] += span;
     if (span <= kBounceBytes / 4) {
-      if (char* pinned = bounce_take(ctx, span)) {
-        memcpy(pinned, m.data, span);
-        from = pinned;
+      if (void* staged = bounce_stage(ctx, m.data, span)) {
+        v->data = staged;
+        return RUYB200_OK;
       }
     }
-    CUDA_TRY(cudaMemcpyAsync(dptr, from, span, cudaMemcpyHostToDevice, ctx->stream));
-    ctx->counters[3] += span;
+    void* dptr = ctx->arena.alloc(span);
+    if (!dptr) return fail(RUYB200_ERR_OOM, "arena allocation of %zu bytes failed", span);
+    CUDA_TRY(cudaMemcpyAsync(dptr, m.data, span, cudaMemcpyHostToDevice, ctx->stream));
     v->data = dptr;
     return RUYB200_OK;
   };
@@ -565,7 +594,8 @@ int prepare_side(ruyb200_ctx* ctx, const ruyb200_matrix& m, int side, int depth,
       e.sums = integer ? (int32_t*)((char*)buf + data_bytes) : nullptr;
       e.packed_depth = pd;
       e.bytes = total;
-      cudaError_t ce = launch_pack(staged, depth, pd, e.packed, e.sums, ctx->stream);
+      cudaError_t ce = bounce_flush(ctx);
+      if (ce == cudaSuccess) ce = launch_pack(staged, depth, pd, e.packed, e.sums, ctx->stream);
       ctx->counters[0]++;
       if (ce != cudaSuccess) {
         cache_free(ctx, e);
@@ -600,7 +630,8 @@ int prepare_side(ruyb200_ctx* ctx, const ruyb200_matrix& m, int side, int depth,
     const bool with_sums = (need_sums || sums_if_packed) && integer;
     int32_t* sums = with_sums ? (int32_t*)ctx->arena.alloc(sizeof(int32_t) * v.width) : nullptr;
     if (!packed || (with_sums && !sums)) return fail(RUYB200_ERR_OOM, "arena allocation failed");
-    cudaError_t ce = launch_pack(v, depth, pd, packed, sums, ctx->stream);
+    cudaError_t ce = bounce_flush(ctx);
+    if (ce == cudaSuccess) ce = launch_pack(v, depth, pd, packed, sums, ctx->stream);
     ctx->counters[0]++;
     if (ce != cudaSuccess) return fail(RUYB200_ERR_CUDA, "pack launch: %s", cudaGetErrorString(ce));
     v.data = packed;
@@ -610,7 +641,8 @@ int prepare_side(ruyb200_ctx* ctx, const ruyb200_matrix& m, int side, int depth,
   } else if (need_sums) {
     int32_t* sums = (int32_t*)ctx->arena.alloc(sizeof(int32_t) * v.width);
     if (!sums) return fail(RUYB200_ERR_OOM, "arena allocation failed");
-    cudaError_t ce = launch_sums(v, depth, sums, ctx->stream);
+    cudaError_t ce = bounce_flush(ctx);
+    if (ce == cudaSuccess) ce = launch_sums(v, depth, sums, ctx->stream);
     ctx->counters[0]++;
     if (ce != cudaSuccess) return fail(RUYB200_ERR_CUDA, "sums launch: %s", cudaGetErrorString(ce));
     *sums_out = sums;
@@ -627,15 +659,14 @@ int stage_vector(ruyb200_ctx* ctx, const void* p, size_t count, const void** out
   *out = p;
   if (!p || count == 0 || is_device_pointer(p)) return RUYB200_OK;
   const size_t bytes = count * elem;
+  ctx->counters[3] += bytes;
+  if (void* staged = bounce_stage(ctx, p, bytes)) {
+    *out = staged;
+    return RUYB200_OK;
+  }
   void* d = ctx->arena.alloc(bytes);
   if (!d) return fail(RUYB200_ERR_OOM, "arena allocation failed");
-  const void* src = p;
-  if (char* pinned = bounce_take(ctx, bytes)) {
-    memcpy(pinned, p, bytes);
-    src = pinned;
-  }
-  CUDA_TRY(cudaMemcpyAsync(d, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
-  ctx->counters[3] += bytes;
+  CUDA_TRY(cudaMemcpyAsync(d, p, bytes, cudaMemcpyHostToDevice, ctx->stream));
   *out = d;
   return RUYB200_OK;
 }
@@ -809,7 +840,7 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
     }
   }
   ctx->arena.reset(synchronous);
-  ctx->bounce_off = 0;
+  ctx->bounce_off = ctx->bounce_h2d_end = ctx->bounce_flushed = 0;
 
   const int depth = d.lhs.cols;
   // double accumulation (ruy's mixed float/double cases) runs on the CUDA-core kernel only, straight from the
@@ -985,7 +1016,9 @@ int run_mul(ruyb200_ctx* ctx, const ruyb200_mul_desc* desc, bool synchronous, vo
   ep.zp_n = r.n_side.zero_point;
   r.ep = ep;
 
-  cudaError_t ce;
+  // every small host operand and vector staged above goes up in one copy, ahead of the kernel that reads them
+  cudaError_t ce = bounce_flush(ctx);
+  if (ce != cudaSuccess) return fail(RUYB200_ERR_CUDA, "upload of staged host data: %s", cudaGetErrorString(ce));
   if (tc) {
     if (!tc_i8_eligible(r.m_side, r.n_side)) return fail(RUYB200_ERR_CUDA, "internal: operands not packed for the tensor-core kernel");
     TcI8Launch L;
@@ -1241,6 +1274,7 @@ int ruyb200_ctx_destroy(ruyb200_ctx* ctx) {
   ctx->cache_slabs.clear();
   ctx->arena.release();
   if (ctx->bounce) cudaFreeHost(ctx->bounce);
+  if (ctx->d_bounce) cudaFree(ctx->d_bounce);
   for (auto& kv : ctx->store_maps) cudaFree(kv.second);
   if (ctx->d_status) cudaFree(ctx->d_status);
   if (ctx->h_status) cudaFreeHost(ctx->h_status);
