@@ -17,7 +17,6 @@ import hashlib
 
 import numpy as np
 
-from . import _abi
 from .api import (CachePolicy, ChannelDimension, Layout, Matrix, MulParams, Order, Rounding)
 
 

@@ -9,7 +9,6 @@ import ctypes as C
 import torch
 import torch.distributed as dist
 
-from . import _abi
 from ._lib import lib
 from .api import _check, make_desc
 
