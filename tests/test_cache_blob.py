@@ -38,6 +38,19 @@ def test_hand_written_blob_is_accepted():
                     "depth": 40, "packed_depth": 48, "zero_point": -3, "data_bytes": 24 * 48, "sums_bytes": 96}
 
 
+def test_both_row_lengths_of_deep_8bit_rows_are_accepted():
+    """8-bit rows of 256 bytes and more are written padded to whole 128-byte lines; a blob whose rows are padded to 16
+    bytes only (the earlier layout) is still taken; any other row length is refused."""
+    assert cache_blob_info(make_blob(width=8, depth=300, packed_depth=384))["packed_depth"] == 384
+    assert cache_blob_info(make_blob(width=8, depth=300, packed_depth=304))["packed_depth"] == 304
+    with pytest.raises(ruy_b200.RuyError) as e:
+        cache_blob_info(make_blob(width=8, depth=300, packed_depth=320))
+    assert e.value.status == _abi.ERR_INVALID
+    # below 256 bytes of depth there is only the 16-byte rounding
+    with pytest.raises(ruy_b200.RuyError):
+        cache_blob_info(make_blob(width=8, depth=200, packed_depth=256))
+
+
 @pytest.mark.parametrize("damage", ["magic", "abi", "format", "truncated", "payload", "header_field", "packed_depth", "short"])
 def test_damaged_or_foreign_blobs_are_refused(damage):
     blob = bytearray(make_blob())
