@@ -227,6 +227,38 @@ def test_cache_export_import_round_trip():
             assert b.prepacked_cache_entries() == 0
 
 
+def test_blob_with_rows_padded_to_16_bytes_only_is_still_usable():
+    """8-bit rows of 256 bytes and more are cached (and exported) padded to whole 128-byte lines.  A blob of the same
+    weights with rows padded to 16 bytes only, as earlier versions wrote them, imports and multiplies to the same bits."""
+    import struct
+    from test_cache_blob import fnv1a
+    c = cases.random_case(64, 300, 48, "int8", "int8", "int8", orders="RCC", perchannel=True, symmetric=False, seed=41,
+                          lhs_cache=CachePolicy.kAlwaysCache)
+    want = util.run_oracle(c, Rounding.kReference)
+    dst = torch.zeros(c.dst_storage_elems(), dtype=torch.int8, device=DEV)
+    lhs, rhs, p, d, keep = c.bind(dst, device=DEV, rounding=Rounding.kReference)
+    with ruy_b200.Context(0) as a:
+        ruy_b200.mul(lhs, rhs, p, a, d)
+        blob = a.cache_export(lhs, 0)
+    info = ruy_b200.api.cache_blob_info(blob)
+    assert info["packed_depth"] == 384 and info["depth"] == 300
+    rows = np.frombuffer(blob, dtype=np.int8, count=64 * 384, offset=64).reshape(64, 384)
+    sums = blob[64 + 64 * 384:]
+    payload = np.ascontiguousarray(rows[:, :304]).tobytes() + sums
+    head = bytearray(blob[:56])
+    struct.pack_into("<i", head, 28, 304)                  # packed depth
+    struct.pack_into("<Q", head, 40, 64 * 304)             # data bytes
+    old = bytes(head) + struct.pack("<Q", fnv1a(payload, fnv1a(bytes(head)))) + payload
+    assert ruy_b200.api.cache_blob_info(old)["packed_depth"] == 304
+    with ruy_b200.Context(0) as b:
+        b.cache_import(lhs, 0, old)
+        before = b.counters()
+        dst.zero_()
+        ruy_b200.mul(lhs, rhs, p, b, d)
+        assert b.counters()["cache_hits"] - before["cache_hits"] == 1
+        assert np.array_equal(c.dst_view(dst.cpu().numpy()), want)
+
+
 # ---- bounded waits ------------------------------------------------------------------------------------
 
 def test_peer_wait_gives_up_and_the_context_stays_usable():
